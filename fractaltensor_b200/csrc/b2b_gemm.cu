@@ -1,0 +1,346 @@
+// Back-to-back GEMM  D = (A . B) . C  for 16-bit inputs on sm_100a.
+//
+// Arithmetic follows KeBack2BackGemm (kaleido/core/device/kernels/cutlass_wmma.h:489-533):
+// S = A.B accumulated in fp32, rounded to the 16-bit input type, D = S.C
+// accumulated in fp32, rounded to the 16-bit type.  Unlike the reference, which
+// re-reads the A tile for every N tile, every byte of A is read once: the shape
+// is HBM-bound, so the kernel is organised around keeping TMA loads of A and TMA
+// stores of D in flight while two small MMAs and two conversions run per tile.
+//
+// One persistent CTA per SM owns a contiguous range of 128-row tiles.
+//   warp 0      TMA producer: B and C of the current batch entry, ring of A tiles
+//   warp 1      MMA issuer: S = A.B^T into TMEM, then O = P.C^T into TMEM
+//   warps 2..5  convert S -> P (16-bit, written to shared memory in the 128-byte
+//               swizzled K-major layout the second MMA reads), convert O -> D
+//               staging, TMA store of D
+#include "../../include/ftb200.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace ftb {
+namespace {
+
+constexpr int kTile = 128;              // rows per tile; also N, K, P
+constexpr int kHalfBytes = 128 * 128;   // one 64-column half of a 128x128 16-bit tile
+constexpr int kTileBytes = 2 * kHalfBytes;
+constexpr int kAStages = 3;
+constexpr int kThreads = 192;
+constexpr uint32_t kSmemBytes = (2 + kAStages + 2) * kTileBytes + 1024;  // B, C, A ring, P, D staging
+
+// Writes 32 fp32 accumulator columns [col0, col0+32) of row `row` as 16-bit
+// values into a 128x128 tile laid out as two 64-column halves of 128-byte
+// swizzled rows.
+template <typename T>
+__device__ __forceinline__ void write_row_chunk_sw128(uint8_t* tile, int row, int col0, const uint32_t (&r)[32]) {
+  uint8_t* half_base = tile + (col0 >> 6) * kHalfBytes + row * 128;
+  const int c0 = (col0 & 63) >> 3;  // first 16-byte chunk inside the 128-byte row
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 u;
+    u.x = Fmt<T>::pack2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+    u.y = Fmt<T>::pack2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+    u.z = Fmt<T>::pack2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+    u.w = Fmt<T>::pack2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+    const int chunk = (c0 + j) ^ (row & 7);
+    *reinterpret_cast<uint4*>(half_base + chunk * 16) = u;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapD,
+                int total_tiles, int tiles_per_batch, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t a_full[kAStages], a_empty[kAStages];
+  __shared__ uint64_t bc_full, bc_empty, p_full, p_empty;
+  __shared__ uint64_t s_full[2], s_empty[2], o_full[2], o_empty[2];
+  __shared__ uint64_t d_free, d_ready;  // staging tile handshakes between the epilogue warps and the storing thread
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort;
+
+  if (*reinterpret_cast<volatile int*>(status) != 0) return;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sB = smem;
+  uint8_t* sC = sB + kTileBytes;
+  uint8_t* sA = sC + kTileBytes;
+  uint8_t* sP = sA + kAStages * kTileBytes;
+  uint8_t* sD = sP + kTileBytes;
+
+  // Contiguous tile range of this CTA.
+  const int per = total_tiles / gridDim.x, rem = total_tiles % gridDim.x;
+  const int first = blockIdx.x * per + (blockIdx.x < rem ? blockIdx.x : rem);
+  const int count = per + (blockIdx.x < rem ? 1 : 0);
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&mapA);
+    prefetch_tmap(&mapB);
+    prefetch_tmap(&mapC);
+    prefetch_tmap(&mapD);
+    for (int i = 0; i < kAStages; ++i) {
+      mbar_init(&a_full[i], 1);
+      mbar_init(&a_empty[i], 1);
+    }
+    mbar_init(&bc_full, 1);
+    mbar_init(&bc_empty, 1);
+    mbar_init(&p_full, 4);
+    mbar_init(&p_empty, 1);
+    mbar_init(&d_free, 1);
+    mbar_init(&d_ready, 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+      mbar_init(&o_full[i], 1);
+      mbar_init(&o_empty[i], 4);
+    }
+    s_abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  // TMEM columns: S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512).
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, bc_phase = 0;
+      int cur_batch = -1;
+      for (int i = 0; i < count; ++i) {
+        const int tile = first + i;
+        const int b = tile / tiles_per_batch;
+        if (!mbar_wait(&a_empty[stage], phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT)) break;
+        uint8_t* dst = sA + stage * kTileBytes;
+        mbar_arrive_expect_tx(&a_full[stage], kTileBytes);
+        tma_load_2d(dst, &mapA, &a_full[stage], 0, tile * kTile);
+        tma_load_2d(dst + kHalfBytes, &mapA, &a_full[stage], 64, tile * kTile);
+        if (++stage == kAStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (b != cur_batch) {
+          // B and C are single-buffered: wait until the MMAs of the previous
+          // batch entry have finished reading them.
+          if (!mbar_wait(&bc_empty, bc_phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT)) break;
+          mbar_arrive_expect_tx(&bc_full, 2 * kTileBytes);
+          tma_load_2d(sB, &mapB, &bc_full, 0, b * kTile);
+          tma_load_2d(sB + kHalfBytes, &mapB, &bc_full, 64, b * kTile);
+          tma_load_2d(sC, &mapC, &bc_full, 0, b * kTile);
+          tma_load_2d(sC + kHalfBytes, &mapC, &bc_full, 64, b * kTile);
+          bc_phase ^= 1u;
+          cur_batch = b;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(128, 128, Fmt<T>::kind, 0, 0);
+      const uint32_t aB = smem_u32(sB), aC = smem_u32(sC), aP = smem_u32(sP);
+      int stage = 0;
+      uint32_t a_phase = 0, bc_phase = 0, p_phase = 0;
+      uint32_t s_phase[2] = {0, 0}, o_phase[2] = {0, 0};
+      int cur_batch = -1;
+      bool ok = true;
+
+      // GEMM 1 of tile i: S[i&1] = A . B^T
+      auto gemm1 = [&](int i) -> bool {
+        const int b = (first + i) / tiles_per_batch;
+        if (b != cur_batch) {
+          if (!mbar_wait(&bc_full, bc_phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
+          bc_phase ^= 1u;
+          cur_batch = b;
+        }
+        const int sb = i & 1;
+        if (!mbar_wait(&s_empty[sb], s_phase[sb] ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
+        s_phase[sb] ^= 1u;
+        if (!mbar_wait(&a_full[stage], a_phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
+        tc_fence_after();
+        const uint32_t aA = smem_u32(sA + stage * kTileBytes);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(tmem_base + sb * 128, make_sdesc_sw128(aA + off, 16, 1024), make_sdesc_sw128(aB + off, 16, 1024),
+                  idesc, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&a_empty[stage]);
+        umma_commit(&s_full[sb]);
+        if (++stage == kAStages) {
+          stage = 0;
+          a_phase ^= 1u;
+        }
+        return true;
+      };
+      // GEMM 2 of tile i: O[i&1] = P . C^T
+      auto gemm2 = [&](int i, bool last_of_batch) -> bool {
+        const int ob = i & 1;
+        if (!mbar_wait(&o_empty[ob], o_phase[ob] ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
+        o_phase[ob] ^= 1u;
+        if (!mbar_wait(&p_full, p_phase, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
+        p_phase ^= 1u;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(tmem_base + 256 + ob * 128, make_sdesc_sw128(aP + off, 16, 1024),
+                  make_sdesc_sw128(aC + off, 16, 1024), idesc, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&p_empty);
+        umma_commit(&o_full[ob]);
+        if (last_of_batch) umma_commit(&bc_empty);
+        return true;
+      };
+
+      if (count > 0) ok = gemm1(0);
+      for (int i = 0; i < count && ok; ++i) {
+        const bool has_next = i + 1 < count;
+        const bool next_new_batch = has_next && ((first + i + 1) / tiles_per_batch != (first + i) / tiles_per_batch);
+        // Run ahead with GEMM 1 of the next tile unless it needs a new B.
+        if (has_next && !next_new_batch) ok = gemm1(i + 1);
+        if (ok) ok = gemm2(i, next_new_batch);
+        if (ok && has_next && next_new_batch) ok = gemm1(i + 1);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const bool issuer = (warp == 2 && lane == 0);
+    uint32_t s_phase[2] = {0, 0}, o_phase[2] = {0, 0}, pe_phase = 0, d_phase = 0;
+    bool ok = true;
+
+    auto convert_s = [&](int i) -> bool {
+      const int sb = i & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], s_phase[sb], &s_abort, status, FTB_ERR_TIMEOUT_MMA)))
+        return false;
+      s_phase[sb] ^= 1u;
+      // P is single-buffered: GEMM 2 of the previous tile must be done with it.
+      if (!__all_sync(0xffffffffu, mbar_wait(&p_empty, pe_phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_MMA)))
+        return false;
+      pe_phase ^= 1u;
+      tc_fence_after();
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + sb * 128 + ch * 32, r);
+        tmem_ld_wait();
+        write_row_chunk_sw128<T>(sP, row, ch * 32, r);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[sb]);
+        mbar_arrive(&p_full);
+      }
+      return true;
+    };
+    auto output_o = [&](int i) -> bool {
+      const int ob = i & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&o_full[ob], o_phase[ob], &s_abort, status, FTB_ERR_TIMEOUT_MMA)))
+        return false;
+      o_phase[ob] ^= 1u;
+      tc_fence_after();
+      // The previous TMA store must have finished reading the staging tile.
+      if (issuer) {
+        tma_store_wait_read<0>();
+        mbar_arrive(&d_free);
+      }
+      if (!__all_sync(0xffffffffu, mbar_wait(&d_free, d_phase, &s_abort, status, FTB_ERR_TIMEOUT_EPI))) return false;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + 256 + ob * 128 + ch * 32, r);
+        tmem_ld_wait();
+        write_row_chunk_sw128<T>(sD, row, ch * 32, r);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&o_empty[ob]);
+        mbar_arrive(&d_ready);
+      }
+      const bool staged = !issuer || mbar_wait(&d_ready, d_phase, &s_abort, status, FTB_ERR_TIMEOUT_EPI);
+      d_phase ^= 1u;
+      if (issuer && staged) {
+        const int tile = first + i;
+        tma_store_2d(&mapD, sD, 0, tile * kTile);
+        tma_store_2d(&mapD, sD + kHalfBytes, 64, tile * kTile);
+        tma_store_commit();
+      }
+      return true;
+    };
+
+    for (int i = 0; i < count && ok; ++i) {
+      ok = convert_s(i);
+      if (ok && i > 0) ok = output_o(i - 1);
+    }
+    if (ok && count > 0) ok = output_o(count - 1);
+    if (issuer) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (s_abort) {
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename T>
+int launch(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mC, const CUtensorMap& mD, int total,
+           int tiles_per_batch, int* status, int sm_count, cudaStream_t stream) {
+  static bool configured = false;
+  auto kfn = b2b_gemm_kernel<T>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return FTB_ERR_LAUNCH;
+    configured = true;
+  }
+  const int grid = total < sm_count ? total : sm_count;
+  kfn<<<grid, kThreads, kSmemBytes, stream>>>(mA, mB, mC, mD, total, tiles_per_batch, status);
+  return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+}
+
+}  // namespace
+}  // namespace ftb
+
+using namespace ftb;
+
+extern "C" int ftb_b2b_gemm(const void* A, const void* B, const void* C, void* Dout, int batch, int M, int N, int K,
+                            int P, int dtype, void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!A || !B || !C || !Dout || batch <= 0 || M <= 0) return FTB_ERR_ARG;
+  if (dtype != FTB_F16 && dtype != FTB_BF16) return FTB_ERR_ARG;
+  if (N != 128 || K != 128 || P != 128 || M % 128 != 0) return FTB_ERR_ARG;
+  if (static_cast<int64_t>(batch) * M > 0x7fffffffLL) return FTB_ERR_ARG;
+  if (workspace == nullptr || workspace_bytes < ftb_workspace_bytes()) return FTB_ERR_WORKSPACE;
+  int rc = check_device_sm100();
+  if (rc) return rc;
+  if (cudaMemsetAsync(workspace, 0, ftb_workspace_bytes(), stream) != cudaSuccess) return FTB_ERR_LAUNCH;
+  int* status = static_cast<int*>(workspace);
+
+  CUtensorMap mA, mB, mC, mD;
+  const uint64_t rowsA = static_cast<uint64_t>(batch) * M;
+  if ((rc = make_tmap_2d(&mA, A, dtype, rowsA, K, K, 128, 64))) return rc;
+  if ((rc = make_tmap_2d(&mB, B, dtype, static_cast<uint64_t>(batch) * N, K, K, 128, 64))) return rc;
+  if ((rc = make_tmap_2d(&mC, C, dtype, static_cast<uint64_t>(batch) * P, N, N, 128, 64))) return rc;
+  if ((rc = make_tmap_2d(&mD, Dout, dtype, rowsA, P, P, 128, 64))) return rc;
+  const int tiles_per_batch = M / 128;
+  const int total = batch * tiles_per_batch;
+  const int sms = current_sm_count();
+  if (dtype == FTB_F16) return launch<__half>(mA, mB, mC, mD, total, tiles_per_batch, status, sms, stream);
+  return launch<__nv_bfloat16>(mA, mB, mC, mD, total, tiles_per_batch, status, sms, stream);
+}

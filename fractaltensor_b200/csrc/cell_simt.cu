@@ -1,0 +1,137 @@
+// fp32 RNN cell kernel (CUDA cores).  tcgen05 has no fp32 x fp32 MMA kind and
+// kind::tf32 keeps 10 mantissa bits, which cannot meet a 1e-5 relative bound, so
+// the fp32 configurations run on FFMA with the same work-item description and
+// the same packed (K-major, gate-interleaved) weights as the 16-bit kernel.
+// Follows the arithmetic of the reference cell programs
+// (examples/stacked_rnn/stacked_rnn.py:12-36, examples/grid_rnn/grid_rnn.py:42-72).
+#include "cell.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace ftb {
+
+namespace {
+
+constexpr int TM = 32;   // rows per tile
+constexpr int TN = 64;   // accumulator columns per tile (16 LSTM units)
+constexpr int TK = 32;   // K chunk
+constexpr int kSimtThreads = 256;
+
+struct SimtArgs {
+  const float* act[kNumActMaps];
+  int32_t ld_act[kNumActMaps];
+  const float* w;  // packed weights [rows, ldw]
+  int32_t ldw;
+};
+
+__device__ __forceinline__ float sigmoid_acc(float x) { return 1.f / (1.f + expf(-x)); }
+
+template <int EPI>
+__global__ void __launch_bounds__(kSimtThreads)
+cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ CellBatch batch) {
+  __shared__ float sA[TK][TM + 1];
+  __shared__ float sW[TK][TN + 4];
+
+  const int tile = blockIdx.x;
+  int idx = 0;
+  for (int i = 1; i < batch.n_items; ++i)
+    if (tile >= batch.items[i].tile0) idx = i;
+  const CellItem& it = batch.items[idx];
+  const int local = tile - it.tile0;
+  const int n_tile = local / it.m_tiles;
+  const int m_tile = local - n_tile * it.m_tiles;
+
+  const int tx = threadIdx.x & 15;  // 4 consecutive columns: one LSTM unit
+  const int ty = threadIdx.x >> 4;  // 2 consecutive rows
+  float acc[2][4] = {};
+
+  for (int s = 0; s < it.nseg; ++s) {
+    const float* A = args.act[it.seg_map[s]];
+    const int lda = args.ld_act[it.seg_map[s]];
+    const int row0 = it.seg_row[s] + m_tile * TM;
+    const int klen = it.seg_kb[s] * 64;
+    const float* W = args.w + static_cast<size_t>(it.w_row0 + n_tile * TN) * args.ldw + it.seg_wk[s];
+    for (int k0 = 0; k0 < klen; k0 += TK) {
+      // A chunk: 32 rows x 32 k; one float4 per thread.
+      {
+        const int r = threadIdx.x >> 3;
+        const int kq = (threadIdx.x & 7) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (m_tile * TM + r < it.rows)
+          v = *reinterpret_cast<const float4*>(A + static_cast<size_t>(row0 + r) * lda + k0 + kq);
+        sA[kq + 0][r] = v.x; sA[kq + 1][r] = v.y; sA[kq + 2][r] = v.z; sA[kq + 3][r] = v.w;
+      }
+      // W chunk: 64 columns x 32 k; two float4 per thread.
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int c = (threadIdx.x >> 3) + h * 32;
+        const int kq = (threadIdx.x & 7) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(W + static_cast<size_t>(c) * args.ldw + k0 + kq);
+        sW[kq + 0][c] = v.x; sW[kq + 1][c] = v.y; sW[kq + 2][c] = v.z; sW[kq + 3][c] = v.w;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < TK; ++k) {
+        const float a0 = sA[k][2 * ty], a1 = sA[k][2 * ty + 1];
+        const float4 w = *reinterpret_cast<const float4*>(&sW[k][4 * tx]);
+        acc[0][0] = fmaf(a0, w.x, acc[0][0]); acc[0][1] = fmaf(a0, w.y, acc[0][1]);
+        acc[0][2] = fmaf(a0, w.z, acc[0][2]); acc[0][3] = fmaf(a0, w.w, acc[0][3]);
+        acc[1][0] = fmaf(a1, w.x, acc[1][0]); acc[1][1] = fmaf(a1, w.y, acc[1][1]);
+        acc[1][2] = fmaf(a1, w.z, acc[1][2]); acc[1][3] = fmaf(a1, w.w, acc[1][3]);
+      }
+      __syncthreads();
+    }
+  }
+
+  const int col0 = n_tile * TN + 4 * tx;
+  float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (it.bias != nullptr) b = *reinterpret_cast<const float4*>(it.bias + col0);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = m_tile * TM + 2 * ty + i;
+    if (row >= it.rows) continue;
+    if (EPI == EPI_LSTM) {
+      const int unit = col0 >> 2;
+      float* cp = it.c + static_cast<size_t>(row) * batch.ld_c + unit;
+      const float cprev = it.c_zero ? 0.f : *cp;
+      const float gi = sigmoid_acc(acc[i][0] + b.x);
+      const float gf = sigmoid_acc(acc[i][1] + b.y);
+      const float go = sigmoid_acc(acc[i][2] + b.z);
+      const float gc = tanhf(acc[i][3] + b.w);
+      const float cn = gf * cprev + gi * gc;
+      *cp = cn;
+      reinterpret_cast<float*>(it.out)[static_cast<size_t>(row) * batch.ld_out + unit] = go * tanhf(cn);
+    } else {
+      float4 v = make_float4(acc[i][0] + b.x, acc[i][1] + b.y, acc[i][2] + b.z, acc[i][3] + b.w);
+      if (EPI == EPI_TANH) {
+        v.x = tanhf(v.x); v.y = tanhf(v.y); v.z = tanhf(v.z); v.w = tanhf(v.w);
+      }
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(it.out) + static_cast<size_t>(row) * batch.ld_out + col0) = v;
+    }
+  }
+}
+
+}  // namespace
+
+// fp32 twin of launch_cell_gemm.  Tiles are 32 rows x 64 columns, so the
+// batch must have been tiled with m_tiles = ceil(rows / 32) and n_cols % 64 == 0.
+int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* w, int ldw,
+                     const CellBatch& batch, cudaStream_t stream) {
+  SimtArgs a;
+  for (int i = 0; i < kNumActMaps; ++i) {
+    a.act[i] = act[i];
+    a.ld_act[i] = ld_act[i];
+  }
+  a.w = w;
+  a.ldw = ldw;
+  if (batch.total_tiles <= 0) return FTB_OK;
+  switch (epi) {
+    case EPI_STORE: cell_simt_kernel<EPI_STORE><<<batch.total_tiles, kSimtThreads, 0, stream>>>(a, batch); break;
+    case EPI_LSTM: cell_simt_kernel<EPI_LSTM><<<batch.total_tiles, kSimtThreads, 0, stream>>>(a, batch); break;
+    case EPI_TANH: cell_simt_kernel<EPI_TANH><<<batch.total_tiles, kSimtThreads, 0, stream>>>(a, batch); break;
+    default: return FTB_ERR_ARG;
+  }
+  return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+}
+
+}  // namespace ftb

@@ -1,0 +1,379 @@
+// Flash attention forward (non-causal) with online softmax for 16-bit inputs on
+// sm_100a, head dimension 128.
+//
+// Follows the recurrence of attn_func (examples/flash_attention/flash_attention.py:14-44):
+// per key/value block, scores S = scale * q k^T, running row maximum m and row sum
+// l, output rescaled when the maximum moves.  Two algebraic rearrangements that
+// leave the result unchanged up to rounding: the division by l is done once at the
+// end instead of per block, and the running maximum is only advanced when it
+// moves by more than 2^8 (the stale maximum cancels in the final division), so
+// the accumulator in TMEM is rarely touched.  The (m, l) merge itself is the one of
+// the reference's online softmax (kaleido/core/device/kernels/online_softmax.h:15-112).
+//
+// One CTA handles 256 query rows of one (batch, head): two 128-row query tiles
+// that ping-pong through the tensor pipe.
+//   warp 0       TMA producer: Q tiles, ring of K and V tiles
+//   warp 1       MMA issuer: S_t = Q_t K^T and O_t += P_t V, accumulators in TMEM
+//   warps 2..5   softmax warpgroup of query tile 0 (one thread per query row)
+//   warps 6..9   softmax warpgroup of query tile 1
+// P is written to shared memory in the swizzled K-major layout the PV MMA reads;
+// V is consumed MN-major straight from its row-major tile.
+#include "../../include/ftb200.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace ftb {
+namespace {
+
+constexpr int kHalfBytes = 128 * 128;  // 128 rows x 64 16-bit columns
+constexpr int kTileBytes = 2 * kHalfBytes;
+constexpr int kKVSlots = 3;
+constexpr int kThreads = 320;
+constexpr uint32_t kSmemBytes = (2 + 2 + kKVSlots) * kTileBytes + 1024;  // Q0,Q1,P0,P1,KV ring
+constexpr float kRescaleThreshold = 8.0f;
+
+__device__ __forceinline__ void tmem_ld32p(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// 16-byte chunk `chunk16` (0..15) of row `row` in a 128x128 16-bit tile stored as
+// two 64-column halves of 128-byte swizzled rows.
+__device__ __forceinline__ uint8_t* sw128_chunk_ptr(uint8_t* tile, int row, int chunk16) {
+  return tile + (chunk16 >> 3) * kHalfBytes + row * 128 + (((chunk16 & 7) ^ (row & 7)) << 4);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                  const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, int S,
+                  float scale_log2, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t q_full;
+  __shared__ uint64_t kv_full[kKVSlots], kv_empty[kKVSlots];
+  __shared__ uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2], o_staged[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort;
+
+  if (*reinterpret_cast<volatile int*>(status) != 0) return;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sQ = smem;                      // 2 tiles
+  uint8_t* sP = sQ + 2 * kTileBytes;       // 2 tiles
+  uint8_t* sKV = sP + 2 * kTileBytes;      // ring
+
+  const int pairs = S / 256;
+  const int bh = blockIdx.x / pairs;
+  const int qpair = blockIdx.x - bh * pairs;
+  const int row_base = bh * S;            // first row of this (batch, head) in the flattened [B*heads*S, d] view
+  const int q_row0 = row_base + qpair * 256;
+  const int n_kv = S / 128;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&mapQ);
+    prefetch_tmap(&mapK);
+    prefetch_tmap(&mapV);
+    prefetch_tmap(&mapO);
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < kKVSlots; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&pv_done[i], 1);
+      mbar_init(&o_staged[i], 4);
+    }
+    s_abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  // TMEM columns: S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512).
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&q_full, 2 * kTileBytes);
+      for (int t = 0; t < 2; ++t) {
+        tma_load_2d(sQ + t * kTileBytes, &mapQ, &q_full, 0, q_row0 + t * 128);
+        tma_load_2d(sQ + t * kTileBytes + kHalfBytes, &mapQ, &q_full, 64, q_row0 + t * 128);
+      }
+      int slot = 0;
+      uint32_t phase = 0;
+      for (int n = 0; n < 2 * n_kv; ++n) {  // K0, V0, K1, V1, ...
+        const int j = n >> 1;
+        const CUtensorMap* m = (n & 1) ? &mapV : &mapK;
+        if (!mbar_wait(&kv_empty[slot], phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT)) break;
+        uint8_t* dst = sKV + slot * kTileBytes;
+        mbar_arrive_expect_tx(&kv_full[slot], kTileBytes);
+        tma_load_2d(dst, m, &kv_full[slot], 0, row_base + j * 128);
+        tma_load_2d(dst + kHalfBytes, m, &kv_full[slot], 64, row_base + j * 128);
+        if (++slot == kKVSlots) {
+          slot = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_f16(128, 128, Fmt<T>::kind, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_f16(128, 128, Fmt<T>::kind, 0, 1);  // V is MN-major
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP), aKV = smem_u32(sKV);
+      uint32_t full_phase[kKVSlots] = {0, 0, 0};
+      uint32_t se_phase[2] = {0, 0}, pf_phase[2] = {0, 0};
+      bool ok = mbar_wait(&q_full, 0, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
+
+      // S_t(j) = Q_t . K_j^T for both query tiles; releases the K slot.
+      auto issue_s = [&](int j) -> bool {
+        const int slot = (2 * j) % kKVSlots;
+        if (!mbar_wait(&kv_full[slot], full_phase[slot], &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
+        full_phase[slot] ^= 1u;
+        const uint32_t aK = aKV + slot * kTileBytes;
+        for (int t = 0; t < 2; ++t) {
+          if (!mbar_wait(&s_empty[t], se_phase[t] ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
+          se_phase[t] ^= 1u;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+            umma_ss(tmem_base + t * 128, make_sdesc_sw128(aQ + t * kTileBytes + off, 16, 1024),
+                    make_sdesc_sw128(aK + off, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[t]);
+        }
+        umma_commit(&kv_empty[slot]);
+        return true;
+      };
+      // O_t += P_t(j) . V_j for both query tiles; releases the V slot.
+      auto issue_pv = [&](int j) -> bool {
+        const int slot = (2 * j + 1) % kKVSlots;
+        if (!mbar_wait(&kv_full[slot], full_phase[slot], &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
+        full_phase[slot] ^= 1u;
+        const uint32_t aV = aKV + slot * kTileBytes;
+        for (int t = 0; t < 2; ++t) {
+          if (!mbar_wait(&p_full[t], pf_phase[t], &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
+          pf_phase[t] ^= 1u;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            // A: P_t, K-major, 16 keys per step.  B: V, MN-major: 16 keys = two 8-row groups
+            // (1024 B apart), the two 64-column halves of d are 16 KB apart.
+            const uint32_t a_off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+            const uint32_t b_off = k * 2048;
+            umma_ss(tmem_base + 256 + t * 128, make_sdesc_sw128(aP + t * kTileBytes + a_off, 16, 1024),
+                    make_sdesc_sw128(aV + b_off, kHalfBytes, 1024), idesc_pv, (j | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&pv_done[t]);
+        }
+        umma_commit(&kv_empty[slot]);
+        return true;
+      };
+
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) ok = issue_s(j + 1);
+        if (ok) ok = issue_pv(j);
+      }
+    }
+  } else {
+    // ------------------------------------------------- softmax warpgroups (t = 0, 1)
+    const int t = (warp - 2) >> 2;
+    const int q = warp & 3;  // TMEM lane quadrant of this warp
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const uint32_t s_addr = lane_addr + t * 128;
+    const uint32_t o_addr = lane_addr + 256 + t * 128;
+    uint8_t* myP = sP + t * kTileBytes;
+    float m_used = 0.f, l = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_kv && ok; ++j) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t s[128];
+      tmem_ld32p(s_addr + 0, s + 0);
+      tmem_ld32p(s_addr + 32, s + 32);
+      tmem_ld32p(s_addr + 64, s + 64);
+      tmem_ld32p(s_addr + 96, s + 96);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[t]);
+
+      float mx = __uint_as_float(s[0]);
+#pragma unroll
+      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+      const float m_new = mx * scale_log2;
+      bool waited_pv = false;
+      if (j == 0) {
+        m_used = m_new;
+      } else {
+        const bool need = (m_new - m_used) > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          // O_t must be at rest: the PV MMA of the previous block has to be done.
+          if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[t], (j - 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
+            ok = false;
+            break;
+          }
+          waited_pv = true;
+          tc_fence_after();
+          const float alpha = need ? exp2_fast(m_used - m_new) : 1.f;
+          if (need) m_used = m_new;
+          l *= alpha;
+#pragma unroll 1
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + ch * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(o_addr + ch * 32, o);
+          }
+          tmem_st_wait();
+        }
+      }
+
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) {
+        const float p = exp2_fast(fmaf(__uint_as_float(s[i]), scale_log2, -m_used));
+        sum += p;
+        s[i] = __float_as_uint(p);
+      }
+      l += sum;
+
+      // The P tile is single-buffered: PV of the previous block must have read it.
+      if (j > 0 && !waited_pv) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[t], (j - 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
+          ok = false;
+          break;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        uint4 u;
+        u.x = Fmt<T>::pack2(__uint_as_float(s[8 * c + 0]), __uint_as_float(s[8 * c + 1]));
+        u.y = Fmt<T>::pack2(__uint_as_float(s[8 * c + 2]), __uint_as_float(s[8 * c + 3]));
+        u.z = Fmt<T>::pack2(__uint_as_float(s[8 * c + 4]), __uint_as_float(s[8 * c + 5]));
+        u.w = Fmt<T>::pack2(__uint_as_float(s[8 * c + 6]), __uint_as_float(s[8 * c + 7]));
+        *reinterpret_cast<uint4*>(sw128_chunk_ptr(myP, row, c)) = u;
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+
+    // Final: O_t / l -> 16-bit -> staging (the P tile, free once the last PV is done) -> TMA store.
+    if (ok && __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (n_kv - 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
+      tc_fence_after();
+      const float inv_l = 1.f / l;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + ch * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 u;
+          u.x = Fmt<T>::pack2(__uint_as_float(o[8 * c + 0]) * inv_l, __uint_as_float(o[8 * c + 1]) * inv_l);
+          u.y = Fmt<T>::pack2(__uint_as_float(o[8 * c + 2]) * inv_l, __uint_as_float(o[8 * c + 3]) * inv_l);
+          u.z = Fmt<T>::pack2(__uint_as_float(o[8 * c + 4]) * inv_l, __uint_as_float(o[8 * c + 5]) * inv_l);
+          u.w = Fmt<T>::pack2(__uint_as_float(o[8 * c + 6]) * inv_l, __uint_as_float(o[8 * c + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(sw128_chunk_ptr(myP, row, ch * 4 + c)) = u;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_staged[t]);
+      // One thread per warpgroup stores the tile once all four warps have staged their rows.
+      if (lane == 0 && (warp == 2 || warp == 6) &&
+          mbar_wait(&o_staged[t], 0, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) {
+        tma_store_2d(&mapO, myP, 0, q_row0 + t * 128);
+        tma_store_2d(&mapO, myP + kHalfBytes, 64, q_row0 + t * 128);
+        tma_store_commit();
+        tma_store_wait<0>();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (s_abort) {
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename T>
+int launch(const CUtensorMap& mQ, const CUtensorMap& mK, const CUtensorMap& mV, const CUtensorMap& mO, int units,
+           int S, float scale_log2, int* status, cudaStream_t stream) {
+  static bool configured = false;
+  auto kfn = flash_attn_kernel<T>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return FTB_ERR_LAUNCH;
+    configured = true;
+  }
+  kfn<<<units, kThreads, kSmemBytes, stream>>>(mQ, mK, mV, mO, S, scale_log2, status);
+  return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+}
+
+}  // namespace
+}  // namespace ftb
+
+using namespace ftb;
+
+extern "C" int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S,
+                                  int d, float scale, int dtype, void* workspace, size_t workspace_bytes,
+                                  void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!q || !k || !v || !o || B <= 0 || heads <= 0 || S <= 0) return FTB_ERR_ARG;
+  if (dtype != FTB_F16 && dtype != FTB_BF16) return FTB_ERR_ARG;
+  if (d != 128 || S % 256 != 0) return FTB_ERR_ARG;
+  const int64_t rows = static_cast<int64_t>(B) * heads * S;
+  if (rows > 0x7fffffffLL) return FTB_ERR_ARG;
+  if (workspace == nullptr || workspace_bytes < ftb_workspace_bytes()) return FTB_ERR_WORKSPACE;
+  int rc = check_device_sm100();
+  if (rc) return rc;
+  if (cudaMemsetAsync(workspace, 0, ftb_workspace_bytes(), stream) != cudaSuccess) return FTB_ERR_LAUNCH;
+  int* status = static_cast<int*>(workspace);
+
+  CUtensorMap mQ, mK, mV, mO;
+  if ((rc = make_tmap_2d(&mQ, q, dtype, rows, d, d, 128, 64))) return rc;
+  if ((rc = make_tmap_2d(&mK, k, dtype, rows, d, d, 128, 64))) return rc;
+  if ((rc = make_tmap_2d(&mV, v, dtype, rows, d, d, 128, 64))) return rc;
+  if ((rc = make_tmap_2d(&mO, o, dtype, rows, d, d, 128, 64))) return rc;
+  const int units = B * heads * (S / 256);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  if (dtype == FTB_F16) return launch<__half>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
+  return launch<__nv_bfloat16>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
+}

@@ -1,0 +1,33 @@
+// Host-side helpers shared by the C-ABI entry points: TMA tensor-map encoding
+// (through a driver entry point looked up at run time, so the library links
+// against the CUDA runtime only and still loads on a machine without a GPU
+// driver), device checks and small argument checks.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace ftb {
+
+enum DType : int { FTB_F32 = 0, FTB_F16 = 1, FTB_BF16 = 2 };
+
+inline size_t dtype_size(int dt) { return dt == FTB_F32 ? 4 : 2; }
+
+// Encodes a row-major [rows, cols] matrix (row stride `ld` elements) as a 2-D
+// tiled tensor map with box [box_rows, box_cols] and 128-byte swizzle; box_cols
+// times the element size must be 128 bytes or less.  Returns 0 on success.
+int make_tmap_2d(CUtensorMap* out, const void* base, int dtype, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_rows, uint32_t box_cols, bool swizzle128 = true);
+
+// 3-D variant: dims (cols, rows, planes) with byte strides for rows and planes.
+int make_tmap_3d(CUtensorMap* out, const void* base, int dtype, uint64_t cols, uint64_t rows, uint64_t planes,
+                 uint64_t row_stride_bytes, uint64_t plane_stride_bytes, uint32_t box_cols, uint32_t box_rows,
+                 uint32_t box_planes, bool swizzle128 = true);
+
+// 0 when the current device is compute capability 10.x, else FTB_ERR_ARCH.
+int check_device_sm100();
+
+int current_sm_count();
+
+}  // namespace ftb

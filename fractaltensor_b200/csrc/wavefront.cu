@@ -1,0 +1,469 @@
+// Host side of the RNN hot path: wavefront schedulers that turn the
+// fold/scan/map nests of the reference programs into levels of independent
+// cells, one kernel launch per level, plus the C-ABI entry points.
+//
+// The reference derives the same schedules by hand per benchmark
+// (benchmarks/rnn/fractaltensor/stacked_lstm/regions/region3.h:11-28 for the
+// stacked skew m = d + t, dilated_lstm/regions/region2.h:34-93 for the dilated
+// steps, grid_lstm/regions/region8.h:26-53 for m = d + i + j) and executes each
+// hyperplane as gather -> batched GEMM -> elementwise -> scatter.  Here a level
+// is one launch of a fused cell kernel that addresses the hyperplane in place.
+#include <algorithm>
+#include <map>
+#include <vector>
+
+#include "../../include/ftb200.h"
+#include "cell.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace ftb {
+
+int launch_cell_gemm(int dtype, int epi, int bn, const CUtensorMap* maps, const CUtensorMap& mapW,
+                     const CellBatch& batch, int* status, int sm_count, cudaStream_t stream);
+int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* w, int ldw,
+                     const CellBatch& batch, cudaStream_t stream);
+int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I, int H, int dtype,
+              cudaStream_t s);
+int pack_grid(const void* i2h, const void* h2h, void* Wp, int H, int dtype, cudaStream_t s);
+
+namespace {
+
+constexpr size_t kWorkspaceBytes = 256;
+
+// Launch context for one family of cells (one weight buffer, up to three
+// activation buffers).
+struct CellLauncher {
+  int dtype = FTB_BF16;
+  int epi = EPI_STORE;
+  int bn = 128;
+  int n_cols = 0, ld_out = 0, ld_c = 0;
+  int sm_count = 0;
+  int* status = nullptr;
+  cudaStream_t stream = nullptr;
+  // 16-bit path
+  CUtensorMap maps[kNumActMaps];
+  CUtensorMap mapW;
+  // fp32 path
+  const float* act[kNumActMaps] = {nullptr, nullptr, nullptr};
+  int ld_act[kNumActMaps] = {0, 0, 0};
+  const float* w = nullptr;
+  int ldw = 0;
+
+  int rows_per_tile() const { return dtype == FTB_F32 ? 32 : 128; }
+  int cols_per_tile() const { return dtype == FTB_F32 ? 64 : bn; }
+
+  // Launches the cells of one level (any number; split into chunks).
+  int run(std::vector<CellItem>& items) const {
+    const int n_tiles_n = (n_cols + cols_per_tile() - 1) / cols_per_tile();
+    for (size_t off = 0; off < items.size(); off += kMaxItems) {
+      CellBatch b;
+      b.n_items = static_cast<int>(std::min<size_t>(kMaxItems, items.size() - off));
+      b.n_cols = n_cols;
+      b.ld_out = ld_out;
+      b.ld_c = ld_c;
+      b.pad_ = 0;
+      int tiles = 0;
+      for (int i = 0; i < b.n_items; ++i) {
+        CellItem it = items[off + i];
+        it.m_tiles = (it.rows + rows_per_tile() - 1) / rows_per_tile();
+        it.tile0 = tiles;
+        tiles += it.m_tiles * n_tiles_n;
+        b.items[i] = it;
+      }
+      b.total_tiles = tiles;
+      int rc;
+      if (dtype == FTB_F32)
+        rc = launch_cell_simt(epi, act, ld_act, w, ldw, b, stream);
+      else
+        rc = launch_cell_gemm(dtype, epi, bn, maps, mapW, b, status, sm_count, stream);
+      if (rc) return rc;
+    }
+    return FTB_OK;
+  }
+};
+
+CellItem blank_item() {
+  CellItem it;
+  it.out = nullptr;
+  it.c = nullptr;
+  it.bias = nullptr;
+  for (int s = 0; s < kMaxSeg; ++s) it.seg_row[s] = it.seg_kb[s] = it.seg_wk[s] = it.seg_map[s] = 0;
+  it.nseg = 0;
+  it.w_row0 = 0;
+  it.rows = 0;
+  it.c_zero = 0;
+  it.tile0 = 0;
+  it.m_tiles = 0;
+  return it;
+}
+
+void add_seg(CellItem& it, int map, int64_t row, int k_elems, int wk) {
+  const int s = it.nseg++;
+  it.seg_map[s] = map;
+  it.seg_row[s] = static_cast<int32_t>(row);
+  it.seg_kb[s] = k_elems / 64;
+  it.seg_wk[s] = wk;
+}
+
+int begin_call(void* workspace, size_t workspace_bytes, cudaStream_t stream, int** status) {
+  if (workspace == nullptr || workspace_bytes < kWorkspaceBytes) return FTB_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return FTB_ERR_ALIGN;
+  int rc = check_device_sm100();
+  if (rc) return rc;
+  if (cudaMemsetAsync(workspace, 0, kWorkspaceBytes, stream) != cudaSuccess) return FTB_ERR_LAUNCH;
+  *status = static_cast<int*>(workspace);
+  return FTB_OK;
+}
+
+bool valid_dtype(int dt) { return dt == FTB_F32 || dt == FTB_F16 || dt == FTB_BF16; }
+
+int pick_bn(int n_cols, int want) {
+  if (want == 128 || want == 256) return (n_cols % want == 0) ? want : 0;
+  if (want != 0) return 0;
+  if (n_cols % 256 == 0 && n_cols >= 2048) return 256;
+  return (n_cols % 128 == 0) ? 128 : 0;
+}
+
+}  // namespace
+}  // namespace ftb
+
+using namespace ftb;
+
+extern "C" {
+
+int ftb_version(void) { return 1; }
+
+const char* ftb_status_str(int code) {
+  switch (code) {
+    case FTB_OK: return "ok";
+    case FTB_ERR_ARG: return "bad argument (shape, pointer or dtype)";
+    case FTB_ERR_ALIGN: return "pointer or stride not 16-byte aligned";
+    case FTB_ERR_WORKSPACE: return "workspace missing or too small";
+    case FTB_ERR_DRIVER: return "tensor-map encode failed or driver entry point missing";
+    case FTB_ERR_LAUNCH: return "kernel launch failed";
+    case FTB_ERR_ARCH: return "device is not sm_100";
+    case FTB_ERR_TIMEOUT_TMA: return "device wait ran out: TMA stage never arrived";
+    case FTB_ERR_TIMEOUT_MMA: return "device wait ran out: MMA never committed";
+    case FTB_ERR_TIMEOUT_EPI: return "device wait ran out: epilogue never drained";
+    case FTB_ERR_TIMEOUT_SLOT: return "device wait ran out: no free pipeline stage";
+    default: return "unknown status";
+  }
+}
+
+size_t ftb_workspace_bytes(void) { return kWorkspaceBytes; }
+
+int ftb_read_status(const void* workspace, int* status_out, void* stream) {
+  if (workspace == nullptr || status_out == nullptr) return FTB_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(status_out, workspace, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return FTB_ERR_LAUNCH;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return FTB_ERR_LAUNCH;
+  return FTB_OK;
+}
+
+int ftb_lstm_pack_weights(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I,
+                          int H, int dtype, void* stream) {
+  if (!W || !U || !Wp || D <= 0 || I <= 0 || H <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
+  if (bias != nullptr && bias_p == nullptr) return FTB_ERR_ARG;
+  return pack_lstm(W, U, bias, Wp, bias_p, D, I, H, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int ftb_grid_pack_weights(const void* i2h, const void* h2h, void* Wp, int H, int dtype, void* stream) {
+  if (!i2h || !h2h || !Wp || H <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
+  return pack_grid(i2h, h2h, Wp, H, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
+                         int N, int I, int H, int dtype, int layers_per_group, int bn, void* workspace,
+                         size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!x || !Wp || !hs || !c || D <= 0 || L <= 0 || N <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
+  if (H <= 0 || I <= 0 || H % 64 != 0 || I % 64 != 0) return FTB_ERR_ARG;
+  if (D > 1 && I != H) return FTB_ERR_ARG;
+  if (static_cast<int64_t>(D) * L * N > 0x7fffffffLL) return FTB_ERR_ARG;
+  int* status = nullptr;
+  int rc = begin_call(workspace, workspace_bytes, stream, &status);
+  if (rc) return rc;
+
+  const int K = I + H;
+  const size_t es = dtype_size(dtype);
+  CellLauncher cl;
+  cl.dtype = dtype;
+  cl.epi = EPI_LSTM;
+  cl.n_cols = 4 * H;
+  cl.ld_out = H;
+  cl.ld_c = H;
+  cl.status = status;
+  cl.stream = stream;
+  cl.sm_count = current_sm_count();
+  if (dtype == FTB_F32) {
+    cl.act[0] = static_cast<const float*>(x);
+    cl.ld_act[0] = I;
+    cl.act[1] = cl.act[2] = static_cast<const float*>(hs);
+    cl.ld_act[1] = cl.ld_act[2] = H;
+    cl.w = static_cast<const float*>(Wp);
+    cl.ldw = K;
+  } else {
+    cl.bn = pick_bn(4 * H, bn);
+    if (cl.bn == 0) return FTB_ERR_ARG;
+    rc = make_tmap_2d(&cl.maps[0], x, dtype, static_cast<uint64_t>(L) * N, I, I, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.maps[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, 128, 64);
+    if (rc) return rc;
+    cl.maps[2] = cl.maps[1];
+    rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.bn, 64);
+    if (rc) return rc;
+  }
+
+  int G = layers_per_group;
+  if (G <= 0) {
+    // Keep a group's packed weights within about half of L2.
+    int dev = 0, l2 = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev);
+    const double per_layer = 4.0 * H * K * es;
+    G = static_cast<int>((0.5 * l2) / per_layer);
+    G = std::max(1, std::min(G, D));
+    if (per_layer * D <= 0.5 * l2) G = D;
+  }
+  G = std::min(G, D);
+
+  std::vector<CellItem> items;
+  for (int g0 = 0; g0 < D; g0 += G) {
+    const int Lg = std::min(G, D - g0);
+    for (int m = 0; m < Lg + L - 1; ++m) {
+      items.clear();
+      for (int l = g0; l < g0 + Lg; ++l) {
+        const int t = m - (l - g0);
+        if (t < 0 || t >= L) continue;
+        CellItem it = blank_item();
+        if (l == 0)
+          add_seg(it, 0, static_cast<int64_t>(t) * N, I, 0);
+        else
+          add_seg(it, 1, (static_cast<int64_t>(l - 1) * L + t) * N, H, 0);
+        if (t > 0) add_seg(it, 2, (static_cast<int64_t>(l) * L + t - 1) * N, H, I);
+        it.w_row0 = l * 4 * H;
+        it.rows = N;
+        it.c_zero = (t == 0);
+        it.out = static_cast<char*>(hs) + (static_cast<size_t>(l) * L + t) * N * H * es;
+        it.c = c + static_cast<size_t>(l) * N * H;
+        it.bias = bias_p ? bias_p + static_cast<size_t>(l) * 4 * H : nullptr;
+        items.push_back(it);
+      }
+      rc = cl.run(items);
+      if (rc) return rc;
+    }
+  }
+  return FTB_OK;
+}
+
+int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
+                         const int* dilations, int D, int L, int N, int H, int dtype, int bn, void* workspace,
+                         size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!x || !Wp || !hs || !c || !dilations || D <= 0 || L <= 0 || N <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
+  if (H <= 0 || H % 64 != 0) return FTB_ERR_ARG;
+  int max_dil = 1;
+  for (int l = 0; l < D; ++l) {
+    if (dilations[l] <= 0) return FTB_ERR_ARG;
+    max_dil = std::max(max_dil, dilations[l]);
+  }
+  if (static_cast<int64_t>(D) * L * N > 0x7fffffffLL) return FTB_ERR_ARG;
+  int* status = nullptr;
+  int rc = begin_call(workspace, workspace_bytes, stream, &status);
+  if (rc) return rc;
+
+  const int K = 2 * H;
+  const size_t es = dtype_size(dtype);
+  CellLauncher cl;
+  cl.dtype = dtype;
+  cl.epi = EPI_LSTM;
+  cl.n_cols = 4 * H;
+  cl.ld_out = H;
+  cl.ld_c = H;
+  cl.status = status;
+  cl.stream = stream;
+  cl.sm_count = current_sm_count();
+  if (dtype == FTB_F32) {
+    cl.act[0] = static_cast<const float*>(x);
+    cl.act[1] = cl.act[2] = static_cast<const float*>(hs);
+    cl.ld_act[0] = cl.ld_act[1] = cl.ld_act[2] = H;
+    cl.w = static_cast<const float*>(Wp);
+    cl.ldw = K;
+  } else {
+    cl.bn = pick_bn(4 * H, bn);
+    if (cl.bn == 0) return FTB_ERR_ARG;
+    rc = make_tmap_2d(&cl.maps[0], x, dtype, static_cast<uint64_t>(L) * N, H, H, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.maps[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, 128, 64);
+    if (rc) return rc;
+    cl.maps[2] = cl.maps[1];
+    rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.bn, 64);
+    if (rc) return rc;
+  }
+
+  // Layer l advances in steps of dilations[l] consecutive timesteps: those
+  // timesteps only depend on the step before (same layer) and on the layer
+  // below, so one step is one cell of batch dilation*N.  Earliest-start levels.
+  std::map<int, std::vector<CellItem>> levels;
+  std::vector<std::vector<int>> level_of(D);
+  for (int l = 0; l < D; ++l) {
+    const int dl = dilations[l];
+    const int steps = (L + dl - 1) / dl;
+    level_of[l].resize(steps);
+    for (int s = 0; s < steps; ++s) {
+      const int t0 = s * dl;
+      const int t1 = std::min(L, t0 + dl);
+      int lv = 0;
+      if (s > 0) lv = level_of[l][s - 1] + 1;
+      if (l > 0) {
+        const int below = (t1 - 1) / dilations[l - 1];
+        lv = std::max(lv, level_of[l - 1][below] + 1);
+      }
+      level_of[l][s] = lv;
+      CellItem it = blank_item();
+      if (l == 0)
+        add_seg(it, 0, static_cast<int64_t>(t0) * N, H, 0);
+      else
+        add_seg(it, 1, (static_cast<int64_t>(l - 1) * L + t0) * N, H, 0);
+      if (s > 0) add_seg(it, 2, (static_cast<int64_t>(l) * L + t0 - dl) * N, H, H);
+      it.w_row0 = l * 4 * H;
+      it.rows = (t1 - t0) * N;
+      it.c_zero = (s == 0);
+      it.out = static_cast<char*>(hs) + (static_cast<size_t>(l) * L + t0) * N * H * es;
+      it.c = c + static_cast<size_t>(l) * max_dil * N * H;
+      it.bias = bias_p ? bias_p + static_cast<size_t>(l) * 4 * H : nullptr;
+      levels[lv].push_back(it);
+    }
+  }
+  for (auto& kv : levels) {
+    rc = cl.run(kv.second);
+    if (rc) return rc;
+  }
+  return FTB_OK;
+}
+
+int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* Wpy, const float* bias_x,
+                     const float* bias_y, void* hx, void* hy, int D, int A, int B, int N, int H, int dtype,
+                     void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!X || !Y || !Wpx || !Wpy || !hx || !hy || D <= 0 || A <= 0 || B <= 0 || N <= 0 || !valid_dtype(dtype))
+    return FTB_ERR_ARG;
+  if (H <= 0 || H % 64 != 0) return FTB_ERR_ARG;
+  if (static_cast<int64_t>(D) * A * B * N > 0x7fffffffLL) return FTB_ERR_ARG;
+  int* status = nullptr;
+  int rc = begin_call(workspace, workspace_bytes, stream, &status);
+  if (rc) return rc;
+
+  const int K = 3 * H;
+  const size_t es = dtype_size(dtype);
+  // Two launch contexts: direction x reads (X | hx | hy) with Wpx, direction y
+  // reads (Y | hx | hy) with Wpy.
+  CellLauncher dir[2];
+  for (int d = 0; d < 2; ++d) {
+    CellLauncher& cl = dir[d];
+    cl.dtype = dtype;
+    cl.epi = EPI_TANH;
+    cl.n_cols = H;
+    cl.ld_out = H;
+    cl.ld_c = H;
+    cl.status = status;
+    cl.stream = stream;
+    cl.sm_count = current_sm_count();
+    const void* in = d == 0 ? X : Y;
+    const void* wp = d == 0 ? Wpx : Wpy;
+    if (dtype == FTB_F32) {
+      cl.act[0] = static_cast<const float*>(in);
+      cl.act[1] = static_cast<const float*>(hx);
+      cl.act[2] = static_cast<const float*>(hy);
+      cl.ld_act[0] = cl.ld_act[1] = cl.ld_act[2] = H;
+      cl.w = static_cast<const float*>(wp);
+      cl.ldw = K;
+    } else {
+      cl.bn = pick_bn(H, 128);
+      if (cl.bn == 0) return FTB_ERR_ARG;
+      const uint64_t grid_rows = static_cast<uint64_t>(A) * B * N;
+      rc = make_tmap_2d(&cl.maps[0], in, dtype, grid_rows, H, H, 128, 64);
+      if (rc) return rc;
+      rc = make_tmap_2d(&cl.maps[1], hx, dtype, grid_rows * D, H, H, 128, 64);
+      if (rc) return rc;
+      rc = make_tmap_2d(&cl.maps[2], hy, dtype, grid_rows * D, H, H, 128, 64);
+      if (rc) return rc;
+      rc = make_tmap_2d(&cl.mapW, wp, dtype, static_cast<uint64_t>(D) * H, K, K, cl.bn, 64);
+      if (rc) return rc;
+    }
+  }
+
+  std::vector<CellItem> items[2];
+  for (int m = 0; m <= (D - 1) + (A - 1) + (B - 1); ++m) {
+    items[0].clear();
+    items[1].clear();
+    for (int d = 0; d < D; ++d) {
+      for (int a = 0; a < A; ++a) {
+        const int b = m - d - a;
+        if (b < 0 || b >= B) continue;
+        const int64_t cell = (static_cast<int64_t>(d) * A + a) * B + b;
+        for (int dirn = 0; dirn < 2; ++dirn) {
+          CellItem it = blank_item();
+          if (a > 0) add_seg(it, 1, ((static_cast<int64_t>(d) * A + a - 1) * B + b) * N, H, 0);
+          if (b > 0) add_seg(it, 2, (cell - 1) * N, H, H);
+          if (d == 0)
+            add_seg(it, 0, (static_cast<int64_t>(a) * B + b) * N, H, 2 * H);
+          else
+            add_seg(it, dirn == 0 ? 1 : 2, ((static_cast<int64_t>(d - 1) * A + a) * B + b) * N, H, 2 * H);
+          it.w_row0 = d * H;
+          it.rows = N;
+          it.out = static_cast<char*>(dirn == 0 ? hx : hy) + static_cast<size_t>(cell) * N * H * es;
+          const float* bias = dirn == 0 ? bias_x : bias_y;
+          it.bias = bias ? bias + static_cast<size_t>(d) * H : nullptr;
+          items[dirn].push_back(it);
+        }
+      }
+    }
+    for (int dirn = 0; dirn < 2; ++dirn) {
+      rc = dir[dirn].run(items[dirn]);
+      if (rc) return rc;
+    }
+  }
+  return FTB_OK;
+}
+
+int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, int dtype, void* workspace,
+                size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!A || !Bt || !out || M <= 0 || N <= 0 || K <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
+  if (K % 64 != 0) return FTB_ERR_ARG;
+  if (dtype == FTB_F32 ? (N % 64 != 0) : (N % 128 != 0)) return FTB_ERR_ARG;
+  int* status = nullptr;
+  int rc = begin_call(workspace, workspace_bytes, stream, &status);
+  if (rc) return rc;
+  CellLauncher cl;
+  cl.dtype = dtype;
+  cl.epi = EPI_STORE;
+  cl.n_cols = N;
+  cl.ld_out = N;
+  cl.status = status;
+  cl.stream = stream;
+  cl.sm_count = current_sm_count();
+  if (dtype == FTB_F32) {
+    cl.act[0] = cl.act[1] = cl.act[2] = static_cast<const float*>(A);
+    cl.ld_act[0] = cl.ld_act[1] = cl.ld_act[2] = K;
+    cl.w = static_cast<const float*>(Bt);
+    cl.ldw = K;
+  } else {
+    cl.bn = (N % 256 == 0) ? 256 : 128;
+    rc = make_tmap_2d(&cl.maps[0], A, dtype, M, K, K, 128, 64);
+    if (rc) return rc;
+    cl.maps[1] = cl.maps[2] = cl.maps[0];
+    rc = make_tmap_2d(&cl.mapW, Bt, dtype, N, K, K, cl.bn, 64);
+    if (rc) return rc;
+  }
+  std::vector<CellItem> items(1, blank_item());
+  add_seg(items[0], 0, 0, K, 0);
+  items[0].rows = M;
+  items[0].out = out;
+  return cl.run(items);
+}
+
+}  // extern "C"

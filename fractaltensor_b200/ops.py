@@ -1,0 +1,232 @@
+"""Tensor-level operators: torch CUDA tensors in, torch CUDA tensors out, all
+compute in libftb200.so.  PyTorch is used for device memory and streams only.
+
+Layouts follow the reference's C++ benchmarks (time-major activations
+``[L, N, H]``, per-layer states ``[D, L, N, H]``:
+benchmarks/rnn/fractaltensor/stacked_lstm/lstm.cu:31-38); the model-level
+functions in :mod:`fractaltensor_b200.frontend` convert from and to the nested
+FractalTensor views of the reference's Python programs.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+_DT = {torch.float32: _lib.DTYPE_F32, torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16}
+
+_workspaces = {}
+
+
+def _dtype_code(t):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError("unsupported dtype %s (float32, float16 or bfloat16)" % t.dtype)
+
+
+def _req(t, name, dtype=None):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError("%s must be a torch.Tensor" % name)
+    if not t.is_cuda:
+        raise RuntimeError("%s must live on a CUDA device: there is no CPU path" % name)
+    if not t.is_contiguous():
+        raise ValueError("%s must be contiguous" % name)
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+    return t
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def workspace(device):
+    """The per-device workspace handed to every call (holds the status word)."""
+    key = torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(lib.ftb_workspace_bytes(), dtype=torch.uint8, device=torch.device("cuda", key))
+        _workspaces[key] = ws
+    return ws
+
+
+def check_status(device=None):
+    """Synchronises the current stream and raises if a device wait ran out in
+    the last call on `device`."""
+    ws = workspace(device if device is not None else torch.cuda.current_device())
+    out = ctypes.c_int(0)
+    check(lib.ftb_read_status(_ptr(ws), ctypes.byref(out), _stream()), "ftb_read_status")
+    check(out.value, "device kernel")
+
+
+# ----------------------------------------------------------------------- LSTM
+def lstm_pack_weights(W, U, bias=None):
+    """W: [D,4,I,H], U: [D,4,H,H], bias: [D,4,H] or [D,4,1,H] -> (Wp [D,4H,I+H], bias_p fp32 [D,4H] | None)."""
+    _req(W, "W")
+    _req(U, "U", W.dtype)
+    D, four, I, H = W.shape
+    if four != 4 or tuple(U.shape) != (D, 4, H, H):
+        raise ValueError("expected W [D,4,I,H] and U [D,4,H,H], got %s and %s" % (tuple(W.shape), tuple(U.shape)))
+    Wp = torch.empty(D, 4 * H, I + H, dtype=W.dtype, device=W.device)
+    bias_p = None
+    if bias is not None:
+        bias = _req(bias.reshape(D, 4, H).contiguous(), "bias", W.dtype)
+        bias_p = torch.empty(D, 4 * H, dtype=torch.float32, device=W.device)
+    with torch.cuda.device(W.device):
+        check(lib.ftb_lstm_pack_weights(_ptr(W), _ptr(U), _ptr(bias), _ptr(Wp), _ptr(bias_p), D, I, H,
+                                        _dtype_code(W), _stream()), "ftb_lstm_pack_weights")
+    return Wp, bias_p
+
+
+def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0):
+    """x: [L,N,I]; Wp: [D,4H,I+H] -> (hs [D,L,N,H], c fp32 [D,N,H])."""
+    _req(x, "x")
+    _req(Wp, "Wp", x.dtype)
+    L, N, I = x.shape
+    D, H4, K = Wp.shape
+    H = H4 // 4
+    if K != I + H:
+        raise ValueError("Wp %s does not match x %s" % (tuple(Wp.shape), tuple(x.shape)))
+    if bias_p is not None:
+        _req(bias_p, "bias_p", torch.float32)
+    if hs is None:
+        hs = torch.empty(D, L, N, H, dtype=x.dtype, device=x.device)
+    if c is None:
+        c = torch.empty(D, N, H, dtype=torch.float32, device=x.device)
+    _req(hs, "hs", x.dtype)
+    _req(c, "c", torch.float32)
+    ws = workspace(x.device)
+    with torch.cuda.device(x.device):
+        check(lib.ftb_lstm_stacked_fwd(_ptr(x), _ptr(Wp), _ptr(bias_p), _ptr(hs), _ptr(c), D, L, N, I, H,
+                                       _dtype_code(x), layers_per_group, bn, _ptr(ws), ws.numel(), _stream()),
+              "ftb_lstm_stacked_fwd")
+    return hs, c
+
+
+def lstm_dilated(x, Wp, dilations, bias_p=None, hs=None, c=None, bn=0):
+    """x: [L,N,H]; Wp: [D,4H,2H]; dilations: D ints -> (hs [D,L,N,H], c fp32 [D,max_dil*N,H])."""
+    _req(x, "x")
+    _req(Wp, "Wp", x.dtype)
+    L, N, H = x.shape
+    D = Wp.shape[0]
+    if tuple(Wp.shape) != (D, 4 * H, 2 * H) or len(dilations) != D:
+        raise ValueError("Wp %s / dilations do not match x %s" % (tuple(Wp.shape), tuple(x.shape)))
+    if bias_p is not None:
+        _req(bias_p, "bias_p", torch.float32)
+    md = max(int(d) for d in dilations)
+    if hs is None:
+        hs = torch.empty(D, L, N, H, dtype=x.dtype, device=x.device)
+    if c is None:
+        c = torch.empty(D, md * N, H, dtype=torch.float32, device=x.device)
+    dil = (ctypes.c_int * D)(*[int(d) for d in dilations])
+    ws = workspace(x.device)
+    with torch.cuda.device(x.device):
+        check(lib.ftb_lstm_dilated_fwd(_ptr(x), _ptr(Wp), _ptr(bias_p), _ptr(hs), _ptr(c), dil, D, L, N, H,
+                                       _dtype_code(x), bn, _ptr(ws), ws.numel(), _stream()),
+              "ftb_lstm_dilated_fwd")
+    return hs, c
+
+
+# ------------------------------------------------------------------- grid RNN
+def grid_pack_weights(i2h, h2h):
+    """i2h: [D,2H,H], h2h: [D,H,H] -> Wp [D,H,3H]."""
+    _req(i2h, "i2h")
+    _req(h2h, "h2h", i2h.dtype)
+    D, H2, H = i2h.shape
+    if H2 != 2 * H or tuple(h2h.shape) != (D, H, H):
+        raise ValueError("expected i2h [D,2H,H] and h2h [D,H,H]")
+    Wp = torch.empty(D, H, 3 * H, dtype=i2h.dtype, device=i2h.device)
+    with torch.cuda.device(i2h.device):
+        for d in range(D):
+            check(lib.ftb_grid_pack_weights(_ptr(i2h[d]), _ptr(h2h[d]), _ptr(Wp[d]), H, _dtype_code(i2h), _stream()),
+                  "ftb_grid_pack_weights")
+    return Wp
+
+
+def grid_rnn(X, Y, Wpx, Wpy, bias_x=None, bias_y=None):
+    """X,Y: [A,B,N,H]; Wpx,Wpy: [D,H,3H]; bias fp32 [D,H] -> (hx, hy) each [D,A,B,N,H]."""
+    _req(X, "X")
+    _req(Y, "Y", X.dtype)
+    _req(Wpx, "Wpx", X.dtype)
+    _req(Wpy, "Wpy", X.dtype)
+    A, B, N, H = X.shape
+    D = Wpx.shape[0]
+    if tuple(Y.shape) != (A, B, N, H) or tuple(Wpx.shape) != (D, H, 3 * H) or tuple(Wpy.shape) != (D, H, 3 * H):
+        raise ValueError("grid_rnn: inconsistent shapes")
+    for b in (bias_x, bias_y):
+        if b is not None:
+            _req(b, "bias", torch.float32)
+    hx = torch.empty(D, A, B, N, H, dtype=X.dtype, device=X.device)
+    hy = torch.empty_like(hx)
+    ws = workspace(X.device)
+    with torch.cuda.device(X.device):
+        check(lib.ftb_grid_rnn_fwd(_ptr(X), _ptr(Y), _ptr(Wpx), _ptr(Wpy), _ptr(bias_x), _ptr(bias_y), _ptr(hx),
+                                   _ptr(hy), D, A, B, N, H, _dtype_code(X), _ptr(ws), ws.numel(), _stream()),
+              "ftb_grid_rnn_fwd")
+    return hx, hy
+
+
+# ------------------------------------------------------------ B2B GEMM / attention
+def b2b_gemm(A, B, C, out=None):
+    """A: [batch,M,K]; B: [batch,N,K]; C: [batch,P,N] -> D [batch,M,P] = (A.B^T).C^T per batch entry."""
+    _req(A, "A")
+    _req(B, "B", A.dtype)
+    _req(C, "C", A.dtype)
+    batch, M, K = A.shape
+    N = B.shape[1]
+    P = C.shape[1]
+    if tuple(B.shape) != (batch, N, K) or tuple(C.shape) != (batch, P, N):
+        raise ValueError("b2b_gemm: inconsistent shapes")
+    if out is None:
+        out = torch.empty(batch, M, P, dtype=A.dtype, device=A.device)
+    _req(out, "out", A.dtype)
+    ws = workspace(A.device)
+    with torch.cuda.device(A.device):
+        check(lib.ftb_b2b_gemm(_ptr(A), _ptr(B), _ptr(C), _ptr(out), batch, M, N, K, P, _dtype_code(A), _ptr(ws),
+                               ws.numel(), _stream()), "ftb_b2b_gemm")
+    return out
+
+
+def flash_attention(q, k, v, scale=None, out=None):
+    """q,k,v: [B,heads,S,d] -> softmax(scale * q k^T) v, same shape."""
+    _req(q, "q")
+    _req(k, "k", q.dtype)
+    _req(v, "v", q.dtype)
+    B, heads, S, d = q.shape
+    if tuple(k.shape) != tuple(q.shape) or tuple(v.shape) != tuple(q.shape):
+        raise ValueError("flash_attention: q, k, v must have the same shape")
+    if scale is None:
+        scale = 1.0
+    if out is None:
+        out = torch.empty_like(q)
+    _req(out, "out", q.dtype)
+    ws = workspace(q.device)
+    with torch.cuda.device(q.device):
+        check(lib.ftb_flash_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, heads, S, d, float(scale),
+                                     _dtype_code(q), _ptr(ws), ws.numel(), _stream()), "ftb_flash_attn_fwd")
+    return out
+
+
+def gemm_nt(A, Bt, out=None):
+    """A: [M,K]; Bt: [N,K] -> A @ Bt^T."""
+    _req(A, "A")
+    _req(Bt, "Bt", A.dtype)
+    M, K = A.shape
+    N = Bt.shape[0]
+    if Bt.shape[1] != K:
+        raise ValueError("gemm_nt: inner dimensions differ")
+    if out is None:
+        out = torch.empty(M, N, dtype=A.dtype, device=A.device)
+    ws = workspace(A.device)
+    with torch.cuda.device(A.device):
+        check(lib.ftb_gemm_nt(_ptr(A), _ptr(Bt), _ptr(out), M, N, K, _dtype_code(A), _ptr(ws), ws.numel(),
+                              _stream()), "ftb_gemm_nt")
+    return out

@@ -1,0 +1,117 @@
+/* C ABI of libftb200: sm_100a kernels for FractalTensor's nested data-parallel
+ * hot path (RNN cell wavefronts, back-to-back GEMM, flash attention).
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer owned by the caller unless stated
+ *    otherwise; the library allocates nothing in these calls.
+ *  - Matrices are row-major with the last dimension contiguous; base pointers
+ *    must be 16-byte aligned.
+ *  - `dtype`: 0 = fp32, 1 = fp16, 2 = bf16.  16-bit types run on tcgen05 tensor
+ *    cores with fp32 accumulation; fp32 runs on CUDA cores.
+ *  - `stream` is a cudaStream_t passed as void*.  Calls are asynchronous,
+ *    stream-ordered, re-entrant and safe to capture in a CUDA graph.
+ *  - `workspace` is at least ftb_workspace_bytes() bytes.  Its first word is the
+ *    device status word of the call: 0, or the code of the first bounded device
+ *    wait that ran out.  Read it with ftb_read_status() after the stream synced.
+ *  - Return value: 0, or an FTB_ERR_* code (ftb_status_str() names it).
+ *
+ * The reference exposes this path as C++ host functors with compile-time tile
+ * shapes and raw device pointers (kaleido/core/device/kernels/lstm.h,
+ * gemm.h) and as Python programs over kaleido.operations; each entry point
+ * cites what it stands in for.
+ */
+#ifndef FTB200_H_
+#define FTB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FTB_DTYPE_F32 0
+#define FTB_DTYPE_F16 1
+#define FTB_DTYPE_BF16 2
+
+int ftb_version(void);
+const char* ftb_status_str(int code);
+size_t ftb_workspace_bytes(void);
+/* Copies the status word out of `workspace` (synchronises `stream`). */
+int ftb_read_status(const void* workspace, int* status_out, void* stream);
+
+/* Packs LSTM parameters for the cell kernels.
+ * W: [D,4,I,H], U: [D,4,H,H] in the reference's x@W + h@U orientation and gate
+ * order i,f,o,c~ (examples/stacked_rnn/stacked_rnn.py:12-36); bias: [D,4,H] or
+ * NULL.  Wp: [D,4H,I+H] K-major with row u*4+g = gate g of unit u (the reference
+ * kernels take W,U as [4H,K] row-major, kaleido/core/device/kernels/lstm_kernels.h:24-48).
+ * bias_p: fp32 [D,4H] in the same row order (may be NULL when bias is NULL). */
+int ftb_lstm_pack_weights(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I,
+                          int H, int dtype, void* stream);
+
+/* Stacked LSTM forward as a depth x time wavefront.
+ * Stands in for stacked_lstm() (examples/stacked_rnn/stacked_lstm1.py:66-76) and
+ * for StackedLstmRegion1/2/3 (kaleido/core/device/kernels/lstm/stacked_lstm/region{1,2,3}.h,
+ * benchmarks/rnn/fractaltensor/stacked_lstm/lstm.cu:19-60).
+ * x: [L,N,I]; Wp/bias_p from ftb_lstm_pack_weights; hs (out): [D,L,N,H] hidden
+ * states of every layer (top layer = hs[D-1]); c (out): fp32 [D,N,H] final cell
+ * state.  I == H is required for D > 1.  `layers_per_group` > 0 sweeps the
+ * wavefront over groups of that many layers so a group's weights stay in L2;
+ * 0 picks a group size from the L2 size.  `bn` is the accumulator tile width
+ * (128 or 256; 0 = automatic). */
+int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
+                         int N, int I, int H, int dtype, int layers_per_group, int bn, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/* Dilated stacked LSTM forward: layer l reads its own state from 2^l... steps
+ * back, dilations[l] given explicitly.  Stands in for dilated_layer()/model()
+ * (examples/dilated_rnn/dilated_rnn.py:16-41) and DilatedLstmRegion1/2
+ * (kaleido/core/device/kernels/lstm/dilated_lstm/region{1,2}.h).
+ * x: [L,N,H]; hs (out): [D,L,N,H]; c (scratch/out): fp32 [D, max_dilation*N, H].
+ * `dilations` is a HOST array of D ints; L must be a multiple of each. */
+int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
+                         const int* dilations, int D, int L, int N, int H, int dtype, int bn, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/* Packs one direction of a grid-RNN block: i2h [2H,H], h2h [H,H] (x@W
+ * orientation, examples/grid_rnn/grid_rnn.py:21-30,42-50) into Wp [H,3H]
+ * K-major with K order [state_x | state_y | input]. */
+int ftb_grid_pack_weights(const void* i2h, const void* h2h, void* Wp, int H, int dtype, void* stream);
+
+/* Stacked 2-D grid RNN forward (vanilla tanh cells, recurrence along both
+ * axes), anti-diagonal wavefront.  Stands in for stacked_grid_rnns()
+ * (examples/grid_rnn/grid_rnn.py:42-122) and the grid regions
+ * (benchmarks/rnn/fractaltensor/grid_lstm/regions/region{1..8}.h).
+ * X,Y: [A,B,N,H] inputs of the x and y directions at grid point (a,b);
+ * Wpx,Wpy: [D,H,3H] from ftb_grid_pack_weights; bias_x,bias_y: fp32 [D,H] or NULL;
+ * hx,hy (out): [D,A,B,N,H].  state_x = hx[a-1][b], state_y = hy[a][b-1]. */
+int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* Wpy, const float* bias_x,
+                     const float* bias_y, void* hx, void* hy, int D, int A, int B, int N, int H, int dtype,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Back-to-back GEMM D = (A.B).C per batch entry, fp32 accumulation, the
+ * intermediate rounded to the 16-bit input type.  Stands in for B2BGemm /
+ * KeBack2BackGemm (kaleido/core/device/kernels/gemm.h:233-269,
+ * cutlass_wmma.h:440-540).  A: [batch,M,K] row-major; B: [batch,N,K]
+ * (column-major [K,N]); C: [batch,P,N] (column-major [N,P]); Dout: [batch,M,P].
+ * K = N = P = 128, M % 128 == 0; dtype fp16 or bf16. */
+int ftb_b2b_gemm(const void* A, const void* B, const void* C, void* Dout, int batch, int M, int N, int K, int P,
+                 int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Flash attention forward with online softmax, non-causal.  Stands in for
+ * flash_attention() (examples/flash_attention/flash_attention.py:14-88) with the
+ * (max, sum, out) carry started at (-inf, 0, 0).  q,k,v,o: [B,heads,S,d];
+ * d = 128, S % 128 == 0; dtype fp16 or bf16; softmax(scale * q.k^T). */
+int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S, int d,
+                       float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Plain GEMM out[M,N] = A[M,K] . Bt[N,K]^T through the cell kernel's main loop
+ * (support op; the reference's KeCuteGemm, kaleido/core/device/kernels/cutlass_wmma.h:115-181).
+ * 16-bit dtypes: K % 64 == 0, N % 128 == 0.  fp32: K % 64 == 0, N % 64 == 0. */
+int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, int dtype, void* workspace,
+                size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FTB200_H_ */

@@ -1,0 +1,221 @@
+"""CPU oracle: dense PyTorch restatements of the reference's model programs.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the product (``fractaltensor_b200/``) may
+import this package; it is imported by ``tests/``, by ``__graft_entry__.smoke()``
+and by the ``cpu_baseline`` / ``--impl reference`` legs of ``bench.py`` as the
+checker and the timed CPU baseline, never as the thing shipped.
+
+Each function restates, with whole-batch tensor operations, the arithmetic that
+the reference's eager frontend performs one sample and one gate at a time.  The
+restatements are pinned against the reference's own frontend programs, executed
+from the reference tree, by ``tests/golden/generate.py``; the resulting vectors
+are committed under ``tests/golden/`` and checked by ``tests/test_oracle.py``.
+
+All functions compute in the dtype of their inputs (fp32 in every pinned use).
+``round_to`` (a 16-bit torch dtype or None) optionally rounds each hidden state
+the way a 16-bit kernel has to before feeding it back into a matrix multiply;
+the default None is the reference's semantics.
+"""
+import math
+
+import torch
+
+
+def _round(t, round_to):
+    return t if round_to is None else t.to(round_to).to(t.dtype)
+
+
+def lstm_cell_dense(x, h, c, W, U, b):
+    """One LSTM cell for a whole batch.
+
+    Follows gate_f / lstm_cell (examples/stacked_rnn/stacked_rnn.py:12-36):
+    gate k = x @ W[k] + h @ U[k] + b[k], order (i, f, o, c~);
+    c' = sigmoid(f) * c + sigmoid(i) * tanh(c~); h' = sigmoid(o) * tanh(c').
+    x: [N,I]; h,c: [N,H]; W: [4,I,H]; U: [4,H,H]; b: [4,H] or None.
+    """
+    g = [x @ W[k] + h @ U[k] + (0 if b is None else b[k]) for k in range(4)]
+    i, f, o = torch.sigmoid(g[0]), torch.sigmoid(g[1]), torch.sigmoid(g[2])
+    c_new = f * c + i * torch.tanh(g[3])
+    h_new = o * torch.tanh(c_new)
+    return h_new, c_new
+
+
+def stacked_lstm_dense(x, W, U, b=None, round_to=None):
+    """Stacked LSTM: fold over depth of (map over batch of (scan over time)).
+
+    Follows stacked_lstm / lstm_layer / batched_cell
+    (examples/stacked_rnn/stacked_lstm1.py:40-76).  x: [L,N,I] time-major;
+    W: [D,4,I,H]; U: [D,4,H,H]; b: [D,4,H] or None.
+    Returns hs [D,L,N,H] (hidden state of every layer) and c [D,N,H] (final).
+    """
+    D = W.shape[0]
+    L, N, _ = x.shape
+    H = U.shape[-1]
+    hs = x.new_zeros(D, L, N, H)
+    cs = x.new_zeros(D, N, H)
+    inp = x
+    for d in range(D):
+        h = x.new_zeros(N, H)
+        c = x.new_zeros(N, H)
+        for t in range(L):
+            h, c = lstm_cell_dense(inp[t], h, c, W[d], U[d], None if b is None else b[d])
+            h = _round(h, round_to)
+            hs[d, t] = h
+        cs[d] = c
+        inp = hs[d]
+    return hs, cs
+
+
+def dilated_lstm_dense(x, W, U, dilations, b=None, round_to=None):
+    """Stacked dilated LSTM.
+
+    Follows dilated_layer / model (examples/dilated_rnn/dilated_rnn.py:16-41) with
+    DilatedMap (kaleido/frontend/operations/fractaltensor/functional/apply_to_each.py:83-177):
+    layer l splits the sequence into dilations[l] interleaved sub-sequences and
+    scans each from a zero state, i.e. (h,c)[l][t] = cell((h,c)[l][t-dil], x = h[l-1][t]).
+    x: [L,N,H]; W,U: [D,4,H,H].  Returns hs [D,L,N,H].
+    """
+    D = W.shape[0]
+    L, N, H = x.shape
+    hs = x.new_zeros(D, L, N, H)
+    inp = x
+    for l in range(D):
+        dil = int(dilations[l])
+        cs = [None] * L
+        for t in range(L):
+            if t >= dil:
+                hp, cp = hs[l, t - dil], cs[t - dil]
+            else:
+                hp, cp = x.new_zeros(N, H), x.new_zeros(N, H)
+            h, c = lstm_cell_dense(inp[t], hp, cp, W[l], U[l], None if b is None else b[l])
+            hs[l, t] = _round(h, round_to)
+            cs[t] = c
+        inp = hs[l]
+    return hs
+
+
+def grid_rnn_dense(X, Y, i2h_x, h2h_x, b_x, i2h_y, h2h_y, b_y, round_to=None):
+    """Stacked 2-D grid RNN with vanilla tanh cells.
+
+    Follows vanilla_cell / grid_cell / direction_y / direction_x /
+    stacked_grid_rnns (examples/grid_rnn/grid_rnn.py:42-122):
+    s = cat(state_x, state_y); h_x = tanh(s @ i2h_x + x_t @ h2h_x + b_x), h_y alike
+    with the y parameters and y_t; state_x = h_x[a-1][b], state_y = h_y[a][b-1],
+    zeros at the borders; the next layer reads (h_x, h_y) of the layer below.
+    X,Y: [A,B,N,H]; i2h_*: [D,2H,H]; h2h_*: [D,H,H]; b_*: [D,H] or None.
+    Returns hx, hy: [D,A,B,N,H].
+    """
+    D = i2h_x.shape[0]
+    A, B, N, H = X.shape
+    hx = X.new_zeros(D, A, B, N, H)
+    hy = X.new_zeros(D, A, B, N, H)
+    xin, yin = X, Y
+    zero = X.new_zeros(N, H)
+    for d in range(D):
+        bx = 0 if b_x is None else b_x[d]
+        by = 0 if b_y is None else b_y[d]
+        for a in range(A):
+            for b in range(B):
+                sx = hx[d, a - 1, b] if a > 0 else zero
+                sy = hy[d, a, b - 1] if b > 0 else zero
+                s = torch.cat([sx, sy], dim=1)
+                hx[d, a, b] = _round(torch.tanh(s @ i2h_x[d] + xin[a, b] @ h2h_x[d] + bx), round_to)
+                hy[d, a, b] = _round(torch.tanh(s @ i2h_y[d] + yin[a, b] @ h2h_y[d] + by), round_to)
+        xin, yin = hx[d], hy[d]
+    return hx, hy
+
+
+def b2b_gemm_dense(A, B, C):
+    """Back-to-back GEMM with the reference kernel's rounding.
+
+    Follows KeBack2BackGemm (kaleido/core/device/kernels/cutlass_wmma.h:489-533):
+    P = A.B accumulated in fp32 and rounded to the 16-bit input type, D = P.C
+    accumulated in fp32 and rounded again.  A: [batch,M,K]; B: [batch,N,K]
+    (the reference's column-major [K,N]); C: [batch,P,N]; returns [batch,M,P].
+    """
+    lp = A.dtype
+    P = (A.float() @ B.float().transpose(-1, -2)).to(lp)
+    return (P.float() @ C.float().transpose(-1, -2)).to(lp)
+
+
+def flash_attention_dense(q, k, v, scale=1.0, block=64):
+    """Blockwise attention with the online-softmax carry of the reference.
+
+    Follows attn_func / per_block_func (examples/flash_attention/flash_attention.py:14-60)
+    over key/value blocks of `block` rows, for all query rows at once, with the
+    carry started at (max, sum, out) = (-float32.max, 0, 0) in that order and
+    `scale` multiplied into q @ k^T.  q,k,v: [B,heads,S,d]; returns the same shape.
+    """
+    Bsz, heads, S, d = q.shape
+    m = q.new_full((Bsz, heads, S, 1), -torch.finfo(torch.float32).max)
+    l = q.new_zeros(Bsz, heads, S, 1)
+    o = q.new_zeros(Bsz, heads, S, d)
+    for j0 in range(0, S, block):
+        kj, vj = k[:, :, j0:j0 + block], v[:, :, j0:j0 + block]
+        w = (q @ kj.transpose(-1, -2)) * scale
+        cur_m = w.max(dim=-1, keepdim=True).values
+        e = torch.exp(w - cur_m)
+        ev = e @ vj
+        cur_l = e.sum(dim=-1, keepdim=True)
+        new_m = torch.maximum(cur_m, m)
+        r_prev = torch.exp(m - new_m)
+        r_cur = torch.exp(cur_m - new_m)
+        new_l = r_prev * l + r_cur * cur_l
+        o = (o * l * r_prev + r_cur * ev) / new_l
+        m, l = new_m, new_l
+    return o
+
+
+def attention_plain(q, k, v, scale=1.0):
+    """softmax(scale * q k^T) v, the closed form the blockwise carry equals."""
+    return torch.softmax((q @ k.transpose(-1, -2)) * scale, dim=-1) @ v
+
+
+# ------------------------------------------------------------------ seeded inputs
+def _gen(seed):
+    g = torch.Generator()
+    g.manual_seed(seed)
+    return g
+
+
+def make_lstm_inputs(D, L, N, I, H, seed, w_bound, dtype=torch.float32, bias=False):
+    """x ~ N(0,1) [L,N,I]; W,U ~ U(-w_bound, w_bound); bias 0 or ~U when `bias`."""
+    g = _gen(seed)
+    x = torch.randn(L, N, I, generator=g)
+    W = (torch.rand(D, 4, I, H, generator=g) * 2 - 1) * w_bound
+    U = (torch.rand(D, 4, H, H, generator=g) * 2 - 1) * w_bound
+    b = (torch.rand(D, 4, H, generator=g) * 2 - 1) * w_bound if bias else None
+    cast = lambda t: None if t is None else t.to(dtype)
+    return cast(x), cast(W), cast(U), cast(b)
+
+
+def make_grid_inputs(D, A, B, N, H, seed, w_bound, dtype=torch.float32, bias=False):
+    """src [B,N,H], trg [A,N,H] ~ N(0,1); X[a][b] = src[b], Y[a][b] = trg[a]."""
+    g = _gen(seed)
+    src = torch.randn(B, N, H, generator=g)
+    trg = torch.randn(A, N, H, generator=g)
+    X = src[None].expand(A, B, N, H).contiguous()
+    Y = trg[:, None].expand(A, B, N, H).contiguous()
+    mk = lambda *s: (torch.rand(*s, generator=g) * 2 - 1) * w_bound
+    p = dict(i2h_x=mk(D, 2 * H, H), h2h_x=mk(D, H, H), i2h_y=mk(D, 2 * H, H), h2h_y=mk(D, H, H))
+    p["b_x"] = mk(D, H) if bias else None
+    p["b_y"] = mk(D, H) if bias else None
+    cast = lambda t: None if t is None else t.to(dtype)
+    return cast(X), cast(Y), {k_: cast(v_) for k_, v_ in p.items()}
+
+
+def make_b2b_inputs(batch, M, N, K, P, seed, dtype=torch.float16):
+    g = _gen(seed)
+    s = 1.0 / math.sqrt(128.0)
+    A = (torch.randn(batch, M, K, generator=g) * s).to(dtype)
+    B = (torch.randn(batch, N, K, generator=g) * s).to(dtype)
+    C = (torch.randn(batch, P, N, generator=g) * s).to(dtype)
+    return A, B, C
+
+
+def make_attention_inputs(B, heads, S, d, seed, dtype=torch.float16):
+    g = _gen(seed)
+    q = torch.randn(B, heads, S, d, generator=g).to(dtype)
+    k = torch.randn(B, heads, S, d, generator=g).to(dtype)
+    v = torch.randn(B, heads, S, d, generator=g).to(dtype)
+    return q, k, v
