@@ -1,0 +1,255 @@
+"""Headline benchmark: stacked LSTM forward, BASELINE config 4 (depth 16, hidden 1024,
+batch 256 per GPU, 100 steps, bf16 with fp32 cell state), metric samples*steps/s.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --steps K --warmup W    # CPU arm: the oracle port on host cores
+
+One "step" is one full forward pass of the wavefront over one batch of synthetic
+input.  Batch sharding across GPUs is weak scaling (256 samples per GPU, weights
+replicated, one all-gather of the top-layer output shards per step).  Prints one
+JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(D=16, L=100, N=256, I=1024, H=1024, seed=3, w_bound=1.0 / 32)
+METRIC = "lstm_samples_steps_per_s_h1024_d16"
+UNIT = "samples*steps/s"
+FLOPS_PER_SAMPLE_STEP = CFG["D"] * 2 * 4 * CFG["H"] * (CFG["I"] + CFG["H"])  # all layers
+# DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
+# profiles/cell_gemm_lstm_config4.md (None until captured).
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(burst=d["bf16_tflops"], sustained=d["bf16_tflops_sustained"], hbm=d["hbm_gbs"], src="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, src="fallback")
+
+
+class ClockSampler(object):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm = sorted(float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit())
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[3 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_port_rate(sample_steps, threads):
+    """Oracle port (dense fp32 restatement of the reference program) on the host cores:
+    full depth and batch of config 4, `sample_steps` timesteps.  Returns samples*steps/s."""
+    from oracle import dense
+    torch.set_num_threads(threads)
+    x, W, U, _ = dense.make_lstm_inputs(CFG["D"], sample_steps, CFG["N"], CFG["I"], CFG["H"], CFG["seed"],
+                                        CFG["w_bound"], dtype=torch.bfloat16)
+    x, W, U = x.float(), W.float(), U.float()
+    t0 = time.perf_counter()
+    dense.stacked_lstm_dense(x, W, U)
+    dt = time.perf_counter() - t0
+    return CFG["N"] * sample_steps / dt, dt
+
+
+def run_reference(args, rank):
+    """CPU arm: the reference has no GPU implementation that runs here, and its eager Python
+    frontend does not travel; its semantics are timed through the oracle port."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample = 10
+    rates = []
+    for i in range(args.warmup + args.steps):
+        r, dt = cpu_port_rate(sample, threads)
+        if i >= args.warmup:
+            rates.append((r, dt))
+    value = sum(r for r, _ in rates) / len(rates)
+    ms = 1e3 * sum(dt for _, dt in rates) / len(rates)
+    sample_desc = "full depth 16 and batch 256 of config 4, %d of 100 timesteps per step, fp32 on bf16-rounded inputs" % sample
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "stacked LSTM D16 H1024 I1024 N256 L100 (BASELINE config 4)", "sample": sample_desc},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample_desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ftb200", choices=["ftb200", "reference"])
+    ap.add_argument("--layers-per-group", type=int, default=0)
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ftb200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    from fractaltensor_b200 import ops, sharding
+    from fractaltensor_b200._lib import lib
+    from oracle import dense  # seeded synthetic inputs + the cpu_baseline leg only
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    D, L, N, I, H = CFG["D"], CFG["L"], CFG["N"], CFG["I"], CFG["H"]
+    # Every rank draws its own 256-sample shard of the global batch (seed offset by rank).
+    x_host, W, U, _ = dense.make_lstm_inputs(D, L, N, I, H, CFG["seed"] + 1000 * rank, CFG["w_bound"],
+                                             dtype=torch.bfloat16)
+    _, W, U, _ = dense.make_lstm_inputs(D, 1, 1, I, H, CFG["seed"], CFG["w_bound"], dtype=torch.bfloat16)
+    Wp, _ = ops.lstm_pack_weights(W.to(dev), U.to(dev))
+    del W, U
+    x_pinned = x_host.pin_memory()
+    x_dev = x_pinned.to(dev)
+    hs = torch.empty(D, L, N, H, dtype=torch.bfloat16, device=dev)
+    c = torch.empty(D, N, H, dtype=torch.float32, device=dev)
+    out_pinned = torch.empty(L, N, H, dtype=torch.bfloat16).pin_memory()
+    gathered = torch.empty(world * L, N, H, dtype=torch.bfloat16, device=dev) if world > 1 else None
+
+    def step_resident():
+        ops.lstm_stacked(x_dev, Wp, None, hs, c, layers_per_group=args.layers_per_group, bn=args.bn)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, hs[D - 1].reshape(L, N, H))
+
+    def step_e2e():
+        xd = x_pinned.to(dev, non_blocking=True)
+        ops.lstm_stacked(xd, Wp, None, hs, c, layers_per_group=args.layers_per_group, bn=args.bn)
+        out_pinned.copy_(hs[D - 1], non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(args.warmup):
+        step_resident()
+    ops.check_status()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    n0 = lib.ftb_launch_count()
+    total_ms = timed(step_resident, args.steps)
+    launches = lib.ftb_launch_count() - n0
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_status()
+
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps)
+    ops.check_status()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ms_per_step = total_ms / args.steps
+    value = world * N * L / (ms_per_step * 1e-3)
+    e2e_value = world * N * L / (e2e_ms / args.steps * 1e-3)
+    pk = peaks()
+    peak_kind = "sustained" if total_ms >= 1000.0 else "burst"
+    # Dominant kernel: cell_gemm_kernel (LSTM epilogue).  Every launch in the timed region is
+    # that kernel, back to back on one stream, so its average duration is total / launches and
+    # its algorithmic FLOPs per launch are the step's FLOPs / launches per step.
+    flops_per_step = FLOPS_PER_SAMPLE_STEP * N * L
+    achieved = flops_per_step / (ms_per_step * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": pk[peak_kind], "unit": "TFLOP/s",
+                "frac": achieved / pk[peak_kind], "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                "peak_source": "%s %s bf16 GEMM" % (pk["src"], peak_kind),
+                "kernel": "cell_gemm_kernel<bf16, LSTM epilogue>", "launches_per_step": launches / args.steps,
+                "avg_launch_us": 1e3 * total_ms / max(launches, 1)}
+    cpu = None
+    if not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        sample = 50
+        rate, dt = cpu_port_rate(sample, threads)
+        cpu = {"value": rate, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": "full depth 16 and batch 256, %d of 100 timesteps, fp32 on bf16-rounded inputs (%.1f s)" % (sample, dt)}
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "stacked LSTM D16 H1024 I1024 N256/GPU L100, bf16 weights/activations, fp32 cell state "
+                               "(BASELINE config 4)", "global_batch": world * N, "seq_len": L,
+                   "parallelism": "batch-sharded x%d, weights replicated, all-gather of top-layer output" % world,
+                   "cache": "per-step inputs exceed L2 (268 MB weights + 839 MB states vs 126 MB L2); no flush needed",
+                   "layers_per_group": args.layers_per_group, "bn": args.bn},
+        "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_pinned.numel() * 2,
+                "d2h_bytes_per_step": out_pinned.numel() * 2},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -17,6 +17,7 @@ SIGNATURES = {
     "ftb_version": (_i, []),
     "ftb_status_str": (ctypes.c_char_p, [_i]),
     "ftb_workspace_bytes": (_sz, []),
+    "ftb_launch_count": (ctypes.c_longlong, []),
     "ftb_read_status": (_i, [_vp, ctypes.POINTER(_i), _vp]),
     "ftb_lstm_pack_weights": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "ftb_lstm_stacked_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),

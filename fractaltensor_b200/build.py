@@ -47,7 +47,7 @@ def build(verbose=False, force=False):
     if failed:
         raise RuntimeError("nvcc failed")
     if procs or not os.path.exists(LIB):
-        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-cudart", "static"]
+        cmd = [nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-o", LIB] + objs + ["-cudart", "static"]
         subprocess.check_call(cmd)
     return LIB
 

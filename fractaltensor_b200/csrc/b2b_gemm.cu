@@ -311,6 +311,7 @@ int launch(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mC, 
   }
   const int grid = total < sm_count ? total : sm_count;
   kfn<<<grid, kThreads, kSmemBytes, stream>>>(mA, mB, mC, mD, total, tiles_per_batch, status);
+  count_launch();
   return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
 

@@ -304,6 +304,7 @@ int launch_one(const CUtensorMap* maps, const CUtensorMap& mapW, const CellBatch
   int grid = batch.total_tiles < sm_count ? batch.total_tiles : sm_count;
   if (grid <= 0) return FTB_OK;
   kfn<<<grid, kThreads, C::kSmemBytes, stream>>>(maps[0], maps[1], maps[2], mapW, batch, status);
+  count_launch();
   return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
 

@@ -131,6 +131,7 @@ int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const 
     case EPI_TANH: cell_simt_kernel<EPI_TANH><<<batch.total_tiles, kSimtThreads, 0, stream>>>(a, batch); break;
     default: return FTB_ERR_ARG;
   }
+  count_launch();
   return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
 

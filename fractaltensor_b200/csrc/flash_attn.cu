@@ -344,6 +344,7 @@ int launch(const CUtensorMap& mQ, const CUtensorMap& mK, const CUtensorMap& mV, 
     configured = true;
   }
   kfn<<<units, kThreads, kSmemBytes, stream>>>(mQ, mK, mV, mO, S, scale_log2, status);
+  count_launch();
   return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
 

@@ -41,6 +41,7 @@ template <typename E>
 int pack_matrix(const E* in, E* out, int gates, int K, int H, int ldo, int k_off, cudaStream_t s) {
   dim3 grid((H + 31) / 32, (K + 31) / 32, gates), block(32, 8);
   pack_transpose_kernel<E><<<grid, block, 0, s>>>(in, out, gates, K, H, ldo, k_off);
+  count_launch();
   return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
 
@@ -76,6 +77,7 @@ int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* b
       else
         pack_bias_kernel<__nv_bfloat16><<<(n + thr - 1) / thr, thr, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(b), bo, 4, H);
       if (cudaGetLastError() != cudaSuccess) return FTB_ERR_LAUNCH;
+      count_launch();
     }
   }
   return FTB_OK;

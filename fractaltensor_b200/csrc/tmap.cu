@@ -1,5 +1,6 @@
 #include "tmap.h"
 
+#include <atomic>
 #include <mutex>
 
 #include "ptx.cuh"
@@ -78,6 +79,12 @@ int check_device_sm100() {
   if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return FTB_ERR_ARCH;
   return major == 10 ? FTB_OK : FTB_ERR_ARCH;
 }
+
+namespace {
+std::atomic<long long> g_launches{0};
+}
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
 
 int current_sm_count() {
   int dev = 0, n = 0;

@@ -30,4 +30,8 @@ int check_device_sm100();
 
 int current_sm_count();
 
+// Process-wide count of kernels this library has launched (reported by ftb_launch_count()).
+void count_launch(int n = 1);
+long long launches_so_far();
+
 }  // namespace ftb

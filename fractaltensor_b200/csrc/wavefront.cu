@@ -118,11 +118,13 @@ int begin_call(void* workspace, size_t workspace_bytes, cudaStream_t stream, int
 
 bool valid_dtype(int dt) { return dt == FTB_F32 || dt == FTB_F16 || dt == FTB_BF16; }
 
+// Accumulator tile width.  The last column tile of a cell may be partial (the
+// epilogue skips 32-column groups past n_cols), so n_cols % 32 == 0 is enough.
 int pick_bn(int n_cols, int want) {
-  if (want == 128 || want == 256) return (n_cols % want == 0) ? want : 0;
+  if (n_cols % 32 != 0) return 0;
+  if (want == 128 || want == 256) return want;
   if (want != 0) return 0;
-  if (n_cols % 256 == 0 && n_cols >= 2048) return 256;
-  return (n_cols % 128 == 0) ? 128 : 0;
+  return (n_cols % 256 == 0 && n_cols >= 2048) ? 256 : 128;
 }
 
 }  // namespace
@@ -152,6 +154,8 @@ const char* ftb_status_str(int code) {
 }
 
 size_t ftb_workspace_bytes(void) { return kWorkspaceBytes; }
+
+long long ftb_launch_count(void) { return launches_so_far(); }
 
 int ftb_read_status(const void* workspace, int* status_out, void* stream) {
   if (workspace == nullptr || status_out == nullptr) return FTB_ERR_ARG;

@@ -1,0 +1,159 @@
+"""Model-level entry points with the signatures of the reference's programs.
+
+The reference expresses the hot path as nested ``ops.fold / scan / map`` programs
+over ``FractalTensor`` values (flat ``.data`` buffer plus nested ``.indices``):
+
+    stacked_lstm(embs, Wss, Uss, bss)                  examples/stacked_rnn/stacked_lstm1.py:66-76
+    dilated_lstm(embs, Wss, Uss, bss)                  examples/dilated_rnn/dilated_rnn.py:16-41 (the fold in model())
+    stacked_grid_rnns(src_encs, trg_encs, params)      examples/grid_rnn/grid_rnn.py:111-122
+    flash_attention(qsss, ksss, vsss)                  examples/flash_attention/flash_attention.py:75-88
+
+The functions here keep those argument lists and return the same nested values,
+but run the whole nest as one fused wavefront on the GPU.  Arguments may be the
+reference's own ``kaleido.FractalTensor`` objects (only ``.data``, ``.indices``
+and ``.element_shape`` are read) or the light ``FractalTensor`` defined here.  A
+FractalTensor whose nesting is rectangular is exactly a dense array
+``[n1, ..., nk, *element_shape]``; ragged nestings are rejected, since there is
+no CPU fallback to hand them to.
+"""
+import torch
+
+from . import ops
+
+
+class FractalTensor(object):
+    """Minimal stand-in for kaleido.FractalTensor (kaleido/frontend/fractal_tensor.py:85-181):
+    a flat ``data`` buffer, nested-list ``indices`` and the shape of the stored tensors."""
+
+    def __init__(self, data, indices, element_shape):
+        self.data = data.reshape(-1)
+        self.indices = indices
+        self.element_shape = tuple(element_shape)
+
+    @staticmethod
+    def from_dense(t, depth):
+        """t: [n1, ..., n_depth, *element_shape]."""
+        dims = list(t.shape[:depth])
+
+        def nest(ds):
+            if len(ds) == 1:
+                return list(range(ds[0]))
+            return [nest(ds[1:]) for _ in range(ds[0])]
+
+        return FractalTensor(t.contiguous(), nest(dims), t.shape[depth:])
+
+    @property
+    def depth(self):
+        d, x = 0, self.indices
+        while isinstance(x, list):
+            d, x = d + 1, (x[0] if x else None)
+        return d
+
+    def __len__(self):
+        return len(self.indices)
+
+    def to_dense(self):
+        return _dense(self)
+
+
+def _nest_dims(indices):
+    """Lengths of a rectangular nesting; raises ValueError for a ragged one."""
+    dims = []
+    level = [indices]
+    while level and isinstance(level[0], list):
+        n = len(level[0])
+        if any(len(x) != n for x in level):
+            raise ValueError("ragged FractalTensor: variable-length nestings are not accelerated "
+                             "and there is no CPU fallback")
+        dims.append(n)
+        level = [y for x in level for y in x]
+    return dims
+
+
+def _dense(x):
+    """Dense [n1,...,nk,*element_shape] view of a FractalTensor-like value (or a tensor as is)."""
+    if isinstance(x, torch.Tensor):
+        return x
+    if not (hasattr(x, "data") and hasattr(x, "indices")):
+        raise TypeError("expected a FractalTensor or a torch.Tensor, got %s" % type(x).__name__)
+    dims = _nest_dims(x.indices)
+    return x.data.reshape(*dims, *tuple(x.element_shape))
+
+
+def _cuda(t, dtype=None):
+    if not t.is_cuda:
+        raise RuntimeError("inputs must already live on a CUDA device: there is no CPU path")
+    return t if dtype is None else t.to(dtype)
+
+
+def stacked_lstm(embs, Wss, Uss, bss, dtype=None):
+    """fold(depth) of map(batch) of scan(time) of lstm_cell, as one depth x time wavefront.
+
+    embs: [N][L] of [1,I]; Wss: [D][4] of [I,H]; Uss: [D][4] of [H,H]; bss: [D][4] of [1,H].
+    Returns the top layer's hidden states as a FractalTensor [N][L] of [1,H].
+    """
+    x = _cuda(_dense(embs), dtype)
+    W, U, b = _cuda(_dense(Wss), dtype), _cuda(_dense(Uss), dtype), _cuda(_dense(bss), dtype)
+    N, L = x.shape[0], x.shape[1]
+    D, H = U.shape[0], U.shape[-1]
+    Wp, bias_p = ops.lstm_pack_weights(W.contiguous(), U.contiguous(), b.reshape(D, 4, H).contiguous())
+    xt = x.reshape(N, L, -1).transpose(0, 1).contiguous()  # time-major [L,N,I]
+    hs, _ = ops.lstm_stacked(xt, Wp, bias_p)
+    top = hs[D - 1].transpose(0, 1).reshape(N, L, 1, H)
+    return FractalTensor.from_dense(top, 2)
+
+
+def dilated_lstm(embs, Wss, Uss, bss, dilations=None, dtype=None):
+    """map(batch) of fold(layers) of dilated_map(scan(lstm_cell)), dilation 2**layer by default."""
+    x = _cuda(_dense(embs), dtype)
+    W, U, b = _cuda(_dense(Wss), dtype), _cuda(_dense(Uss), dtype), _cuda(_dense(bss), dtype)
+    N, L = x.shape[0], x.shape[1]
+    D, H = U.shape[0], U.shape[-1]
+    if dilations is None:
+        dilations = [2 ** l for l in range(D)]
+    Wp, bias_p = ops.lstm_pack_weights(W.contiguous(), U.contiguous(), b.reshape(D, 4, H).contiguous())
+    xt = x.reshape(N, L, H).transpose(0, 1).contiguous()
+    hs, _ = ops.lstm_dilated(xt, Wp, dilations, bias_p)
+    top = hs[D - 1].transpose(0, 1).reshape(N, L, 1, H)
+    return FractalTensor.from_dense(top, 2)
+
+
+def stacked_grid_rnns(src_encs, trg_encs, stacked_params, dtype=None):
+    """Grid RNN over the src x trg grid for a batch of sentence pairs.
+
+    src_encs: [N][B] of [1,H]; trg_encs: [N][A] of [1,H]; stacked_params: a sequence of
+    ((i2h_x, h2h_x, bias_x), (i2h_y, h2h_y, bias_y)) per layer (tensors or objects with .data).
+    Returns (hx, hy) of the top layer as FractalTensors [N][A][B] of [1,H], where grid
+    point (a, b) pairs trg[a] with src[b].
+    """
+    src = _cuda(_dense(src_encs), dtype)
+    trg = _cuda(_dense(trg_encs), dtype)
+    N, B = src.shape[0], src.shape[1]
+    A = trg.shape[1]
+    H = src.shape[-1]
+    raw = lambda p: p.data if hasattr(p, "data") and not isinstance(p, torch.Tensor) else p
+    stack = lambda d, i: torch.stack([_cuda(raw(layer[d][i]), src.dtype) for layer in stacked_params])
+    Wpx = ops.grid_pack_weights(stack(0, 0).contiguous(), stack(0, 1).contiguous())
+    Wpy = ops.grid_pack_weights(stack(1, 0).contiguous(), stack(1, 1).contiguous())
+    bx = stack(0, 2).reshape(-1, H).float().contiguous()
+    by = stack(1, 2).reshape(-1, H).float().contiguous()
+    s = src.reshape(N, B, H).transpose(0, 1)  # [B,N,H]
+    t = trg.reshape(N, A, H).transpose(0, 1)  # [A,N,H]
+    X = s[None].expand(A, B, N, H).contiguous()
+    Y = t[:, None].expand(A, B, N, H).contiguous()
+    hx, hy = ops.grid_rnn(X, Y, Wpx, Wpy, bx, by)
+    D = Wpx.shape[0]
+    to_ft = lambda h: FractalTensor.from_dense(h[D - 1].permute(2, 0, 1, 3).reshape(N, A, B, 1, H), 3)
+    return to_ft(hx), to_ft(hy)
+
+
+def flash_attention(qsss, ksss, vsss, scale=1.0, dtype=None):
+    """map(batch) of map(heads) of map(query blocks) of reduce(key/value blocks) of attn_func.
+
+    q/k/v: [B][heads][blocks] of [block, d].  Returns the same nesting.
+    """
+    q, k, v = (_cuda(_dense(t), dtype) for t in (qsss, ksss, vsss))
+    Bsz, heads, nblk, blk, d = q.shape
+    flat = lambda t: t.reshape(Bsz, heads, nblk * blk, d).contiguous()
+    o = ops.flash_attention(flat(q), flat(k), flat(v), scale=scale)
+    return FractalTensor.from_dense(o.reshape(Bsz, heads, nblk, blk, d), 3)

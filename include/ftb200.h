@@ -37,6 +37,8 @@ extern "C" {
 int ftb_version(void);
 const char* ftb_status_str(int code);
 size_t ftb_workspace_bytes(void);
+/* Number of kernels this library has launched in this process so far. */
+long long ftb_launch_count(void);
 /* Copies the status word out of `workspace` (synchronises `stream`). */
 int ftb_read_status(const void* workspace, int* status_out, void* stream);
 

@@ -1,0 +1,279 @@
+"""Generates the golden vectors under tests/golden/ by running the REFERENCE's own
+eager frontend (kaleido.frontend, imported from the reference tree) on small
+seeded inputs.  Run once, where the reference tree is mounted:
+
+    python tests/golden/generate.py [/path/to/reference]
+
+The model programs below are restated from the reference examples, calling the
+reference's real ``ops.map / scan / fold / reduce / dilated_map / zip / ...``:
+  stacked   examples/stacked_rnn/stacked_lstm1.py:13-76
+  dilated   examples/dilated_rnn/dilated_rnn.py:16-41
+  grid      examples/grid_rnn/grid_rnn.py:42-122
+  attention examples/flash_attention/flash_attention.py:14-88
+The example modules themselves cannot be imported: they parse and plot their
+functions at import time and need packages that are not installed.  Deliberate
+deviations, each documented where it is applied: the attention carry is started
+in (max, sum, out) order (the shipped example passes (sum, max, out) to a function
+that takes (max, sum, out)); a softmax scale is multiplied into q @ k^T; the grid
+inputs X[a][b], Y[a][b] are built explicitly.
+
+Loader: the reference package does not import as shipped (missing optional
+packages used only for plotting, and a circular import in kaleido/__init__.py).
+Four empty stand-in modules are registered and the frontend sub-modules are
+imported in dependency order; no reference code is modified or copied.
+"""
+import ast
+import importlib
+import os
+import sys
+import types
+import warnings
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "..", ".."))
+
+
+def load_reference_frontend(ref_root):
+    def stub(name, **attrs):
+        m = types.ModuleType(name)
+        for k, v in attrs.items():
+            setattr(m, k, v)
+        sys.modules[name] = m
+
+    class _Empty(object):
+        def __init__(self, *a, **k):
+            pass
+
+        def __iter__(self):
+            return iter(())
+
+    class _Tokens(object):
+        def __init__(self, source, parse=True):
+            self.tree = ast.parse(source)
+
+    stub("anytree", NodeMixin=type("NodeMixin", (object,), {}), AsciiStyle=_Empty, RenderTree=_Empty)
+    stub("astpretty", pprint=lambda *a, **k: None)
+    stub("asttokens", ASTTokens=_Tokens)
+    stub("graphviz", Digraph=_Empty)
+
+    sys.path.insert(0, ref_root)
+    pkg = types.ModuleType("kaleido")
+    pkg.__path__ = [os.path.join(ref_root, "kaleido")]
+    sys.modules["kaleido"] = pkg
+
+    def star(modname):
+        m = importlib.import_module(modname)
+        for n in getattr(m, "__all__", []):
+            setattr(pkg, n, getattr(m, n))
+        return m
+
+    star("kaleido.frontend.fractal_tensor")
+    t = importlib.import_module("kaleido.frontend.tensor")
+    pkg.Tensor, pkg.Parameter = t.Tensor, t.Parameter
+    star("kaleido.frontend.types")
+    ops = importlib.import_module("kaleido.frontend.operations")
+    pkg.operations = ops
+    return pkg, ops
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    warnings.filterwarnings("ignore")
+    kaleido, ops = load_reference_frontend(ref_root)
+    from kaleido import FractalTensor, FractalTensorStorage, Iterative, Tensor, TensorStorage
+    from typing import NamedTuple
+
+    from oracle import dense
+
+    def ft(data, shape, indices):
+        """FractalTensor of [*shape] float32 tensors with the given nesting."""
+        depth = 1 if not isinstance(indices[0], list) else 2
+        st = TensorStorage(list(shape), kaleido.float32, device="cpu")
+        x = FractalTensor(FractalTensorStorage(st) if depth == 2 else st)
+        x.indices = indices
+        x.data = data.clone()
+        return x
+
+    # ------------------------------------------------------------------ LSTM cell
+    def gate_f(w, u, b, x, s):
+        return x @ w + s @ u + b
+
+    def lstm_cell(h_prev, c_prev, inp, ws, us, bs):
+        prev_gate = ops.map(lambda x: gate_f(*x, inp, h_prev), ops.zip(ws, us, bs))
+        gate = ops.map(lambda x: ops.sigmoid(x), prev_gate[:3])
+        c = gate[1] * c_prev + gate[0] * ops.tanh(prev_gate[3])
+        h = gate[2] * ops.tanh(c)
+        return h, c
+
+    def stacked_lstm(embs, Wss, Uss, bss, H):
+        def batched_cell(xs, ws, us, bs):
+            return ops.scan(lambda state, x: lstm_cell(*state, x, ws, us, bs), xs,
+                            initializer=(ops.zeros(shape=(1, H), device="cpu"), ops.zeros(shape=(1, H), device="cpu")))
+
+        def lstm_layer(xss, Ws, Us, bs):
+            hss, css = ops.map(lambda xs: batched_cell(xs, Ws, Us, bs), xss)
+            return hss
+
+        return ops.fold(lambda s, param: lstm_layer(s, *param), ops.zip(Wss, Uss, bss), initializer=embs)
+
+    def run_stacked(D, L, N, H, seed, w_bound, bias):
+        x, W, U, b = dense.make_lstm_inputs(D, L, N, H, H, seed, w_bound, bias=bias)
+        bb = b if b is not None else torch.zeros(D, 4, H)
+        params = lambda t, shape: ft(t.reshape(D * 4, *shape), shape, [list(range(4)) for _ in range(D)])
+        Wss, Uss, bss = params(W, (H, H)), params(U, (H, H)), params(bb, (1, H))
+        # reference layout: batch-major FractalTensor [N][L] of [1,H]
+        embs = ft(x.permute(1, 0, 2).reshape(N * L, 1, H), (1, H), [list(range(L)) for _ in range(N)])
+        out = stacked_lstm(embs, Wss, Uss, bss, H)
+        top = out.data.view(N, L, H).permute(1, 0, 2).contiguous()  # back to [L,N,H]
+        return x, W, U, b, top
+
+    x, W, U, b, top = run_stacked(2, 5, 3, 16, 11, 0.25, True)
+    np.savez_compressed(os.path.join(HERE, "stacked_lstm_small.npz"), x=x.numpy(), W=W.numpy(), U=U.numpy(),
+                        b=b.numpy(), top=top.numpy())
+    print("stacked small", top.shape)
+
+    # BASELINE config 1 at full size through the real frontend; inputs are
+    # regenerated from the seed, the fixture keeps two samples of the output.
+    x, W, U, b, top = run_stacked(4, 64, 32, 256, 0, 1.0 / 16, False)
+    np.savez_compressed(os.path.join(HERE, "stacked_lstm_config1_samples.npz"), samples=np.array([0, 31]),
+                        top=top[:, [0, 31]].numpy(), seed=0)
+    print("stacked config1", top.shape)
+
+    # ---------------------------------------------------------------------- dilated
+    def run_dilated(D, L, N, H, seed, w_bound):
+        x, W, U, _ = dense.make_lstm_inputs(D, L, N, H, H, seed, w_bound)
+        params = lambda t, shape: ft(t.reshape(D * 4, *shape), shape, [list(range(4)) for _ in range(D)])
+        Wss, Uss, bss = params(W, (H, H)), params(U, (H, H)), params(torch.zeros(D, 4, 1, H), (1, H))
+
+        def dilated_layer(state, itr, Ws, Us, bs):
+            zeros = ops.zeros(shape=(1, H), device="cpu", dtype="float")
+            it = int(itr.data) if isinstance(itr, Tensor) else int(itr)
+            h, _ = ops.dilated_map(
+                lambda xs: ops.scan(lambda s, x: lstm_cell(*s, x, Ws, Us, bs), xs, initializer=(zeros, zeros)),
+                state, dilation=2 ** it)
+            return h
+
+        embs = ft(x.permute(1, 0, 2).reshape(N * L, 1, H), (1, H), [list(range(L)) for _ in range(N)])
+        itrs = ops.enumerate(Wss, Uss, bss)
+        outs = ops.map(lambda xs: ops.fold(lambda s, p: dilated_layer(s, *p), itrs, initializer=xs), embs)
+        top = outs.data.view(N, L, H).permute(1, 0, 2).contiguous()
+        return x, W, U, top
+
+    x, W, U, top = run_dilated(3, 11, 2, 16, 4, 0.25)
+    np.savez_compressed(os.path.join(HERE, "dilated_lstm_small.npz"), x=x.numpy(), W=W.numpy(), U=U.numpy(),
+                        dilations=np.array([1, 2, 4]), top=top.numpy())
+    print("dilated small", top.shape)
+
+    # ------------------------------------------------------------------------- grid
+    class CellParams(NamedTuple):
+        i2h: Tensor
+        h2h: Tensor
+        bias: Tensor
+
+    class BlockParams(NamedTuple):
+        x_direction: CellParams
+        y_direction: CellParams
+
+    def run_grid(D, A, B, H, seed, w_bound):
+        # one sample (the reference maps stacked_grid_rnns over the batch)
+        X, Y, p = dense.make_grid_inputs(D, A, B, 1, H, seed, w_bound, bias=True)
+
+        def T_(t):
+            r = Tensor(tuple(t.shape), kaleido.float32, device="cpu")
+            r.data = t.clone()
+            return r
+
+        def vanilla_cell(state, cur, i2h, h2h, bias):
+            return ops.tanh(cur @ i2h + state @ h2h + bias)
+
+        def grid_cell(state, cur_input, block_params):
+            _, state_y = state
+            state_x, (x_t, y_t) = cur_input
+            px, py = block_params
+            s = ops.cat([state_x, state_y], dim=1)
+            return vanilla_cell(x_t, s, *px), vanilla_cell(y_t, s, *py)
+
+        def direction_y(state, cur_input, block_params):
+            state_xs, _ = state
+            zero = ops.zeros(shape=(1, H), device="cpu")
+            return ops.scan(lambda s, x: grid_cell(s, x, block_params), ops.zip(state_xs, ops.zip(*cur_input)),
+                            initializer=(zero, zero))
+
+        def direction_x(state, block_params):
+            zeros = ops.repeat(ops.zeros(shape=(1, H), device="cpu"), len(state[0][0]))
+            ys1, ys2 = ops.scan(lambda s, x: direction_y(s, x, block_params), state, initializer=(zeros, zeros))
+            return ops.zip(ys1, ys2)
+
+        sp = Iterative.make_iterative(*[
+            BlockParams(CellParams(T_(p["i2h_x"][d]), T_(p["h2h_x"][d]), T_(p["b_x"][d][None])),
+                        CellParams(T_(p["i2h_y"][d]), T_(p["h2h_y"][d]), T_(p["b_y"][d][None]))) for d in range(D)])
+        # explicit grids: xss[a][b] = X[a,b], yss[a][b] = Y[a,b] (ops.product would
+        # interleave the y grid differently, so it is not used to build the input)
+        idx = [list(range(B)) for _ in range(A)]
+        xss = ft(X.reshape(A * B, 1, H), (1, H), idx)
+        yss = ft(Y.reshape(A * B, 1, H), (1, H), idx)
+        yss1, yss2 = ops.fold(lambda inputs, params: direction_x(inputs, params), sp, initializer=ops.zip(xss, yss))
+        hx = yss1.data.view(A, B, 1, H)
+        hy = yss2.data.view(A, B, 1, H)
+        return X, Y, p, hx, hy
+
+    X, Y, p, hx, hy = run_grid(2, 4, 5, 8, 4, 0.3)
+    np.savez_compressed(os.path.join(HERE, "grid_rnn_small.npz"), X=X.numpy(), Y=Y.numpy(), hx_top=hx.numpy(),
+                        hy_top=hy.numpy(), **{k: v.numpy() for k, v in p.items()})
+    print("grid small", hx.shape)
+
+    # -------------------------------------------------------------------- attention
+    def run_attention(Bsz, heads, S, d, blk, seed, scale):
+        q, k, v = dense.make_attention_inputs(Bsz, heads, S, d, seed, dtype=torch.float32)
+
+        def attn_func(prev_maxes, prev_sums, prev_out, query, key, value):
+            attn_weights = (query @ key.T) * scale  # scale: deviation (ii)
+            cur_maxes = ops.max(attn_weights, dim=-1, keepdim=True)
+            exp_weights = ops.exp(attn_weights - cur_maxes)
+            exp_values = exp_weights @ value
+            cur_sums = ops.sum(exp_weights, dim=-1, keepdim=True)
+            new_maxes = ops.maximum(cur_maxes, prev_maxes)
+            renorm_prev = ops.exp(prev_maxes - new_maxes)
+            renorm_cur = ops.exp(cur_maxes - new_maxes)
+            new_sums = renorm_prev * prev_sums + renorm_cur * cur_sums
+            o = (prev_out * prev_sums * renorm_prev + renorm_cur * exp_values) / new_sums
+            return new_maxes, new_sums, o
+
+        def per_block_func(query, ks, vs):
+            init_sum = ops.zeros(shape=(blk, 1), device="cpu")
+            init_max = ops.full(shape=(blk, 1), fill_value=-kaleido.float32.max, device="cpu")
+            init_o = ops.zeros(shape=(blk, d), device="cpu")
+            _, _, o = ops.reduce(lambda state, kvs: attn_func(*state, query, *kvs), ops.zip(ks, vs),
+                                 initializer=(init_max, init_sum, init_o))  # order: deviation (i)
+            return o
+
+        def per_head_func(qs, ks, vs):
+            return ops.map(lambda q_: per_block_func(q_, ks, vs), qs)
+
+        def flash_attention(qsss, ksss, vsss):
+            return ops.map(lambda xss: ops.map(lambda xs: per_head_func(*xs), ops.zip(*xss)),
+                           ops.zip(qsss, ksss, vsss))
+
+        def to_ft(t):
+            nb = S // blk
+            st = TensorStorage([blk, d], kaleido.float32, device="cpu")
+            x = FractalTensor(FractalTensorStorage(FractalTensorStorage(st)))
+            x.indices = [[list(range(nb)) for _ in range(heads)] for _ in range(Bsz)]
+            x.data = t.reshape(-1).clone()
+            return x
+
+        o = flash_attention(to_ft(q), to_ft(k), to_ft(v))
+        return q, k, v, o.data.view(Bsz, heads, S, d)
+
+    scale = 1.0 / 32 ** 0.5
+    q, k, v, o = run_attention(1, 2, 256, 32, 64, 2, scale)
+    np.savez_compressed(os.path.join(HERE, "flash_attention_small.npz"), q=q.numpy(), k=k.numpy(), v=v.numpy(),
+                        o=o.numpy(), scale=scale, block=64)
+    print("attention small", o.shape)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,79 @@
+"""Host-side logic that needs no GPU: FractalTensor views, batch sharding, and
+the two-rank gather over gloo."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from fractaltensor_b200 import frontend, sharding
+
+
+def test_fractaltensor_dense_roundtrip():
+    t = torch.arange(2 * 3 * 4.0).reshape(2, 3, 1, 4)
+    ft = frontend.FractalTensor.from_dense(t, 2)
+    assert ft.depth == 2 and len(ft) == 2 and ft.element_shape == (1, 4)
+    assert ft.indices == [[0, 1, 2], [0, 1, 2]]
+    assert torch.equal(ft.to_dense(), t)
+
+
+def test_ragged_nesting_is_rejected():
+    ft = frontend.FractalTensor(torch.zeros(5 * 4), [[0, 1, 2], [0, 1]], (1, 4))
+    with pytest.raises(ValueError, match="ragged"):
+        ft.to_dense()
+
+
+def test_cpu_tensors_are_rejected_not_computed():
+    x = frontend.FractalTensor.from_dense(torch.zeros(2, 3, 1, 64), 2)
+    w = frontend.FractalTensor.from_dense(torch.zeros(1, 4, 64, 64), 2)
+    b = frontend.FractalTensor.from_dense(torch.zeros(1, 4, 1, 64), 2)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        frontend.stacked_lstm(x, w, w, b)
+    from fractaltensor_b200 import ops
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.gemm_nt(torch.zeros(128, 64), torch.zeros(128, 64))
+
+
+@pytest.mark.parametrize("n,world", [(256, 1), (256, 2), (256, 8), (10, 4), (3, 4)])
+def test_shard_range_partitions_the_batch(n, world):
+    spans = [sharding.shard_range(n, r, world) for r in range(world)]
+    assert spans[0][0] == 0 and spans[-1][1] == n
+    for (a, b), (c, d) in zip(spans, spans[1:]):
+        assert b == c and b - a >= d - c >= b - a - 1
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, n, dim, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    full_shape = [4, 4, 4]
+    full_shape[dim] = n
+    full = torch.arange(float(torch.tensor(full_shape).prod())).reshape(full_shape)
+    local = sharding.shard_batch(full, dim, rank, world) * 1.0
+    out = sharding.gather_batch(local, dim, n, None)
+    q.put((rank, bool(torch.equal(out, full))))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n,dim", [(8, 0), (7, 1)])
+def test_two_rank_shard_and_gather_gloo(n, dim):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, n, dim, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(res) == [(0, True), (1, True)]

@@ -1,0 +1,99 @@
+"""The dense oracle against the golden vectors produced by the reference's own
+frontend (tests/golden/generate.py) and against closed forms."""
+import math
+import os
+
+import numpy as np
+import torch
+
+from oracle import dense
+
+
+def _load(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name))
+    return {k: (torch.from_numpy(z[k]) if z[k].ndim > 0 else z[k].item()) for k in z.files}
+
+
+def test_stacked_lstm_small_matches_reference_frontend(golden_dir):
+    g = _load(golden_dir, "stacked_lstm_small.npz")
+    hs, _ = dense.stacked_lstm_dense(g["x"], g["W"], g["U"], g["b"])
+    assert torch.allclose(hs[-1], g["top"], rtol=1e-5, atol=1e-6)
+    assert (hs[-1] - g["top"]).abs().max().item() <= 1e-6
+
+
+def test_stacked_lstm_config1_matches_reference_frontend(golden_dir):
+    """BASELINE config 1 at full size (D4, H256, N32, L64, seed 0): the fixture holds
+    two samples of the frontend's output; samples are independent."""
+    g = _load(golden_dir, "stacked_lstm_config1_samples.npz")
+    x, W, U, _ = dense.make_lstm_inputs(4, 64, 32, 256, 256, 0, 1.0 / 16)
+    idx = g["samples"].long()
+    hs, _ = dense.stacked_lstm_dense(x[:, idx], W, U)
+    err = (hs[-1] - g["top"]).abs().max().item()
+    assert err <= 1e-5 * g["top"].abs().max().item(), err
+
+
+def test_dilated_lstm_matches_reference_frontend(golden_dir):
+    g = _load(golden_dir, "dilated_lstm_small.npz")
+    hs = dense.dilated_lstm_dense(g["x"], g["W"], g["U"], g["dilations"].tolist())
+    assert (hs[-1] - g["top"]).abs().max().item() <= 1e-6
+
+
+def test_grid_rnn_matches_reference_frontend(golden_dir):
+    g = _load(golden_dir, "grid_rnn_small.npz")
+    hx, hy = dense.grid_rnn_dense(g["X"], g["Y"], g["i2h_x"], g["h2h_x"], g["b_x"], g["i2h_y"], g["h2h_y"], g["b_y"])
+    assert (hx[-1] - g["hx_top"]).abs().max().item() <= 1e-6
+    assert (hy[-1] - g["hy_top"]).abs().max().item() <= 1e-6
+
+
+def test_flash_attention_matches_reference_frontend(golden_dir):
+    g = _load(golden_dir, "flash_attention_small.npz")
+    o = dense.flash_attention_dense(g["q"], g["k"], g["v"], scale=g["scale"], block=int(g["block"]))
+    assert (o - g["o"]).abs().max().item() <= 2e-6
+    # and the carry equals the closed form
+    ref = dense.attention_plain(g["q"], g["k"], g["v"], scale=g["scale"])
+    assert (o - ref).abs().max().item() <= 2e-6
+
+
+def test_flash_attention_block_size_does_not_matter():
+    q, k, v = dense.make_attention_inputs(1, 2, 128, 16, 7, dtype=torch.float32)
+    a = dense.flash_attention_dense(q, k, v, scale=0.25, block=32)
+    b = dense.flash_attention_dense(q, k, v, scale=0.25, block=128)
+    assert (a - b).abs().max().item() <= 2e-6
+
+
+def test_b2b_rounds_the_intermediate():
+    """P = A.B is rounded to fp16 before the second product (cutlass_wmma.h:512-517)."""
+    A, B, C = dense.make_b2b_inputs(2, 64, 128, 128, 128, 1)
+    out = dense.b2b_gemm_dense(A, B, C)
+    assert out.dtype == torch.float16 and tuple(out.shape) == (2, 64, 128)
+    P = (A.double() @ B.double().transpose(-1, -2)).half()
+    want = (P.double() @ C.double().transpose(-1, -2)).half()
+    assert (out.float() - want.float()).abs().max().item() <= 2e-3
+    unrounded = (A.double() @ B.double().transpose(-1, -2) @ C.double().transpose(-1, -2))
+    assert (out.double() - unrounded).abs().max().item() > 0
+
+
+def test_lstm_zero_weights_closed_form():
+    """With zero weights every gate is sigmoid(0)=0.5 / tanh(0)=0: c and h stay 0."""
+    x = torch.randn(3, 2, 8)
+    W = torch.zeros(2, 4, 8, 8)
+    U = torch.zeros(2, 4, 8, 8)
+    hs, c = dense.stacked_lstm_dense(x, W, U)
+    assert hs.abs().max().item() == 0 and c.abs().max().item() == 0
+
+
+def test_dilation_one_equals_stacked():
+    x, W, U, _ = dense.make_lstm_inputs(2, 7, 3, 8, 8, 5, 0.3)
+    a, _ = dense.stacked_lstm_dense(x, W, U)
+    b = dense.dilated_lstm_dense(x, W, U, [1, 1])
+    assert torch.equal(a, b)
+
+
+def test_seeded_inputs_are_deterministic():
+    a = dense.make_lstm_inputs(1, 2, 2, 4, 4, 3, 1 / 32)[0]
+    b = dense.make_lstm_inputs(1, 2, 2, 4, 4, 3, 1 / 32)[0]
+    assert torch.equal(a, b)
+    q1 = dense.make_attention_inputs(1, 1, 4, 4, 2)[0]
+    q2 = dense.make_attention_inputs(1, 1, 4, 4, 2)[0]
+    assert torch.equal(q1, q2)
+    assert abs(dense.make_b2b_inputs(1, 256, 128, 128, 128, 1)[0].float().std().item() - 1 / math.sqrt(128)) < 0.01
