@@ -47,4 +47,16 @@ struct CellBatch {
   CellItem items[kMaxItems];
 };
 
+// Device-resident schedule for the persistent (single-launch) wavefront: the
+// same CellItem records in launch order (tile0 increasing) plus, per item and
+// per activation segment, the inclusive range of items whose output the segment
+// reads (-1 = external input).  done[i] counts finished epilogue warps of item
+// i; item i is complete when done[i] == target[i] (4 warps x tiles of the item).
+struct PlanView {
+  const CellItem* items;
+  const int32_t* dep;     // [n_items][kMaxSeg][2]
+  const int32_t* target;  // [n_items]
+  int32_t* done;          // [n_items], zero before the launch
+};
+
 }  // namespace ftb

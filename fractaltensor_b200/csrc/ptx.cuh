@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, no cluster multicast anywhere),
+// mbarrier, TMA tensor copies (every load is addressed to one CTA only),
 // tcgen05 (TMEM alloc / mma / commit / ld / st) and the UMMA descriptors.
 //
 // Every wait is bounded: a wait that runs out records a code in a global
@@ -27,6 +27,8 @@ enum Status : int {
   FTB_ERR_TIMEOUT_MMA = 17,   // device: waited too long for an MMA commit
   FTB_ERR_TIMEOUT_EPI = 18,   // device: waited too long for the epilogue to drain
   FTB_ERR_TIMEOUT_SLOT = 19,  // device: producer waited too long for a free stage
+  FTB_ERR_TIMEOUT_DEP = 20,   // device: a cell waited too long for the cells it depends on
+  FTB_ERR_TMEM_LAYOUT = 21,   // device: the two CTAs of a pair got different TMEM columns
 };
 
 #ifndef FTB_WAIT_TIMEOUT_NS
@@ -93,6 +95,39 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   uint32_t it = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (((++it) & 0x3F) == 0) {
+      if (*s_abort) return false;
+      if (globaltimer_ns() - t0 > FTB_WAIT_TIMEOUT_NS) {
+        *s_abort = 1;
+        atomicCAS(g_status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------- inter-CTA flags (global memory)
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Orders this thread's generic-proxy accesses (any state space) with async-proxy
+// accesses (TMA): used on both sides of a flag when one CTA's plain stores feed
+// another CTA's TMA loads.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded wait for a global counter to reach `target`.
+__device__ __forceinline__ bool flag_wait_ge(const int* flag, int target, volatile int* s_abort, int* g_status,
+                                             int code) {
+  if (ld_acquire_gpu(flag) >= target) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  for (;;) {
+    if (ld_acquire_gpu(flag) >= target) return true;
     if (((++it) & 0x3F) == 0) {
       if (*s_abort) return false;
       if (globaltimer_ns() - t0 > FTB_WAIT_TIMEOUT_NS) {
@@ -246,6 +281,61 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, int fmt, int
   return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
          (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
          (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// ------------------------------------------------------- CTA pairs (cluster of 2)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Shared-memory address of the same variable in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Tensor copy into this CTA's shared memory whose completion is counted on an
+// mbarrier that may live in the pair's other CTA (`bar_cluster_addr`).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(m), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+// One MMA across both SMs of a pair: each CTA supplies its 128 rows of A and
+// its half of B's rows; each CTA's TMEM receives its 128 rows of D.
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier at the same shared-memory offset in both CTAs of the
+// pair once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(mask)
+      : "memory");
 }
 
 // ------------------------------------------------------------------------ math

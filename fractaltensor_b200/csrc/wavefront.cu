@@ -19,8 +19,11 @@
 
 namespace ftb {
 
-int launch_cell_gemm(int dtype, int epi, int bn, const CUtensorMap* maps, const CUtensorMap& mapW,
+int launch_cell_gemm(int dtype, int epi, int bn, int pair, const CUtensorMap* maps, const CUtensorMap& mapW,
                      const CellBatch& batch, int* status, int sm_count, cudaStream_t stream);
+int launch_cell_gemm_persistent(int dtype, int epi, int bn, int pair, const CUtensorMap* maps,
+                                const CUtensorMap& mapW, const CellBatch& header, const PlanView& plan, int* status,
+                                int sm_count, cudaStream_t stream);
 int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* w, int ldw,
                      const CellBatch& batch, cudaStream_t stream);
 int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I, int H, int dtype,
@@ -37,6 +40,7 @@ struct CellLauncher {
   int dtype = FTB_BF16;
   int epi = EPI_STORE;
   int bn = 128;
+  int pair = 0;  // 16-bit path: run CTAs as pairs on 256-row blocks
   int n_cols = 0, ld_out = 0, ld_c = 0;
   int sm_count = 0;
   int* status = nullptr;
@@ -51,6 +55,11 @@ struct CellLauncher {
   int ldw = 0;
 
   int rows_per_tile() const { return dtype == FTB_F32 ? 32 : 128; }
+  int m_tiles_for(int rows) const {
+    if (dtype != FTB_F32 && pair) return 2 * ((rows + 255) / 256);
+    return (rows + rows_per_tile() - 1) / rows_per_tile();
+  }
+  int w_box_rows() const { return pair ? bn / 2 : bn; }
   int cols_per_tile() const { return dtype == FTB_F32 ? 64 : bn; }
 
   // Launches the cells of one level (any number; split into chunks).
@@ -66,7 +75,7 @@ struct CellLauncher {
       int tiles = 0;
       for (int i = 0; i < b.n_items; ++i) {
         CellItem it = items[off + i];
-        it.m_tiles = (it.rows + rows_per_tile() - 1) / rows_per_tile();
+        it.m_tiles = m_tiles_for(it.rows);
         it.tile0 = tiles;
         tiles += it.m_tiles * n_tiles_n;
         b.items[i] = it;
@@ -76,7 +85,7 @@ struct CellLauncher {
       if (dtype == FTB_F32)
         rc = launch_cell_simt(epi, act, ld_act, w, ldw, b, stream);
       else
-        rc = launch_cell_gemm(dtype, epi, bn, maps, mapW, b, status, sm_count, stream);
+        rc = launch_cell_gemm(dtype, epi, bn, pair, maps, mapW, b, status, sm_count, stream);
       if (rc) return rc;
     }
     return FTB_OK;
@@ -117,6 +126,108 @@ int begin_call(void* workspace, size_t workspace_bytes, cudaStream_t stream, int
 }
 
 bool valid_dtype(int dt) { return dt == FTB_F32 || dt == FTB_F16 || dt == FTB_BF16; }
+
+// Optional tuning knobs of the wavefront entry points (0 = automatic).
+struct Tuning {
+  int layers_per_group = 0, bn = 0, schedule = 0, skew = 0, pair = 0;
+  explicit Tuning(const int* t) {
+    if (t != nullptr) {
+      layers_per_group = t[0];
+      bn = t[1];
+      schedule = t[2];
+      skew = t[3];
+      pair = t[4];
+    }
+  }
+  // pair: 0 = automatic (pairs when a cell has more than 128 rows), 1 = never, 2 = always.
+  int use_pair(int rows) const { return pair == 2 || (pair == 0 && rows > 128); }
+};
+
+// ---------------------------------------------------------- persistent schedule
+// Workspace layout of a persistent stacked-LSTM call: status block, then the
+// item table, the dependency table, the completion targets and the counters.
+struct PlanLayout {
+  size_t items, dep, target, done, total;
+};
+PlanLayout plan_layout(int n_items) {
+  PlanLayout p;
+  auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+  p.items = kWorkspaceBytes;
+  p.dep = up(p.items + sizeof(CellItem) * n_items);
+  p.target = up(p.dep + sizeof(int32_t) * 2 * kMaxSeg * n_items);
+  p.done = up(p.target + sizeof(int32_t) * n_items);
+  p.total = up(p.done + sizeof(int32_t) * n_items);
+  return p;
+}
+
+struct StackedPlanArgs {
+  int D, L, N, I, H, G, skew, es, tiles_per_item, m_tiles;
+  char* hs;
+  float* c;
+  const float* bias_p;
+  CellItem* items;
+  int32_t* dep;
+  int32_t* target;
+};
+
+// Position of cell (l, t) in the launch order: groups of G layers one after the
+// other; inside a group level by level, level m = skew * j + t with j the layer's
+// index in the group, lower layers first.  A cell reads (l, t-1), one level back,
+// and (l-1, t), `skew` levels back (or in an earlier group): with skew >= 2 the
+// input half of a cell's K loop can run while the cells of the previous level,
+// which feed its recurrent half, are still finishing.
+__device__ int stacked_item_index(const StackedPlanArgs& a, int l, int t) {
+  const int g0 = (l / a.G) * a.G;
+  const int Lg = min(a.G, a.D - g0);
+  const int j = l - g0;
+  const int m = a.skew * j + t;
+  int before = 0;
+  for (int q = 0; q < m; ++q) {
+    const int j_lo = (max(0, q - a.L + 1) + a.skew - 1) / a.skew;
+    const int j_hi = min(Lg - 1, q / a.skew);
+    before += max(0, j_hi - j_lo + 1);
+  }
+  const int j_min = (max(0, m - a.L + 1) + a.skew - 1) / a.skew;
+  return g0 * a.L + before + (j - j_min);
+}
+
+__global__ void plan_stacked_kernel(const StackedPlanArgs a) {
+  const int id = blockIdx.x * blockDim.x + threadIdx.x;
+  if (id >= a.D * a.L) return;
+  const int l = id / a.L, t = id - l * a.L;
+  const int pos = stacked_item_index(a, l, t);
+  CellItem it;
+  for (int s = 0; s < kMaxSeg; ++s) it.seg_row[s] = it.seg_kb[s] = it.seg_wk[s] = it.seg_map[s] = 0;
+  int32_t dep[kMaxSeg][2] = {{-1, -1}, {-1, -1}, {-1, -1}};
+  int ns = 0;
+  if (l == 0) {
+    it.seg_map[ns] = 0; it.seg_row[ns] = t * a.N; it.seg_kb[ns] = a.I / 64; it.seg_wk[ns] = 0;
+  } else {
+    it.seg_map[ns] = 1; it.seg_row[ns] = ((l - 1) * a.L + t) * a.N; it.seg_kb[ns] = a.H / 64; it.seg_wk[ns] = 0;
+    dep[ns][0] = dep[ns][1] = stacked_item_index(a, l - 1, t);
+  }
+  ++ns;
+  if (t > 0) {
+    it.seg_map[ns] = 2; it.seg_row[ns] = (l * a.L + t - 1) * a.N; it.seg_kb[ns] = a.H / 64; it.seg_wk[ns] = a.I;
+    dep[ns][0] = dep[ns][1] = stacked_item_index(a, l, t - 1);
+    ++ns;
+  }
+  it.nseg = ns;
+  it.w_row0 = l * 4 * a.H;
+  it.rows = a.N;
+  it.c_zero = (t == 0);
+  it.out = a.hs + (static_cast<size_t>(l) * a.L + t) * a.N * a.H * a.es;
+  it.c = a.c + static_cast<size_t>(l) * a.N * a.H;
+  it.bias = a.bias_p ? a.bias_p + static_cast<size_t>(l) * 4 * a.H : nullptr;
+  it.m_tiles = a.m_tiles;
+  it.tile0 = pos * a.tiles_per_item;
+  a.items[pos] = it;
+  for (int s = 0; s < kMaxSeg; ++s) {
+    a.dep[(pos * kMaxSeg + s) * 2 + 0] = dep[s][0];
+    a.dep[(pos * kMaxSeg + s) * 2 + 1] = dep[s][1];
+  }
+  a.target[pos] = 4 * a.tiles_per_item;
+}
 
 // Accumulator tile width.  The last column tile of a cell may be partial (the
 // epilogue skips 32-column groups past n_cols), so n_cols % 32 == 0 is enough.
@@ -178,10 +289,17 @@ int ftb_grid_pack_weights(const void* i2h, const void* h2h, void* Wp, int H, int
   return pack_grid(i2h, h2h, Wp, H, dtype, static_cast<cudaStream_t>(stream));
 }
 
+size_t ftb_lstm_stacked_workspace_bytes(int D, int L) {
+  if (D <= 0 || L <= 0) return kWorkspaceBytes;
+  return plan_layout(D * L).total;
+}
+
 int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
-                         int N, int I, int H, int dtype, int layers_per_group, int bn, void* workspace,
-                         size_t workspace_bytes, void* stream_) {
+                         int N, int I, int H, int dtype, const int* tuning, void* workspace, size_t workspace_bytes,
+                         void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const Tuning tune(tuning);
+  const int layers_per_group = tune.layers_per_group, bn = tune.bn, schedule = tune.schedule, skew = tune.skew;
   if (!x || !Wp || !hs || !c || D <= 0 || L <= 0 || N <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
   if (H <= 0 || I <= 0 || H % 64 != 0 || I % 64 != 0) return FTB_ERR_ARG;
   if (D > 1 && I != H) return FTB_ERR_ARG;
@@ -211,12 +329,13 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
   } else {
     cl.bn = pick_bn(4 * H, bn);
     if (cl.bn == 0) return FTB_ERR_ARG;
+    cl.pair = tune.use_pair(N);
     rc = make_tmap_2d(&cl.maps[0], x, dtype, static_cast<uint64_t>(L) * N, I, I, 128, 64);
     if (rc) return rc;
     rc = make_tmap_2d(&cl.maps[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, 128, 64);
     if (rc) return rc;
     cl.maps[2] = cl.maps[1];
-    rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.bn, 64);
+    rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.w_box_rows(), 64);
     if (rc) return rc;
   }
 
@@ -232,6 +351,40 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
     if (per_layer * D <= 0.5 * l2) G = D;
   }
   G = std::min(G, D);
+
+  const int n_cells = D * L;
+  const PlanLayout lay = plan_layout(n_cells);
+  const bool persistent = dtype != FTB_F32 && schedule != 1 && (schedule == 2 || workspace_bytes >= lay.total);
+  if (persistent) {
+    if (workspace_bytes < lay.total) return FTB_ERR_WORKSPACE;
+    char* ws = static_cast<char*>(workspace);
+    StackedPlanArgs pa;
+    pa.D = D; pa.L = L; pa.N = N; pa.I = I; pa.H = H; pa.G = G; pa.es = static_cast<int>(es);
+    pa.skew = skew > 0 ? skew : 2;
+    pa.m_tiles = cl.m_tiles_for(N);
+    pa.tiles_per_item = pa.m_tiles * ((4 * H + cl.bn - 1) / cl.bn);
+    pa.hs = static_cast<char*>(hs);
+    pa.c = c;
+    pa.bias_p = bias_p;
+    pa.items = reinterpret_cast<CellItem*>(ws + lay.items);
+    pa.dep = reinterpret_cast<int32_t*>(ws + lay.dep);
+    pa.target = reinterpret_cast<int32_t*>(ws + lay.target);
+    int32_t* done = reinterpret_cast<int32_t*>(ws + lay.done);
+    if (cudaMemsetAsync(done, 0, sizeof(int32_t) * n_cells, stream) != cudaSuccess) return FTB_ERR_LAUNCH;
+    plan_stacked_kernel<<<(n_cells + 127) / 128, 128, 0, stream>>>(pa);
+    if (cudaGetLastError() != cudaSuccess) return FTB_ERR_LAUNCH;
+    count_launch();
+    CellBatch header;
+    header.n_items = n_cells;
+    header.n_cols = 4 * H;
+    header.ld_out = H;
+    header.ld_c = H;
+    header.total_tiles = n_cells * pa.tiles_per_item;
+    header.pad_ = 0;
+    PlanView pv = {pa.items, pa.dep, pa.target, done};
+    return launch_cell_gemm_persistent(dtype, EPI_LSTM, cl.bn, cl.pair, cl.maps, cl.mapW, header, pv, status,
+                                       cl.sm_count, stream);
+  }
 
   std::vector<CellItem> items;
   for (int g0 = 0; g0 < D; g0 += G) {
@@ -263,9 +416,11 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
 }
 
 int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
-                         const int* dilations, int D, int L, int N, int H, int dtype, int bn, void* workspace,
-                         size_t workspace_bytes, void* stream_) {
+                         const int* dilations, int D, int L, int N, int H, int dtype, const int* tuning,
+                         void* workspace, size_t workspace_bytes, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const Tuning tune(tuning);
+  const int bn = tune.bn;
   if (!x || !Wp || !hs || !c || !dilations || D <= 0 || L <= 0 || N <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
   if (H <= 0 || H % 64 != 0) return FTB_ERR_ARG;
   int max_dil = 1;
@@ -298,12 +453,13 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
   } else {
     cl.bn = pick_bn(4 * H, bn);
     if (cl.bn == 0) return FTB_ERR_ARG;
+    cl.pair = tune.use_pair(2 * N);
     rc = make_tmap_2d(&cl.maps[0], x, dtype, static_cast<uint64_t>(L) * N, H, H, 128, 64);
     if (rc) return rc;
     rc = make_tmap_2d(&cl.maps[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, 128, 64);
     if (rc) return rc;
     cl.maps[2] = cl.maps[1];
-    rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.bn, 64);
+    rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.w_box_rows(), 64);
     if (rc) return rc;
   }
 
@@ -433,9 +589,10 @@ int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* 
   return FTB_OK;
 }
 
-int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, int dtype, void* workspace,
-                size_t workspace_bytes, void* stream_) {
+int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, int dtype, const int* tuning,
+                void* workspace, size_t workspace_bytes, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const Tuning tune(tuning);
   if (!A || !Bt || !out || M <= 0 || N <= 0 || K <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
   if (K % 64 != 0) return FTB_ERR_ARG;
   if (dtype == FTB_F32 ? (N % 64 != 0) : (N % 128 != 0)) return FTB_ERR_ARG;
@@ -456,11 +613,13 @@ int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, i
     cl.w = static_cast<const float*>(Bt);
     cl.ldw = K;
   } else {
-    cl.bn = (N % 256 == 0) ? 256 : 128;
+    cl.bn = tune.bn ? tune.bn : ((N % 256 == 0) ? 256 : 128);
+    if (cl.bn != 128 && cl.bn != 256) return FTB_ERR_ARG;
+    cl.pair = tune.use_pair(M);
     rc = make_tmap_2d(&cl.maps[0], A, dtype, M, K, K, 128, 64);
     if (rc) return rc;
     cl.maps[1] = cl.maps[2] = cl.maps[0];
-    rc = make_tmap_2d(&cl.mapW, Bt, dtype, N, K, K, cl.bn, 64);
+    rc = make_tmap_2d(&cl.mapW, Bt, dtype, N, K, K, cl.w_box_rows(), 64);
     if (rc) return rc;
   }
   std::vector<CellItem> items(1, blank_item());

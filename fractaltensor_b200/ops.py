@@ -46,16 +46,22 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def workspace(device):
-    """The per-device workspace handed to every call (holds the status word)."""
+def workspace(device, nbytes=0):
+    """The per-device workspace handed to every call: the status word, plus the
+    schedule tables and completion counters of a persistent wavefront.  Grown on demand."""
     key = torch.device(device).index
     if key is None:
         key = torch.cuda.current_device()
+    need = max(int(nbytes), lib.ftb_workspace_bytes())
     ws = _workspaces.get(key)
-    if ws is None:
-        ws = torch.zeros(lib.ftb_workspace_bytes(), dtype=torch.uint8, device=torch.device("cuda", key))
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=torch.device("cuda", key))
         _workspaces[key] = ws
     return ws
+
+
+def _tuning(layers_per_group=0, bn=0, schedule=0, skew=0, pair=0):
+    return (ctypes.c_int * 5)(int(layers_per_group), int(bn), int(schedule), int(skew), int(pair))
 
 
 def check_status(device=None):
@@ -86,8 +92,10 @@ def lstm_pack_weights(W, U, bias=None):
     return Wp, bias_p
 
 
-def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0):
-    """x: [L,N,I]; Wp: [D,4H,I+H] -> (hs [D,L,N,H], c fp32 [D,N,H])."""
+def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0, schedule=0, skew=0, pair=0):
+    """x: [L,N,I]; Wp: [D,4H,I+H] -> (hs [D,L,N,H], c fp32 [D,N,H]).
+    schedule: 0 auto, 1 one launch per anti-diagonal, 2 one persistent kernel; pair: 0 auto, 1 single CTAs,
+    2 CTA pairs."""
     _req(x, "x")
     _req(Wp, "Wp", x.dtype)
     L, N, I = x.shape
@@ -103,15 +111,15 @@ def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0):
         c = torch.empty(D, N, H, dtype=torch.float32, device=x.device)
     _req(hs, "hs", x.dtype)
     _req(c, "c", torch.float32)
-    ws = workspace(x.device)
+    ws = workspace(x.device, lib.ftb_lstm_stacked_workspace_bytes(D, L))
     with torch.cuda.device(x.device):
         check(lib.ftb_lstm_stacked_fwd(_ptr(x), _ptr(Wp), _ptr(bias_p), _ptr(hs), _ptr(c), D, L, N, I, H,
-                                       _dtype_code(x), layers_per_group, bn, _ptr(ws), ws.numel(), _stream()),
-              "ftb_lstm_stacked_fwd")
+                                       _dtype_code(x), _tuning(layers_per_group, bn, schedule, skew, pair), _ptr(ws), ws.numel(),
+                                       _stream()), "ftb_lstm_stacked_fwd")
     return hs, c
 
 
-def lstm_dilated(x, Wp, dilations, bias_p=None, hs=None, c=None, bn=0):
+def lstm_dilated(x, Wp, dilations, bias_p=None, hs=None, c=None, bn=0, pair=0):
     """x: [L,N,H]; Wp: [D,4H,2H]; dilations: D ints -> (hs [D,L,N,H], c fp32 [D,max_dil*N,H])."""
     _req(x, "x")
     _req(Wp, "Wp", x.dtype)
@@ -130,7 +138,7 @@ def lstm_dilated(x, Wp, dilations, bias_p=None, hs=None, c=None, bn=0):
     ws = workspace(x.device)
     with torch.cuda.device(x.device):
         check(lib.ftb_lstm_dilated_fwd(_ptr(x), _ptr(Wp), _ptr(bias_p), _ptr(hs), _ptr(c), dil, D, L, N, H,
-                                       _dtype_code(x), bn, _ptr(ws), ws.numel(), _stream()),
+                                       _dtype_code(x), _tuning(bn=bn, pair=pair), _ptr(ws), ws.numel(), _stream()),
               "ftb_lstm_dilated_fwd")
     return hs, c
 
@@ -215,7 +223,7 @@ def flash_attention(q, k, v, scale=None, out=None):
     return out
 
 
-def gemm_nt(A, Bt, out=None):
+def gemm_nt(A, Bt, out=None, bn=0, pair=0):
     """A: [M,K]; Bt: [N,K] -> A @ Bt^T."""
     _req(A, "A")
     _req(Bt, "Bt", A.dtype)
@@ -227,6 +235,6 @@ def gemm_nt(A, Bt, out=None):
         out = torch.empty(M, N, dtype=A.dtype, device=A.device)
     ws = workspace(A.device)
     with torch.cuda.device(A.device):
-        check(lib.ftb_gemm_nt(_ptr(A), _ptr(Bt), _ptr(out), M, N, K, _dtype_code(A), _ptr(ws), ws.numel(),
+        check(lib.ftb_gemm_nt(_ptr(A), _ptr(Bt), _ptr(out), M, N, K, _dtype_code(A), _tuning(bn=bn, pair=pair), _ptr(ws), ws.numel(),
                               _stream()), "ftb_gemm_nt")
     return out

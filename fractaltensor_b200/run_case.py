@@ -1,0 +1,84 @@
+"""Runs one operator of the hot path once (or a few times) on seeded synthetic inputs.
+
+    python -m fractaltensor_b200.run_case lstm --D 16 --L 20 --N 256 --H 1024 --dtype bf16 --iters 2
+    python -m fractaltensor_b200.run_case b2b --batch 16 --M 16384
+    python -m fractaltensor_b200.run_case attn --B 4 --heads 16 --S 2048
+
+A small, fixed workload to put under a profiler or to time by hand; prints the
+average time per call measured with CUDA events.
+"""
+import argparse
+import math
+
+import torch
+
+from . import ops
+
+DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["lstm", "dilated", "grid", "b2b", "attn"])
+    ap.add_argument("--D", type=int, default=16)
+    ap.add_argument("--L", type=int, default=20)
+    ap.add_argument("--N", type=int, default=256)
+    ap.add_argument("--H", type=int, default=1024)
+    ap.add_argument("--A", type=int, default=32)
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--M", type=int, default=16384)
+    ap.add_argument("--B", type=int, default=16)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--S", type=int, default=2048)
+    ap.add_argument("--dtype", default="bf16", choices=sorted(DT))
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--layers-per-group", type=int, default=0)
+    ap.add_argument("--bn", type=int, default=0)
+    a = ap.parse_args()
+    dt, dev = DT[a.dtype], torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    uni = lambda bound, *s: (torch.rand(*s, device=dev, generator=g) * 2 - 1) * bound
+
+    if a.case == "lstm":
+        x = rnd(a.L, a.N, a.H).to(dt)
+        Wp, _ = ops.lstm_pack_weights(uni(1 / 32, a.D, 4, a.H, a.H).to(dt), uni(1 / 32, a.D, 4, a.H, a.H).to(dt))
+        hs = torch.empty(a.D, a.L, a.N, a.H, dtype=dt, device=dev)
+        c = torch.empty(a.D, a.N, a.H, device=dev)
+        fn = lambda: ops.lstm_stacked(x, Wp, None, hs, c, layers_per_group=a.layers_per_group, bn=a.bn)
+    elif a.case == "dilated":
+        x = rnd(a.L, a.N, a.H).to(dt)
+        Wp, _ = ops.lstm_pack_weights(uni(1 / 16, a.D, 4, a.H, a.H).to(dt), uni(1 / 16, a.D, 4, a.H, a.H).to(dt))
+        dil = [2 ** l for l in range(a.D)]
+        fn = lambda: ops.lstm_dilated(x, Wp, dil, bn=a.bn)
+    elif a.case == "grid":
+        X, Y = rnd(a.A, a.A, a.N, a.H).to(dt), rnd(a.A, a.A, a.N, a.H).to(dt)
+        Wpx = ops.grid_pack_weights(uni(1 / 16, a.D, 2 * a.H, a.H).to(dt), uni(1 / 16, a.D, a.H, a.H).to(dt))
+        Wpy = ops.grid_pack_weights(uni(1 / 16, a.D, 2 * a.H, a.H).to(dt), uni(1 / 16, a.D, a.H, a.H).to(dt))
+        fn = lambda: ops.grid_rnn(X, Y, Wpx, Wpy)
+    elif a.case == "b2b":
+        s = 1 / math.sqrt(128)
+        A_, B_, C_ = (rnd(a.batch, a.M, 128) * s).to(dt), (rnd(a.batch, 128, 128) * s).to(dt), (rnd(a.batch, 128, 128) * s).to(dt)
+        out = torch.empty_like(A_)
+        fn = lambda: ops.b2b_gemm(A_, B_, C_, out)
+    else:
+        q, k, v = (rnd(a.B, a.heads, a.S, 128).to(dt) for _ in range(3))
+        out = torch.empty_like(q)
+        fn = lambda: ops.flash_attention(q, k, v, scale=1 / math.sqrt(128), out=out)
+
+    for _ in range(a.warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("%s: %.3f ms per call" % (a.case, e0.elapsed_time(e1) / a.iters))
+
+
+if __name__ == "__main__":
+    main()

@@ -51,29 +51,42 @@ int ftb_read_status(const void* workspace, int* status_out, void* stream);
 int ftb_lstm_pack_weights(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I,
                           int H, int dtype, void* stream);
 
+/* Optional tuning knobs of the wavefront entry points: NULL (all automatic) or a
+ * HOST array of FTB_TUNING_INTS ints, 0 = automatic for each:
+ *  [0] layers_per_group  stacked LSTM: sweep the wavefront over groups of this many
+ *                        layers so that a group's weights stay in L2
+ *  [1] bn                accumulator tile width, 128 or 256
+ *  [2] schedule          1 = one kernel launch per wavefront level; 2 = one persistent
+ *                        cooperative kernel, cells chained through completion counters
+ *                        in the workspace (16-bit dtypes only)
+ *  [3] skew              persistent schedule: layer j of a group runs `skew` levels
+ *                        behind layer j-1
+ *  [4] pair              1 = single CTAs, 2 = CTA pairs (tcgen05 cta_group::2) on
+ *                        256-row blocks; automatic = pairs when a cell has > 128 rows */
+#define FTB_TUNING_INTS 5
+
 /* Stacked LSTM forward as a depth x time wavefront.
  * Stands in for stacked_lstm() (examples/stacked_rnn/stacked_lstm1.py:66-76) and
  * for StackedLstmRegion1/2/3 (kaleido/core/device/kernels/lstm/stacked_lstm/region{1,2,3}.h,
  * benchmarks/rnn/fractaltensor/stacked_lstm/lstm.cu:19-60).
  * x: [L,N,I]; Wp/bias_p from ftb_lstm_pack_weights; hs (out): [D,L,N,H] hidden
  * states of every layer (top layer = hs[D-1]); c (out): fp32 [D,N,H] final cell
- * state.  I == H is required for D > 1.  `layers_per_group` > 0 sweeps the
- * wavefront over groups of that many layers so a group's weights stay in L2;
- * 0 picks a group size from the L2 size.  `bn` is the accumulator tile width
- * (128 or 256; 0 = automatic). */
+ * state.  I == H is required for D > 1.  The persistent schedule needs
+ * ftb_lstm_stacked_workspace_bytes(D, L) bytes of workspace; with less, one kernel
+ * is launched per level. */
+size_t ftb_lstm_stacked_workspace_bytes(int D, int L);
 int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
-                         int N, int I, int H, int dtype, int layers_per_group, int bn, void* workspace,
-                         size_t workspace_bytes, void* stream);
+                         int N, int I, int H, int dtype, const int* tuning, void* workspace, size_t workspace_bytes,
+                         void* stream);
 
-/* Dilated stacked LSTM forward: layer l reads its own state from 2^l... steps
- * back, dilations[l] given explicitly.  Stands in for dilated_layer()/model()
- * (examples/dilated_rnn/dilated_rnn.py:16-41) and DilatedLstmRegion1/2
- * (kaleido/core/device/kernels/lstm/dilated_lstm/region{1,2}.h).
+/* Dilated stacked LSTM forward: layer l reads its own state dilations[l] steps
+ * back.  Stands in for dilated_layer()/model() (examples/dilated_rnn/dilated_rnn.py:16-41)
+ * and DilatedLstmRegion1/2 (kaleido/core/device/kernels/lstm/dilated_lstm/region{1,2}.h).
  * x: [L,N,H]; hs (out): [D,L,N,H]; c (scratch/out): fp32 [D, max_dilation*N, H].
- * `dilations` is a HOST array of D ints; L must be a multiple of each. */
+ * `dilations` is a HOST array of D ints. */
 int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
-                         const int* dilations, int D, int L, int N, int H, int dtype, int bn, void* workspace,
-                         size_t workspace_bytes, void* stream);
+                         const int* dilations, int D, int L, int N, int H, int dtype, const int* tuning,
+                         void* workspace, size_t workspace_bytes, void* stream);
 
 /* Packs one direction of a grid-RNN block: i2h [2H,H], h2h [H,H] (x@W
  * orientation, examples/grid_rnn/grid_rnn.py:21-30,42-50) into Wp [H,3H]
@@ -110,8 +123,8 @@ int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int
 /* Plain GEMM out[M,N] = A[M,K] . Bt[N,K]^T through the cell kernel's main loop
  * (support op; the reference's KeCuteGemm, kaleido/core/device/kernels/cutlass_wmma.h:115-181).
  * 16-bit dtypes: K % 64 == 0, N % 128 == 0.  fp32: K % 64 == 0, N % 64 == 0. */
-int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, int dtype, void* workspace,
-                size_t workspace_bytes, void* stream);
+int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, int dtype, const int* tuning,
+                void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

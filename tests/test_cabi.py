@@ -45,21 +45,21 @@ def test_status_strings(lib):
 def test_bad_arguments_are_rejected_without_a_device(lib):
     z = ctypes.c_void_p(0)
     one = ctypes.c_void_p(16)  # never dereferenced: argument checks come first
-    assert lib.ftb_lstm_stacked_fwd(z, z, z, z, z, 1, 1, 1, 64, 64, 2, 0, 0, z, 0, z) == 1
+    assert lib.ftb_lstm_stacked_fwd(z, z, z, z, z, 1, 1, 1, 64, 64, 2, None, z, 0, z) == 1
     # H not a multiple of 64
-    assert lib.ftb_lstm_stacked_fwd(one, one, z, one, one, 1, 1, 1, 64, 48, 2, 0, 0, one, 256, z) == 1
+    assert lib.ftb_lstm_stacked_fwd(one, one, z, one, one, 1, 1, 1, 64, 48, 2, None, one, 256, z) == 1
     # I != H with more than one layer
-    assert lib.ftb_lstm_stacked_fwd(one, one, z, one, one, 2, 1, 1, 128, 64, 2, 0, 0, one, 256, z) == 1
+    assert lib.ftb_lstm_stacked_fwd(one, one, z, one, one, 2, 1, 1, 128, 64, 2, None, one, 256, z) == 1
     # missing workspace
-    assert lib.ftb_lstm_stacked_fwd(one, one, z, one, one, 1, 1, 1, 64, 64, 2, 0, 0, z, 0, z) == 3
+    assert lib.ftb_lstm_stacked_fwd(one, one, z, one, one, 1, 1, 1, 64, 64, 2, None, z, 0, z) == 3
     assert lib.ftb_b2b_gemm(one, one, one, one, 1, 128, 64, 128, 128, 1, one, 256, z) == 1   # N != 128
     assert lib.ftb_b2b_gemm(one, one, one, one, 1, 100, 128, 128, 128, 1, one, 256, z) == 1  # M % 128
     assert lib.ftb_b2b_gemm(one, one, one, one, 1, 128, 128, 128, 128, 0, one, 256, z) == 1  # fp32
     assert lib.ftb_flash_attn_fwd(one, one, one, one, 1, 1, 256, 64, 1.0, 1, one, 256, z) == 1  # d != 128
     assert lib.ftb_flash_attn_fwd(one, one, one, one, 1, 1, 100, 128, 1.0, 1, one, 256, z) == 1  # S % 256
-    assert lib.ftb_gemm_nt(one, one, one, 8, 128, 60, 1, one, 256, z) == 1  # K % 64
+    assert lib.ftb_gemm_nt(one, one, one, 8, 128, 60, 1, None, one, 256, z) == 1  # K % 64
     dil = (ctypes.c_int * 2)(1, 0)
-    assert lib.ftb_lstm_dilated_fwd(one, one, z, one, one, dil, 2, 4, 1, 64, 1, 0, one, 256, z) == 1  # dilation 0
+    assert lib.ftb_lstm_dilated_fwd(one, one, z, one, one, dil, 2, 4, 1, 64, 1, None, one, 256, z) == 1  # dilation 0
 
 
 def test_no_fallback_when_library_is_missing(monkeypatch, tmp_path):
