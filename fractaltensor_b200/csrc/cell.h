@@ -12,7 +12,7 @@
 namespace ftb {
 
 constexpr int kMaxSeg = 3;     // activation sources concatenated along K
-constexpr int kMaxItems = 32;  // cells per launch (a level with more is split)
+constexpr int kMaxItems = 24;  // cells per launch (a level with more is split)
 constexpr int kNumActMaps = 3;
 
 enum Epilogue : int {
@@ -34,7 +34,11 @@ struct CellItem {
   int32_t rows;    // valid activation rows (batch entries) of this cell
   int32_t c_zero;  // LSTM only: 1 when the previous cell state is zero (c is not read)
   int32_t tile0;   // index of this cell's first tile inside the launch
-  int32_t m_tiles; // ceil(rows / 128)
+  int32_t m_tiles; // row tiles of this cell (128 rows each; even when CTAs run as pairs)
+  int32_t out_row0;  // 16-bit LSTM path: row of `out` in the tensor map `out_map` (TMA stores)
+  int32_t c_row0;    // 16-bit LSTM path: row of `c` in the cell-state tensor map
+  int32_t out_map;   // activation map index that covers `out`
+  int32_t pad_;
 };
 
 struct CellBatch {
@@ -50,13 +54,30 @@ struct CellBatch {
 // Device-resident schedule for the persistent (single-launch) wavefront: the
 // same CellItem records in launch order (tile0 increasing) plus, per item and
 // per activation segment, the inclusive range of items whose output the segment
-// reads (-1 = external input).  done[i] counts finished epilogue warps of item
-// i; item i is complete when done[i] == target[i] (4 warps x tiles of the item).
+// reads (-1 = external input).
+//
+// Completion counters (all zero before the launch):
+//   coarse (fine == 0)  done[i] counts epilogue warps of item i that have written
+//       their part of the item's output; complete at target[i] (8 warps x tiles).
+//       done[n_items + i] counts tiles of item i whose new LSTM cell state is
+//       written (complete at target[i] / 8).
+//   fine (fine == 1)    for schedules in which a cell and the cells it reads share
+//       one row tiling and each segment reads exactly one item: tile_done[t] counts
+//       the epilogue warps of tile t (complete at 8) and c_done[t] is 1 once the
+//       tile's cell state is written.  K block kb of a segment then waits only
+//       for the producer tile(s) that hold those 64 activation columns, so a cell's
+//       K loop follows the cells it reads tile by tile instead of waiting for all
+//       of them.
 struct PlanView {
   const CellItem* items;
   const int32_t* dep;     // [n_items][kMaxSeg][2]
   const int32_t* target;  // [n_items]
-  int32_t* done;          // [n_items], zero before the launch
+  int32_t* done;          // [2 * n_items]
+  int32_t* tile_done;     // [total_tiles] (fine)
+  int32_t* c_done;        // [total_tiles] (fine)
+  int32_t fine;
+  int32_t units_per_tile; // activation columns produced by one tile (fine)
+  unsigned long long* trace;  // debug builds (FTB_TRACE): [total_tiles][4] globaltimer stamps, else nullptr
 };
 
 }  // namespace ftb

@@ -120,6 +120,27 @@ __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
 // another CTA's TMA loads.
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
+__device__ __forceinline__ int ld_relaxed_gpu(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+
+// Polls counters base[(from + i) * stride], i = 0 .. count-1 (count <= 16), with independent
+// loads (one memory round trip) and returns how many of them, from the first on, have reached
+// `target`.  The caller fences before it relies on what those counters guard.
+__device__ __forceinline__ int flags_ready_prefix(const int* base, int stride, int from, int count, int target) {
+  int v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = (i < count) ? ld_relaxed_gpu(base + (from + i) * stride) : 0;
+  int n = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    if (i == n && i < count && v[i] >= target) ++n;
+  return n;
+}
+
 // Bounded wait for a global counter to reach `target`.
 __device__ __forceinline__ bool flag_wait_ge(const int* flag, int target, volatile int* s_abort, int* g_status,
                                              int code) {

@@ -20,10 +20,11 @@
 namespace ftb {
 
 int launch_cell_gemm(int dtype, int epi, int bn, int pair, const CUtensorMap* maps, const CUtensorMap& mapW,
-                     const CellBatch& batch, int* status, int sm_count, cudaStream_t stream);
+                     const CUtensorMap& mapC, const CellBatch& batch, int* status, int sm_count,
+                     cudaStream_t stream);
 int launch_cell_gemm_persistent(int dtype, int epi, int bn, int pair, const CUtensorMap* maps,
-                                const CUtensorMap& mapW, const CellBatch& header, const PlanView& plan, int* status,
-                                int sm_count, cudaStream_t stream);
+                                const CUtensorMap& mapW, const CUtensorMap& mapC, const CellBatch& header,
+                                const PlanView& plan, int* status, int sm_count, cudaStream_t stream);
 int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* w, int ldw,
                      const CellBatch& batch, cudaStream_t stream);
 int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I, int H, int dtype,
@@ -48,6 +49,7 @@ struct CellLauncher {
   // 16-bit path
   CUtensorMap maps[kNumActMaps];
   CUtensorMap mapW;
+  CUtensorMap mapC;  // fp32 cell state (LSTM); a copy of maps[0] otherwise
   // fp32 path
   const float* act[kNumActMaps] = {nullptr, nullptr, nullptr};
   int ld_act[kNumActMaps] = {0, 0, 0};
@@ -85,7 +87,7 @@ struct CellLauncher {
       if (dtype == FTB_F32)
         rc = launch_cell_simt(epi, act, ld_act, w, ldw, b, stream);
       else
-        rc = launch_cell_gemm(dtype, epi, bn, pair, maps, mapW, b, status, sm_count, stream);
+        rc = launch_cell_gemm(dtype, epi, bn, pair, maps, mapW, mapC, b, status, sm_count, stream);
       if (rc) return rc;
     }
     return FTB_OK;
@@ -104,6 +106,10 @@ CellItem blank_item() {
   it.c_zero = 0;
   it.tile0 = 0;
   it.m_tiles = 0;
+  it.out_row0 = 0;
+  it.c_row0 = 0;
+  it.out_map = 1;
+  it.pad_ = 0;
   return it;
 }
 
@@ -129,7 +135,7 @@ bool valid_dtype(int dt) { return dt == FTB_F32 || dt == FTB_F16 || dt == FTB_BF
 
 // Optional tuning knobs of the wavefront entry points (0 = automatic).
 struct Tuning {
-  int layers_per_group = 0, bn = 0, schedule = 0, skew = 0, pair = 0;
+  int layers_per_group = 0, bn = 0, schedule = 0, skew = 0, pair = 0, fine_deps = 0;
   explicit Tuning(const int* t) {
     if (t != nullptr) {
       layers_per_group = t[0];
@@ -137,6 +143,7 @@ struct Tuning {
       schedule = t[2];
       skew = t[3];
       pair = t[4];
+      fine_deps = t[5];
     }
   }
   // pair: 0 = automatic (pairs when a cell has more than 128 rows), 1 = never, 2 = always.
@@ -147,16 +154,25 @@ struct Tuning {
 // Workspace layout of a persistent stacked-LSTM call: status block, then the
 // item table, the dependency table, the completion targets and the counters.
 struct PlanLayout {
-  size_t items, dep, target, done, total;
+  size_t items, dep, target, done, tile_done, c_done, counters_end, trace, total;
 };
-PlanLayout plan_layout(int n_items) {
+PlanLayout plan_layout(int n_items, int max_tiles_per_item = 64) {
   PlanLayout p;
   auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
   p.items = kWorkspaceBytes;
   p.dep = up(p.items + sizeof(CellItem) * n_items);
   p.target = up(p.dep + sizeof(int32_t) * 2 * kMaxSeg * n_items);
   p.done = up(p.target + sizeof(int32_t) * n_items);
-  p.total = up(p.done + sizeof(int32_t) * n_items);
+  const size_t max_tiles = static_cast<size_t>(n_items) * max_tiles_per_item;
+  p.tile_done = up(p.done + sizeof(int32_t) * 2 * n_items);
+  p.c_done = up(p.tile_done + sizeof(int32_t) * max_tiles);
+  p.counters_end = up(p.c_done + sizeof(int32_t) * max_tiles);
+  p.trace = p.counters_end;
+#ifdef FTB_TRACE
+  p.total = up(p.trace + 8 * 4 * max_tiles);
+#else
+  p.total = p.trace;
+#endif
   return p;
 }
 
@@ -217,7 +233,11 @@ __global__ void plan_stacked_kernel(const StackedPlanArgs a) {
   it.rows = a.N;
   it.c_zero = (t == 0);
   it.out = a.hs + (static_cast<size_t>(l) * a.L + t) * a.N * a.H * a.es;
+  it.out_row0 = (l * a.L + t) * a.N;
+  it.out_map = 1;
+  it.pad_ = 0;
   it.c = a.c + static_cast<size_t>(l) * a.N * a.H;
+  it.c_row0 = l * a.N;
   it.bias = a.bias_p ? a.bias_p + static_cast<size_t>(l) * 4 * a.H : nullptr;
   it.m_tiles = a.m_tiles;
   it.tile0 = pos * a.tiles_per_item;
@@ -226,7 +246,7 @@ __global__ void plan_stacked_kernel(const StackedPlanArgs a) {
     a.dep[(pos * kMaxSeg + s) * 2 + 0] = dep[s][0];
     a.dep[(pos * kMaxSeg + s) * 2 + 1] = dep[s][1];
   }
-  a.target[pos] = 4 * a.tiles_per_item;
+  a.target[pos] = 8 * a.tiles_per_item;  // eight epilogue warps per tile
 }
 
 // Accumulator tile width.  The last column tile of a cell may be partial (the
@@ -289,9 +309,12 @@ int ftb_grid_pack_weights(const void* i2h, const void* h2h, void* Wp, int H, int
   return pack_grid(i2h, h2h, Wp, H, dtype, static_cast<cudaStream_t>(stream));
 }
 
-size_t ftb_lstm_stacked_workspace_bytes(int D, int L) {
-  if (D <= 0 || L <= 0) return kWorkspaceBytes;
-  return plan_layout(D * L).total;
+// Upper bound of tiles per cell over the tile shapes the library may pick.
+static int stacked_max_tiles_per_cell(int N, int H) { return 2 * ((N + 255) / 256) * ((4 * H + 127) / 128); }
+
+size_t ftb_lstm_stacked_workspace_bytes(int D, int L, int N, int H) {
+  if (D <= 0 || L <= 0 || N <= 0 || H <= 0) return kWorkspaceBytes;
+  return plan_layout(D * L, stacked_max_tiles_per_cell(N, H)).total;
 }
 
 int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
@@ -337,6 +360,8 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
     cl.maps[2] = cl.maps[1];
     rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.w_box_rows(), 64);
     if (rc) return rc;
+    rc = make_tmap_2d(&cl.mapC, c, FTB_F32, static_cast<uint64_t>(D) * N, H, H, 128, 32);
+    if (rc) return rc;
   }
 
   int G = layers_per_group;
@@ -346,21 +371,21 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev);
     const double per_layer = 4.0 * H * K * es;
-    G = static_cast<int>((0.5 * l2) / per_layer);
+    G = static_cast<int>((0.55 * l2) / per_layer);
     G = std::max(1, std::min(G, D));
-    if (per_layer * D <= 0.5 * l2) G = D;
+    if (per_layer * D <= 0.55 * l2) G = D;
   }
   G = std::min(G, D);
 
   const int n_cells = D * L;
-  const PlanLayout lay = plan_layout(n_cells);
+  const PlanLayout lay = plan_layout(n_cells, stacked_max_tiles_per_cell(N, H));
   const bool persistent = dtype != FTB_F32 && schedule != 1 && (schedule == 2 || workspace_bytes >= lay.total);
   if (persistent) {
     if (workspace_bytes < lay.total) return FTB_ERR_WORKSPACE;
     char* ws = static_cast<char*>(workspace);
     StackedPlanArgs pa;
     pa.D = D; pa.L = L; pa.N = N; pa.I = I; pa.H = H; pa.G = G; pa.es = static_cast<int>(es);
-    pa.skew = skew > 0 ? skew : 2;
+    pa.skew = skew > 0 ? skew : 1;
     pa.m_tiles = cl.m_tiles_for(N);
     pa.tiles_per_item = pa.m_tiles * ((4 * H + cl.bn - 1) / cl.bn);
     pa.hs = static_cast<char*>(hs);
@@ -370,7 +395,7 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
     pa.dep = reinterpret_cast<int32_t*>(ws + lay.dep);
     pa.target = reinterpret_cast<int32_t*>(ws + lay.target);
     int32_t* done = reinterpret_cast<int32_t*>(ws + lay.done);
-    if (cudaMemsetAsync(done, 0, sizeof(int32_t) * n_cells, stream) != cudaSuccess) return FTB_ERR_LAUNCH;
+    if (cudaMemsetAsync(done, 0, lay.counters_end - lay.done, stream) != cudaSuccess) return FTB_ERR_LAUNCH;
     plan_stacked_kernel<<<(n_cells + 127) / 128, 128, 0, stream>>>(pa);
     if (cudaGetLastError() != cudaSuccess) return FTB_ERR_LAUNCH;
     count_launch();
@@ -381,9 +406,13 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
     header.ld_c = H;
     header.total_tiles = n_cells * pa.tiles_per_item;
     header.pad_ = 0;
-    PlanView pv = {pa.items, pa.dep, pa.target, done};
-    return launch_cell_gemm_persistent(dtype, EPI_LSTM, cl.bn, cl.pair, cl.maps, cl.mapW, header, pv, status,
-                                       cl.sm_count, stream);
+    PlanView pv = {pa.items, pa.dep, pa.target, done, reinterpret_cast<int32_t*>(ws + lay.tile_done),
+                   reinterpret_cast<int32_t*>(ws + lay.c_done), tune.fine_deps == 1 ? 1 : 0, cl.bn / 4, nullptr};
+#ifdef FTB_TRACE
+    pv.trace = reinterpret_cast<unsigned long long*>(ws + lay.trace);
+#endif
+    return launch_cell_gemm_persistent(dtype, EPI_LSTM, cl.bn, cl.pair, cl.maps, cl.mapW, cl.mapC, header, pv,
+                                       status, cl.sm_count, stream);
   }
 
   std::vector<CellItem> items;
@@ -404,7 +433,10 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
         it.rows = N;
         it.c_zero = (t == 0);
         it.out = static_cast<char*>(hs) + (static_cast<size_t>(l) * L + t) * N * H * es;
+        it.out_row0 = static_cast<int32_t>((static_cast<int64_t>(l) * L + t) * N);
+        it.out_map = 1;
         it.c = c + static_cast<size_t>(l) * N * H;
+        it.c_row0 = l * N;
         it.bias = bias_p ? bias_p + static_cast<size_t>(l) * 4 * H : nullptr;
         items.push_back(it);
       }
@@ -461,6 +493,8 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
     cl.maps[2] = cl.maps[1];
     rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.w_box_rows(), 64);
     if (rc) return rc;
+    rc = make_tmap_2d(&cl.mapC, c, FTB_F32, static_cast<uint64_t>(D) * max_dil * N, H, H, 128, 32);
+    if (rc) return rc;
   }
 
   // Layer l advances in steps of dilations[l] consecutive timesteps: those
@@ -492,7 +526,10 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
       it.rows = (t1 - t0) * N;
       it.c_zero = (s == 0);
       it.out = static_cast<char*>(hs) + (static_cast<size_t>(l) * L + t0) * N * H * es;
+      it.out_row0 = static_cast<int32_t>((static_cast<int64_t>(l) * L + t0) * N);
+      it.out_map = 1;
       it.c = c + static_cast<size_t>(l) * max_dil * N * H;
+      it.c_row0 = l * max_dil * N;
       it.bias = bias_p ? bias_p + static_cast<size_t>(l) * 4 * H : nullptr;
       levels[lv].push_back(it);
     }
@@ -552,6 +589,7 @@ int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* 
       if (rc) return rc;
       rc = make_tmap_2d(&cl.mapW, wp, dtype, static_cast<uint64_t>(D) * H, K, K, cl.bn, 64);
       if (rc) return rc;
+      cl.mapC = cl.maps[0];
     }
   }
 
@@ -621,6 +659,7 @@ int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, i
     cl.maps[1] = cl.maps[2] = cl.maps[0];
     rc = make_tmap_2d(&cl.mapW, Bt, dtype, N, K, K, cl.w_box_rows(), 64);
     if (rc) return rc;
+    cl.mapC = cl.maps[0];
   }
   std::vector<CellItem> items(1, blank_item());
   add_seg(items[0], 0, 0, K, 0);

@@ -60,8 +60,8 @@ def workspace(device, nbytes=0):
     return ws
 
 
-def _tuning(layers_per_group=0, bn=0, schedule=0, skew=0, pair=0):
-    return (ctypes.c_int * 5)(int(layers_per_group), int(bn), int(schedule), int(skew), int(pair))
+def _tuning(layers_per_group=0, bn=0, schedule=0, skew=0, pair=0, fine_deps=0):
+    return (ctypes.c_int * 6)(int(layers_per_group), int(bn), int(schedule), int(skew), int(pair), int(fine_deps))
 
 
 def check_status(device=None):
@@ -92,7 +92,8 @@ def lstm_pack_weights(W, U, bias=None):
     return Wp, bias_p
 
 
-def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0, schedule=0, skew=0, pair=0):
+def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0, schedule=0, skew=0, pair=0,
+                 fine_deps=0):
     """x: [L,N,I]; Wp: [D,4H,I+H] -> (hs [D,L,N,H], c fp32 [D,N,H]).
     schedule: 0 auto, 1 one launch per anti-diagonal, 2 one persistent kernel; pair: 0 auto, 1 single CTAs,
     2 CTA pairs."""
@@ -111,10 +112,11 @@ def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0, 
         c = torch.empty(D, N, H, dtype=torch.float32, device=x.device)
     _req(hs, "hs", x.dtype)
     _req(c, "c", torch.float32)
-    ws = workspace(x.device, lib.ftb_lstm_stacked_workspace_bytes(D, L))
+    ws = workspace(x.device, lib.ftb_lstm_stacked_workspace_bytes(D, L, N, H))
     with torch.cuda.device(x.device):
         check(lib.ftb_lstm_stacked_fwd(_ptr(x), _ptr(Wp), _ptr(bias_p), _ptr(hs), _ptr(c), D, L, N, I, H,
-                                       _dtype_code(x), _tuning(layers_per_group, bn, schedule, skew, pair), _ptr(ws), ws.numel(),
+                                       _dtype_code(x), _tuning(layers_per_group, bn, schedule, skew, pair, fine_deps), _ptr(ws),
+                                       ws.numel(),
                                        _stream()), "ftb_lstm_stacked_fwd")
     return hs, c
 

@@ -62,8 +62,10 @@ int ftb_lstm_pack_weights(const void* W, const void* U, const void* bias, void* 
  *  [3] skew              persistent schedule: layer j of a group runs `skew` levels
  *                        behind layer j-1
  *  [4] pair              1 = single CTAs, 2 = CTA pairs (tcgen05 cta_group::2) on
- *                        256-row blocks; automatic = pairs when a cell has > 128 rows */
-#define FTB_TUNING_INTS 5
+ *                        256-row blocks; automatic = pairs when a cell has > 128 rows
+ *  [5] fine_deps         persistent schedule: 1 = each K block waits only for the producer
+ *                        tile that holds its columns; otherwise a cell waits for whole cells */
+#define FTB_TUNING_INTS 6
 
 /* Stacked LSTM forward as a depth x time wavefront.
  * Stands in for stacked_lstm() (examples/stacked_rnn/stacked_lstm1.py:66-76) and
@@ -72,9 +74,9 @@ int ftb_lstm_pack_weights(const void* W, const void* U, const void* bias, void* 
  * x: [L,N,I]; Wp/bias_p from ftb_lstm_pack_weights; hs (out): [D,L,N,H] hidden
  * states of every layer (top layer = hs[D-1]); c (out): fp32 [D,N,H] final cell
  * state.  I == H is required for D > 1.  The persistent schedule needs
- * ftb_lstm_stacked_workspace_bytes(D, L) bytes of workspace; with less, one kernel
+ * ftb_lstm_stacked_workspace_bytes(D, L, N, H) bytes of workspace; with less, one kernel
  * is launched per level. */
-size_t ftb_lstm_stacked_workspace_bytes(int D, int L);
+size_t ftb_lstm_stacked_workspace_bytes(int D, int L, int N, int H);
 int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
                          int N, int I, int H, int dtype, const int* tuning, void* workspace, size_t workspace_bytes,
                          void* stream);

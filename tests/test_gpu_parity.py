@@ -121,9 +121,27 @@ def test_stacked_lstm_16bit(ops, dt, shape, kw):
 
 def test_stacked_lstm_grouping_is_bit_identical(ops):
     x, W, U, _ = dense.make_lstm_inputs(4, 5, 128, 256, 256, 9, 1.0 / 16, dtype=torch.bfloat16)
-    a, ca = _run_stacked(ops, x, W, U, None, layers_per_group=4, bn=128)
-    b, cb = _run_stacked(ops, x, W, U, None, layers_per_group=1, bn=128)
+    a, ca = _run_stacked(ops, x, W, U, None, layers_per_group=4, bn=128, schedule=1)
+    b, cb = _run_stacked(ops, x, W, U, None, layers_per_group=1, bn=128, schedule=1)
     assert torch.equal(a, b) and torch.equal(ca, cb)
+
+
+@pytest.mark.parametrize("shape", [(4, 7, 256, 256), (5, 9, 300, 128), (3, 4, 100, 512), (2, 3, 128, 64)])
+@pytest.mark.parametrize("kw", [
+    {"schedule": 2, "pair": 1}, {"schedule": 2, "pair": 2}, {"schedule": 2, "pair": 2, "skew": 2},
+    {"schedule": 2, "pair": 2, "fine_deps": 1}, {"schedule": 2, "pair": 1, "fine_deps": 1, "bn": 128},
+    {"schedule": 1, "pair": 2}, {"schedule": 2, "pair": 2, "layers_per_group": 2, "bn": 128},
+])
+def test_stacked_lstm_schedules_agree_bit_for_bit(ops, shape, kw):
+    """One launch per level, the persistent cooperative kernel, single CTAs and CTA pairs, coarse and
+    per-tile dependencies: same arithmetic in the same order, so the same bits."""
+    D, L, N, H = shape
+    x, W, U, b = dense.make_lstm_inputs(D, L, N, H, H, 3, 1.0 / 8, dtype=torch.bfloat16, bias=True)
+    ref_h, ref_c = _run_stacked(ops, x, W, U, b, schedule=1, pair=1, bn=kw.get("bn", 0))
+    h, c = _run_stacked(ops, x, W, U, b, **kw)
+    assert torch.equal(h, ref_h) and torch.equal(c, ref_c)
+    rhs, _ = dense.stacked_lstm_dense(*_f32(x, W, U, b))
+    _assert_16(h, rhs)
 
 
 def test_stacked_lstm_config4_properties(ops):
@@ -271,9 +289,14 @@ def test_b2b_config2_full_size(ops):
     out = ops.b2b_gemm(Ad, Bd, Cd)
     ops.check_status()
     _assert_16(out, dense.b2b_gemm_dense(A, B, C).float(), tol=4e-3)
-    out2 = ops.b2b_gemm(Ad * 2, Bd, Cd)
+    # rows of A are independent: rolling them rolls the rows of D, bit for bit
+    out2 = ops.b2b_gemm(torch.roll(Ad, 37, dims=1).contiguous(), Bd, Cd)
     ops.check_status()
-    assert torch.equal(out2, out * 2)
+    assert torch.equal(out2, torch.roll(out, 37, dims=1))
+    # a power-of-two scale of A carries through both products (up to fp16 subnormals)
+    out3 = ops.b2b_gemm(Ad * 2, Bd, Cd)
+    ops.check_status()
+    assert (out3.float() - 2 * out.float()).abs().max().item() <= 1e-3
 
 
 # ------------------------------------------------------------- flash attention
