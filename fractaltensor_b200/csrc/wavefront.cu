@@ -280,6 +280,8 @@ const char* ftb_status_str(int code) {
     case FTB_ERR_TIMEOUT_MMA: return "device wait ran out: MMA never committed";
     case FTB_ERR_TIMEOUT_EPI: return "device wait ran out: epilogue never drained";
     case FTB_ERR_TIMEOUT_SLOT: return "device wait ran out: no free pipeline stage";
+    case FTB_ERR_TIMEOUT_DEP: return "device wait ran out: a cell's inputs never completed";
+    case FTB_ERR_TMEM_LAYOUT: return "the two CTAs of a pair got different TMEM columns";
     default: return "unknown status";
   }
 }
