@@ -23,6 +23,7 @@ enum Status : int {
   FTB_ERR_DRIVER = 4,      // tensor-map encode or driver entry point failed
   FTB_ERR_LAUNCH = 5,      // kernel launch failed
   FTB_ERR_ARCH = 6,        // device is not sm_100
+  FTB_ERR_SCRATCH_LIMIT = 7,  // problem too large for the built-in static scratch buffer
   FTB_ERR_TIMEOUT_TMA = 16,   // device: consumer waited too long for a TMA stage
   FTB_ERR_TIMEOUT_MMA = 17,   // device: waited too long for an MMA commit
   FTB_ERR_TIMEOUT_EPI = 18,   // device: waited too long for the epilogue to drain

@@ -10,6 +10,7 @@
 // is one launch of a fused cell kernel that addresses the hyperplane in place.
 #include <algorithm>
 #include <map>
+#include <mutex>
 #include <vector>
 
 #include "../../include/ftb200.h"
@@ -276,6 +277,7 @@ const char* ftb_status_str(int code) {
     case FTB_ERR_DRIVER: return "tensor-map encode failed or driver entry point missing";
     case FTB_ERR_LAUNCH: return "kernel launch failed";
     case FTB_ERR_ARCH: return "device is not sm_100";
+    case FTB_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the built-in static buffer holds";
     case FTB_ERR_TIMEOUT_TMA: return "device wait ran out: TMA stage never arrived";
     case FTB_ERR_TIMEOUT_MMA: return "device wait ran out: MMA never committed";
     case FTB_ERR_TIMEOUT_EPI: return "device wait ran out: epilogue never drained";
@@ -668,6 +670,69 @@ int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, i
   items[0].rows = M;
   items[0].out = out;
   return cl.run(items);
+}
+
+// ------------------------------------------------------------------------------
+// Stacked LSTM forward for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need a
+// forward pass: a real-time loop that must not enter the allocator, a
+// plugin whose host application owns the allocator and hands out nothing but the
+// input and output buffers, or a process whose memory pool is already carved up.
+// ftb_lstm_stacked_fwd needs a caller-provided workspace for its schedule tables,
+// completion counters and status word; this variant keeps that scratch in a
+// fixed-size array that is part of the library image instead.
+//
+// Cost and limits: every GPU that loads the library holds FTB_STATIC_SCRATCH_BYTES
+// of device memory for the array until the process exits.  Problems whose
+// ftb_lstm_stacked_workspace_bytes(D, L, N, H) exceeds that size are rejected with
+// FTB_ERR_SCRATCH_LIMIT.  Only the persistent schedule (16-bit dtypes) is offered.
+// All calls on a device share the one array, and it keeps whatever the previous
+// call left in it: each call re-zeroes the status word and the counters it uses on
+// its stream before launching, so back-to-back calls on one stream are fine, but two
+// calls whose kernels can overlap on the GPU (different streams, or different host
+// threads) race on the tables and counters and must be serialised by the caller.
+//
+// The first call on each device resolves the array's device address
+// (cudaGetSymbolAddress; the array's name is only a host-side handle, not an
+// address a kernel could use) and caches it; make that first call outside any
+// stream capture.
+#define FTB_STATIC_SCRATCH_BYTES (4u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[FTB_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_scratch_mu;
+void* g_static_scratch_ptr[64] = {};
+}  // namespace
+
+int ftb_lstm_stacked_fwd_noalloc(const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D,
+                                 int L, int N, int I, int H, int dtype, const int* tuning, void** scratch_out,
+                                 void* stream) {
+  if (D <= 0 || L <= 0 || N <= 0 || H <= 0) return FTB_ERR_ARG;
+  if (dtype != FTB_F16 && dtype != FTB_BF16) return FTB_ERR_ARG;
+  if (ftb_lstm_stacked_workspace_bytes(D, L, N, H) > FTB_STATIC_SCRATCH_BYTES) return FTB_ERR_SCRATCH_LIMIT;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FTB_ERR_ARCH;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+        cudaGetLastError();
+        return FTB_ERR_DRIVER;
+      }
+      g_static_scratch_ptr[dev] = p;
+    }
+    scratch = g_static_scratch_ptr[dev];
+  }
+  if (scratch_out != nullptr) *scratch_out = scratch;
+  int t[FTB_TUNING_INTS] = {0, 0, 0, 0, 0, 0};
+  if (tuning != nullptr)
+    for (int i = 0; i < FTB_TUNING_INTS; ++i) t[i] = tuning[i];
+  t[2] = 2;  // persistent schedule: the only one whose host side builds nothing on the heap
+  return ftb_lstm_stacked_fwd(x, Wp, bias_p, hs, c, D, L, N, I, H, dtype, t, scratch, FTB_STATIC_SCRATCH_BYTES,
+                              stream);
 }
 
 }  // extern "C"

@@ -81,6 +81,22 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
                          int N, int I, int H, int dtype, const int* tuning, void* workspace, size_t workspace_bytes,
                          void* stream);
 
+/* Stacked LSTM forward without a caller workspace.  No counterpart in the reference: it exists
+ * for hosts that cannot allocate device memory where they call the forward pass (in a
+ * real-time loop, in a plugin that is only handed input and output buffers, under a
+ * fully committed memory pool).  Same arguments and results as ftb_lstm_stacked_fwd with the
+ * persistent schedule, but the schedule tables, completion counters and status word live in
+ * a 4 MiB array inside the library image (held on every GPU that loads the library).
+ * Returns FTB_ERR_SCRATCH_LIMIT (7) when ftb_lstm_stacked_workspace_bytes(D, L, N, H) exceeds
+ * 4 MiB; fp16/bf16 only.  The array is shared by all calls on a device: calls that can
+ * overlap on the GPU race and must be serialised by the caller; consecutive calls on one
+ * stream are safe.  The first call on a device looks the array's address up and should be
+ * made outside stream capture.  `scratch_out` (may be NULL) receives the array's device
+ * address, usable as the `workspace` argument of ftb_read_status(). */
+int ftb_lstm_stacked_fwd_noalloc(const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D,
+                                 int L, int N, int I, int H, int dtype, const int* tuning, void** scratch_out,
+                                 void* stream);
+
 /* Dilated stacked LSTM forward: layer l reads its own state dilations[l] steps
  * back.  Stands in for dilated_layer()/model() (examples/dilated_rnn/dilated_rnn.py:16-41)
  * and DilatedLstmRegion1/2 (kaleido/core/device/kernels/lstm/dilated_lstm/region{1,2}.h).
