@@ -63,19 +63,25 @@ class ClockSampler(object):
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples taken inside [t_begin, t_end] (host clock), all samples if that
+        window caught none."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         self.t.join(timeout=2)
-        sm = sorted(float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit())
-        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        rows = [r for ts, r in self.rows if t_begin is None or t_begin <= ts <= t_end + 0.15]
+        if not rows:
+            rows = [r for _, r in self.rows]
+        sm = sorted(float(r[0]) for r in rows if len(r) >= 7 and r[0].replace(".", "").isdigit())
+        mx = [float(r[1]) for r in rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        pw = [float(r[2]) for r in rows if len(r) >= 7 and r[2].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[3 + i] == "Active" for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[3 + i] == "Active" for r in rows)]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "power_w_max": max(pw) if pw else None, "reasons": reasons, "samples": len(sm)}
 
 
 def cpu_port_rate(sample_steps, threads):
@@ -188,17 +194,19 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to start: launch it before the warm-up
     for _ in range(args.warmup):
         step_resident()
     ops.check_status()
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     n0 = lib.ftb_launch_count()
+    t_begin = time.perf_counter()
     total_ms = timed(step_resident, args.steps)
+    t_end = time.perf_counter()
     launches = lib.ftb_launch_count() - n0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     ops.check_status()
 
     for _ in range(2):
@@ -216,16 +224,17 @@ def main():
     e2e_value = world * N * L / (e2e_ms / args.steps * 1e-3)
     pk = peaks()
     peak_kind = "sustained" if total_ms >= 1000.0 else "burst"
-    # Dominant kernel: cell_gemm_kernel (LSTM epilogue).  Every launch in the timed region is
-    # that kernel, back to back on one stream, so its average duration is total / launches and
-    # its algorithmic FLOPs per launch are the step's FLOPs / launches per step.
+    # Dominant kernel: cell_gemm_kernel (LSTM epilogue, persistent schedule): one launch per step
+    # does the whole wavefront (6.872 TFLOP); the only other launch of a step is the few-microsecond
+    # plan kernel (see profiles/), so the launch's duration is the step's.
     flops_per_step = FLOPS_PER_SAMPLE_STEP * N * L
     achieved = flops_per_step / (ms_per_step * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": achieved, "peak": pk[peak_kind], "unit": "TFLOP/s",
                 "frac": achieved / pk[peak_kind], "traffic": TRAFFIC_BYTES_PER_LAUNCH,
                 "peak_source": "%s %s bf16 GEMM" % (pk["src"], peak_kind),
-                "kernel": "cell_gemm_kernel<bf16, LSTM epilogue>", "launches_per_step": launches / args.steps,
-                "avg_launch_us": 1e3 * total_ms / max(launches, 1)}
+                "kernel": "cell_gemm_kernel<bf16, BN256, LSTM, persistent, CTA pairs>",
+                "launches_per_step": launches / args.steps, "dominant_launches_per_step": 1,
+                "avg_launch_us": 1e3 * ms_per_step, "flops_per_launch": flops_per_step}
     cpu = None
     if not args.no_cpu_baseline:
         threads = os.cpu_count() or 1

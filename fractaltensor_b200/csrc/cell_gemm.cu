@@ -31,6 +31,8 @@
 // (kaleido/core/device/kernels/lstm_kernels.h:24-126, lstm/inner.h:594-662) and
 // of VanillaRNNCellBMM (benchmarks/rnn/fractaltensor/utils.h:627-700); it is a
 // new design, not a translation of them.
+#include <cstdlib>
+
 #include "cell.h"
 #include "ptx.cuh"
 #include "tmap.h"
@@ -170,6 +172,9 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // Weights are re-read at every step of a sweep: ask L2 to keep them over the
+      // activations that stream through.
+      const uint64_t w_policy = l2_policy_evict_last();
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         const CellItem* it = cur.seek(tile);
         const int local = tile - it->tile0;
@@ -221,10 +226,10 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
             if (PAIR) {
               // Both CTAs' copies are counted on the leader's barrier; only the leader arms it.
               if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], C::kTxBytes);
-              tma_load_2d_pair(sb, &mapW, lead_bar, wk + kb * BK, w_row);
+              tma_load_2d_pair_hint(sb, &mapW, lead_bar, wk + kb * BK, w_row, w_policy);
             } else {
               mbar_arrive_expect_tx(&full_bar[stage], C::kTxBytes);
-              tma_load_2d(sb, &mapW, &full_bar[stage], wk + kb * BK, w_row);
+              tma_load_2d_hint(sb, &mapW, &full_bar[stage], wk + kb * BK, w_row, w_policy);
             }
             if (PERSIST && dep_tile0 >= 0) {
               // Activation columns [64 kb, 64 kb + 64) come from producer tiles up to n_last.
@@ -590,7 +595,14 @@ int launch_one(const CUtensorMap* maps, const CUtensorMap& mapW, const CUtensorM
     attrs[na].val.clusterDim.z = 1;
     ++na;
   }
-  if (PERSIST) {
+  // FTB_NO_COOPERATIVE=1 drops the cooperative attribute (profilers that cannot replay
+  // cooperative launches); residency then rests on grid <= SM count on an otherwise idle
+  // device, and the bounded waits turn a violated assumption into a status code.
+  static const bool no_coop = [] {
+    const char* e = getenv("FTB_NO_COOPERATIVE");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (PERSIST && !no_coop) {
     // Cooperative launch: every CTA is resident, so a CTA that waits on another
     // CTA's counter always makes progress.
     attrs[na].id = cudaLaunchAttributeCooperative;

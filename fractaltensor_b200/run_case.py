@@ -35,6 +35,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--layers-per-group", type=int, default=0)
     ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--schedule", type=int, default=0)
+    ap.add_argument("--pair", type=int, default=0)
     a = ap.parse_args()
     dt, dev = DT[a.dtype], torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(0)
@@ -46,7 +48,8 @@ def main():
         Wp, _ = ops.lstm_pack_weights(uni(1 / 32, a.D, 4, a.H, a.H).to(dt), uni(1 / 32, a.D, 4, a.H, a.H).to(dt))
         hs = torch.empty(a.D, a.L, a.N, a.H, dtype=dt, device=dev)
         c = torch.empty(a.D, a.N, a.H, device=dev)
-        fn = lambda: ops.lstm_stacked(x, Wp, None, hs, c, layers_per_group=a.layers_per_group, bn=a.bn)
+        fn = lambda: ops.lstm_stacked(x, Wp, None, hs, c, layers_per_group=a.layers_per_group, bn=a.bn,
+                                      schedule=a.schedule, pair=a.pair)
     elif a.case == "dilated":
         x = rnd(a.L, a.N, a.H).to(dt)
         Wp, _ = ops.lstm_pack_weights(uni(1 / 16, a.D, 4, a.H, a.H).to(dt), uni(1 / 16, a.D, 4, a.H, a.H).to(dt))
