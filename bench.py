@@ -55,7 +55,7 @@ class ClockSampler(object):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except OSError:
@@ -224,15 +224,15 @@ def main():
     e2e_value = world * N * L / (e2e_ms / args.steps * 1e-3)
     pk = peaks()
     peak_kind = "sustained" if total_ms >= 1000.0 else "burst"
-    # Dominant kernel: cell_gemm_kernel (LSTM epilogue, persistent schedule): one launch per step
-    # does the whole wavefront (6.872 TFLOP); the only other launch of a step is the few-microsecond
-    # plan kernel (see profiles/), so the launch's duration is the step's.
+    # Dominant kernel: lstm_static_kernel, one cooperative launch per step that does the whole
+    # wavefront (6.872 TFLOP); nothing else of ours launches in a step, so the launch's duration
+    # is the step's.
     flops_per_step = FLOPS_PER_SAMPLE_STEP * N * L
     achieved = flops_per_step / (ms_per_step * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": achieved, "peak": pk[peak_kind], "unit": "TFLOP/s",
                 "frac": achieved / pk[peak_kind], "traffic": TRAFFIC_BYTES_PER_LAUNCH,
                 "peak_source": "%s %s bf16 GEMM" % (pk["src"], peak_kind),
-                "kernel": "cell_gemm_kernel<bf16, BN256, LSTM, persistent, CTA pairs>",
+                "kernel": "lstm_static_kernel<bf16> (persistent, CTA pairs, static tile ownership)",
                 "launches_per_step": launches / args.steps, "dominant_launches_per_step": 1,
                 "avg_launch_us": 1e3 * ms_per_step, "flops_per_launch": flops_per_step}
     cpu = None

@@ -26,6 +26,10 @@ int launch_cell_gemm(int dtype, int epi, int bn, int pair, const CUtensorMap* ma
 int launch_cell_gemm_persistent(int dtype, int epi, int bn, int pair, const CUtensorMap* maps,
                                 const CUtensorMap& mapW, const CUtensorMap& mapC, const CellBatch& header,
                                 const PlanView& plan, int* status, int sm_count, cudaStream_t stream);
+bool lstm_static_supported(int dtype, int D, int N, int I, int H, int G, int sm_count);
+int launch_lstm_static(int dtype, const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
+                       int N, int I, int H, int G, int* done, int* status, unsigned long long* trace,
+                       cudaStream_t stream);
 int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* w, int ldw,
                      const CellBatch& batch, cudaStream_t stream);
 int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I, int H, int dtype,
@@ -383,10 +387,23 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
 
   const int n_cells = D * L;
   const PlanLayout lay = plan_layout(n_cells, stacked_max_tiles_per_cell(N, H));
-  const bool persistent = dtype != FTB_F32 && schedule != 1 && (schedule == 2 || workspace_bytes >= lay.total);
+  const bool persistent = dtype != FTB_F32 && schedule != 1 && (schedule >= 2 || workspace_bytes >= lay.total);
   if (persistent) {
     if (workspace_bytes < lay.total) return FTB_ERR_WORKSPACE;
     char* ws = static_cast<char*>(workspace);
+    // Static tile ownership (schedule 3, and the automatic choice when it applies): CTA pairs
+    // keep their slice of a layer, cell state in registers, for a whole sweep over time.
+    const bool can_static = tune.pair != 1 && (bn == 0 || bn == 256) && !tune.fine_deps &&
+                            lstm_static_supported(dtype, D, N, I, H, G, cl.sm_count);
+    if (schedule == 3 && !can_static) return FTB_ERR_ARG;
+    if ((schedule == 3 || schedule == 0) && can_static) {
+      unsigned long long* trace = nullptr;
+#ifdef FTB_TRACE
+      trace = reinterpret_cast<unsigned long long*>(ws + lay.trace);
+#endif
+      return launch_lstm_static(dtype, x, Wp, bias_p, hs, c, D, L, N, I, H, G,
+                                reinterpret_cast<int*>(ws + lay.done), status, trace, stream);
+    }
     StackedPlanArgs pa;
     pa.D = D; pa.L = L; pa.N = N; pa.I = I; pa.H = H; pa.G = G; pa.es = static_cast<int>(es);
     pa.skew = skew > 0 ? skew : 1;

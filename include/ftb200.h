@@ -58,7 +58,10 @@ int ftb_lstm_pack_weights(const void* W, const void* U, const void* bias, void* 
  *  [1] bn                accumulator tile width, 128 or 256
  *  [2] schedule          1 = one kernel launch per wavefront level; 2 = one persistent
  *                        cooperative kernel, cells chained through completion counters
- *                        in the workspace (16-bit dtypes only)
+ *                        in the workspace (16-bit dtypes only); 3 = persistent with static
+ *                        tile ownership (stacked LSTM: every CTA pair keeps its slice of a
+ *                        layer, cell state in registers, over a whole sweep; needs a layer
+ *                        group's tiles to fit on the device; the automatic choice when so)
  *  [3] skew              persistent schedule: layer j of a group runs `skew` levels
  *                        behind layer j-1
  *  [4] pair              1 = single CTAs, 2 = CTA pairs (tcgen05 cta_group::2) on

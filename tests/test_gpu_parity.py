@@ -131,11 +131,14 @@ def test_stacked_lstm_grouping_is_bit_identical(ops):
     {"schedule": 2, "pair": 1}, {"schedule": 2, "pair": 2}, {"schedule": 2, "pair": 2, "skew": 2},
     {"schedule": 2, "pair": 2, "fine_deps": 1}, {"schedule": 2, "pair": 1, "fine_deps": 1, "bn": 128},
     {"schedule": 1, "pair": 2}, {"schedule": 2, "pair": 2, "layers_per_group": 2, "bn": 128},
+    {"schedule": 3}, {"schedule": 3, "layers_per_group": 1}, {"schedule": 0},
 ])
 def test_stacked_lstm_schedules_agree_bit_for_bit(ops, shape, kw):
     """One launch per level, the persistent cooperative kernel, single CTAs and CTA pairs, coarse and
     per-tile dependencies: same arithmetic in the same order, so the same bits."""
     D, L, N, H = shape
+    if kw.get("schedule") == 3 and kw.get("layers_per_group", 0) == 0 and D * (4 * H // 256) * 2 * ((N + 255) // 256) > 148:
+        kw = dict(kw, layers_per_group=1)  # static ownership needs a group's tiles to fit on the device
     x, W, U, b = dense.make_lstm_inputs(D, L, N, H, H, 3, 1.0 / 8, dtype=torch.bfloat16, bias=True)
     ref_h, ref_c = _run_stacked(ops, x, W, U, b, schedule=1, pair=1, bn=kw.get("bn", 0))
     h, c = _run_stacked(ops, x, W, U, b, **kw)
