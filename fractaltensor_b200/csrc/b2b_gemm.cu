@@ -330,7 +330,8 @@ extern "C" int ftb_b2b_gemm(const void* A, const void* B, const void* C, void* D
   if (workspace == nullptr || workspace_bytes < ftb_workspace_bytes()) return FTB_ERR_WORKSPACE;
   int rc = check_device_sm100();
   if (rc) return rc;
-  if (cudaMemsetAsync(workspace, 0, ftb_workspace_bytes(), stream) != cudaSuccess) return FTB_ERR_LAUNCH;
+  // The status word is sticky: the caller zeroes the workspace once; after a device wait ran out
+  // every later call on that workspace is a no-op until the caller clears the word.
   int* status = static_cast<int*>(workspace);
 
   CUtensorMap mA, mB, mC, mD;

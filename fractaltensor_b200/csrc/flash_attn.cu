@@ -223,9 +223,15 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[t]);
 
-      float mx = __uint_as_float(s[0]);
+      // Row maximum with eight independent chains (two softmax warps per scheduler leave
+      // little latency hiding; a single 128-long dependent chain would dominate).
+      float mx8[8];
 #pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+      for (int i = 0; i < 8; ++i) mx8[i] = __uint_as_float(s[i]);
+#pragma unroll
+      for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[i]));
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       const float m_new = mx * scale_log2;
       bool waited_pv = false;
       if (j == 0) {
@@ -256,14 +262,14 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         }
       }
 
-      float sum = 0.f;
+      float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 128; ++i) {
         const float p = exp2_fast(fmaf(__uint_as_float(s[i]), scale_log2, -m_used));
-        sum += p;
+        sum8[i & 7] += p;
         s[i] = __float_as_uint(p);
       }
-      l += sum;
+      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
 
       // The P tile is single-buffered: PV of the previous block must have read it.
       if (j > 0 && !waited_pv) {
@@ -365,7 +371,8 @@ extern "C" int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, v
   if (workspace == nullptr || workspace_bytes < ftb_workspace_bytes()) return FTB_ERR_WORKSPACE;
   int rc = check_device_sm100();
   if (rc) return rc;
-  if (cudaMemsetAsync(workspace, 0, ftb_workspace_bytes(), stream) != cudaSuccess) return FTB_ERR_LAUNCH;
+  // The status word is sticky: the caller zeroes the workspace once; after a device wait ran out
+  // every later call on that workspace is a no-op until the caller clears the word.
   int* status = static_cast<int*>(workspace);
 
   CUtensorMap mQ, mK, mV, mO;

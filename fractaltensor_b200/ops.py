@@ -70,6 +70,8 @@ def check_status(device=None):
     ws = workspace(device if device is not None else torch.cuda.current_device())
     out = ctypes.c_int(0)
     check(lib.ftb_read_status(_ptr(ws), ctypes.byref(out), _stream()), "ftb_read_status")
+    if out.value != 0:
+        ws[:8].zero_()  # the status word is sticky for some entry points: clear it for the next call
     check(out.value, "device kernel")
 
 

@@ -10,9 +10,13 @@
  *    cores with fp32 accumulation; fp32 runs on CUDA cores.
  *  - `stream` is a cudaStream_t passed as void*.  Calls are asynchronous,
  *    stream-ordered, re-entrant and safe to capture in a CUDA graph.
- *  - `workspace` is at least ftb_workspace_bytes() bytes.  Its first word is the
- *    device status word of the call: 0, or the code of the first bounded device
- *    wait that ran out.  Read it with ftb_read_status() after the stream synced.
+ *  - `workspace` is at least ftb_workspace_bytes() bytes, zero-filled by the caller
+ *    before its first use.  Its first word is the device status word: 0, or the
+ *    code of the first bounded device wait that ran out.  Read it with
+ *    ftb_read_status() after the stream synced.  The RNN entry points clear it at
+ *    the start of every call; for ftb_b2b_gemm and ftb_flash_attn_fwd it is sticky
+ *    (a call on a workspace whose status is non-zero does nothing) until the
+ *    caller zeroes it again.
  *  - Return value: 0, or an FTB_ERR_* code (ftb_status_str() names it).
  *
  * The reference exposes this path as C++ host functors with compile-time tile
