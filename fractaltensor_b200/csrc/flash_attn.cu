@@ -16,8 +16,12 @@
 //   warp 1       MMA issuer: S_t = Q_t K^T and O_t += P_t V, accumulators in TMEM
 //   warps 2..5   softmax warpgroup of query tile 0 (one thread per query row)
 //   warps 6..9   softmax warpgroup of query tile 1
-// P is written to shared memory in the swizzled K-major layout the PV MMA reads;
-// V is consumed MN-major straight from its row-major tile.
+// P never touches shared memory: the softmax threads write it (16-bit pairs) with
+// tcgen05.st over the TMEM columns of the S tile they have just read, and the PV
+// MMA takes its A operand from TMEM.  V is consumed MN-major straight from its
+// row-major tile.  Per query tile the tensor pipe sees S(j), [softmax], PV(j),
+// S(j+1), ...; the two query tiles are offset so that one is in its softmax while
+// the other one's MMAs run.
 #include "../../include/ftb200.h"
 #include "ptx.cuh"
 #include "tmap.h"
@@ -27,9 +31,9 @@ namespace {
 
 constexpr int kHalfBytes = 128 * 128;  // 128 rows x 64 16-bit columns
 constexpr int kTileBytes = 2 * kHalfBytes;
-constexpr int kKVSlots = 3;
+constexpr int kKVSlots = 5;
 constexpr int kThreads = 320;
-constexpr uint32_t kSmemBytes = (2 + 2 + kKVSlots) * kTileBytes + 1024;  // Q0,Q1,P0,P1,KV ring
+constexpr uint32_t kSmemBytes = (2 + kKVSlots) * kTileBytes + 1024;  // Q0, Q1 (reused as output staging), KV ring
 constexpr float kRescaleThreshold = 8.0f;
 
 __device__ __forceinline__ void tmem_ld32p(uint32_t taddr, uint32_t* r) {
@@ -51,6 +55,13 @@ __device__ __forceinline__ uint8_t* sw128_chunk_ptr(uint8_t* tile, int row, int 
   return tile + (chunk16 >> 3) * kHalfBytes + row * 128 + (((chunk16 & 7) ^ (row & 7)) << 4);
 }
 
+#ifdef FTB_TRACE
+__device__ unsigned long long g_fa_trace[2][32][8];
+#define FA_STAMP(tt, jj, k) if (blockIdx.x == 300 && lane == 0 && q == 0) g_fa_trace[tt][jj][k] = globaltimer_ns()
+#else
+#define FA_STAMP(tt, jj, k)
+#endif
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
@@ -59,7 +70,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t q_full;
   __shared__ uint64_t kv_full[kKVSlots], kv_empty[kKVSlots];
-  __shared__ uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2], o_staged[2];
+  __shared__ uint64_t s_full[2], p_full[2], pv_done[2], o_staged[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
 
@@ -69,8 +80,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   const int lane = threadIdx.x & 31;
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sQ = smem;                      // 2 tiles
-  uint8_t* sP = sQ + 2 * kTileBytes;       // 2 tiles
-  uint8_t* sKV = sP + 2 * kTileBytes;      // ring
+  uint8_t* sKV = sQ + 2 * kTileBytes;      // ring
 
   const int pairs = S / 256;
   const int bh = blockIdx.x / pairs;
@@ -91,7 +101,6 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
       mbar_init(&p_full[i], 4);
       mbar_init(&pv_done[i], 1);
       mbar_init(&o_staged[i], 4);
@@ -107,7 +116,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
-  // TMEM columns: S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512).
+  // TMEM columns: S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512); P_t overlays S_t's first 64.
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -138,61 +147,67 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(128, 128, Fmt<T>::kind, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_f16(128, 128, Fmt<T>::kind, 0, 1);  // V is MN-major
-      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP), aKV = smem_u32(sKV);
-      uint32_t full_phase[kKVSlots] = {0, 0, 0};
-      uint32_t se_phase[2] = {0, 0}, pf_phase[2] = {0, 0};
+      const uint32_t aQ = smem_u32(sQ), aKV = smem_u32(sKV);
+      uint32_t full_phase[kKVSlots] = {};
       bool ok = mbar_wait(&q_full, 0, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
 
-      // S_t(j) = Q_t . K_j^T for both query tiles; releases the K slot.
-      auto issue_s = [&](int j) -> bool {
-        const int slot = (2 * j) % kKVSlots;
+      auto wait_slot = [&](int n) -> bool {  // n-th tile of the K0, V0, K1, V1, ... stream
+        const int slot = n % kKVSlots;
         if (!mbar_wait(&kv_full[slot], full_phase[slot], &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
         full_phase[slot] ^= 1u;
-        const uint32_t aK = aKV + slot * kTileBytes;
-        for (int t = 0; t < 2; ++t) {
-          if (!mbar_wait(&s_empty[t], se_phase[t] ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
-          se_phase[t] ^= 1u;
-          tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-            umma_ss(tmem_base + t * 128, make_sdesc_sw128(aQ + t * kTileBytes + off, 16, 1024),
-                    make_sdesc_sw128(aK + off, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
-          }
-          umma_commit(&s_full[t]);
-        }
-        umma_commit(&kv_empty[slot]);
+        tc_fence_after();
         return true;
       };
-      // O_t += P_t(j) . V_j for both query tiles; releases the V slot.
-      auto issue_pv = [&](int j) -> bool {
-        const int slot = (2 * j + 1) % kKVSlots;
-        if (!mbar_wait(&kv_full[slot], full_phase[slot], &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
-        full_phase[slot] ^= 1u;
-        const uint32_t aV = aKV + slot * kTileBytes;
-        for (int t = 0; t < 2; ++t) {
-          if (!mbar_wait(&p_full[t], pf_phase[t], &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
-          pf_phase[t] ^= 1u;
-          tc_fence_after();
+      // S_t(j) = Q_t . K_j^T
+      auto issue_s = [&](int t, int j) {
+        const uint32_t aK = aKV + ((2 * j) % kKVSlots) * kTileBytes;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            // A: P_t, K-major, 16 keys per step.  B: V, MN-major: 16 keys = two 8-row groups
-            // (1024 B apart), the two 64-column halves of d are 16 KB apart.
-            const uint32_t a_off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-            const uint32_t b_off = k * 2048;
-            umma_ss(tmem_base + 256 + t * 128, make_sdesc_sw128(aP + t * kTileBytes + a_off, 16, 1024),
-                    make_sdesc_sw128(aV + b_off, kHalfBytes, 1024), idesc_pv, (j | k) != 0 ? 1u : 0u);
-          }
-          umma_commit(&pv_done[t]);
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(tmem_base + t * 128, make_sdesc_sw128(aQ + t * kTileBytes + off, 16, 1024),
+                  make_sdesc_sw128(aK + off, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
         }
-        umma_commit(&kv_empty[slot]);
-        return true;
+        umma_commit(&s_full[t]);
+      };
+      // O_t += P_t(j) . V_j: A = P_t from TMEM (16 keys = 8 packed columns per step); B = V,
+      // MN-major: 16 keys = two 8-row groups (1024 B apart), the two 64-column halves of d are
+      // 16 KB apart.
+      auto issue_pv = [&](int t, int j) {
+        const uint32_t aV = aKV + ((2 * j + 1) % kKVSlots) * kTileBytes;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
+                  make_sdesc_sw128(aV + k * 2048, kHalfBytes, 1024), idesc_pv, (j | k) != 0 ? 1u : 0u);
+        umma_commit(&pv_done[t]);
       };
 
-      if (ok) ok = issue_s(0);
+      // (Running tile 1 half a step behind tile 0, so that the two softmaxes alternate on the
+      // special-function units, was measured and is slower than this per-block interleave.)
+      if (ok) ok = wait_slot(0);
+      if (ok) {
+        issue_s(0, 0);
+        issue_s(1, 0);
+        umma_commit(&kv_empty[0]);
+      }
       for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) ok = issue_s(j + 1);
-        if (ok) ok = issue_pv(j);
+        const bool more = j + 1 < n_kv;
+        if (!wait_slot(2 * j + 1)) break;            // V_j
+        if (more && !wait_slot(2 * j + 2)) break;    // K_{j+1}
+        for (int t = 0; t < 2 && ok; ++t) {
+          // P_t(j) is in TMEM (and the softmax is done with S_t(j)).
+          if (!mbar_wait(&p_full[t], j & 1, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_pv(t, j);
+          // The tensor pipe runs MMAs in issue order: S_t(j+1) overwrites S_t / P_t only after
+          // PV_t(j) has read P_t.
+          if (more) issue_s(t, j + 1);
+        }
+        if (!ok) break;
+        umma_commit(&kv_empty[(2 * j + 1) % kKVSlots]);
+        if (more) umma_commit(&kv_empty[(2 * j + 2) % kKVSlots]);
       }
     }
   } else {
@@ -203,7 +218,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     const uint32_t s_addr = lane_addr + t * 128;
     const uint32_t o_addr = lane_addr + 256 + t * 128;
-    uint8_t* myP = sP + t * kTileBytes;
+    uint8_t* my_stage = sQ + t * kTileBytes;  // output staging: Q_t is dead once the last S MMA is done
     float m_used = 0.f, l = 0.f;
     bool ok = true;
 
@@ -213,15 +228,14 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         break;
       }
       tc_fence_after();
+      FA_STAMP(t, j, 0);
       uint32_t s[128];
       tmem_ld32p(s_addr + 0, s + 0);
       tmem_ld32p(s_addr + 32, s + 32);
       tmem_ld32p(s_addr + 64, s + 64);
       tmem_ld32p(s_addr + 96, s + 96);
       tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[t]);
+      FA_STAMP(t, j, 1);
 
       // Row maximum with eight independent chains (two softmax warps per scheduler leave
       // little latency hiding; a single 128-long dependent chain would dominate).
@@ -233,7 +247,6 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
                              fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       const float m_new = mx * scale_log2;
-      bool waited_pv = false;
       if (j == 0) {
         m_used = m_new;
       } else {
@@ -244,7 +257,6 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             ok = false;
             break;
           }
-          waited_pv = true;
           tc_fence_after();
           const float alpha = need ? exp2_fast(m_used - m_new) : 1.f;
           if (need) m_used = m_new;
@@ -262,38 +274,37 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         }
       }
 
-      float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      FA_STAMP(t, j, 2);
+      // P_t(j) = 2^(scale*S - m) as 16-bit pairs over the first 64 columns of S_t (S_t(j) is in
+      // registers now; the MMA that overwrites these columns next, S_t(j+1), is issued after
+      // PV_t(j)); row sums for l.  (Packed fp16 exponentials, two per MUFU op, were measured
+      // and are no faster: the softmax is not MUFU-bound here.)
+      {
+        float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 128; ++i) {
-        const float p = exp2_fast(fmaf(__uint_as_float(s[i]), scale_log2, -m_used));
-        sum8[i & 7] += p;
-        s[i] = __float_as_uint(p);
-      }
-      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
-
-      // The P tile is single-buffered: PV of the previous block must have read it.
-      if (j > 0 && !waited_pv) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[t], (j - 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
-          ok = false;
-          break;
+        for (int i = 0; i < 128; ++i) {
+          const float p = exp2_fast(fmaf(__uint_as_float(s[i]), scale_log2, -m_used));
+          sum8[i & 7] += p;
+          s[i] = __float_as_uint(p);
         }
-      }
+        l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
+        uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        uint4 u;
-        u.x = Fmt<T>::pack2(__uint_as_float(s[8 * c + 0]), __uint_as_float(s[8 * c + 1]));
-        u.y = Fmt<T>::pack2(__uint_as_float(s[8 * c + 2]), __uint_as_float(s[8 * c + 3]));
-        u.z = Fmt<T>::pack2(__uint_as_float(s[8 * c + 4]), __uint_as_float(s[8 * c + 5]));
-        u.w = Fmt<T>::pack2(__uint_as_float(s[8 * c + 6]), __uint_as_float(s[8 * c + 7]));
-        *reinterpret_cast<uint4*>(sw128_chunk_ptr(myP, row, c)) = u;
+        for (int hlf = 0; hlf < 2; ++hlf) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            pk[c] = Fmt<T>::pack2(__uint_as_float(s[64 * hlf + 2 * c]), __uint_as_float(s[64 * hlf + 2 * c + 1]));
+          tmem_st32(s_addr + 32 * hlf, pk);
+        }
+        tmem_st_wait();
       }
+      FA_STAMP(t, j, 3);
       tc_fence_before();
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
     }
 
-    // Final: O_t / l -> 16-bit -> staging (the P tile, free once the last PV is done) -> TMA store.
+    // Final: O_t / l -> 16-bit -> staging (the Q tile, dead once the last PV is done) -> TMA store.
     if (ok && __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (n_kv - 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
       tc_fence_after();
       const float inv_l = 1.f / l;
@@ -309,7 +320,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           u.y = Fmt<T>::pack2(__uint_as_float(o[8 * c + 2]) * inv_l, __uint_as_float(o[8 * c + 3]) * inv_l);
           u.z = Fmt<T>::pack2(__uint_as_float(o[8 * c + 4]) * inv_l, __uint_as_float(o[8 * c + 5]) * inv_l);
           u.w = Fmt<T>::pack2(__uint_as_float(o[8 * c + 6]) * inv_l, __uint_as_float(o[8 * c + 7]) * inv_l);
-          *reinterpret_cast<uint4*>(sw128_chunk_ptr(myP, row, ch * 4 + c)) = u;
+          *reinterpret_cast<uint4*>(sw128_chunk_ptr(my_stage, row, ch * 4 + c)) = u;
         }
       }
       tc_fence_before();
@@ -319,8 +330,8 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       // One thread per warpgroup stores the tile once all four warps have staged their rows.
       if (lane == 0 && (warp == 2 || warp == 6) &&
           mbar_wait(&o_staged[t], 0, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) {
-        tma_store_2d(&mapO, myP, 0, q_row0 + t * 128);
-        tma_store_2d(&mapO, myP + kHalfBytes, 64, q_row0 + t * 128);
+        tma_store_2d(&mapO, my_stage, 0, q_row0 + t * 128);
+        tma_store_2d(&mapO, my_stage + kHalfBytes, 64, q_row0 + t * 128);
         tma_store_commit();
         tma_store_wait<0>();
       }
@@ -358,6 +369,12 @@ int launch(const CUtensorMap& mQ, const CUtensorMap& mK, const CUtensorMap& mV, 
 }  // namespace ftb
 
 using namespace ftb;
+
+#ifdef FTB_TRACE
+extern "C" int ftb_debug_fa_trace(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_fa_trace, sizeof(unsigned long long) * 2 * 32 * 8) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 extern "C" int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S,
                                   int d, float scale, int dtype, void* workspace, size_t workspace_bytes,
