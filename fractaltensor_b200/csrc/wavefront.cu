@@ -99,6 +99,12 @@ struct CellLauncher {
   }
 };
 
+// Runs a whole wavefront as one persistent launch: `items` in an order in which every item
+// only depends on earlier ones, `deps[i]` = per segment the inclusive range of item indices the
+// segment reads (-1 = external).  Tables go to the workspace with stream-ordered copies.
+int run_persistent(const CellLauncher& cl, std::vector<CellItem>& items, const std::vector<int32_t>& deps,
+                   char* ws, const struct PlanLayout& lay);
+
 CellItem blank_item() {
   CellItem it;
   it.out = nullptr;
@@ -179,6 +185,42 @@ PlanLayout plan_layout(int n_items, int max_tiles_per_item = 64) {
   p.total = p.trace;
 #endif
   return p;
+}
+
+int run_persistent(const CellLauncher& cl, std::vector<CellItem>& items, const std::vector<int32_t>& deps,
+                   char* ws, const PlanLayout& lay) {
+  const int n = static_cast<int>(items.size());
+  const int n_tiles_n = (cl.n_cols + cl.cols_per_tile() - 1) / cl.cols_per_tile();
+  std::vector<int32_t> target(n);
+  int tiles = 0;
+  for (int i = 0; i < n; ++i) {
+    items[i].m_tiles = cl.m_tiles_for(items[i].rows);
+    items[i].tile0 = tiles;
+    tiles += items[i].m_tiles * n_tiles_n;
+    target[i] = 8 * items[i].m_tiles * n_tiles_n;  // eight epilogue warps per tile
+  }
+  // The host vectors die with this call; cudaMemcpyAsync from pageable memory returns once the
+  // bytes are staged.
+  if (cudaMemcpyAsync(ws + lay.items, items.data(), sizeof(CellItem) * n, cudaMemcpyHostToDevice, cl.stream) !=
+          cudaSuccess ||
+      cudaMemcpyAsync(ws + lay.dep, deps.data(), sizeof(int32_t) * 2 * kMaxSeg * n, cudaMemcpyHostToDevice,
+                      cl.stream) != cudaSuccess ||
+      cudaMemcpyAsync(ws + lay.target, target.data(), sizeof(int32_t) * n, cudaMemcpyHostToDevice, cl.stream) !=
+          cudaSuccess ||
+      cudaMemsetAsync(ws + lay.done, 0, sizeof(int32_t) * 2 * n, cl.stream) != cudaSuccess)
+    return FTB_ERR_LAUNCH;
+  CellBatch header;
+  header.n_items = n;
+  header.n_cols = cl.n_cols;
+  header.ld_out = cl.ld_out;
+  header.ld_c = cl.ld_c;
+  header.total_tiles = tiles;
+  header.pad_ = 0;
+  PlanView pv = {reinterpret_cast<const CellItem*>(ws + lay.items), reinterpret_cast<const int32_t*>(ws + lay.dep),
+                 reinterpret_cast<const int32_t*>(ws + lay.target), reinterpret_cast<int32_t*>(ws + lay.done),
+                 nullptr, nullptr, 0, 0, nullptr};
+  return launch_cell_gemm_persistent(cl.dtype, cl.epi, cl.bn, cl.pair, cl.maps, cl.mapW, cl.mapC, header, pv,
+                                     cl.status, cl.sm_count, cl.stream);
 }
 
 struct StackedPlanArgs {
@@ -506,7 +548,7 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
   } else {
     cl.bn = pick_bn(4 * H, bn);
     if (cl.bn == 0) return FTB_ERR_ARG;
-    cl.pair = tune.use_pair(2 * N);
+    cl.pair = tune.pair == 2;  // cells here are latency-bound: single CTAs measured faster than pairs
     rc = make_tmap_2d(&cl.maps[0], x, dtype, static_cast<uint64_t>(L) * N, H, H, 128, 64);
     if (rc) return rc;
     rc = make_tmap_2d(&cl.maps[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, 128, 64);
@@ -522,6 +564,7 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
   // timesteps only depend on the step before (same layer) and on the layer
   // below, so one step is one cell of batch dilation*N.  Earliest-start levels.
   std::map<int, std::vector<CellItem>> levels;
+  std::map<int, std::vector<std::pair<int, int>>> level_ids;  // (layer, step) of each item, same order
   std::vector<std::vector<int>> level_of(D);
   for (int l = 0; l < D; ++l) {
     const int dl = dilations[l];
@@ -553,13 +596,54 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
       it.c_row0 = l * max_dil * N;
       it.bias = bias_p ? bias_p + static_cast<size_t>(l) * 4 * H : nullptr;
       levels[lv].push_back(it);
+      level_ids[lv].push_back(std::make_pair(l, s));
     }
+  }
+  int n_items = 0;
+  for (auto& kv : levels) n_items += static_cast<int>(kv.second.size());
+  const PlanLayout lay = plan_layout(n_items, 0);
+  const bool persistent = dtype != FTB_F32 && tune.schedule != 1 && (tune.schedule >= 2 || workspace_bytes >= lay.total);
+  if (persistent) {
+    if (workspace_bytes < lay.total) return FTB_ERR_WORKSPACE;
+    // Launch order = level order.  A step of layer l reads the layer below up to the step that
+    // holds its last timestep (the steps of a layer complete in order, so waiting for that one
+    // is enough) and the step before it in its own layer.
+    std::vector<CellItem> order;
+    std::vector<std::vector<int>> index_of(D);
+    for (int l = 0; l < D; ++l) index_of[l].resize(level_of[l].size());
+    for (auto& kv : levels)
+      for (size_t i = 0; i < kv.second.size(); ++i) {
+        const std::pair<int, int> id = level_ids[kv.first][i];
+        index_of[id.first][id.second] = static_cast<int>(order.size());
+        order.push_back(kv.second[i]);
+      }
+    std::vector<int32_t> deps(static_cast<size_t>(n_items) * kMaxSeg * 2, -1);
+    for (int l = 0; l < D; ++l)
+      for (size_t s = 0; s < index_of[l].size(); ++s) {
+        const int me = index_of[l][s];
+        const int dl = dilations[l];
+        const int t1 = std::min(L, static_cast<int>(s + 1) * dl);
+        if (l > 0) {
+          const int below = index_of[l - 1][(t1 - 1) / dilations[l - 1]];
+          deps[(me * kMaxSeg + 0) * 2 + 0] = deps[(me * kMaxSeg + 0) * 2 + 1] = below;
+        }
+        if (s > 0) {
+          const int prev = index_of[l][s - 1];
+          deps[(me * kMaxSeg + 1) * 2 + 0] = deps[(me * kMaxSeg + 1) * 2 + 1] = prev;
+        }
+      }
+    return run_persistent(cl, order, deps, static_cast<char*>(workspace), lay);
   }
   for (auto& kv : levels) {
     rc = cl.run(kv.second);
     if (rc) return rc;
   }
   return FTB_OK;
+}
+
+size_t ftb_lstm_dilated_workspace_bytes(int D, int L) {
+  if (D <= 0 || L <= 0) return kWorkspaceBytes;
+  return plan_layout(D * L, 0).total;
 }
 
 int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* Wpy, const float* bias_x,

@@ -123,7 +123,7 @@ def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0, 
     return hs, c
 
 
-def lstm_dilated(x, Wp, dilations, bias_p=None, hs=None, c=None, bn=0, pair=0):
+def lstm_dilated(x, Wp, dilations, bias_p=None, hs=None, c=None, bn=0, pair=0, schedule=0):
     """x: [L,N,H]; Wp: [D,4H,2H]; dilations: D ints -> (hs [D,L,N,H], c fp32 [D,max_dil*N,H])."""
     _req(x, "x")
     _req(Wp, "Wp", x.dtype)
@@ -139,11 +139,11 @@ def lstm_dilated(x, Wp, dilations, bias_p=None, hs=None, c=None, bn=0, pair=0):
     if c is None:
         c = torch.empty(D, md * N, H, dtype=torch.float32, device=x.device)
     dil = (ctypes.c_int * D)(*[int(d) for d in dilations])
-    ws = workspace(x.device)
+    ws = workspace(x.device, lib.ftb_lstm_dilated_workspace_bytes(D, L))
     with torch.cuda.device(x.device):
         check(lib.ftb_lstm_dilated_fwd(_ptr(x), _ptr(Wp), _ptr(bias_p), _ptr(hs), _ptr(c), dil, D, L, N, H,
-                                       _dtype_code(x), _tuning(bn=bn, pair=pair), _ptr(ws), ws.numel(), _stream()),
-              "ftb_lstm_dilated_fwd")
+                                       _dtype_code(x), _tuning(bn=bn, pair=pair, schedule=schedule), _ptr(ws), ws.numel(),
+                                       _stream()), "ftb_lstm_dilated_fwd")
     return hs, c
 
 

@@ -108,7 +108,10 @@ int ftb_lstm_stacked_fwd_noalloc(const void* x, const void* Wp, const float* bia
  * back.  Stands in for dilated_layer()/model() (examples/dilated_rnn/dilated_rnn.py:16-41)
  * and DilatedLstmRegion1/2 (kaleido/core/device/kernels/lstm/dilated_lstm/region{1,2}.h).
  * x: [L,N,H]; hs (out): [D,L,N,H]; c (scratch/out): fp32 [D, max_dilation*N, H].
- * `dilations` is a HOST array of D ints. */
+ * `dilations` is a HOST array of D ints.  With ftb_lstm_dilated_workspace_bytes(D, L) bytes of
+ * workspace (16-bit dtypes) the whole wavefront runs as one persistent launch; its schedule
+ * tables are copied from host memory on `stream`, so that form is not for stream capture. */
+size_t ftb_lstm_dilated_workspace_bytes(int D, int L);
 int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
                          const int* dilations, int D, int L, int N, int H, int dtype, const int* tuning,
                          void* workspace, size_t workspace_bytes, void* stream);

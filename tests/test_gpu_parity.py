@@ -196,6 +196,20 @@ def test_dilated_lstm(ops, dt, dils, L):
         _assert_16(hs, ref)
 
 
+def test_dilated_schedules_agree_bit_for_bit(ops):
+    dils = [1, 2, 4, 8]
+    x, W, U, b = dense.make_lstm_inputs(4, 24, 256, 128, 128, 6, 1.0 / 8, dtype=torch.float16, bias=True)
+    xd, Wd, Ud, bd = _dev(x, W, U, b)
+    Wp, bp = ops.lstm_pack_weights(Wd, Ud, bd)
+    ref, _ = ops.lstm_dilated(xd, Wp, dils, bp, schedule=1, pair=1)
+    ops.check_status()
+    for kw in ({"schedule": 2, "pair": 1}, {"schedule": 2, "pair": 2}, {"schedule": 1, "pair": 2}, {}):
+        hs, _ = ops.lstm_dilated(xd, Wp, dils, bp, **kw)
+        ops.check_status()
+        assert torch.equal(hs, ref), kw
+    _assert_16(ref, dense.dilated_lstm_dense(*_f32(x, W, U), dils, b.float()))
+
+
 def test_dilated_config5a_prefix(ops):
     """BASELINE config 5a shape (6 layers, dilations 1..32, H256, N256) on the first 64 steps
     (the recurrence up to step t only needs inputs up to t)."""
