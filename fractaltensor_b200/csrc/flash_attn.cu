@@ -57,9 +57,11 @@ __device__ __forceinline__ uint8_t* sw128_chunk_ptr(uint8_t* tile, int row, int 
 
 #ifdef FTB_TRACE
 __device__ unsigned long long g_fa_trace[2][32][8];
-#define FA_STAMP(tt, jj, k) if (blockIdx.x == 300 && lane == 0 && q == 0) g_fa_trace[tt][jj][k] = globaltimer_ns()
+#define FA_STAMP(tt, jj, k) if (blockIdx.x == 300 && lane == 0 && q == 0) g_fa_trace[tt][jj][k] = clock64()
+#define FA_STAMP_MMA(tt, jj, k) if (blockIdx.x == 300) g_fa_trace[tt][jj][k] = clock64()
 #else
 #define FA_STAMP(tt, jj, k)
+#define FA_STAMP_MMA(tt, jj, k)
 #endif
 
 template <typename T>
@@ -200,10 +202,12 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             break;
           }
           tc_fence_after();
+          FA_STAMP_MMA(t, j, 5);
           issue_pv(t, j);
           // The tensor pipe runs MMAs in issue order: S_t(j+1) overwrites S_t / P_t only after
           // PV_t(j) has read P_t.
           if (more) issue_s(t, j + 1);
+          FA_STAMP_MMA(t, j, 6);
         }
         if (!ok) break;
         umma_commit(&kv_empty[(2 * j + 1) % kKVSlots]);
@@ -277,8 +281,8 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       FA_STAMP(t, j, 2);
       // P_t(j) = 2^(scale*S - m) as 16-bit pairs over the first 64 columns of S_t (S_t(j) is in
       // registers now; the MMA that overwrites these columns next, S_t(j+1), is issued after
-      // PV_t(j)); row sums for l.  (Packed fp16 exponentials, two per MUFU op, were measured
-      // and are no faster: the softmax is not MUFU-bound here.)
+      // PV_t(j)); row sums for l.  (Packed fp16 exponentials, two per MUFU op, and a cubic
+      // 2^x on the FMA pipes for every other element were both measured and are no faster.)
       {
         float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -288,6 +292,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           s[i] = __float_as_uint(p);
         }
         l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
+        FA_STAMP(t, j, 4);
         uint32_t pk[32];
 #pragma unroll
         for (int hlf = 0; hlf < 2; ++hlf) {
