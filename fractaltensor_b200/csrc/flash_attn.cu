@@ -241,15 +241,17 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       tmem_ld_wait();
       FA_STAMP(t, j, 1);
 
-      // Row maximum with eight independent chains (two softmax warps per scheduler leave
-      // little latency hiding; a single 128-long dependent chain would dominate).
+      // Row maximum: eight independent chains of three-input maxima (two softmax warps per
+      // scheduler leave little latency hiding; one 128-long dependent chain would dominate).
       float mx8[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mx8[i] = __uint_as_float(s[i]);
+      for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(__uint_as_float(s[i]), __uint_as_float(s[8 + i]));
 #pragma unroll
-      for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[i]));
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      for (int i = 16; i < 128; i += 16) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mx8[k] = fmax3(mx8[k], __uint_as_float(s[i + k]), __uint_as_float(s[i + 8 + k]));
+      }
+      const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       const float m_new = mx * scale_log2;
       if (j == 0) {
         m_used = m_new;

@@ -401,6 +401,13 @@ __device__ __forceinline__ float exp2_fast(float x) {
   return y;
 }
 
+// Three-input maximum (one instruction on sm_100).
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <typename T>
 struct Fmt;
 template <>
