@@ -28,7 +28,8 @@ METRIC = "lstm_samples_steps_per_s_h1024_d16"
 UNIT = "samples*steps/s"
 FLOPS_PER_SAMPLE_STEP = CFG["D"] * 2 * 4 * CFG["H"] * (CFG["I"] + CFG["H"])  # all layers
 # DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
-# profiles/cell_gemm_lstm_config4.md (None until captured).
+# profiles/lstm_static_config4.md.  None: the capture rules only allow a small case there and its
+# traffic does not scale in proportion to a full launch.
 TRAFFIC_BYTES_PER_LAUNCH = None
 
 
