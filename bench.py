@@ -27,10 +27,10 @@ CFG = dict(D=16, L=100, N=256, I=1024, H=1024, seed=3, w_bound=1.0 / 32)
 METRIC = "lstm_samples_steps_per_s_h1024_d16"
 UNIT = "samples*steps/s"
 FLOPS_PER_SAMPLE_STEP = CFG["D"] * 2 * 4 * CFG["H"] * (CFG["I"] + CFG["H"])  # all layers
-# DRAM bytes per launch of the dominant kernel from the ncu capture summarised in
-# profiles/lstm_static_config4.md.  None: the capture rules only allow a small case there and its
-# traffic does not scale in proportion to a full launch.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes (read + write) of one launch of the dominant kernel at this exact workload, from the
+# one-pass ncu capture summarised in profiles/lstm_static_config4.md (775.7 MB read + 832.0 MB
+# written; compulsory: 268 MB weights + 52 MB x read, 839 MB hidden states written).
+TRAFFIC_BYTES_PER_LAUNCH = 1607.7e6
 
 
 def peaks():
