@@ -602,6 +602,12 @@ int launch_one(const CUtensorMap* maps, const CUtensorMap& mapW, const CUtensorM
     const char* e = getenv("FTB_NO_COOPERATIVE");
     return e != nullptr && e[0] == '1';
   }();
+  // FTB_REFUSE_COOPERATIVE=1 makes this function answer as if the driver had refused the
+  // cooperative launch (host-side failure injection for the schedule fallback's tests).
+  {
+    const char* e = getenv("FTB_REFUSE_COOPERATIVE");
+    if (PERSIST && e != nullptr && e[0] == '1') return FTB_ERR_LAUNCH;
+  }
   if (PERSIST && !no_coop) {
     // Cooperative launch: every CTA is resident, so a CTA that waits on another
     // CTA's counter always makes progress.

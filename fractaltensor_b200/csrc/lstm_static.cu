@@ -399,6 +399,12 @@ int launch(const CUtensorMap& mX, const CUtensorMap& mH, const CUtensorMap& mW, 
     const char* e = getenv("FTB_NO_COOPERATIVE");
     return e != nullptr && e[0] == '1';
   }();
+  // FTB_REFUSE_COOPERATIVE=1 makes this function answer as if the driver had refused the
+  // cooperative launch (host-side failure injection for the schedule fallback's tests).
+  {
+    const char* e = getenv("FTB_REFUSE_COOPERATIVE");
+    if (e != nullptr && e[0] == '1') return FTB_ERR_LAUNCH;
+  }
   if (!no_coop) {
     attrs[na].id = cudaLaunchAttributeCooperative;
     attrs[na].val.cooperative = 1;

@@ -443,8 +443,13 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
 #ifdef FTB_TRACE
       trace = reinterpret_cast<unsigned long long*>(ws + lay.trace);
 #endif
-      return launch_lstm_static(dtype, x, Wp, bias_p, hs, c, D, L, N, I, H, G,
-                                reinterpret_cast<int*>(ws + lay.done), status, trace, stream);
+      rc = launch_lstm_static(dtype, x, Wp, bias_p, hs, c, D, L, N, I, H, G,
+                              reinterpret_cast<int*>(ws + lay.done), status, trace, stream);
+      // A cooperative launch can be refused (device shared through MPS, SMs reserved, ...).
+      // With an explicit schedule that is the caller's error to see; the automatic choice
+      // falls back to one launch per level, which needs no co-residency.
+      if (rc != FTB_ERR_LAUNCH || schedule != 0) return rc;
+      goto level_schedule;
     }
     StackedPlanArgs pa;
     pa.D = D; pa.L = L; pa.N = N; pa.I = I; pa.H = H; pa.G = G; pa.es = static_cast<int>(es);
@@ -474,10 +479,12 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
 #ifdef FTB_TRACE
     pv.trace = reinterpret_cast<unsigned long long*>(ws + lay.trace);
 #endif
-    return launch_cell_gemm_persistent(dtype, EPI_LSTM, cl.bn, cl.pair, cl.maps, cl.mapW, cl.mapC, header, pv,
-                                       status, cl.sm_count, stream);
+    rc = launch_cell_gemm_persistent(dtype, EPI_LSTM, cl.bn, cl.pair, cl.maps, cl.mapW, cl.mapC, header, pv,
+                                     status, cl.sm_count, stream);
+    if (rc != FTB_ERR_LAUNCH || schedule != 0) return rc;
   }
 
+level_schedule:
   std::vector<CellItem> items;
   for (int g0 = 0; g0 < D; g0 += G) {
     const int Lg = std::min(G, D - g0);

@@ -147,6 +147,29 @@ def test_stacked_lstm_schedules_agree_bit_for_bit(ops, shape, kw):
     _assert_16(h, rhs)
 
 
+def test_stacked_lstm_falls_back_when_cooperative_launch_is_refused(ops, monkeypatch):
+    """The automatic schedule must survive a refused cooperative launch (host-side injection: the
+    launcher answers FTB_ERR_LAUNCH without touching the device) by running one launch per level;
+    an explicitly requested cooperative schedule reports the refusal instead."""
+    from fractaltensor_b200 import _lib
+    D, L, N, H = 4, 6, 256, 256
+    x, W, U, b = dense.make_lstm_inputs(D, L, N, H, H, 3, 1.0 / 8, dtype=torch.bfloat16, bias=True)
+    ref_h, ref_c = _run_stacked(ops, x, W, U, b)
+    n0 = _lib.lib.ftb_launch_count()
+    _run_stacked(ops, x, W, U, b)
+    coop_launches = _lib.lib.ftb_launch_count() - n0
+    monkeypatch.setenv("FTB_REFUSE_COOPERATIVE", "1")
+    n0 = _lib.lib.ftb_launch_count()
+    h, c = _run_stacked(ops, x, W, U, b)
+    level_launches = _lib.lib.ftb_launch_count() - n0
+    assert torch.equal(h, ref_h) and torch.equal(c, ref_c)
+    # both runs pack the weights; the level schedule trades one launch for one per level
+    assert level_launches - coop_launches >= D + L - 2
+    for sched in (2, 3):
+        with pytest.raises(RuntimeError):
+            _run_stacked(ops, x, W, U, b, schedule=sched)
+
+
 def test_stacked_lstm_config4_properties(ops):
     """BASELINE config 4 at full size (D16 H1024 N256 L100 bf16).  The oracle needs minutes
     there, so: (1) the first layers/steps depend only on earlier layers/steps and are checked
