@@ -66,6 +66,42 @@ def stacked_lstm_dense(x, W, U, b=None, round_to=None):
     return hs, cs
 
 
+def stacked_lstm_varlen_dense(x, active_rows, W, U, b=None, round_to=None):
+    """Stacked LSTM over a length-sorted, time-major batch of variable-length sequences.
+
+    Follows batched_cell / lstm_layer / stacked_lstm of the time-major program
+    (examples/stacked_rnn/stacked_rnn.py:40-79): step t holds only the active_rows[t]
+    sequences that are still running (the batch is sorted by decreasing length, so
+    these are rows 0..active_rows[t]-1, examples/utils/data_utils.py:42-66) and carries
+    ``hs_prev[0:xs.length]``, ``cs_prev[0:xs.length]`` into the cell.
+    x: [T,I] with T = sum(active_rows), the rows of step t stored after those of step
+    t-1 (the flat FractalTensor buffer); W: [D,4,I,H]; U: [D,4,H,H]; b: [D,4,H] or None.
+    Returns hs [D,T,H] in the same packed order and c [D,N,H], N = active_rows[0]: the
+    cell state each sequence had after its own last step.
+    """
+    active_rows = [int(n) for n in active_rows]
+    D = W.shape[0]
+    H = U.shape[-1]
+    T, N = sum(active_rows), active_rows[0]
+    off = [0]
+    for n in active_rows:
+        off.append(off[-1] + n)
+    hs = x.new_zeros(D, T, H)
+    cs = x.new_zeros(D, N, H)
+    inp = x
+    for d in range(D):
+        h = x.new_zeros(N, H)
+        c = x.new_zeros(N, H)
+        for t, n in enumerate(active_rows):
+            hn, cn = lstm_cell_dense(inp[off[t]:off[t + 1]], h[:n], c[:n], W[d], U[d], None if b is None else b[d])
+            hn = _round(hn, round_to)
+            h, c = hn, cn
+            hs[d, off[t]:off[t + 1]] = hn
+            cs[d, :n] = cn
+        inp = hs[d]
+    return hs, cs
+
+
 def dilated_lstm_dense(x, W, U, dilations, b=None, round_to=None):
     """Stacked dilated LSTM.
 
@@ -187,6 +223,15 @@ def make_lstm_inputs(D, L, N, I, H, seed, w_bound, dtype=torch.float32, bias=Fal
     b = (torch.rand(D, 4, H, generator=g) * 2 - 1) * w_bound if bias else None
     cast = lambda t: None if t is None else t.to(dtype)
     return cast(x), cast(W), cast(U), cast(b)
+
+
+def make_active_rows(L, N, seed, min_len=1):
+    """Rows still active at each of L steps for N sequences whose lengths are drawn
+    uniformly from [min_len, L] and sorted in decreasing order (the longest has L steps)."""
+    g = _gen(seed)
+    lens = torch.randint(min_len, L + 1, (N,), generator=g)
+    lens[0] = L
+    return [int((lens > t).sum()) for t in range(L)]
 
 
 def make_grid_inputs(D, A, B, N, H, seed, w_bound, dtype=torch.float32, bias=False):

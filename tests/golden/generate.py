@@ -2,11 +2,14 @@
 eager frontend (kaleido.frontend, imported from the reference tree) on small
 seeded inputs.  Run once, where the reference tree is mounted:
 
-    python tests/golden/generate.py [/path/to/reference]
+    python tests/golden/generate.py [/path/to/reference] [fixture-name ...]
+
+(with fixture names, e.g. ``stacked_lstm_varlen_small``, only those files are rewritten).
 
 The model programs below are restated from the reference examples, calling the
 reference's real ``ops.map / scan / fold / reduce / dilated_map / zip / ...``:
   stacked   examples/stacked_rnn/stacked_lstm1.py:13-76
+  varlen    examples/stacked_rnn/stacked_rnn.py:40-79 (time-major, length-sorted ragged batch)
   dilated   examples/dilated_rnn/dilated_rnn.py:16-41
   grid      examples/grid_rnn/grid_rnn.py:42-122
   attention examples/flash_attention/flash_attention.py:14-88
@@ -81,6 +84,13 @@ def load_reference_frontend(ref_root):
 
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    only = set(sys.argv[2:])
+
+    def save(name, **arrays):
+        if only and name not in only:
+            return
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrays)
+        print("wrote", name)
     warnings.filterwarnings("ignore")
     kaleido, ops = load_reference_frontend(ref_root)
     from kaleido import FractalTensor, FractalTensorStorage, Iterative, Tensor, TensorStorage
@@ -131,16 +141,47 @@ def main():
         return x, W, U, b, top
 
     x, W, U, b, top = run_stacked(2, 5, 3, 16, 11, 0.25, True)
-    np.savez_compressed(os.path.join(HERE, "stacked_lstm_small.npz"), x=x.numpy(), W=W.numpy(), U=U.numpy(),
+    save("stacked_lstm_small", x=x.numpy(), W=W.numpy(), U=U.numpy(),
                         b=b.numpy(), top=top.numpy())
     print("stacked small", top.shape)
 
     # BASELINE config 1 at full size through the real frontend; inputs are
     # regenerated from the seed, the fixture keeps two samples of the output.
-    x, W, U, b, top = run_stacked(4, 64, 32, 256, 0, 1.0 / 16, False)
-    np.savez_compressed(os.path.join(HERE, "stacked_lstm_config1_samples.npz"), samples=np.array([0, 31]),
-                        top=top[:, [0, 31]].numpy(), seed=0)
+    if not only or "stacked_lstm_config1_samples" in only:
+        x, W, U, b, top = run_stacked(4, 64, 32, 256, 0, 1.0 / 16, False)
+        save("stacked_lstm_config1_samples", samples=np.array([0, 31]), top=top[:, [0, 31]].numpy(), seed=0)
     print("stacked config1", top.shape)
+
+    # --------------------------------------------- stacked, variable-length, time-major
+    def stacked_lstm_time_major(embs, Wss, Uss, bss, H):
+        def batched_cell(hs_prev, cs_prev, xs, ws, us, bs):
+            return ops.map(lambda x: lstm_cell(*x, ws, us, bs),
+                           ops.zip(hs_prev[0:xs.length], cs_prev[0:xs.length], xs))
+
+        def lstm_layer(xss, ws, us, bs):
+            init = ops.repeat(ops.zeros(shape=(1, H), device="cpu"), xss[0].length)
+            hss, css = ops.scan(lambda state, x: batched_cell(*state, x, ws, us, bs), xss, initializer=(init, init))
+            return hss
+
+        return ops.fold(lambda s, param: lstm_layer(s, *param), ops.zip(Wss, Uss, bss), initializer=embs)
+
+    def run_stacked_varlen(D, L, N, H, seed, w_bound):
+        active = dense.make_active_rows(L, N, seed, min_len=2)
+        T = sum(active)
+        xfull, W, U, b = dense.make_lstm_inputs(D, T, 1, H, H, seed, w_bound, bias=True)
+        x = xfull.reshape(T, H)
+        params = lambda t, shape: ft(t.reshape(D * 4, *shape), shape, [list(range(4)) for _ in range(D)])
+        Wss, Uss, bss = params(W, (H, H)), params(U, (H, H)), params(b, (1, H))
+        # reference layout: time-major FractalTensor [L][active[t]] of [1,H]
+        embs = ft(x.reshape(T, 1, H), (1, H), [list(range(n)) for n in active])
+        out = stacked_lstm_time_major(embs, Wss, Uss, bss, H)
+        assert [len(i) for i in out.indices] == active
+        return active, x, W, U, b, out.data.view(T, H).clone()
+
+    active, x, W, U, b, top = run_stacked_varlen(2, 7, 5, 16, 12, 0.25)
+    save("stacked_lstm_varlen_small", active_rows=np.array(active), x=x.numpy(), W=W.numpy(), U=U.numpy(),
+         b=b.numpy(), top=top.numpy())
+    print("stacked varlen", active, top.shape)
 
     # ---------------------------------------------------------------------- dilated
     def run_dilated(D, L, N, H, seed, w_bound):
@@ -163,7 +204,7 @@ def main():
         return x, W, U, top
 
     x, W, U, top = run_dilated(3, 11, 2, 16, 4, 0.25)
-    np.savez_compressed(os.path.join(HERE, "dilated_lstm_small.npz"), x=x.numpy(), W=W.numpy(), U=U.numpy(),
+    save("dilated_lstm_small", x=x.numpy(), W=W.numpy(), U=U.numpy(),
                         dilations=np.array([1, 2, 4]), top=top.numpy())
     print("dilated small", top.shape)
 
@@ -221,7 +262,7 @@ def main():
         return X, Y, p, hx, hy
 
     X, Y, p, hx, hy = run_grid(2, 4, 5, 8, 4, 0.3)
-    np.savez_compressed(os.path.join(HERE, "grid_rnn_small.npz"), X=X.numpy(), Y=Y.numpy(), hx_top=hx.numpy(),
+    save("grid_rnn_small", X=X.numpy(), Y=Y.numpy(), hx_top=hx.numpy(),
                         hy_top=hy.numpy(), **{k: v.numpy() for k, v in p.items()})
     print("grid small", hx.shape)
 
@@ -270,7 +311,7 @@ def main():
 
     scale = 1.0 / 32 ** 0.5
     q, k, v, o = run_attention(1, 2, 256, 32, 64, 2, scale)
-    np.savez_compressed(os.path.join(HERE, "flash_attention_small.npz"), q=q.numpy(), k=k.numpy(), v=v.numpy(),
+    save("flash_attention_small", q=q.numpy(), k=k.numpy(), v=v.numpy(),
                         o=o.numpy(), scale=scale, block=64)
     print("attention small", o.shape)
 

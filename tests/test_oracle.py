@@ -32,6 +32,35 @@ def test_stacked_lstm_config1_matches_reference_frontend(golden_dir):
     assert err <= 1e-5 * g["top"].abs().max().item(), err
 
 
+def test_stacked_lstm_varlen_matches_reference_frontend(golden_dir):
+    """Length-sorted ragged batch through the reference's time-major program."""
+    g = _load(golden_dir, "stacked_lstm_varlen_small.npz")
+    hs, _ = dense.stacked_lstm_varlen_dense(g["x"], g["active_rows"].tolist(), g["W"], g["U"], g["b"])
+    assert (hs[-1] - g["top"]).abs().max().item() <= 1e-6
+
+
+def test_stacked_lstm_varlen_equals_per_sequence_runs():
+    """Each sequence of the ragged batch sees only its own steps: running it alone, as a
+    rectangular batch of one, gives the same rows and the same final cell state."""
+    D, L, N, H = 2, 6, 4, 8
+    active = dense.make_active_rows(L, N, 5)
+    T = sum(active)
+    x, W, U, b = dense.make_lstm_inputs(D, T, 1, H, H, 5, 0.3, bias=True)
+    x = x.reshape(T, H)
+    hs, cs = dense.stacked_lstm_varlen_dense(x, active, W, U, b)
+    off = np.concatenate([[0], np.cumsum(active)])
+    for n in range(N):
+        steps = [t for t in range(L) if active[t] > n]
+        rows = [int(off[t]) + n for t in steps]
+        h1, c1 = dense.stacked_lstm_dense(x[rows][:, None], W, U, b)
+        assert torch.allclose(hs[:, rows], h1[:, :, 0], atol=1e-6)
+        assert torch.allclose(cs[:, n], c1[:, 0], atol=1e-6)
+    # equal lengths: the rectangular program
+    hs2, cs2 = dense.stacked_lstm_varlen_dense(x[:L * 2], [2] * L, W, U, b)
+    h3, c3 = dense.stacked_lstm_dense(x[:L * 2].reshape(L, 2, H), W, U, b)
+    assert torch.equal(hs2.reshape(D, L, 2, H), h3) and torch.equal(cs2, c3)
+
+
 def test_dilated_lstm_matches_reference_frontend(golden_dir):
     g = _load(golden_dir, "dilated_lstm_small.npz")
     hs = dense.dilated_lstm_dense(g["x"], g["W"], g["U"], g["dilations"].tolist())
