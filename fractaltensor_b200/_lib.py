@@ -24,6 +24,8 @@ SIGNATURES = {
     "ftb_lstm_stacked_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, ctypes.POINTER(_i), _vp, _sz, _vp]),
     "ftb_lstm_stacked_fwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, ctypes.POINTER(_i),
                                           ctypes.POINTER(_vp), _vp]),
+    "ftb_lstm_stacked_varlen_workspace_bytes": (_sz, [_i, _i]),
+    "ftb_lstm_stacked_varlen_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_i), _i, _i, _i, _i, _i, ctypes.POINTER(_i), _vp, _sz, _vp]),
     "ftb_lstm_dilated_workspace_bytes": (_sz, [_i, _i]),
     "ftb_lstm_dilated_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_i), _i, _i, _i, _i, _i, ctypes.POINTER(_i), _vp, _sz, _vp]),
     "ftb_grid_pack_weights": (_i, [_vp, _vp, _vp, _i, _i, _vp]),

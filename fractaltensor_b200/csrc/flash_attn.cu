@@ -12,12 +12,18 @@
 //
 // One CTA handles 256 query rows of one (batch, head): two 128-row query tiles
 // that ping-pong through the tensor pipe.
-//   warp 0       TMA producer: Q tiles, ring of K and V tiles
-//   warp 1       MMA issuer: S_t = Q_t K^T and O_t += P_t V, accumulators in TMEM
-//   warps 2..5   softmax warpgroup of query tile 0 (one thread per query row)
-//   warps 6..9   softmax warpgroup of query tile 1
+//   warp 0        TMA producer: Q tiles, ring of K and V tiles
+//   warp 1        MMA issuer: S_t = Q_t K^T and O_t += P_t V, accumulators in TMEM
+//   warps 2..9    softmax of query tile 0: two threads per query row, one per half
+//                 of the 128 keys of a block (warps 2..5 keys 0..63, warps 6..9 keys 64..127)
+//   warps 10..17  softmax of query tile 1, same split
+// A row's chain per key/value block (S ready -> maximum -> exponentials -> P written) is
+// serial and sits between two dependent MMAs, so its length, not the arithmetic, bounds
+// the tensor pipe; splitting the row over two threads halves it.  The two threads of a
+// row exchange their partial maximum through shared memory (one float each per block) and
+// their partial row sums once at the end.
 // P never touches shared memory: the softmax threads write it (16-bit pairs) with
-// tcgen05.st over the TMEM columns of the S tile they have just read, and the PV
+// tcgen05.st over the TMEM columns of the S values they have just read, and the PV
 // MMA takes its A operand from TMEM.  V is consumed MN-major straight from its
 // row-major tile.  Per query tile the tensor pipe sees S(j), [softmax], PV(j),
 // S(j+1), ...; the two query tiles are offset so that one is in its softmax while
@@ -32,9 +38,23 @@ namespace {
 constexpr int kHalfBytes = 128 * 128;  // 128 rows x 64 16-bit columns
 constexpr int kTileBytes = 2 * kHalfBytes;
 constexpr int kKVSlots = 5;
-constexpr int kThreads = 320;
-constexpr uint32_t kSmemBytes = (2 + kKVSlots) * kTileBytes + 1024;  // Q0, Q1 (reused as output staging), KV ring
+constexpr int kThreads = 64 + 512;
 constexpr float kRescaleThreshold = 8.0f;
+
+// Shared memory, all dynamic so that the 1024-byte alignment of the swizzled tiles costs
+// no more than the bytes actually skipped: tiles, then the small control block.
+struct Control {
+  float xchg[2][2][128];  // [query tile][key half][row]: partial row maximum / row sum
+  uint64_t q_full;
+  uint64_t kv_full[kKVSlots], kv_empty[kKVSlots];
+  uint64_t s_full[2], p_full[2], pv_done[2], o_staged[2];
+  uint64_t pair_bar[2][4];  // [query tile][TMEM lane quadrant]: the two warps that share 32 rows
+  uint32_t tmem_base;
+  int abort;
+};
+constexpr uint32_t kTilesBytes = (2 + kKVSlots) * kTileBytes;  // Q0, Q1 (reused as output staging), KV ring
+constexpr uint32_t kSmemBytes = 232448;                        // everything an SM offers one CTA
+static_assert(kTilesBytes + sizeof(Control) + 512 <= kSmemBytes, "shared memory budget");
 
 __device__ __forceinline__ void tmem_ld32p(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -57,7 +77,7 @@ __device__ __forceinline__ uint8_t* sw128_chunk_ptr(uint8_t* tile, int row, int 
 
 #ifdef FTB_TRACE
 __device__ unsigned long long g_fa_trace[2][32][8];
-#define FA_STAMP(tt, jj, k) if (blockIdx.x == 300 && lane == 0 && q == 0) g_fa_trace[tt][jj][k] = clock64()
+#define FA_STAMP(tt, jj, k) if (blockIdx.x == 300 && lane == 0 && q == 0 && h == 0) g_fa_trace[tt][jj][k] = clock64()
 #define FA_STAMP_MMA(tt, jj, k) if (blockIdx.x == 300) g_fa_trace[tt][jj][k] = clock64()
 #else
 #define FA_STAMP(tt, jj, k)
@@ -70,19 +90,22 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                   const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, int S,
                   float scale_log2, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full;
-  __shared__ uint64_t kv_full[kKVSlots], kv_empty[kKVSlots];
-  __shared__ uint64_t s_full[2], p_full[2], pv_done[2], o_staged[2];
-  __shared__ uint32_t tmem_base_s;
-  __shared__ int s_abort;
 
   if (*reinterpret_cast<volatile int*>(status) != 0) return;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
+  if (pad + kTilesBytes + sizeof(Control) > kSmemBytes) {
+    // The dynamic segment starts later than this layout allows for: report, do not run.
+    if (threadIdx.x == 0) atomicCAS(status, 0, FTB_ERR_ALIGN);
+    return;
+  }
+  uint8_t* smem = smem_raw + pad;
   uint8_t* sQ = smem;                      // 2 tiles
   uint8_t* sKV = sQ + 2 * kTileBytes;      // ring
+  Control& ctl = *reinterpret_cast<Control*>(smem + kTilesBytes);
+  volatile int* s_abort = &ctl.abort;
 
   const int pairs = S / 256;
   const int bh = blockIdx.x / pairs;
@@ -96,48 +119,51 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     prefetch_tmap(&mapK);
     prefetch_tmap(&mapV);
     prefetch_tmap(&mapO);
-    mbar_init(&q_full, 1);
+    mbar_init(&ctl.q_full, 1);
     for (int i = 0; i < kKVSlots; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&ctl.kv_full[i], 1);
+      mbar_init(&ctl.kv_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 4);
-      mbar_init(&pv_done[i], 1);
-      mbar_init(&o_staged[i], 4);
+      mbar_init(&ctl.s_full[i], 1);
+      mbar_init(&ctl.p_full[i], 8);
+      mbar_init(&ctl.pv_done[i], 1);
+      mbar_init(&ctl.o_staged[i], 8);
+      for (int k = 0; k < 4; ++k) mbar_init(&ctl.pair_bar[i][k], 2);
     }
-    s_abort = 0;
+    ctl.abort = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(&tmem_base_s, 512);
+    tmem_alloc(&ctl.tmem_base, 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = tmem_base_s;
-  // TMEM columns: S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512); P_t overlays S_t's first 64.
+  const uint32_t tmem_base = ctl.tmem_base;
+  // TMEM columns: S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512).  P_t (16-bit pairs)
+  // overlays S_t: keys 0..63 in columns [0,32), keys 64..127 in columns [64,96), i.e. each
+  // half of the row over the S columns its own thread has read.
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(&q_full, 2 * kTileBytes);
+      mbar_arrive_expect_tx(&ctl.q_full, 2 * kTileBytes);
       for (int t = 0; t < 2; ++t) {
-        tma_load_2d(sQ + t * kTileBytes, &mapQ, &q_full, 0, q_row0 + t * 128);
-        tma_load_2d(sQ + t * kTileBytes + kHalfBytes, &mapQ, &q_full, 64, q_row0 + t * 128);
+        tma_load_2d(sQ + t * kTileBytes, &mapQ, &ctl.q_full, 0, q_row0 + t * 128);
+        tma_load_2d(sQ + t * kTileBytes + kHalfBytes, &mapQ, &ctl.q_full, 64, q_row0 + t * 128);
       }
       int slot = 0;
       uint32_t phase = 0;
       for (int n = 0; n < 2 * n_kv; ++n) {  // K0, V0, K1, V1, ...
         const int j = n >> 1;
         const CUtensorMap* m = (n & 1) ? &mapV : &mapK;
-        if (!mbar_wait(&kv_empty[slot], phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT)) break;
+        if (!mbar_wait(&ctl.kv_empty[slot], phase ^ 1u, s_abort, status, FTB_ERR_TIMEOUT_SLOT)) break;
         uint8_t* dst = sKV + slot * kTileBytes;
-        mbar_arrive_expect_tx(&kv_full[slot], kTileBytes);
-        tma_load_2d(dst, m, &kv_full[slot], 0, row_base + j * 128);
-        tma_load_2d(dst + kHalfBytes, m, &kv_full[slot], 64, row_base + j * 128);
+        mbar_arrive_expect_tx(&ctl.kv_full[slot], kTileBytes);
+        tma_load_2d(dst, m, &ctl.kv_full[slot], 0, row_base + j * 128);
+        tma_load_2d(dst + kHalfBytes, m, &ctl.kv_full[slot], 64, row_base + j * 128);
         if (++slot == kKVSlots) {
           slot = 0;
           phase ^= 1u;
@@ -151,11 +177,11 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       constexpr uint32_t idesc_pv = make_idesc_f16(128, 128, Fmt<T>::kind, 0, 1);  // V is MN-major
       const uint32_t aQ = smem_u32(sQ), aKV = smem_u32(sKV);
       uint32_t full_phase[kKVSlots] = {};
-      bool ok = mbar_wait(&q_full, 0, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
+      bool ok = mbar_wait(&ctl.q_full, 0, s_abort, status, FTB_ERR_TIMEOUT_TMA);
 
       auto wait_slot = [&](int n) -> bool {  // n-th tile of the K0, V0, K1, V1, ... stream
         const int slot = n % kKVSlots;
-        if (!mbar_wait(&kv_full[slot], full_phase[slot], &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
+        if (!mbar_wait(&ctl.kv_full[slot], full_phase[slot], s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
         full_phase[slot] ^= 1u;
         tc_fence_after();
         return true;
@@ -169,27 +195,25 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           umma_ss(tmem_base + t * 128, make_sdesc_sw128(aQ + t * kTileBytes + off, 16, 1024),
                   make_sdesc_sw128(aK + off, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[t]);
+        umma_commit(&ctl.s_full[t]);
       };
-      // O_t += P_t(j) . V_j: A = P_t from TMEM (16 keys = 8 packed columns per step); B = V,
-      // MN-major: 16 keys = two 8-row groups (1024 B apart), the two 64-column halves of d are
-      // 16 KB apart.
+      // O_t += P_t(j) . V_j: A = P_t from TMEM (16 keys = 8 packed columns per step; the two
+      // key halves start 64 columns apart); B = V, MN-major: 16 keys = two 8-row groups
+      // (1024 B apart), the two 64-column halves of d are 16 KB apart.
       auto issue_pv = [&](int t, int j) {
         const uint32_t aV = aKV + ((2 * j + 1) % kKVSlots) * kTileBytes;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
+          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + (k >> 2) * 64 + (k & 3) * 8,
                   make_sdesc_sw128(aV + k * 2048, kHalfBytes, 1024), idesc_pv, (j | k) != 0 ? 1u : 0u);
-        umma_commit(&pv_done[t]);
+        umma_commit(&ctl.pv_done[t]);
       };
 
-      // (Running tile 1 half a step behind tile 0, so that the two softmaxes alternate on the
-      // special-function units, was measured and is slower than this per-block interleave.)
       if (ok) ok = wait_slot(0);
       if (ok) {
         issue_s(0, 0);
         issue_s(1, 0);
-        umma_commit(&kv_empty[0]);
+        umma_commit(&ctl.kv_empty[0]);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
         const bool more = j + 1 < n_kv;
@@ -197,7 +221,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         if (more && !wait_slot(2 * j + 2)) break;    // K_{j+1}
         for (int t = 0; t < 2 && ok; ++t) {
           // P_t(j) is in TMEM (and the softmax is done with S_t(j)).
-          if (!mbar_wait(&p_full[t], j & 1, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) {
+          if (!mbar_wait(&ctl.p_full[t], j & 1, s_abort, status, FTB_ERR_TIMEOUT_EPI)) {
             ok = false;
             break;
           }
@@ -210,56 +234,70 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           FA_STAMP_MMA(t, j, 6);
         }
         if (!ok) break;
-        umma_commit(&kv_empty[(2 * j + 1) % kKVSlots]);
-        if (more) umma_commit(&kv_empty[(2 * j + 2) % kKVSlots]);
+        umma_commit(&ctl.kv_empty[(2 * j + 1) % kKVSlots]);
+        if (more) umma_commit(&ctl.kv_empty[(2 * j + 2) % kKVSlots]);
       }
     }
   } else {
-    // ------------------------------------------------- softmax warpgroups (t = 0, 1)
-    const int t = (warp - 2) >> 2;
+    // ----------------------------------- softmax: query tile t, key half h, lane quadrant q
+    const int t = (warp - 2) >> 3;
+    const int h = ((warp - 2) >> 2) & 1;
     const int q = warp & 3;  // TMEM lane quadrant of this warp
     const int row = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    const uint32_t s_addr = lane_addr + t * 128;
-    const uint32_t o_addr = lane_addr + 256 + t * 128;
+    const uint32_t s_addr = lane_addr + t * 128 + h * 64;        // this thread's 64 scores; P over the first 32
+    const uint32_t o_addr = lane_addr + 256 + t * 128 + h * 64;  // its 64 output columns (rescale, final pass)
     uint8_t* my_stage = sQ + t * kTileBytes;  // output staging: Q_t is dead once the last S MMA is done
+    float* my_x = &ctl.xchg[t][h][row];
+    const float* peer_x = &ctl.xchg[t][h ^ 1][row];
+    uint64_t* pair = &ctl.pair_bar[t][q];
     float m_used = 0.f, l = 0.f;
     bool ok = true;
 
     for (int j = 0; j < n_kv && ok; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&ctl.s_full[t], j & 1, s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
         ok = false;
         break;
       }
       tc_fence_after();
       FA_STAMP(t, j, 0);
-      uint32_t s[128];
+      uint32_t s[64];
       tmem_ld32p(s_addr + 0, s + 0);
       tmem_ld32p(s_addr + 32, s + 32);
-      tmem_ld32p(s_addr + 64, s + 64);
-      tmem_ld32p(s_addr + 96, s + 96);
       tmem_ld_wait();
       FA_STAMP(t, j, 1);
 
-      // Row maximum: eight independent chains of three-input maxima (two softmax warps per
-      // scheduler leave little latency hiding; one 128-long dependent chain would dominate).
+      // Maximum of this half of the row: eight independent chains of three-input maxima.
       float mx8[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(__uint_as_float(s[i]), __uint_as_float(s[8 + i]));
 #pragma unroll
-      for (int i = 16; i < 128; i += 16) {
+      for (int i = 16; i < 64; i += 16) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) mx8[k] = fmax3(mx8[k], __uint_as_float(s[i + k]), __uint_as_float(s[i + 8 + k]));
       }
-      const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmaxf(fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      // Row maximum = the larger of the two halves.  The slot written here was last read by the
+      // other thread before its arrival on p_full of the previous block, which the MMA warp waited
+      // for before it issued the S this block started from: no second buffer is needed.
+      *my_x = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair);
+      if (!__all_sync(0xffffffffu, mbar_wait(pair, j & 1, s_abort, status, FTB_ERR_TIMEOUT_EPI))) {
+        ok = false;
+        break;
+      }
+      mx = fmaxf(mx, *peer_x);
       const float m_new = mx * scale_log2;
       if (j == 0) {
         m_used = m_new;
       } else {
+        // Both threads of a row see the same m_new and m_used, so both take the same branch.
         const bool need = (m_new - m_used) > kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {
           // O_t must be at rest: the PV MMA of the previous block has to be done.
-          if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[t], (j - 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
+          if (!__all_sync(0xffffffffu,
+                          mbar_wait(&ctl.pv_done[t], (j - 1) & 1, s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
             ok = false;
             break;
           }
@@ -269,54 +307,62 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           l *= alpha;
 #pragma unroll 1
           for (int ch = 0; ch < 4; ++ch) {
-            uint32_t o[32];
-            tmem_ld32(o_addr + ch * 32, o);
+            uint32_t o[16];
+            tmem_ld16(o_addr + ch * 16, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(o_addr + ch * 32, o);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st16(o_addr + ch * 16, o);
           }
           tmem_st_wait();
         }
       }
 
       FA_STAMP(t, j, 2);
-      // P_t(j) = 2^(scale*S - m) as 16-bit pairs over the first 64 columns of S_t (S_t(j) is in
-      // registers now; the MMA that overwrites these columns next, S_t(j+1), is issued after
-      // PV_t(j)); row sums for l.  (Packed fp16 exponentials, two per MUFU op, and a cubic
+      // P_t(j) = 2^(scale*S - m) as 16-bit pairs over the first 32 of this thread's 64 S columns
+      // (they are in registers now; the MMA that overwrites them next, S_t(j+1), is issued after
+      // PV_t(j)); partial row sum for l.  (Packed fp16 exponentials, two per MUFU op, and a cubic
       // 2^x on the FMA pipes for every other element were both measured and are no faster.)
       {
         float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          const float p = exp2_fast(fmaf(__uint_as_float(s[i]), scale_log2, -m_used));
-          sum8[i & 7] += p;
-          s[i] = __float_as_uint(p);
+        for (int part = 0; part < 2; ++part) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float p0 = exp2_fast(fmaf(__uint_as_float(s[32 * part + 2 * c]), scale_log2, -m_used));
+            const float p1 = exp2_fast(fmaf(__uint_as_float(s[32 * part + 2 * c + 1]), scale_log2, -m_used));
+            sum8[(2 * c) & 7] += p0;
+            sum8[(2 * c + 1) & 7] += p1;
+            pk[c] = Fmt<T>::pack2(p0, p1);
+          }
+          tmem_st16(s_addr + 16 * part, pk);
         }
         l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
         FA_STAMP(t, j, 4);
-        uint32_t pk[32];
-#pragma unroll
-        for (int hlf = 0; hlf < 2; ++hlf) {
-#pragma unroll
-          for (int c = 0; c < 32; ++c)
-            pk[c] = Fmt<T>::pack2(__uint_as_float(s[64 * hlf + 2 * c]), __uint_as_float(s[64 * hlf + 2 * c + 1]));
-          tmem_st32(s_addr + 32 * hlf, pk);
-        }
         tmem_st_wait();
       }
       FA_STAMP(t, j, 3);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[t]);
+      if (lane == 0) mbar_arrive(&ctl.p_full[t]);
     }
 
+    // Row sum = the two halves' sums (same exchange, one more phase of the pair barrier).
+    if (ok) {
+      *my_x = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair);
+      ok = __all_sync(0xffffffffu, mbar_wait(pair, n_kv & 1, s_abort, status, FTB_ERR_TIMEOUT_EPI));
+      if (ok) l += *peer_x;
+    }
     // Final: O_t / l -> 16-bit -> staging (the Q tile, dead once the last PV is done) -> TMA store.
-    if (ok && __all_sync(0xffffffffu, mbar_wait(&pv_done[t], (n_kv - 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
+    if (ok && __all_sync(0xffffffffu,
+                         mbar_wait(&ctl.pv_done[t], (n_kv - 1) & 1, s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
       tc_fence_after();
       const float inv_l = 1.f / l;
 #pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < 2; ++ch) {
         uint32_t o[32];
         tmem_ld32(o_addr + ch * 32, o);
         tmem_ld_wait();
@@ -327,16 +373,16 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           u.y = Fmt<T>::pack2(__uint_as_float(o[8 * c + 2]) * inv_l, __uint_as_float(o[8 * c + 3]) * inv_l);
           u.z = Fmt<T>::pack2(__uint_as_float(o[8 * c + 4]) * inv_l, __uint_as_float(o[8 * c + 5]) * inv_l);
           u.w = Fmt<T>::pack2(__uint_as_float(o[8 * c + 6]) * inv_l, __uint_as_float(o[8 * c + 7]) * inv_l);
-          *reinterpret_cast<uint4*>(sw128_chunk_ptr(my_stage, row, ch * 4 + c)) = u;
+          *reinterpret_cast<uint4*>(sw128_chunk_ptr(my_stage, row, (h * 2 + ch) * 4 + c)) = u;
         }
       }
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&o_staged[t]);
-      // One thread per warpgroup stores the tile once all four warps have staged their rows.
-      if (lane == 0 && (warp == 2 || warp == 6) &&
-          mbar_wait(&o_staged[t], 0, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) {
+      if (lane == 0) mbar_arrive(&ctl.o_staged[t]);
+      // One thread per query tile stores it once all eight warps have staged their part.
+      if (lane == 0 && h == 0 && q == 2 &&
+          mbar_wait(&ctl.o_staged[t], 0, s_abort, status, FTB_ERR_TIMEOUT_EPI)) {
         tma_store_2d(&mapO, my_stage, 0, q_row0 + t * 128);
         tma_store_2d(&mapO, my_stage + kHalfBytes, 64, q_row0 + t * 128);
         tma_store_commit();
@@ -348,7 +394,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
-    if (s_abort) {
+    if (ctl.abort) {
       const uint64_t t0 = globaltimer_ns();
       while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     }

@@ -517,6 +517,146 @@ level_schedule:
   return FTB_OK;
 }
 
+int ftb_lstm_stacked_varlen_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
+                                const int* active_rows, int D, int L, int I, int H, int dtype, const int* tuning,
+                                void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const Tuning tune(tuning);
+  if (!x || !Wp || !hs || !c || !active_rows || D <= 0 || L <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
+  if (H <= 0 || I <= 0 || H % 64 != 0 || I % 64 != 0) return FTB_ERR_ARG;
+  if (D > 1 && I != H) return FTB_ERR_ARG;
+  // Row offset of every step in the packed buffers; the batch must be sorted by decreasing length.
+  std::vector<int64_t> off(L + 1, 0);
+  for (int t = 0; t < L; ++t) {
+    if (active_rows[t] <= 0 || (t > 0 && active_rows[t] > active_rows[t - 1])) return FTB_ERR_ARG;
+    off[t + 1] = off[t] + active_rows[t];
+  }
+  const int64_t T = off[L];
+  const int N = active_rows[0];
+  if (static_cast<int64_t>(D) * T > 0x7fffffffLL) return FTB_ERR_ARG;
+  int* status = nullptr;
+  int rc = begin_call(workspace, workspace_bytes, stream, &status);
+  if (rc) return rc;
+
+  const int K = I + H;
+  const size_t es = dtype_size(dtype);
+  CellLauncher cl;
+  cl.dtype = dtype;
+  cl.epi = EPI_LSTM;
+  cl.n_cols = 4 * H;
+  cl.ld_out = H;
+  cl.ld_c = H;
+  cl.status = status;
+  cl.stream = stream;
+  cl.sm_count = current_sm_count();
+  if (dtype == FTB_F32) {
+    cl.act[0] = static_cast<const float*>(x);
+    cl.ld_act[0] = I;
+    cl.act[1] = cl.act[2] = static_cast<const float*>(hs);
+    cl.ld_act[1] = cl.ld_act[2] = H;
+    cl.w = static_cast<const float*>(Wp);
+    cl.ldw = K;
+  } else {
+    cl.bn = pick_bn(4 * H, tune.bn);
+    if (cl.bn == 0) return FTB_ERR_ARG;
+    cl.pair = tune.use_pair(N);
+    rc = make_tmap_2d(&cl.maps[0], x, dtype, static_cast<uint64_t>(T), I, I, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.maps[1], hs, dtype, static_cast<uint64_t>(D) * T, H, H, 128, 64);
+    if (rc) return rc;
+    cl.maps[2] = cl.maps[1];
+    rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.w_box_rows(), 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.mapC, c, FTB_F32, static_cast<uint64_t>(D) * N, H, H, 128, 32);
+    if (rc) return rc;
+  }
+
+  // Layers run in groups whose packed weights stay in L2, as in the rectangular entry point.
+  int G = tune.layers_per_group;
+  if (G <= 0) {
+    int dev = 0, l2 = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev);
+    const double per_layer = 4.0 * H * K * es;
+    G = static_cast<int>((0.55 * l2) / per_layer);
+    G = std::max(1, G);
+  }
+  G = std::min(G, D);
+
+  // Cell (l, t) holds the active_rows[t] sequences still running: it reads the layer below (or
+  // x) at step t and the first active_rows[t] rows of its own layer's step t-1.
+  auto make_item = [&](int l, int t) {
+    CellItem it = blank_item();
+    if (l == 0)
+      add_seg(it, 0, off[t], I, 0);
+    else
+      add_seg(it, 1, static_cast<int64_t>(l - 1) * T + off[t], H, 0);
+    if (t > 0) add_seg(it, 2, static_cast<int64_t>(l) * T + off[t - 1], H, I);
+    it.w_row0 = l * 4 * H;
+    it.rows = active_rows[t];
+    it.c_zero = (t == 0);
+    it.out = static_cast<char*>(hs) + (static_cast<size_t>(l) * T + off[t]) * H * es;
+    it.out_row0 = static_cast<int32_t>(static_cast<int64_t>(l) * T + off[t]);
+    it.out_map = 1;
+    it.c = c + static_cast<size_t>(l) * N * H;
+    it.c_row0 = l * N;
+    it.bias = bias_p ? bias_p + static_cast<size_t>(l) * 4 * H : nullptr;
+    return it;
+  };
+
+  const int n_cells = D * L;
+  const PlanLayout lay = plan_layout(n_cells, 0);
+  bool persistent = dtype != FTB_F32 && tune.schedule != 1 && (tune.schedule >= 2 || workspace_bytes >= lay.total);
+  if (persistent) {
+    if (workspace_bytes < lay.total) return FTB_ERR_WORKSPACE;
+    // Launch order: group by group, level by level (level = layer-in-group + step), so every
+    // cell comes after the two it reads.
+    std::vector<CellItem> order;
+    order.reserve(n_cells);
+    std::vector<int> index_of(n_cells, -1);
+    for (int g0 = 0; g0 < D; g0 += G) {
+      const int Lg = std::min(G, D - g0);
+      for (int m = 0; m < Lg + L - 1; ++m)
+        for (int l = g0; l < g0 + Lg; ++l) {
+          const int t = m - (l - g0);
+          if (t < 0 || t >= L) continue;
+          index_of[l * L + t] = static_cast<int>(order.size());
+          order.push_back(make_item(l, t));
+        }
+    }
+    std::vector<int32_t> deps(static_cast<size_t>(n_cells) * kMaxSeg * 2, -1);
+    for (int l = 0; l < D; ++l)
+      for (int t = 0; t < L; ++t) {
+        const int me = index_of[l * L + t];
+        if (l > 0) deps[(me * kMaxSeg + 0) * 2 + 0] = deps[(me * kMaxSeg + 0) * 2 + 1] = index_of[(l - 1) * L + t];
+        if (t > 0) deps[(me * kMaxSeg + 1) * 2 + 0] = deps[(me * kMaxSeg + 1) * 2 + 1] = index_of[l * L + t - 1];
+      }
+    rc = run_persistent(cl, order, deps, static_cast<char*>(workspace), lay);
+    if (rc != FTB_ERR_LAUNCH || tune.schedule != 0) return rc;
+  }
+
+  std::vector<CellItem> items;
+  for (int g0 = 0; g0 < D; g0 += G) {
+    const int Lg = std::min(G, D - g0);
+    for (int m = 0; m < Lg + L - 1; ++m) {
+      items.clear();
+      for (int l = g0; l < g0 + Lg; ++l) {
+        const int t = m - (l - g0);
+        if (t < 0 || t >= L) continue;
+        items.push_back(make_item(l, t));
+      }
+      rc = cl.run(items);
+      if (rc) return rc;
+    }
+  }
+  return FTB_OK;
+}
+
+size_t ftb_lstm_stacked_varlen_workspace_bytes(int D, int L) {
+  if (D <= 0 || L <= 0) return kWorkspaceBytes;
+  return plan_layout(D * L, 0).total;
+}
+
 int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
                          const int* dilations, int D, int L, int N, int H, int dtype, const int* tuning,
                          void* workspace, size_t workspace_bytes, void* stream_) {

@@ -4,6 +4,7 @@ The reference expresses the hot path as nested ``ops.fold / scan / map`` program
 over ``FractalTensor`` values (flat ``.data`` buffer plus nested ``.indices``):
 
     stacked_lstm(embs, Wss, Uss, bss)                  examples/stacked_rnn/stacked_lstm1.py:66-76
+    stacked_lstm_time_major(embs, Wss, Uss, bss)       examples/stacked_rnn/stacked_rnn.py:69-79
     dilated_lstm(embs, Wss, Uss, bss)                  examples/dilated_rnn/dilated_rnn.py:16-41 (the fold in model())
     stacked_grid_rnns(src_encs, trg_encs, params)      examples/grid_rnn/grid_rnn.py:111-122
     flash_attention(qsss, ksss, vsss)                  examples/flash_attention/flash_attention.py:75-88
@@ -13,8 +14,10 @@ but run the whole nest as one fused wavefront on the GPU.  Arguments may be the
 reference's own ``kaleido.FractalTensor`` objects (only ``.data``, ``.indices``
 and ``.element_shape`` are read) or the light ``FractalTensor`` defined here.  A
 FractalTensor whose nesting is rectangular is exactly a dense array
-``[n1, ..., nk, *element_shape]``; ragged nestings are rejected, since there is
-no CPU fallback to hand them to.
+``[n1, ..., nk, *element_shape]``.  The stacked LSTM also takes ragged batches
+(sequences of different lengths): time-major and sorted by decreasing length as
+the reference builds them, or batch-major in any order.  The other programs
+reject ragged nestings, since there is no CPU fallback to hand them to.
 """
 import torch
 
@@ -86,12 +89,75 @@ def _cuda(t, dtype=None):
     return t if dtype is None else t.to(dtype)
 
 
+def _is_ragged(x):
+    if isinstance(x, torch.Tensor):
+        return False
+    try:
+        _nest_dims(x.indices)
+        return False
+    except ValueError:
+        return True
+
+
+def _packed_weights(Wss, Uss, bss, dtype):
+    W, U, b = _cuda(_dense(Wss), dtype), _cuda(_dense(Uss), dtype), _cuda(_dense(bss), dtype)
+    D, H = U.shape[0], U.shape[-1]
+    Wp, bias_p = ops.lstm_pack_weights(W.contiguous(), U.contiguous(), b.reshape(D, 4, H).contiguous())
+    return Wp, bias_p, D, H
+
+
+def stacked_lstm_time_major(embs, Wss, Uss, bss, dtype=None):
+    """The time-major stacked LSTM: fold(depth) of scan(time) of map(active sequences) of lstm_cell.
+
+    embs: [L][n_t] of [1,I], n_t the sequences still running at step t (non-increasing: the batch
+    is sorted by decreasing length and sequence n sits at position n of every step it is in).
+    Returns the top layer's hidden states with the same nesting, [L][n_t] of [1,H].
+    """
+    if isinstance(embs, torch.Tensor):
+        active = [embs.shape[1]] * embs.shape[0]
+        flat = embs.reshape(embs.shape[0] * embs.shape[1], -1)
+    else:
+        active = [len(step) for step in embs.indices]
+        flat = embs.data.reshape(sum(active), -1)
+    x = _cuda(flat, dtype).contiguous()
+    Wp, bias_p, D, H = _packed_weights(Wss, Uss, bss, x.dtype)
+    hs, _ = ops.lstm_stacked_varlen(x, active, Wp, bias_p)
+    return FractalTensor(hs[D - 1], [list(range(n)) for n in active], (1, H))
+
+
+def _stacked_lstm_ragged(embs, Wss, Uss, bss, dtype):
+    """Batch-major ragged batch [N][L_n]: sort by decreasing length, transpose into the
+    time-major packed layout on the device, run, and put the rows back where they were."""
+    lens = [len(seq) for seq in embs.indices]
+    if min(lens) <= 0:
+        raise ValueError("empty sequence in the batch")
+    flat = _cuda(embs.data.reshape(sum(lens), -1), dtype)
+    dev = flat.device
+    order = sorted(range(len(lens)), key=lambda n: -lens[n])
+    start = [0]
+    for n in lens:
+        start.append(start[-1] + n)
+    L = lens[order[0]]
+    active = [sum(1 for n in lens if n > t) for t in range(L)]
+    # src[k] = position in the batch-major buffer of the k-th row of the time-major one
+    src = torch.tensor([start[order[r]] + t for t in range(L) for r in range(active[t])], dtype=torch.long,
+                       device=dev)
+    Wp, bias_p, D, H = _packed_weights(Wss, Uss, bss, flat.dtype)
+    hs, _ = ops.lstm_stacked_varlen(flat.index_select(0, src).contiguous(), active, Wp, bias_p)
+    out = torch.empty(sum(lens), H, dtype=hs.dtype, device=dev)
+    out.index_copy_(0, src, hs[D - 1])
+    return FractalTensor(out, [list(range(n)) for n in lens], (1, H))
+
+
 def stacked_lstm(embs, Wss, Uss, bss, dtype=None):
     """fold(depth) of map(batch) of scan(time) of lstm_cell, as one depth x time wavefront.
 
-    embs: [N][L] of [1,I]; Wss: [D][4] of [I,H]; Uss: [D][4] of [H,H]; bss: [D][4] of [1,H].
+    embs: [N][L] of [1,I] (sequences may differ in length); Wss: [D][4] of [I,H]; Uss: [D][4] of
+    [H,H]; bss: [D][4] of [1,H].
     Returns the top layer's hidden states as a FractalTensor [N][L] of [1,H].
     """
+    if _is_ragged(embs):
+        return _stacked_lstm_ragged(embs, Wss, Uss, bss, dtype)
     x = _cuda(_dense(embs), dtype)
     W, U, b = _cuda(_dense(Wss), dtype), _cuda(_dense(Uss), dtype), _cuda(_dense(bss), dtype)
     N, L = x.shape[0], x.shape[1]

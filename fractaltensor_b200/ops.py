@@ -123,6 +123,44 @@ def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0, 
     return hs, c
 
 
+def lstm_stacked_varlen(x, active_rows, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0, schedule=0,
+                        pair=0):
+    """Stacked LSTM over a length-sorted batch of variable-length sequences, time-major packed.
+
+    active_rows: L non-increasing ints, the sequences still running at each step; x: [T,I] with
+    T = sum(active_rows), rows of step t after those of step t-1; Wp: [D,4H,I+H]
+    -> (hs [D,T,H] in the same packed order, c fp32 [D,N,H] with N = active_rows[0]).
+    schedule: 0 auto, 1 one launch per anti-diagonal, 2 one persistent kernel."""
+    _req(x, "x")
+    _req(Wp, "Wp", x.dtype)
+    active_rows = [int(n) for n in active_rows]
+    L = len(active_rows)
+    if L == 0 or active_rows[-1] <= 0 or any(a < b for a, b in zip(active_rows, active_rows[1:])):
+        raise ValueError("active_rows must be non-increasing and positive (sort the batch by decreasing length)")
+    T, I = x.shape
+    D, H4, K = Wp.shape
+    H = H4 // 4
+    if K != I + H or T != sum(active_rows):
+        raise ValueError("Wp %s / active_rows (sum %d) do not match x %s" % (tuple(Wp.shape), sum(active_rows),
+                                                                           tuple(x.shape)))
+    if bias_p is not None:
+        _req(bias_p, "bias_p", torch.float32)
+    N = active_rows[0]
+    if hs is None:
+        hs = torch.empty(D, T, H, dtype=x.dtype, device=x.device)
+    if c is None:
+        c = torch.empty(D, N, H, dtype=torch.float32, device=x.device)
+    _req(hs, "hs", x.dtype)
+    _req(c, "c", torch.float32)
+    rows = (ctypes.c_int * L)(*active_rows)
+    ws = workspace(x.device, lib.ftb_lstm_stacked_varlen_workspace_bytes(D, L))
+    with torch.cuda.device(x.device):
+        check(lib.ftb_lstm_stacked_varlen_fwd(_ptr(x), _ptr(Wp), _ptr(bias_p), _ptr(hs), _ptr(c), rows, D, L, I, H,
+                                              _dtype_code(x), _tuning(layers_per_group, bn, schedule, 0, pair, 0),
+                                              _ptr(ws), ws.numel(), _stream()), "ftb_lstm_stacked_varlen_fwd")
+    return hs, c
+
+
 def lstm_dilated(x, Wp, dilations, bias_p=None, hs=None, c=None, bn=0, pair=0, schedule=0):
     """x: [L,N,H]; Wp: [D,4H,2H]; dilations: D ints -> (hs [D,L,N,H], c fp32 [D,max_dil*N,H])."""
     _req(x, "x")

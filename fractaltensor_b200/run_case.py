@@ -1,6 +1,7 @@
 """Runs one operator of the hot path once (or a few times) on seeded synthetic inputs.
 
     python -m fractaltensor_b200.run_case lstm --D 16 --L 20 --N 256 --H 1024 --dtype bf16 --iters 2
+    python -m fractaltensor_b200.run_case varlen --D 16 --L 100 --N 256 --H 1024 --min-len 20
     python -m fractaltensor_b200.run_case b2b --batch 16 --M 16384
     python -m fractaltensor_b200.run_case attn --B 4 --heads 16 --S 2048
 
@@ -19,7 +20,7 @@ DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["lstm", "dilated", "grid", "b2b", "attn"])
+    ap.add_argument("case", choices=["lstm", "varlen", "dilated", "grid", "b2b", "attn"])
     ap.add_argument("--D", type=int, default=16)
     ap.add_argument("--L", type=int, default=20)
     ap.add_argument("--N", type=int, default=256)
@@ -37,6 +38,7 @@ def main():
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--schedule", type=int, default=0)
     ap.add_argument("--pair", type=int, default=0)
+    ap.add_argument("--min-len", type=int, default=1, help="varlen: lengths are uniform in [min-len, L]")
     a = ap.parse_args()
     dt, dev = DT[a.dtype], torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(0)
@@ -50,6 +52,18 @@ def main():
         c = torch.empty(a.D, a.N, a.H, device=dev)
         fn = lambda: ops.lstm_stacked(x, Wp, None, hs, c, layers_per_group=a.layers_per_group, bn=a.bn,
                                       schedule=a.schedule, pair=a.pair)
+    elif a.case == "varlen":
+        lens = torch.randint(a.min_len, a.L + 1, (a.N,), generator=torch.Generator().manual_seed(0))
+        lens[0] = a.L
+        active = [int((lens > t).sum()) for t in range(a.L)]
+        T = sum(active)
+        x = rnd(T, a.H).to(dt)
+        Wp, _ = ops.lstm_pack_weights(uni(1 / 32, a.D, 4, a.H, a.H).to(dt), uni(1 / 32, a.D, 4, a.H, a.H).to(dt))
+        hs = torch.empty(a.D, T, a.H, dtype=dt, device=dev)
+        c = torch.empty(a.D, a.N, a.H, device=dev)
+        print("varlen: %d of %d rows active (%.1f%%)" % (T, a.L * a.N, 100.0 * T / (a.L * a.N)))
+        fn = lambda: ops.lstm_stacked_varlen(x, active, Wp, None, hs, c, layers_per_group=a.layers_per_group,
+                                             bn=a.bn, schedule=a.schedule, pair=a.pair)
     elif a.case == "dilated":
         x = rnd(a.L, a.N, a.H).to(dt)
         Wp, _ = ops.lstm_pack_weights(uni(1 / 16, a.D, 4, a.H, a.H).to(dt), uni(1 / 16, a.D, 4, a.H, a.H).to(dt))

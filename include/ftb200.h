@@ -104,6 +104,25 @@ int ftb_lstm_stacked_fwd_noalloc(const void* x, const void* Wp, const float* bia
                                  int L, int N, int I, int H, int dtype, const int* tuning, void** scratch_out,
                                  void* stream);
 
+/* Stacked LSTM forward over a length-sorted batch of variable-length sequences in the
+ * time-major packed layout of a ragged FractalTensor [L][active_rows[t]] (flat buffer:
+ * the rows of step t follow those of step t-1).  Stands in for batched_cell()/lstm_layer()/
+ * stacked_lstm() of the time-major program (examples/stacked_rnn/stacked_rnn.py:40-79, which
+ * carries hs_prev[0:xs.length]) on batches built like gen_dataset_time_major()
+ * (examples/utils/data_utils.py:42-66), and for the variable-length mode of the reference's
+ * cuDNN baseline (benchmarks/rnn/cuDNN/utils.h:44-61).
+ * `active_rows` is a HOST array of L ints, non-increasing, active_rows[L-1] >= 1: the number
+ * of sequences still running at step t (sequence n occupies row n of every step it is in).
+ * With T = sum(active_rows) and N = active_rows[0]: x: [T,I]; hs (out): [D,T,H] in the same
+ * packed order; c (out): fp32 [D,N,H], the cell state of each sequence after its own last step.
+ * Only tiles that hold active rows are computed.  With ftb_lstm_stacked_varlen_workspace_bytes(D, L)
+ * bytes of workspace (16-bit dtypes) the wavefront runs as one persistent launch whose schedule
+ * tables are copied from host memory on `stream`; with less it runs one launch per level. */
+size_t ftb_lstm_stacked_varlen_workspace_bytes(int D, int L);
+int ftb_lstm_stacked_varlen_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
+                                const int* active_rows, int D, int L, int I, int H, int dtype, const int* tuning,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
 /* Dilated stacked LSTM forward: layer l reads its own state dilations[l] steps
  * back.  Stands in for dilated_layer()/model() (examples/dilated_rnn/dilated_rnn.py:16-41)
  * and DilatedLstmRegion1/2 (kaleido/core/device/kernels/lstm/dilated_lstm/region{1,2}.h).

@@ -58,6 +58,13 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
     assert lib.ftb_flash_attn_fwd(one, one, one, one, 1, 1, 256, 64, 1.0, 1, one, 256, z) == 1  # d != 128
     assert lib.ftb_flash_attn_fwd(one, one, one, one, 1, 1, 100, 128, 1.0, 1, one, 256, z) == 1  # S % 256
     assert lib.ftb_gemm_nt(one, one, one, 8, 128, 60, 1, None, one, 256, z) == 1  # K % 64
+    rows = (ctypes.c_int * 3)(4, 5, 1)  # not sorted by decreasing length
+    assert lib.ftb_lstm_stacked_varlen_fwd(one, one, z, one, one, rows, 1, 3, 64, 64, 1, None, one, 256, z) == 1
+    rows = (ctypes.c_int * 3)(4, 2, 0)  # a step without sequences
+    assert lib.ftb_lstm_stacked_varlen_fwd(one, one, z, one, one, rows, 1, 3, 64, 64, 1, None, one, 256, z) == 1
+    rows = (ctypes.c_int * 3)(4, 2, 1)
+    assert lib.ftb_lstm_stacked_varlen_fwd(one, one, z, one, one, rows, 1, 3, 64, 64, 1, None, z, 0, z) == 3
+    assert lib.ftb_lstm_stacked_varlen_workspace_bytes(16, 100) > lib.ftb_workspace_bytes()
     dil = (ctypes.c_int * 2)(1, 0)
     assert lib.ftb_lstm_dilated_fwd(one, one, z, one, one, dil, 2, 4, 1, 64, 1, None, one, 256, z) == 1  # dilation 0
 

@@ -189,6 +189,141 @@ def test_stacked_lstm_config4_properties(ops):
     assert torch.equal(half, hs[:, :, :128])
 
 
+# ------------------------------------------------- stacked LSTM, variable lengths
+def _varlen_inputs(D, L, N, I, H, seed, dt, min_len=1, w_bound=1.0 / 8):
+    active = dense.make_active_rows(L, N, seed, min_len)
+    T = sum(active)
+    x, W, U, b = dense.make_lstm_inputs(D, T, 1, I, H, seed, w_bound, dtype=dt, bias=True)
+    return active, x.reshape(T, I), W, U, b
+
+
+def _run_varlen(ops, active, x, W, U, b, **kw):
+    xd, Wd, Ud, bd = _dev(x, W, U, b)
+    Wp, bp = ops.lstm_pack_weights(Wd, Ud, bd)
+    hs, c = ops.lstm_stacked_varlen(xd, active, Wp, bp, **kw)
+    ops.check_status()
+    return hs, c
+
+
+def test_varlen_lstm_golden_fp32(ops, golden_dir):
+    """The reference frontend's time-major ragged program (H=16 embedded in H=64 with zeros)."""
+    g = _load(golden_dir, "stacked_lstm_varlen_small.npz")
+    D, H, HP = 2, 16, 64
+    active = g["active_rows"].tolist()
+    T = sum(active)
+    x = torch.zeros(T, HP); x[:, :H] = g["x"]
+    W = torch.zeros(D, 4, HP, HP); W[:, :, :H, :H] = g["W"]
+    U = torch.zeros(D, 4, HP, HP); U[:, :, :H, :H] = g["U"]
+    b = torch.zeros(D, 4, HP); b[..., :H] = g["b"]
+    hs, _ = _run_varlen(ops, active, x, W, U, b)
+    _assert_fp32(hs[-1][:, :H], g["top"])
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape,kw", [
+    ((1, 1, 5, 64, 64), {}),                       # one step
+    ((2, 6, 40, 64, 64), {}),
+    ((3, 9, 300, 128, 128), {}),                   # three batch tiles, shrinking to one
+    ((1, 5, 130, 192, 64), {}),                    # I != H
+    ((3, 7, 300, 256, 256), {"schedule": 1}),
+    ((3, 7, 300, 256, 256), {"schedule": 2, "pair": 1}),
+    ((4, 8, 260, 256, 256), {"schedule": 2, "pair": 2, "layers_per_group": 2, "bn": 128}),
+])
+def test_varlen_lstm(ops, dt, shape, kw):
+    D, L, N, I, H = shape
+    if dt == torch.float32 and kw.get("schedule") == 2:
+        pytest.skip("the fp32 path has no persistent schedule")
+    active, x, W, U, b = _varlen_inputs(D, L, N, I, H, 21, dt)
+    hs, c = _run_varlen(ops, active, x, W, U, b, **kw)
+    rhs, rc = dense.stacked_lstm_varlen_dense(*_f32(x), active, *_f32(W, U, b))
+    if dt == torch.float32:
+        _assert_fp32(hs, rhs)
+        _assert_fp32(c, rc)
+    else:
+        _assert_16(hs, rhs)
+        _assert_16(c, rc)
+
+
+def test_varlen_lstm_equal_lengths_is_the_rectangular_program(ops):
+    D, L, N, H = 3, 6, 200, 256
+    x, W, U, b = dense.make_lstm_inputs(D, L, N, H, H, 3, 1.0 / 8, dtype=torch.bfloat16, bias=True)
+    ref_h, ref_c = _run_stacked(ops, x, W, U, b, schedule=1)
+    for kw in ({"schedule": 1}, {"schedule": 2}, {}):
+        hs, c = _run_varlen(ops, [N] * L, x.reshape(L * N, H), W, U, b, **kw)
+        assert torch.equal(hs.reshape(D, L, N, H), ref_h) and torch.equal(c, ref_c)
+
+
+def test_varlen_lstm_sequences_are_independent(ops):
+    """Dropping the shorter sequences from the batch leaves the others' rows bit for bit as they
+    were, whichever tile position they land in; so do the two schedules."""
+    D, L, N, H = 3, 8, 280, 256
+    active, x, W, U, b = _varlen_inputs(D, L, N, H, H, 22, torch.bfloat16)
+    hs, c = _run_varlen(ops, active, x, W, U, b, schedule=2)
+    hs1, c1 = _run_varlen(ops, active, x, W, U, b, schedule=1)
+    assert torch.equal(hs, hs1) and torch.equal(c, c1)
+    keep = 70
+    off = np.concatenate([[0], np.cumsum(active)])
+    sub_active = [min(n, keep) for n in active]
+    rows = torch.tensor([off[t] + r for t in range(L) for r in range(sub_active[t])])
+    sub_h, sub_c = _run_varlen(ops, sub_active, x[rows], W, U, b)
+    assert torch.equal(sub_h.cpu(), hs.cpu()[:, rows]) and torch.equal(sub_c.cpu(), c.cpu()[:, :keep])
+
+
+def test_varlen_lstm_config4_size_properties(ops):
+    """BASELINE config 4's shape (D16 H1024 L100 N256 bf16) with lengths uniform in [20, 100]:
+    the first layers and steps against the oracle, and batch independence, as for the rectangular case."""
+    D, L, N, H = 16, 100, 256, 1024
+    active, x, W, U, b = _varlen_inputs(D, L, N, H, H, 23, torch.bfloat16, min_len=20, w_bound=1.0 / 32)
+    xd, Wd, Ud, bd = _dev(x, W, U, b)
+    Wp, bp = ops.lstm_pack_weights(Wd, Ud, bd)
+    hs, c = ops.lstm_stacked_varlen(xd, active, Wp, bp)
+    ops.check_status()
+    assert torch.isfinite(hs.float()).all() and torch.isfinite(c).all()
+    T4 = sum(active[:4])
+    rhs, _ = dense.stacked_lstm_varlen_dense(x[:T4].float(), active[:4], *_f32(W[:2], U[:2], b[:2]))
+    _assert_16(hs[:2, :T4], rhs)
+    keep = 100
+    off = np.concatenate([[0], np.cumsum(active)])
+    sub_active = [min(n, keep) for n in active]
+    rows = torch.tensor([off[t] + r for t in range(L) for r in range(sub_active[t])]).cuda()
+    sub_h, sub_c = ops.lstm_stacked_varlen(xd[rows].contiguous(), sub_active, Wp, bp)
+    ops.check_status()
+    assert torch.equal(sub_h, hs[:, rows]) and torch.equal(sub_c, c[:, :keep])
+
+
+def test_varlen_frontend_batch_major_and_time_major(ops):
+    """Ragged batches through the model-level signatures: batch-major in arbitrary order
+    (examples/stacked_rnn/stacked_lstm1.py) and time-major sorted (examples/stacked_rnn/stacked_rnn.py)."""
+    from fractaltensor_b200 import frontend
+    D, H = 2, 64
+    lens = [3, 7, 1, 5, 7, 2]
+    g = torch.Generator().manual_seed(8)
+    seqs = [torch.randn(n, H, generator=g) for n in lens]
+    W = (torch.rand(D, 4, H, H, generator=g) * 2 - 1) / 8
+    U = (torch.rand(D, 4, H, H, generator=g) * 2 - 1) / 8
+    b = (torch.rand(D, 4, H, generator=g) * 2 - 1) / 8
+    ft = lambda t, d: frontend.FractalTensor.from_dense(t.cuda(), d)
+    Wss, Uss, bss = ft(W, 2), ft(U, 2), ft(b.reshape(D, 4, 1, H), 2)
+    embs = frontend.FractalTensor(torch.cat(seqs).cuda(), [list(range(n)) for n in lens], (1, H))
+    out = frontend.stacked_lstm(embs, Wss, Uss, bss)
+    assert [len(i) for i in out.indices] == lens
+    flat = out.data.reshape(-1, H).cpu()
+    pos = 0
+    for n, seq in zip(lens, seqs):
+        rhs, _ = dense.stacked_lstm_dense(seq[:, None], W, U, b)
+        _assert_fp32(flat[pos:pos + n], rhs[-1][:, 0])
+        pos += n
+    # time-major: sort by decreasing length, step t holds the sequences longer than t
+    order = sorted(range(len(lens)), key=lambda n: -lens[n])
+    active = [sum(1 for n in lens if n > t) for t in range(max(lens))]
+    packed = torch.cat([seqs[order[r]][t][None] for t in range(max(lens)) for r in range(active[t])])
+    tm = frontend.FractalTensor(packed.cuda(), [list(range(n)) for n in active], (1, H))
+    out_tm = frontend.stacked_lstm_time_major(tm, Wss, Uss, bss)
+    assert [len(i) for i in out_tm.indices] == active
+    rhs, _ = dense.stacked_lstm_varlen_dense(packed, active, W, U, b)
+    _assert_fp32(out_tm.data.reshape(-1, H).cpu(), rhs[-1])
+
+
 # ---------------------------------------------------------------- dilated LSTM
 def test_dilated_lstm_golden_fp32(ops, golden_dir):
     g = _load(golden_dir, "dilated_lstm_small.npz")

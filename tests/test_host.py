@@ -25,6 +25,20 @@ def test_ragged_nesting_is_rejected():
         ft.to_dense()
 
 
+def test_ragged_batches_are_routed_not_densified():
+    """The stacked LSTM takes ragged batches; with CPU data the call must stop at the device
+    check (no CPU path), not at the nesting check."""
+    x = frontend.FractalTensor(torch.zeros(5 * 64), [[0, 1, 2], [0, 1]], (1, 64))
+    w = frontend.FractalTensor.from_dense(torch.zeros(1, 4, 64, 64), 2)
+    b = frontend.FractalTensor.from_dense(torch.zeros(1, 4, 1, 64), 2)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        frontend.stacked_lstm(x, w, w, b)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        frontend.stacked_lstm_time_major(x, w, w, b)
+    with pytest.raises(ValueError, match="ragged"):
+        frontend.dilated_lstm(x, w, w, b)
+
+
 def test_cpu_tensors_are_rejected_not_computed():
     x = frontend.FractalTensor.from_dense(torch.zeros(2, 3, 1, 64), 2)
     w = frontend.FractalTensor.from_dense(torch.zeros(1, 4, 64, 64), 2)
