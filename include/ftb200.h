@@ -163,7 +163,8 @@ int ftb_b2b_gemm(const void* A, const void* B, const void* C, void* Dout, int ba
 /* Flash attention forward with online softmax, non-causal.  Stands in for
  * flash_attention() (examples/flash_attention/flash_attention.py:14-88) with the
  * (max, sum, out) carry started at (-inf, 0, 0).  q,k,v,o: [B,heads,S,d];
- * d = 128, S % 128 == 0; dtype fp16 or bf16; softmax(scale * q.k^T). */
+ * d = 128, S % 256 == 0 (a CTA takes two 128-row query tiles); dtype fp16 or bf16;
+ * softmax(scale * q.k^T). */
 int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S, int d,
                        float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
