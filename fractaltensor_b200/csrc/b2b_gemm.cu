@@ -10,9 +10,11 @@
 // One persistent CTA per SM owns a contiguous range of 128-row tiles.
 //   warp 0      TMA producer: B and C of the current batch entry, ring of A tiles
 //   warp 1      MMA issuer: S = A.B^T into TMEM, then O = P.C^T into TMEM
-//   warps 2..5  convert S -> P (16-bit, written to shared memory in the 128-byte
-//               swizzled K-major layout the second MMA reads), convert O -> D
-//               staging, TMA store of D
+//   warps 2..5  convert S -> P (16-bit pairs written with tcgen05.st over the TMEM columns
+//               of the S tile just read; the second MMA takes its A operand from TMEM),
+//               convert O -> D staging, TMA store of D
+// P never touches shared memory, which leaves room for a fourth A tile in flight: the shape
+// is bound by how many bytes each SM keeps outstanding against DRAM latency.
 #include "../../include/ftb200.h"
 #include "ptx.cuh"
 #include "tmap.h"
@@ -23,9 +25,9 @@ namespace {
 constexpr int kTile = 128;              // rows per tile; also N, K, P
 constexpr int kHalfBytes = 128 * 128;   // one 64-column half of a 128x128 16-bit tile
 constexpr int kTileBytes = 2 * kHalfBytes;
-constexpr int kAStages = 3;
+constexpr int kAStages = 4;
 constexpr int kThreads = 192;
-constexpr uint32_t kSmemBytes = (2 + kAStages + 2) * kTileBytes + 1024;  // B, C, A ring, P, D staging
+constexpr uint32_t kSmemBytes = (2 + kAStages + 1) * kTileBytes + 1024;  // B, C, A ring, D staging
 
 // Writes 32 fp32 accumulator columns [col0, col0+32) of row `row` as 16-bit
 // values into a 128x128 tile laid out as two 64-column halves of 128-byte
@@ -53,8 +55,8 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 int total_tiles, int tiles_per_batch, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t a_full[kAStages], a_empty[kAStages];
-  __shared__ uint64_t bc_full, bc_empty, p_full, p_empty;
-  __shared__ uint64_t s_full[2], s_empty[2], o_full[2], o_empty[2];
+  __shared__ uint64_t bc_full, bc_empty, p_full;
+  __shared__ uint64_t s_full[2], o_full[2], o_empty[2];
   __shared__ uint64_t d_free, d_ready;  // staging tile handshakes between the epilogue warps and the storing thread
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
@@ -67,8 +69,7 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   uint8_t* sB = smem;
   uint8_t* sC = sB + kTileBytes;
   uint8_t* sA = sC + kTileBytes;
-  uint8_t* sP = sA + kAStages * kTileBytes;
-  uint8_t* sD = sP + kTileBytes;
+  uint8_t* sD = sA + kAStages * kTileBytes;
 
   // Contiguous tile range of this CTA.
   const int per = total_tiles / gridDim.x, rem = total_tiles % gridDim.x;
@@ -87,12 +88,10 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     mbar_init(&bc_full, 1);
     mbar_init(&bc_empty, 1);
     mbar_init(&p_full, 4);
-    mbar_init(&p_empty, 1);
     mbar_init(&d_free, 1);
     mbar_init(&d_ready, 4);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
       mbar_init(&o_full[i], 1);
       mbar_init(&o_empty[i], 4);
     }
@@ -107,7 +106,8 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
-  // TMEM columns: S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512).
+  // TMEM columns: S0 [0,128), S1 [128,256), O0 [256,384), O1 [384,512); P_i (16-bit pairs)
+  // overlays the first 64 columns of S_i.
 
   if (warp == 0) {
     if (lane == 0) {
@@ -143,14 +143,15 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(128, 128, Fmt<T>::kind, 0, 0);
-      const uint32_t aB = smem_u32(sB), aC = smem_u32(sC), aP = smem_u32(sP);
+      const uint32_t aB = smem_u32(sB), aC = smem_u32(sC);
       int stage = 0;
       uint32_t a_phase = 0, bc_phase = 0, p_phase = 0;
-      uint32_t s_phase[2] = {0, 0}, o_phase[2] = {0, 0};
+      uint32_t o_phase[2] = {0, 0};
       int cur_batch = -1;
       bool ok = true;
 
-      // GEMM 1 of tile i: S[i&1] = A . B^T
+      // GEMM 1 of tile i: S[i&1] = A . B^T.  The buffer last held S/P of tile i-2, whose GEMM 2 was
+      // issued before this one and so runs before it on the tensor pipe.
       auto gemm1 = [&](int i) -> bool {
         const int b = (first + i) / tiles_per_batch;
         if (b != cur_batch) {
@@ -159,8 +160,6 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           cur_batch = b;
         }
         const int sb = i & 1;
-        if (!mbar_wait(&s_empty[sb], s_phase[sb] ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
-        s_phase[sb] ^= 1u;
         if (!mbar_wait(&a_full[stage], a_phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
         tc_fence_after();
         const uint32_t aA = smem_u32(sA + stage * kTileBytes);
@@ -178,7 +177,8 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         }
         return true;
       };
-      // GEMM 2 of tile i: O[i&1] = P . C^T
+      // GEMM 2 of tile i: O[i&1] = P . C^T, P from TMEM (16 of the 128 inner positions = 8 packed
+      // columns per step).
       auto gemm2 = [&](int i, bool last_of_batch) -> bool {
         const int ob = i & 1;
         if (!mbar_wait(&o_empty[ob], o_phase[ob] ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
@@ -189,10 +189,9 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(tmem_base + 256 + ob * 128, make_sdesc_sw128(aP + off, 16, 1024),
-                  make_sdesc_sw128(aC + off, 16, 1024), idesc, k != 0 ? 1u : 0u);
+          umma_ts(tmem_base + 256 + ob * 128, tmem_base + ob * 128 + k * 8, make_sdesc_sw128(aC + off, 16, 1024),
+                  idesc, k != 0 ? 1u : 0u);
         }
-        umma_commit(&p_empty);
         umma_commit(&o_full[ob]);
         if (last_of_batch) umma_commit(&bc_empty);
         return true;
@@ -213,7 +212,7 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     const int row = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     const bool issuer = (warp == 2 && lane == 0);
-    uint32_t s_phase[2] = {0, 0}, o_phase[2] = {0, 0}, pe_phase = 0, d_phase = 0;
+    uint32_t s_phase[2] = {0, 0}, o_phase[2] = {0, 0}, d_phase = 0;
     bool ok = true;
 
     auto convert_s = [&](int i) -> bool {
@@ -221,25 +220,23 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], s_phase[sb], &s_abort, status, FTB_ERR_TIMEOUT_MMA)))
         return false;
       s_phase[sb] ^= 1u;
-      // P is single-buffered: GEMM 2 of the previous tile must be done with it.
-      if (!__all_sync(0xffffffffu, mbar_wait(&p_empty, pe_phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_MMA)))
-        return false;
-      pe_phase ^= 1u;
       tc_fence_after();
-#pragma unroll 1
+      // 32 fp32 columns in, 16 columns of 16-bit pairs out, in place: the columns written at step
+      // ch lie below the ones still to be read.
+#pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t r[32];
         tmem_ld32(lane_addr + sb * 128 + ch * 32, r);
         tmem_ld_wait();
-        write_row_chunk_sw128<T>(sP, row, ch * 32, r);
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) pk[c] = Fmt<T>::pack2(__uint_as_float(r[2 * c]), __uint_as_float(r[2 * c + 1]));
+        tmem_st16(lane_addr + sb * 128 + ch * 16, pk);
       }
+      tmem_st_wait();
       tc_fence_before();
-      fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_empty[sb]);
-        mbar_arrive(&p_full);
-      }
+      if (lane == 0) mbar_arrive(&p_full);
       return true;
     };
     auto output_o = [&](int i) -> bool {
