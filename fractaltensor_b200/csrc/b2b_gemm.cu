@@ -25,9 +25,12 @@ namespace {
 constexpr int kTile = 128;              // rows per tile; also N, K, P
 constexpr int kHalfBytes = 128 * 128;   // one 64-column half of a 128x128 16-bit tile
 constexpr int kTileBytes = 2 * kHalfBytes;
-constexpr int kAStages = 4;
+#ifndef FTB_B2B_STAGES
+#define FTB_B2B_STAGES 2
+#endif
+constexpr int kAStages = FTB_B2B_STAGES;  // A tiles in flight per SM (2, 3 and 4 measured the same)
 constexpr int kThreads = 192;
-constexpr uint32_t kSmemBytes = (2 + kAStages + 1) * kTileBytes + 1024;  // B, C, A ring, D staging
+constexpr uint32_t kSmemBytes = (4 + kAStages + 1) * kTileBytes + 1024;  // two (B, C) pairs, A ring, D staging
 
 // Writes 32 fp32 accumulator columns [col0, col0+32) of row `row` as 16-bit
 // values into a 128x128 tile laid out as two 64-column halves of 128-byte
@@ -48,6 +51,16 @@ __device__ __forceinline__ void write_row_chunk_sw128(uint8_t* tile, int row, in
   }
 }
 
+#ifdef FTB_TRACE
+__device__ unsigned long long g_b2b_trace[16][8];
+#define B2B_STAMP(i, k) if (blockIdx.x == 5 && (i) < 16) g_b2b_trace[i][k] = clock64()
+__device__ unsigned long long g_b2b_wall[148][4];
+#define B2B_WALL(k) if (blockIdx.x < 148) g_b2b_wall[blockIdx.x][k] = globaltimer_ns()
+#else
+#define B2B_WALL(k)
+#define B2B_STAMP(i, k)
+#endif
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
@@ -55,20 +68,20 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 int total_tiles, int tiles_per_batch, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t a_full[kAStages], a_empty[kAStages];
-  __shared__ uint64_t bc_full, bc_empty, p_full;
-  __shared__ uint64_t s_full[2], o_full[2], o_empty[2];
+  __shared__ uint64_t bc_full[2], bc_empty[2];
+  __shared__ uint64_t s_full[2], p_full[2], o_full[2], o_empty[2];
   __shared__ uint64_t d_free, d_ready;  // staging tile handshakes between the epilogue warps and the storing thread
   __shared__ uint32_t tmem_base_s;
   __shared__ int s_abort;
 
+  if (threadIdx.x == 0) B2B_WALL(0);
   if (*reinterpret_cast<volatile int*>(status) != 0) return;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t* sB = smem;
-  uint8_t* sC = sB + kTileBytes;
-  uint8_t* sA = sC + kTileBytes;
+  uint8_t* sBC = smem;  // pair p: B at p * 2 tiles, C one tile further
+  uint8_t* sA = sBC + 4 * kTileBytes;
   uint8_t* sD = sA + kAStages * kTileBytes;
 
   // Contiguous tile range of this CTA.
@@ -85,13 +98,15 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       mbar_init(&a_full[i], 1);
       mbar_init(&a_empty[i], 1);
     }
-    mbar_init(&bc_full, 1);
-    mbar_init(&bc_empty, 1);
-    mbar_init(&p_full, 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bc_full[i], 1);
+      mbar_init(&bc_empty[i], 1);
+    }
     mbar_init(&d_free, 1);
     mbar_init(&d_ready, 4);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
       mbar_init(&o_full[i], 1);
       mbar_init(&o_empty[i], 4);
     }
@@ -112,11 +127,31 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0;
-      uint32_t phase = 0, bc_phase = 0;
-      int cur_batch = -1;
-      for (int i = 0; i < count; ++i) {
+      uint32_t phase = 0;
+      // B and C of a batch entry travel together into one of two buffer pairs, one batch entry
+      // ahead of the tiles: a CTA whose range crosses into the next batch entry finds its B and C
+      // already there instead of draining its pipeline at the boundary.
+      const int batch0 = count > 0 ? first / tiles_per_batch : 0;
+      const int batch_last = count > 0 ? (first + count - 1) / tiles_per_batch : -1;
+      int next_bc = batch0;
+      bool ok = true;
+      auto load_bc = [&](int b) -> bool {
+        const int n = b - batch0, pair = n & 1;
+        if (!mbar_wait(&bc_empty[pair], ((n >> 1) & 1) ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT)) return false;
+        uint8_t* dB = sBC + pair * 2 * kTileBytes;
+        uint8_t* dC = dB + kTileBytes;
+        mbar_arrive_expect_tx(&bc_full[pair], 2 * kTileBytes);
+        tma_load_2d(dB, &mapB, &bc_full[pair], 0, b * kTile);
+        tma_load_2d(dB + kHalfBytes, &mapB, &bc_full[pair], 64, b * kTile);
+        tma_load_2d(dC, &mapC, &bc_full[pair], 0, b * kTile);
+        tma_load_2d(dC + kHalfBytes, &mapC, &bc_full[pair], 64, b * kTile);
+        return true;
+      };
+      for (int i = 0; i < count && ok; ++i) {
         const int tile = first + i;
         const int b = tile / tiles_per_batch;
+        while (ok && next_bc <= b) ok = load_bc(next_bc++);
+        if (!ok) break;
         if (!mbar_wait(&a_empty[stage], phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT)) break;
         uint8_t* dst = sA + stage * kTileBytes;
         mbar_arrive_expect_tx(&a_full[stage], kTileBytes);
@@ -126,27 +161,20 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           stage = 0;
           phase ^= 1u;
         }
-        if (b != cur_batch) {
-          // B and C are single-buffered: wait until the MMAs of the previous
-          // batch entry have finished reading them.
-          if (!mbar_wait(&bc_empty, bc_phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT)) break;
-          mbar_arrive_expect_tx(&bc_full, 2 * kTileBytes);
-          tma_load_2d(sB, &mapB, &bc_full, 0, b * kTile);
-          tma_load_2d(sB + kHalfBytes, &mapB, &bc_full, 64, b * kTile);
-          tma_load_2d(sC, &mapC, &bc_full, 0, b * kTile);
-          tma_load_2d(sC + kHalfBytes, &mapC, &bc_full, 64, b * kTile);
-          bc_phase ^= 1u;
-          cur_batch = b;
-        }
+        // Prefetch the next batch entry's B, C.  Only after this tile's A is on its way: the
+        // buffer pair frees up when the MMAs of the batch entry before this one are done, and the
+        // MMA warp issues this tile's first product ahead of the previous tile's second.
+        while (ok && next_bc <= batch_last && next_bc <= b + 1) ok = load_bc(next_bc++);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(128, 128, Fmt<T>::kind, 0, 0);
-      const uint32_t aB = smem_u32(sB), aC = smem_u32(sC);
+      const uint32_t aBC = smem_u32(sBC);
+      const int batch0 = count > 0 ? first / tiles_per_batch : 0;
       int stage = 0;
-      uint32_t a_phase = 0, bc_phase = 0, p_phase = 0;
-      uint32_t o_phase[2] = {0, 0};
+      uint32_t a_phase = 0;
+      uint32_t o_phase[2] = {0, 0}, p_phase[2] = {0, 0};
       int cur_batch = -1;
       bool ok = true;
 
@@ -154,14 +182,17 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       // issued before this one and so runs before it on the tensor pipe.
       auto gemm1 = [&](int i) -> bool {
         const int b = (first + i) / tiles_per_batch;
+        const int n = b - batch0;
         if (b != cur_batch) {
-          if (!mbar_wait(&bc_full, bc_phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
-          bc_phase ^= 1u;
+          if (!mbar_wait(&bc_full[n & 1], (n >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
           cur_batch = b;
         }
+        const uint32_t aB = aBC + (n & 1) * 2 * kTileBytes;
         const int sb = i & 1;
         if (!mbar_wait(&a_full[stage], a_phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
         tc_fence_after();
+        B2B_STAMP(i, 0);
+        if (i == 0) B2B_WALL(1);
         const uint32_t aA = smem_u32(sA + stage * kTileBytes);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -181,11 +212,16 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       // columns per step).
       auto gemm2 = [&](int i, bool last_of_batch) -> bool {
         const int ob = i & 1;
+        const int n = (first + i) / tiles_per_batch - batch0;
+        const uint32_t aC = aBC + ((n & 1) * 2 + 1) * kTileBytes;
         if (!mbar_wait(&o_empty[ob], o_phase[ob] ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
         o_phase[ob] ^= 1u;
-        if (!mbar_wait(&p_full, p_phase, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
-        p_phase ^= 1u;
+        // One barrier per S/P buffer: the converting warps can be a whole tile ahead of this wait
+        // (S of the next tile is ready early), and a parity wait must not fall two phases behind.
+        if (!mbar_wait(&p_full[ob], p_phase[ob], &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
+        p_phase[ob] ^= 1u;
         tc_fence_after();
+        B2B_STAMP(i, 3);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
@@ -193,7 +229,7 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                   idesc, k != 0 ? 1u : 0u);
         }
         umma_commit(&o_full[ob]);
-        if (last_of_batch) umma_commit(&bc_empty);
+        if (last_of_batch) umma_commit(&bc_empty[n & 1]);
         return true;
       };
 
@@ -201,10 +237,10 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       for (int i = 0; i < count && ok; ++i) {
         const bool has_next = i + 1 < count;
         const bool next_new_batch = has_next && ((first + i + 1) / tiles_per_batch != (first + i) / tiles_per_batch);
-        // Run ahead with GEMM 1 of the next tile unless it needs a new B.
-        if (has_next && !next_new_batch) ok = gemm1(i + 1);
-        if (ok) ok = gemm2(i, next_new_batch);
-        if (ok && has_next && next_new_batch) ok = gemm1(i + 1);
+        // Run ahead with GEMM 1 of the next tile (its B sits in the other buffer pair if it
+        // belongs to the next batch entry).
+        if (has_next) ok = gemm1(i + 1);
+        if (ok) ok = gemm2(i, next_new_batch || !has_next);
       }
     }
   } else {
@@ -221,6 +257,7 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         return false;
       s_phase[sb] ^= 1u;
       tc_fence_after();
+      if (threadIdx.x == 64) B2B_STAMP(i, 1);
       // 32 fp32 columns in, 16 columns of 16-bit pairs out, in place: the columns written at step
       // ch lie below the ones still to be read.
 #pragma unroll
@@ -236,7 +273,8 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full);
+      if (lane == 0) mbar_arrive(&p_full[sb]);
+      if (threadIdx.x == 64) B2B_STAMP(i, 2);
       return true;
     };
     auto output_o = [&](int i) -> bool {
@@ -245,12 +283,14 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         return false;
       o_phase[ob] ^= 1u;
       tc_fence_after();
+      if (threadIdx.x == 64) B2B_STAMP(i, 4);
       // The previous TMA store must have finished reading the staging tile.
       if (issuer) {
         tma_store_wait_read<0>();
         mbar_arrive(&d_free);
       }
       if (!__all_sync(0xffffffffu, mbar_wait(&d_free, d_phase, &s_abort, status, FTB_ERR_TIMEOUT_EPI))) return false;
+      if (threadIdx.x == 64) B2B_STAMP(i, 5);
 #pragma unroll 1
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t r[32];
@@ -265,6 +305,7 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         mbar_arrive(&o_empty[ob]);
         mbar_arrive(&d_ready);
       }
+      if (threadIdx.x == 64) B2B_STAMP(i, 6);
       const bool staged = !issuer || mbar_wait(&d_ready, d_phase, &s_abort, status, FTB_ERR_TIMEOUT_EPI);
       d_phase ^= 1u;
       if (issuer && staged) {
@@ -272,6 +313,7 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         tma_store_2d(&mapD, sD, 0, tile * kTile);
         tma_store_2d(&mapD, sD + kHalfBytes, 64, tile * kTile);
         tma_store_commit();
+        B2B_STAMP(i, 7);
       }
       return true;
     };
@@ -281,6 +323,7 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       if (ok && i > 0) ok = output_o(i - 1);
     }
     if (ok && count > 0) ok = output_o(count - 1);
+    if (issuer) B2B_WALL(2);
     if (issuer) tma_store_wait<0>();
   }
 
@@ -293,6 +336,7 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     }
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+    if (lane == 0) B2B_WALL(3);
   }
 }
 
@@ -316,6 +360,15 @@ int launch(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mC, 
 }  // namespace ftb
 
 using namespace ftb;
+
+#ifdef FTB_TRACE
+extern "C" int ftb_debug_b2b_trace(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_b2b_trace, sizeof(unsigned long long) * 16 * 8) == cudaSuccess ? 0 : 1;
+}
+extern "C" int ftb_debug_b2b_wall(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_b2b_wall, sizeof(unsigned long long) * 148 * 4) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 extern "C" int ftb_b2b_gemm(const void* A, const void* B, const void* C, void* Dout, int batch, int M, int N, int K,
                             int P, int dtype, void* workspace, size_t workspace_bytes, void* stream_) {
