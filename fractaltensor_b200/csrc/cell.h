@@ -4,7 +4,8 @@
 //
 // A cell computes  acc[rows, n_cols] = sum_s  A_s[rows, K_s] * Wp[w_row0 .. , wk_s ..]^T
 // where the A_s are up to three activation row-blocks (the cell's input, its
-// recurrent state(s)) and Wp holds the cell's weights K-major, one row per
+// recurrent state(s)), each read from one of four activation buffers, and Wp (one of
+// two packed weight buffers, `w_map`) holds the cell's weights K-major, one row per
 // output column.  The epilogue turns acc into the cell's outputs.
 #pragma once
 #include <stdint.h>
@@ -13,7 +14,8 @@ namespace ftb {
 
 constexpr int kMaxSeg = 3;     // activation sources concatenated along K
 constexpr int kMaxItems = 24;  // cells per launch (a level with more is split)
-constexpr int kNumActMaps = 3;
+constexpr int kNumActMaps = 4;
+constexpr int kNumWeightMaps = 2;
 
 enum Epilogue : int {
   EPI_STORE = 0,  // out = acc
@@ -38,7 +40,7 @@ struct CellItem {
   int32_t out_row0;  // 16-bit LSTM path: row of `out` in the tensor map `out_map` (TMA stores)
   int32_t c_row0;    // 16-bit LSTM path: row of `c` in the cell-state tensor map
   int32_t out_map;   // activation map index that covers `out`
-  int32_t pad_;
+  int32_t w_map;     // which packed weight buffer the cell reads (0 or 1)
 };
 
 struct CellBatch {

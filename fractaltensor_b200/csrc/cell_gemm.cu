@@ -98,8 +98,8 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
 template <typename T, int BN, int EPI, bool PERSIST, bool PAIR>
 __global__ void __launch_bounds__((Cfg<BN, EPI, PAIR>::kThreads), 1)
 cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
-                 const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapW,
-                 const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CellBatch batch,
+                 const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapA3,
+                 const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CellBatch batch,
                  const PlanView plan, int* __restrict__ status) {
   using C = Cfg<BN, EPI, PAIR>;
   constexpr int S = C::kStages;
@@ -128,6 +128,7 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     prefetch_tmap(&mapA0);
     prefetch_tmap(&mapA1);
     prefetch_tmap(&mapA2);
+    prefetch_tmap(&mapA3);
     prefetch_tmap(&mapW);
     if (C::kStaged) prefetch_tmap(&mapC);
     for (int i = 0; i < S; ++i) {
@@ -210,7 +211,10 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
 #endif
           }
           const int mi = it->seg_map[s];
-          const CUtensorMap* am = (mi == 0) ? &mapA0 : ((mi == 1) ? &mapA1 : &mapA2);
+          const CUtensorMap* am = (mi == 0) ? &mapA0 : ((mi == 1) ? &mapA1 : ((mi == 2) ? &mapA2 : &mapA3));
+          // Cells without a cell state (no staging traffic) may read a second weight buffer: its
+          // map travels in the otherwise unused cell-state slot.
+          const CUtensorMap* wm = (!C::kStaged && it->w_map != 0) ? &mapC : &mapW;
           const int a_row = it->seg_row[s] + m_tile * BM;
           const int wk = it->seg_wk[s];
           const int nkb = it->seg_kb[s];
@@ -226,10 +230,10 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
             if (PAIR) {
               // Both CTAs' copies are counted on the leader's barrier; only the leader arms it.
               if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], C::kTxBytes);
-              tma_load_2d_pair_hint(sb, &mapW, lead_bar, wk + kb * BK, w_row, w_policy);
+              tma_load_2d_pair_hint(sb, wm, lead_bar, wk + kb * BK, w_row, w_policy);
             } else {
               mbar_arrive_expect_tx(&full_bar[stage], C::kTxBytes);
-              tma_load_2d_hint(sb, &mapW, &full_bar[stage], wk + kb * BK, w_row, w_policy);
+              tma_load_2d_hint(sb, wm, &full_bar[stage], wk + kb * BK, w_row, w_policy);
             }
             if (PERSIST && dep_tile0 >= 0) {
               // Activation columns [64 kb, 64 kb + 64) come from producer tiles up to n_last.
@@ -617,7 +621,7 @@ int launch_one(const CUtensorMap* maps, const CUtensorMap& mapW, const CUtensorM
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  if (cudaLaunchKernelEx(&cfg, kfn, maps[0], maps[1], maps[2], mapW, mapC, batch, plan, status) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kfn, maps[0], maps[1], maps[2], maps[3], mapW, mapC, batch, plan, status) != cudaSuccess) {
     cudaGetLastError();
     return FTB_ERR_LAUNCH;
   }
@@ -660,11 +664,12 @@ int launch_any(int dtype, int epi, int bn, const CUtensorMap* maps, const CUtens
 
 }  // namespace
 
-// Launches one wavefront level.  `maps` are the three activation tensor maps
+// Launches one wavefront level.  `maps` are the four activation tensor maps
 // (box 128 rows x 64 elements; LSTM outputs are stored through the map named by
 // each item's out_map), `mapW` the packed-weight map (box `bn` rows x 64
 // elements, or bn/2 rows when `pair` is set), `mapC` the fp32 cell-state map (box
-// 128 rows x 32 elements; LSTM only).  With `pair`, every item's m_tiles must be
+// 128 rows x 32 elements) for LSTM cells and, for the other epilogues, the map of the
+// second packed-weight buffer (items with w_map == 1).  With `pair`, every item's m_tiles must be
 // even.
 int launch_cell_gemm(int dtype, int epi, int bn, int pair, const CUtensorMap* maps, const CUtensorMap& mapW,
                      const CUtensorMap& mapC, const CellBatch& batch, int* status, int sm_count,

@@ -20,7 +20,7 @@ constexpr int kSimtThreads = 256;
 struct SimtArgs {
   const float* act[kNumActMaps];
   int32_t ld_act[kNumActMaps];
-  const float* w;  // packed weights [rows, ldw]
+  const float* w[kNumWeightMaps];  // packed weights [rows, ldw]
   int32_t ldw;
 };
 
@@ -50,7 +50,7 @@ cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ 
     const int lda = args.ld_act[it.seg_map[s]];
     const int row0 = it.seg_row[s] + m_tile * TM;
     const int klen = it.seg_kb[s] * 64;
-    const float* W = args.w + static_cast<size_t>(it.w_row0 + n_tile * TN) * args.ldw + it.seg_wk[s];
+    const float* W = args.w[it.w_map] + static_cast<size_t>(it.w_row0 + n_tile * TN) * args.ldw + it.seg_wk[s];
     for (int k0 = 0; k0 < klen; k0 += TK) {
       // A chunk: 32 rows x 32 k; one float4 per thread.
       {
@@ -115,14 +115,14 @@ cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ 
 
 // fp32 twin of launch_cell_gemm.  Tiles are 32 rows x 64 columns, so the
 // batch must have been tiled with m_tiles = ceil(rows / 32) and n_cols % 64 == 0.
-int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* w, int ldw,
+int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* const* w, int ldw,
                      const CellBatch& batch, cudaStream_t stream) {
   SimtArgs a;
   for (int i = 0; i < kNumActMaps; ++i) {
     a.act[i] = act[i];
     a.ld_act[i] = ld_act[i];
   }
-  a.w = w;
+  for (int i = 0; i < kNumWeightMaps; ++i) a.w[i] = w[i];
   a.ldw = ldw;
   if (batch.total_tiles <= 0) return FTB_OK;
   switch (epi) {

@@ -30,7 +30,7 @@ bool lstm_static_supported(int dtype, int D, int N, int I, int H, int G, int sm_
 int launch_lstm_static(int dtype, const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
                        int N, int I, int H, int G, int* done, int* status, unsigned long long* trace,
                        cudaStream_t stream);
-int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* w, int ldw,
+int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* const* w, int ldw,
                      const CellBatch& batch, cudaStream_t stream);
 int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I, int H, int dtype,
               cudaStream_t s);
@@ -40,7 +40,7 @@ namespace {
 
 constexpr size_t kWorkspaceBytes = 256;
 
-// Launch context for one family of cells (one weight buffer, up to three
+// Launch context for one family of cells (up to two weight buffers, up to four
 // activation buffers).
 struct CellLauncher {
   int dtype = FTB_BF16;
@@ -54,11 +54,12 @@ struct CellLauncher {
   // 16-bit path
   CUtensorMap maps[kNumActMaps];
   CUtensorMap mapW;
-  CUtensorMap mapC;  // fp32 cell state (LSTM); a copy of maps[0] otherwise
+  CUtensorMap mapC;  // fp32 cell state (LSTM); otherwise the second weight buffer's map (or a copy of mapW)
   // fp32 path
-  const float* act[kNumActMaps] = {nullptr, nullptr, nullptr};
-  int ld_act[kNumActMaps] = {0, 0, 0};
-  const float* w = nullptr;
+  const float* act[kNumActMaps] = {nullptr, nullptr, nullptr, nullptr};
+  int ld_act[kNumActMaps] = {0, 0, 0, 0};
+  const float* w = nullptr;   // weight buffer 0
+  const float* w2 = nullptr;  // weight buffer 1 (cells with w_map == 1), same row length
   int ldw = 0;
 
   int rows_per_tile() const { return dtype == FTB_F32 ? 32 : 128; }
@@ -89,10 +90,12 @@ struct CellLauncher {
       }
       b.total_tiles = tiles;
       int rc;
-      if (dtype == FTB_F32)
-        rc = launch_cell_simt(epi, act, ld_act, w, ldw, b, stream);
-      else
+      if (dtype == FTB_F32) {
+        const float* ws[kNumWeightMaps] = {w, w2 ? w2 : w};
+        rc = launch_cell_simt(epi, act, ld_act, ws, ldw, b, stream);
+      } else {
         rc = launch_cell_gemm(dtype, epi, bn, pair, maps, mapW, mapC, b, status, sm_count, stream);
+      }
       if (rc) return rc;
     }
     return FTB_OK;
@@ -120,7 +123,7 @@ CellItem blank_item() {
   it.out_row0 = 0;
   it.c_row0 = 0;
   it.out_map = 1;
-  it.pad_ = 0;
+  it.w_map = 0;
   return it;
 }
 
@@ -282,7 +285,7 @@ __global__ void plan_stacked_kernel(const StackedPlanArgs a) {
   it.out = a.hs + (static_cast<size_t>(l) * a.L + t) * a.N * a.H * a.es;
   it.out_row0 = (l * a.L + t) * a.N;
   it.out_map = 1;
-  it.pad_ = 0;
+  it.w_map = 0;
   it.c = a.c + static_cast<size_t>(l) * a.N * a.H;
   it.c_row0 = l * a.N;
   it.bias = a.bias_p ? a.bias_p + static_cast<size_t>(l) * 4 * a.H : nullptr;
@@ -408,6 +411,7 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
     rc = make_tmap_2d(&cl.maps[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, 128, 64);
     if (rc) return rc;
     cl.maps[2] = cl.maps[1];
+    cl.maps[3] = cl.maps[0];
     rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.w_box_rows(), 64);
     if (rc) return rc;
     rc = make_tmap_2d(&cl.mapC, c, FTB_F32, static_cast<uint64_t>(D) * N, H, H, 128, 32);
@@ -565,6 +569,7 @@ int ftb_lstm_stacked_varlen_fwd(const void* x, const void* Wp, const float* bias
     rc = make_tmap_2d(&cl.maps[1], hs, dtype, static_cast<uint64_t>(D) * T, H, H, 128, 64);
     if (rc) return rc;
     cl.maps[2] = cl.maps[1];
+    cl.maps[3] = cl.maps[0];
     rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.w_box_rows(), 64);
     if (rc) return rc;
     rc = make_tmap_2d(&cl.mapC, c, FTB_F32, static_cast<uint64_t>(D) * N, H, H, 128, 32);
@@ -701,6 +706,7 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
     rc = make_tmap_2d(&cl.maps[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, 128, 64);
     if (rc) return rc;
     cl.maps[2] = cl.maps[1];
+    cl.maps[3] = cl.maps[0];
     rc = make_tmap_2d(&cl.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, cl.w_box_rows(), 64);
     if (rc) return rc;
     rc = make_tmap_2d(&cl.mapC, c, FTB_F32, static_cast<uint64_t>(D) * max_dil * N, H, H, 128, 32);
@@ -807,76 +813,132 @@ int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* 
 
   const int K = 3 * H;
   const size_t es = dtype_size(dtype);
-  // Two launch contexts: direction x reads (X | hx | hy) with Wpx, direction y
-  // reads (Y | hx | hy) with Wpy.
-  CellLauncher dir[2];
-  for (int d = 0; d < 2; ++d) {
-    CellLauncher& cl = dir[d];
-    cl.dtype = dtype;
-    cl.epi = EPI_TANH;
-    cl.n_cols = H;
-    cl.ld_out = H;
-    cl.ld_c = H;
-    cl.status = status;
-    cl.stream = stream;
-    cl.sm_count = current_sm_count();
-    const void* in = d == 0 ? X : Y;
-    const void* wp = d == 0 ? Wpx : Wpy;
-    if (dtype == FTB_F32) {
-      cl.act[0] = static_cast<const float*>(in);
-      cl.act[1] = static_cast<const float*>(hx);
-      cl.act[2] = static_cast<const float*>(hy);
-      cl.ld_act[0] = cl.ld_act[1] = cl.ld_act[2] = H;
-      cl.w = static_cast<const float*>(wp);
-      cl.ldw = K;
-    } else {
-      cl.bn = pick_bn(H, 128);
-      if (cl.bn == 0) return FTB_ERR_ARG;
-      const uint64_t grid_rows = static_cast<uint64_t>(A) * B * N;
-      rc = make_tmap_2d(&cl.maps[0], in, dtype, grid_rows, H, H, 128, 64);
-      if (rc) return rc;
-      rc = make_tmap_2d(&cl.maps[1], hx, dtype, grid_rows * D, H, H, 128, 64);
-      if (rc) return rc;
-      rc = make_tmap_2d(&cl.maps[2], hy, dtype, grid_rows * D, H, H, 128, 64);
-      if (rc) return rc;
-      rc = make_tmap_2d(&cl.mapW, wp, dtype, static_cast<uint64_t>(D) * H, K, K, cl.bn, 64);
-      if (rc) return rc;
-      cl.mapC = cl.maps[0];
-    }
+  // One launch context for both directions: activation buffers 0..3 = X, Y, hx, hy; weight
+  // buffer 0 = direction x, 1 = direction y.  Direction x reads (hx | hy | X or hx below),
+  // direction y reads (hx | hy | Y or hy below).
+  CellLauncher cl;
+  cl.dtype = dtype;
+  cl.epi = EPI_TANH;
+  cl.n_cols = H;
+  cl.ld_out = H;
+  cl.ld_c = H;
+  cl.status = status;
+  cl.stream = stream;
+  cl.sm_count = current_sm_count();
+  if (dtype == FTB_F32) {
+    cl.act[0] = static_cast<const float*>(X);
+    cl.act[1] = static_cast<const float*>(Y);
+    cl.act[2] = static_cast<const float*>(hx);
+    cl.act[3] = static_cast<const float*>(hy);
+    cl.ld_act[0] = cl.ld_act[1] = cl.ld_act[2] = cl.ld_act[3] = H;
+    cl.w = static_cast<const float*>(Wpx);
+    cl.w2 = static_cast<const float*>(Wpy);
+    cl.ldw = K;
+  } else {
+    cl.bn = pick_bn(H, 128);
+    if (cl.bn == 0) return FTB_ERR_ARG;
+    const uint64_t grid_rows = static_cast<uint64_t>(A) * B * N;
+    rc = make_tmap_2d(&cl.maps[0], X, dtype, grid_rows, H, H, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.maps[1], Y, dtype, grid_rows, H, H, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.maps[2], hx, dtype, grid_rows * D, H, H, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.maps[3], hy, dtype, grid_rows * D, H, H, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.mapW, Wpx, dtype, static_cast<uint64_t>(D) * H, K, K, cl.bn, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.mapC, Wpy, dtype, static_cast<uint64_t>(D) * H, K, K, cl.bn, 64);
+    if (rc) return rc;
   }
 
-  std::vector<CellItem> items[2];
-  for (int m = 0; m <= (D - 1) + (A - 1) + (B - 1); ++m) {
-    items[0].clear();
-    items[1].clear();
-    for (int d = 0; d < D; ++d) {
+  // Cell (d, a, b) of direction dirn, and which earlier cell each of its K segments reads
+  // (-1: an input of the call).  Anti-diagonal level = d + a + b.
+  auto cell_index = [&](int d, int a, int b) { return (static_cast<int64_t>(d) * A + a) * B + b; };
+  auto make_item = [&](int d, int a, int b, int dirn, int64_t (&src)[kMaxSeg]) {
+    CellItem it = blank_item();
+    const int64_t cell = cell_index(d, a, b);
+    for (int s = 0; s < kMaxSeg; ++s) src[s] = -1;
+    // The cell's own input first: it is an input of the call (layer 0) or was finished two
+    // levels ago, so its K blocks run while the two neighbours of the previous level finish.
+    if (d == 0) {
+      add_seg(it, dirn, (static_cast<int64_t>(a) * B + b) * N, H, 2 * H);
+    } else {
+      src[it.nseg] = cell_index(d - 1, a, b) * 2 + dirn;
+      add_seg(it, 2 + dirn, cell_index(d - 1, a, b) * N, H, 2 * H);
+    }
+    if (a > 0) {
+      src[it.nseg] = cell_index(d, a - 1, b) * 2 + 0;
+      add_seg(it, 2, cell_index(d, a - 1, b) * N, H, 0);
+    }
+    if (b > 0) {
+      src[it.nseg] = (cell - 1) * 2 + 1;
+      add_seg(it, 3, (cell - 1) * N, H, H);
+    }
+    it.w_row0 = d * H;
+    it.w_map = dirn;
+    it.rows = N;
+    it.out = static_cast<char*>(dirn == 0 ? hx : hy) + static_cast<size_t>(cell) * N * H * es;
+    const float* bias = dirn == 0 ? bias_x : bias_y;
+    it.bias = bias ? bias + static_cast<size_t>(d) * H : nullptr;
+    return it;
+  };
+
+  const int n_items = 2 * D * A * B;
+  const int levels = (D - 1) + (A - 1) + (B - 1) + 1;
+  const PlanLayout lay = plan_layout(n_items, 0);
+  const bool persistent = dtype != FTB_F32 && workspace_bytes >= lay.total;
+  if (persistent) {
+    // One cooperative launch for the whole grid: items in level order, each K segment waiting
+    // for the one earlier cell it reads.
+    std::vector<CellItem> order;
+    order.reserve(n_items);
+    std::vector<int> index_of(n_items, -1);
+    std::vector<int64_t> srcs;
+    srcs.reserve(static_cast<size_t>(n_items) * kMaxSeg);
+    for (int m = 0; m < levels; ++m)
+      for (int d = 0; d < D; ++d)
+        for (int a = 0; a < A; ++a) {
+          const int b = m - d - a;
+          if (b < 0 || b >= B) continue;
+          for (int dirn = 0; dirn < 2; ++dirn) {
+            int64_t src[kMaxSeg];
+            index_of[cell_index(d, a, b) * 2 + dirn] = static_cast<int>(order.size());
+            order.push_back(make_item(d, a, b, dirn, src));
+            for (int s = 0; s < kMaxSeg; ++s) srcs.push_back(src[s]);
+          }
+        }
+    std::vector<int32_t> deps(static_cast<size_t>(n_items) * kMaxSeg * 2, -1);
+    for (int i = 0; i < n_items; ++i)
+      for (int s = 0; s < kMaxSeg; ++s) {
+        const int64_t src = srcs[static_cast<size_t>(i) * kMaxSeg + s];
+        if (src >= 0) deps[(i * kMaxSeg + s) * 2 + 0] = deps[(i * kMaxSeg + s) * 2 + 1] = index_of[src];
+      }
+    rc = run_persistent(cl, order, deps, static_cast<char*>(workspace), lay);
+    if (rc != FTB_ERR_LAUNCH) return rc;  // a refused cooperative launch falls back to levels
+  }
+
+  std::vector<CellItem> items;
+  for (int m = 0; m < levels; ++m) {
+    items.clear();
+    for (int d = 0; d < D; ++d)
       for (int a = 0; a < A; ++a) {
         const int b = m - d - a;
         if (b < 0 || b >= B) continue;
-        const int64_t cell = (static_cast<int64_t>(d) * A + a) * B + b;
         for (int dirn = 0; dirn < 2; ++dirn) {
-          CellItem it = blank_item();
-          if (a > 0) add_seg(it, 1, ((static_cast<int64_t>(d) * A + a - 1) * B + b) * N, H, 0);
-          if (b > 0) add_seg(it, 2, (cell - 1) * N, H, H);
-          if (d == 0)
-            add_seg(it, 0, (static_cast<int64_t>(a) * B + b) * N, H, 2 * H);
-          else
-            add_seg(it, dirn == 0 ? 1 : 2, ((static_cast<int64_t>(d - 1) * A + a) * B + b) * N, H, 2 * H);
-          it.w_row0 = d * H;
-          it.rows = N;
-          it.out = static_cast<char*>(dirn == 0 ? hx : hy) + static_cast<size_t>(cell) * N * H * es;
-          const float* bias = dirn == 0 ? bias_x : bias_y;
-          it.bias = bias ? bias + static_cast<size_t>(d) * H : nullptr;
-          items[dirn].push_back(it);
+          int64_t src[kMaxSeg];
+          items.push_back(make_item(d, a, b, dirn, src));
         }
       }
-    }
-    for (int dirn = 0; dirn < 2; ++dirn) {
-      rc = dir[dirn].run(items[dirn]);
-      if (rc) return rc;
-    }
+    rc = cl.run(items);
+    if (rc) return rc;
   }
   return FTB_OK;
+}
+
+size_t ftb_grid_rnn_workspace_bytes(int D, int A, int B) {
+  if (D <= 0 || A <= 0 || B <= 0) return kWorkspaceBytes;
+  return plan_layout(2 * D * A * B, 0).total;
 }
 
 int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, int dtype, const int* tuning,
@@ -908,7 +970,7 @@ int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, i
     cl.pair = tune.use_pair(M);
     rc = make_tmap_2d(&cl.maps[0], A, dtype, M, K, K, 128, 64);
     if (rc) return rc;
-    cl.maps[1] = cl.maps[2] = cl.maps[0];
+    cl.maps[1] = cl.maps[2] = cl.maps[3] = cl.maps[0];
     rc = make_tmap_2d(&cl.mapW, Bt, dtype, N, K, K, cl.w_box_rows(), 64);
     if (rc) return rc;
     cl.mapC = cl.maps[0];

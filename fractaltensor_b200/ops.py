@@ -201,8 +201,9 @@ def grid_pack_weights(i2h, h2h):
     return Wp
 
 
-def grid_rnn(X, Y, Wpx, Wpy, bias_x=None, bias_y=None):
-    """X,Y: [A,B,N,H]; Wpx,Wpy: [D,H,3H]; bias fp32 [D,H] -> (hx, hy) each [D,A,B,N,H]."""
+def grid_rnn(X, Y, Wpx, Wpy, bias_x=None, bias_y=None, schedule=0):
+    """X,Y: [A,B,N,H]; Wpx,Wpy: [D,H,3H]; bias fp32 [D,H] -> (hx, hy) each [D,A,B,N,H].
+    schedule: 0 auto (one persistent kernel for 16-bit inputs), 1 one launch per anti-diagonal."""
     _req(X, "X")
     _req(Y, "Y", X.dtype)
     _req(Wpx, "Wpx", X.dtype)
@@ -216,10 +217,12 @@ def grid_rnn(X, Y, Wpx, Wpy, bias_x=None, bias_y=None):
             _req(b, "bias", torch.float32)
     hx = torch.empty(D, A, B, N, H, dtype=X.dtype, device=X.device)
     hy = torch.empty_like(hx)
-    ws = workspace(X.device)
+    # The library picks the persistent schedule when the workspace has room for its tables.
+    ws = workspace(X.device, 0 if schedule == 1 else lib.ftb_grid_rnn_workspace_bytes(D, A, B))
+    ws_bytes = lib.ftb_workspace_bytes() if schedule == 1 else ws.numel()
     with torch.cuda.device(X.device):
         check(lib.ftb_grid_rnn_fwd(_ptr(X), _ptr(Y), _ptr(Wpx), _ptr(Wpy), _ptr(bias_x), _ptr(bias_y), _ptr(hx),
-                                   _ptr(hy), D, A, B, N, H, _dtype_code(X), _ptr(ws), ws.numel(), _stream()),
+                                   _ptr(hy), D, A, B, N, H, _dtype_code(X), _ptr(ws), ws_bytes, _stream()),
               "ftb_grid_rnn_fwd")
     return hx, hy
 

@@ -73,7 +73,7 @@ def main():
         X, Y = rnd(a.A, a.A, a.N, a.H).to(dt), rnd(a.A, a.A, a.N, a.H).to(dt)
         Wpx = ops.grid_pack_weights(uni(1 / 16, a.D, 2 * a.H, a.H).to(dt), uni(1 / 16, a.D, a.H, a.H).to(dt))
         Wpy = ops.grid_pack_weights(uni(1 / 16, a.D, 2 * a.H, a.H).to(dt), uni(1 / 16, a.D, a.H, a.H).to(dt))
-        fn = lambda: ops.grid_rnn(X, Y, Wpx, Wpy)
+        fn = lambda: ops.grid_rnn(X, Y, Wpx, Wpy, schedule=a.schedule)
     elif a.case == "b2b":
         s = 1 / math.sqrt(128)
         A_, B_, C_ = (rnd(a.batch, a.M, 128) * s).to(dt), (rnd(a.batch, 128, 128) * s).to(dt), (rnd(a.batch, 128, 128) * s).to(dt)

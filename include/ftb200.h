@@ -146,7 +146,11 @@ int ftb_grid_pack_weights(const void* i2h, const void* h2h, void* Wp, int H, int
  * (benchmarks/rnn/fractaltensor/grid_lstm/regions/region{1..8}.h).
  * X,Y: [A,B,N,H] inputs of the x and y directions at grid point (a,b);
  * Wpx,Wpy: [D,H,3H] from ftb_grid_pack_weights; bias_x,bias_y: fp32 [D,H] or NULL;
- * hx,hy (out): [D,A,B,N,H].  state_x = hx[a-1][b], state_y = hy[a][b-1]. */
+ * hx,hy (out): [D,A,B,N,H].  state_x = hx[a-1][b], state_y = hy[a][b-1].
+ * Both directions of a level run in one launch.  With ftb_grid_rnn_workspace_bytes(D, A, B)
+ * bytes of workspace (16-bit dtypes) the whole grid runs as one persistent launch whose
+ * schedule tables are copied from host memory on `stream`; with less, one launch per level. */
+size_t ftb_grid_rnn_workspace_bytes(int D, int A, int B);
 int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* Wpy, const float* bias_x,
                      const float* bias_y, void* hx, void* hy, int D, int A, int B, int N, int H, int dtype,
                      void* workspace, size_t workspace_bytes, void* stream);

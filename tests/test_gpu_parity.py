@@ -383,14 +383,14 @@ def test_dilated_config5a_prefix(ops):
 
 
 # -------------------------------------------------------------------- grid RNN
-def _run_grid(ops, X, Y, p):
+def _run_grid(ops, X, Y, p, **kw):
     Xd, Yd = _dev(X, Y)
     pd = {k: (None if v is None else v.cuda()) for k, v in p.items()}
     Wpx = ops.grid_pack_weights(pd["i2h_x"], pd["h2h_x"])
     Wpy = ops.grid_pack_weights(pd["i2h_y"], pd["h2h_y"])
     bx = None if pd["b_x"] is None else pd["b_x"].float()
     by = None if pd["b_y"] is None else pd["b_y"].float()
-    hx, hy = ops.grid_rnn(Xd, Yd, Wpx, Wpy, bx, by)
+    hx, hy = ops.grid_rnn(Xd, Yd, Wpx, Wpy, bx, by, **kw)
     ops.check_status()
     return hx, hy
 
@@ -433,6 +433,25 @@ def test_grid_rnn(ops, dt, shape):
     check = _assert_fp32 if dt == torch.float32 else _assert_16
     check(hx, rx)
     check(hy, ry)
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 4, 16, 64), (3, 5, 4, 130, 128), (1, 9, 7, 64, 256)])
+def test_grid_schedules_agree_bit_for_bit(ops, shape):
+    """One launch per anti-diagonal and the single persistent launch: same arithmetic, same bits."""
+    from fractaltensor_b200 import _lib
+    D, A, B, N, H = shape
+    X, Y, p = dense.make_grid_inputs(D, A, B, N, H, 6, 1.0 / 8, dtype=torch.bfloat16, bias=True)
+    n0 = _lib.lib.ftb_launch_count()
+    hx1, hy1 = _run_grid(ops, X, Y, p, schedule=1)
+    n1 = _lib.lib.ftb_launch_count()
+    hx2, hy2 = _run_grid(ops, X, Y, p)
+    n2 = _lib.lib.ftb_launch_count()
+    assert torch.equal(hx1, hx2) and torch.equal(hy1, hy2)
+    # both runs pack the weights (two launches); levels: one launch each; persistent: one in all
+    assert (n1 - n0) - (n2 - n1) == (D + A + B - 2) - 1
+    rx, ry = _grid_ref(X, Y, p)
+    _assert_16(hx2, rx)
+    _assert_16(hy2, ry)
 
 
 def test_grid_config5b_corner(ops):
