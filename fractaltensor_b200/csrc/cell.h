@@ -41,6 +41,8 @@ struct CellItem {
   int32_t c_row0;    // 16-bit LSTM path: row of `c` in the cell-state tensor map
   int32_t out_map;   // activation map index that covers `out`
   int32_t w_map;     // which packed weight buffer the cell reads (0 or 1)
+  int32_t skip;      // persistent schedule: index of the item that holds tile (tile0 + grid size)
+  int32_t pad_;
 };
 
 struct CellBatch {
@@ -79,6 +81,13 @@ struct PlanView {
   int32_t* c_done;        // [total_tiles] (fine)
   int32_t fine;
   int32_t units_per_tile; // activation columns produced by one tile (fine)
+  // Finding the item of a tile without walking the table (every step of a walk is a dependent
+  // load from L2): either all items have the same number of tiles (tiles_per_item > 0), or
+  // cta_first[cta] is the item of the CTA's first tile and CellItem::skip leads from the item
+  // of one of its tiles to (at most a few items before) the item of its next tile.
+  int32_t tiles_per_item;
+  int32_t pad_;
+  const int32_t* cta_first;
   unsigned long long* trace;  // debug builds (FTB_TRACE): [total_tiles][4] globaltimer stamps, else nullptr
 };
 

@@ -76,10 +76,26 @@ struct ItemCursor {
   const CellItem* items;
   int n_items;
   int idx;
-  __device__ ItemCursor(const CellBatch& b, const PlanView& p) : n_items(b.n_items), idx(0) {
+  int tiles_per_item;
+  bool first;
+  const int32_t* cta_first;
+  __device__ ItemCursor(const CellBatch& b, const PlanView& p)
+      : n_items(b.n_items), idx(0), tiles_per_item(PERSIST ? p.tiles_per_item : 0), first(true),
+        cta_first(PERSIST ? p.cta_first : nullptr) {
     items = PERSIST ? p.items : b.items;
   }
   __device__ __forceinline__ const CellItem* seek(int tile) {
+    if (PERSIST && tiles_per_item > 0) {
+      idx = tile / tiles_per_item;
+      return items + idx;
+    }
+    if (PERSIST && cta_first != nullptr) {
+      // Jump close to the item, then walk the last few steps (every step of a walk through the
+      // table is a dependent load from L2).
+      const int hint = first ? cta_first[blockIdx.x] : items[idx].skip;
+      idx = hint > idx ? hint : idx;
+      first = false;
+    }
     while (idx + 1 < n_items && tile >= items[idx + 1].tile0) ++idx;
     return items + idx;
   }
@@ -448,6 +464,9 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         if (!__all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, &s_abort, status, FTB_ERR_TIMEOUT_MMA)))
           break;
         tc_fence_after();
+#ifdef FTB_TRACE
+        if (PERSIST && plan.trace && warp == 2 && lane == 0) plan.trace[tile * 4 + 2] = globaltimer_ns();
+#endif
 #pragma unroll 1
         for (int cc = 0; cc < kChunksPerWarp; ++cc) {
           const int ch = half * kChunksPerWarp + cc;
@@ -479,6 +498,9 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         __syncwarp();
         if (lane == 0) {
           if (PERSIST) red_release_gpu_add(plan.fine ? plan.tile_done + tile : plan.done + cur.idx, 1);
+#ifdef FTB_TRACE
+          if (PERSIST && plan.trace && warp == 2) plan.trace[tile * 4 + 3] = globaltimer_ns();
+#endif
           if (PAIR)
             mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
           else
@@ -674,7 +696,7 @@ int launch_any(int dtype, int epi, int bn, const CUtensorMap* maps, const CUtens
 int launch_cell_gemm(int dtype, int epi, int bn, int pair, const CUtensorMap* maps, const CUtensorMap& mapW,
                      const CUtensorMap& mapC, const CellBatch& batch, int* status, int sm_count,
                      cudaStream_t stream) {
-  PlanView none = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, nullptr};
+  PlanView none = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, nullptr, nullptr};
   if (pair) return launch_any<false, true>(dtype, epi, bn, maps, mapW, mapC, batch, none, status, sm_count, stream);
   return launch_any<false, false>(dtype, epi, bn, maps, mapW, mapC, batch, none, status, sm_count, stream);
 }

@@ -124,6 +124,8 @@ CellItem blank_item() {
   it.c_row0 = 0;
   it.out_map = 1;
   it.w_map = 0;
+  it.skip = 0;
+  it.pad_ = 0;
   return it;
 }
 
@@ -167,8 +169,9 @@ struct Tuning {
 // ---------------------------------------------------------- persistent schedule
 // Workspace layout of a persistent stacked-LSTM call: status block, then the
 // item table, the dependency table, the completion targets and the counters.
+constexpr int kMaxCtas = 1024;  // entries of the per-CTA first-item table
 struct PlanLayout {
-  size_t items, dep, target, done, tile_done, c_done, counters_end, trace, total;
+  size_t items, dep, target, cta_first, done, tile_done, c_done, counters_end, trace, total;
 };
 PlanLayout plan_layout(int n_items, int max_tiles_per_item = 64) {
   PlanLayout p;
@@ -176,7 +179,8 @@ PlanLayout plan_layout(int n_items, int max_tiles_per_item = 64) {
   p.items = kWorkspaceBytes;
   p.dep = up(p.items + sizeof(CellItem) * n_items);
   p.target = up(p.dep + sizeof(int32_t) * 2 * kMaxSeg * n_items);
-  p.done = up(p.target + sizeof(int32_t) * n_items);
+  p.cta_first = up(p.target + sizeof(int32_t) * n_items);
+  p.done = up(p.cta_first + sizeof(int32_t) * kMaxCtas);
   const size_t max_tiles = static_cast<size_t>(n_items) * max_tiles_per_item;
   p.tile_done = up(p.done + sizeof(int32_t) * 2 * n_items);
   p.c_done = up(p.tile_done + sizeof(int32_t) * max_tiles);
@@ -191,7 +195,7 @@ PlanLayout plan_layout(int n_items, int max_tiles_per_item = 64) {
 }
 
 int run_persistent(const CellLauncher& cl, std::vector<CellItem>& items, const std::vector<int32_t>& deps,
-                   char* ws, const PlanLayout& lay) {
+                   char* ws, const PlanLayout& lay, size_t ws_bytes = 0) {
   const int n = static_cast<int>(items.size());
   const int n_tiles_n = (cl.n_cols + cl.cols_per_tile() - 1) / cl.cols_per_tile();
   std::vector<int32_t> target(n);
@@ -202,6 +206,29 @@ int run_persistent(const CellLauncher& cl, std::vector<CellItem>& items, const s
     tiles += items[i].m_tiles * n_tiles_n;
     target[i] = 8 * items[i].m_tiles * n_tiles_n;  // eight epilogue warps per tile
   }
+  // Tile -> item lookups without a table walk on the device (the grid size computed here is
+  // the one launch_cell_gemm_persistent uses): for every item the item that holds the tile one
+  // grid stride further, and for every CTA the item of its first tile.
+  int grid = std::min(tiles, cl.sm_count);
+  if (cl.pair) grid &= ~1;
+  if (grid <= 0) return FTB_OK;
+  if (grid > kMaxCtas) return FTB_ERR_ARG;
+  {
+    int j = 0;
+    for (int i = 0; i < n; ++i) {
+      const int t = items[i].tile0 + grid;
+      while (j + 1 < n && t >= items[j + 1].tile0) ++j;
+      items[i].skip = j;
+    }
+  }
+  std::vector<int32_t> cta_first(grid);
+  {
+    int j = 0;
+    for (int c = 0; c < grid; ++c) {
+      while (j + 1 < n && c >= items[j + 1].tile0) ++j;
+      cta_first[c] = j;
+    }
+  }
   // The host vectors die with this call; cudaMemcpyAsync from pageable memory returns once the
   // bytes are staged.
   if (cudaMemcpyAsync(ws + lay.items, items.data(), sizeof(CellItem) * n, cudaMemcpyHostToDevice, cl.stream) !=
@@ -210,6 +237,8 @@ int run_persistent(const CellLauncher& cl, std::vector<CellItem>& items, const s
                       cl.stream) != cudaSuccess ||
       cudaMemcpyAsync(ws + lay.target, target.data(), sizeof(int32_t) * n, cudaMemcpyHostToDevice, cl.stream) !=
           cudaSuccess ||
+      cudaMemcpyAsync(ws + lay.cta_first, cta_first.data(), sizeof(int32_t) * grid, cudaMemcpyHostToDevice,
+                      cl.stream) != cudaSuccess ||
       cudaMemsetAsync(ws + lay.done, 0, sizeof(int32_t) * 2 * n, cl.stream) != cudaSuccess)
     return FTB_ERR_LAUNCH;
   CellBatch header;
@@ -221,7 +250,12 @@ int run_persistent(const CellLauncher& cl, std::vector<CellItem>& items, const s
   header.pad_ = 0;
   PlanView pv = {reinterpret_cast<const CellItem*>(ws + lay.items), reinterpret_cast<const int32_t*>(ws + lay.dep),
                  reinterpret_cast<const int32_t*>(ws + lay.target), reinterpret_cast<int32_t*>(ws + lay.done),
-                 nullptr, nullptr, 0, 0, nullptr};
+                 nullptr, nullptr, 0, 0, 0, 0, reinterpret_cast<const int32_t*>(ws + lay.cta_first), nullptr};
+#ifdef FTB_TRACE
+  // Debug build: four time stamps per tile behind the tables, when the caller left room.
+  if (ws_bytes >= lay.total + static_cast<size_t>(32) * tiles)
+    pv.trace = reinterpret_cast<unsigned long long*>(ws + lay.total);
+#endif
   return launch_cell_gemm_persistent(cl.dtype, cl.epi, cl.bn, cl.pair, cl.maps, cl.mapW, cl.mapC, header, pv,
                                      cl.status, cl.sm_count, cl.stream);
 }
@@ -286,6 +320,8 @@ __global__ void plan_stacked_kernel(const StackedPlanArgs a) {
   it.out_row0 = (l * a.L + t) * a.N;
   it.out_map = 1;
   it.w_map = 0;
+  it.skip = 0;
+  it.pad_ = 0;
   it.c = a.c + static_cast<size_t>(l) * a.N * a.H;
   it.c_row0 = l * a.N;
   it.bias = a.bias_p ? a.bias_p + static_cast<size_t>(l) * 4 * a.H : nullptr;
@@ -479,7 +515,8 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
     header.total_tiles = n_cells * pa.tiles_per_item;
     header.pad_ = 0;
     PlanView pv = {pa.items, pa.dep, pa.target, done, reinterpret_cast<int32_t*>(ws + lay.tile_done),
-                   reinterpret_cast<int32_t*>(ws + lay.c_done), tune.fine_deps == 1 ? 1 : 0, cl.bn / 4, nullptr};
+                   reinterpret_cast<int32_t*>(ws + lay.c_done), tune.fine_deps == 1 ? 1 : 0, cl.bn / 4,
+                   pa.tiles_per_item, 0, nullptr, nullptr};
 #ifdef FTB_TRACE
     pv.trace = reinterpret_cast<unsigned long long*>(ws + lay.trace);
 #endif
@@ -636,7 +673,7 @@ int ftb_lstm_stacked_varlen_fwd(const void* x, const void* Wp, const float* bias
         if (l > 0) deps[(me * kMaxSeg + 0) * 2 + 0] = deps[(me * kMaxSeg + 0) * 2 + 1] = index_of[(l - 1) * L + t];
         if (t > 0) deps[(me * kMaxSeg + 1) * 2 + 0] = deps[(me * kMaxSeg + 1) * 2 + 1] = index_of[l * L + t - 1];
       }
-    rc = run_persistent(cl, order, deps, static_cast<char*>(workspace), lay);
+    rc = run_persistent(cl, order, deps, static_cast<char*>(workspace), lay, workspace_bytes);
     if (rc != FTB_ERR_LAUNCH || tune.schedule != 0) return rc;
   }
 
@@ -785,7 +822,7 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
           deps[(me * kMaxSeg + 1) * 2 + 0] = deps[(me * kMaxSeg + 1) * 2 + 1] = prev;
         }
       }
-    return run_persistent(cl, order, deps, static_cast<char*>(workspace), lay);
+    return run_persistent(cl, order, deps, static_cast<char*>(workspace), lay, workspace_bytes);
   }
   for (auto& kv : levels) {
     rc = cl.run(kv.second);
@@ -914,7 +951,7 @@ int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* 
         const int64_t src = srcs[static_cast<size_t>(i) * kMaxSeg + s];
         if (src >= 0) deps[(i * kMaxSeg + s) * 2 + 0] = deps[(i * kMaxSeg + s) * 2 + 1] = index_of[src];
       }
-    rc = run_persistent(cl, order, deps, static_cast<char*>(workspace), lay);
+    rc = run_persistent(cl, order, deps, static_cast<char*>(workspace), lay, workspace_bytes);
     if (rc != FTB_ERR_LAUNCH) return rc;  // a refused cooperative launch falls back to levels
   }
 
