@@ -124,6 +124,84 @@ def run_reference(args, rank):
     }))
 
 
+def other_configs(ops, dense, dev, pk):
+    """The path's other BASELINE configurations, each timed alone on the resident data with CUDA
+    events after 3 warm-up calls (rank 0, single-GPU runs only): the B2B GEMM against the HBM
+    roofline, attention against the tensor roofline, and the latency-bound wavefronts as times."""
+    import math
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ops.check_status()
+        return e0.elapsed_time(e1) / iters
+
+    out = []
+    g = torch.Generator(device=dev).manual_seed(1)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    uni = lambda b, *s: (torch.rand(*s, device=dev, generator=g) * 2 - 1) * b
+
+    # config 2: 16 x [16384,128].[128,128].[128,128], fp16; three buffer sets in turn (each > L2)
+    s = 1 / math.sqrt(128)
+    sets = [((rnd(16, 16384, 128) * s).half(), (rnd(16, 128, 128) * s).half(), (rnd(16, 128, 128) * s).half(),
+             torch.empty(16, 16384, 128, device=dev, dtype=torch.half)) for _ in range(3)]
+    turn = [0]
+
+    def b2b():
+        turn[0] = (turn[0] + 1) % 3
+        ops.b2b_gemm(*sets[turn[0]])
+
+    ms = timed(b2b, 60)
+    nbytes = 16 * (2 * 16384 * 128 + 2 * 128 * 128) * 2
+    out.append({"config": "2: fused two GEMMs 16x(16384x128x128x128) fp16", "ms": ms, "bound": "hbm",
+                "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": pk["hbm"], "unit": "GB/s",
+                "frac": nbytes / (ms * 1e-3) / 1e9 / pk["hbm"], "tflops": 16 * 4 * 16384 * 128 * 128 / (ms * 1e-3) / 1e12,
+                "cache": "three rotating buffer sets of 135 MB"})
+    del sets
+
+    # config 3: attention B16 h16 S2048 d128 fp16 (q, k, v, o: 537 MB > L2)
+    q, k, v = (rnd(16, 16, 2048, 128).half() for _ in range(3))
+    o = torch.empty_like(q)
+    ms = timed(lambda: ops.flash_attention(q, k, v, scale=1 / math.sqrt(128), out=o), 20)
+    fl = 4 * 16 * 16 * 2048 * 2048 * 128
+    out.append({"config": "3: flash attention B16 h16 S2048 d128 fp16", "ms": ms, "bound": "tensor",
+                "achieved": fl / (ms * 1e-3) / 1e12, "peak": pk["burst"], "unit": "TFLOP/s",
+                "frac": fl / (ms * 1e-3) / 1e12 / pk["burst"]})
+    del q, k, v, o
+
+    # config 5a: dilated LSTM, 6 layers, dilation 2^l, H256 N256 L512 fp16
+    x = rnd(512, 256, 256).half()
+    Wp, _ = ops.lstm_pack_weights(uni(1 / 16, 6, 4, 256, 256).half(), uni(1 / 16, 6, 4, 256, 256).half())
+    dil = [2 ** l for l in range(6)]
+    ms = timed(lambda: ops.lstm_dilated(x, Wp, dil), 5)
+    out.append({"config": "5a: dilated LSTM 6 layers H256 N256 L512 fp16", "ms": ms,
+                "samples_steps_per_s": 256 * 512 / (ms * 1e-3), "bound": "latency (about 520 dependent levels)"})
+
+    # config 5b: grid RNN 32x32, H256, N64, fp16
+    X, Y = rnd(32, 32, 64, 256).half(), rnd(32, 32, 64, 256).half()
+    Wpx = ops.grid_pack_weights(uni(1 / 16, 1, 512, 256).half(), uni(1 / 16, 1, 256, 256).half())
+    Wpy = ops.grid_pack_weights(uni(1 / 16, 1, 512, 256).half(), uni(1 / 16, 1, 256, 256).half())
+    ms = timed(lambda: ops.grid_rnn(X, Y, Wpx, Wpy), 10)
+    out.append({"config": "5b: grid RNN 32x32 H256 N64 fp16", "ms": ms,
+                "cells_per_s": 32 * 32 * 64 / (ms * 1e-3), "bound": "latency (63 anti-diagonals)"})
+
+    # config 1: stacked LSTM fp32 D4 H256 N32 L64 (CUDA cores; the reference's own CPU-runnable case)
+    x1, W1, U1, _ = dense.make_lstm_inputs(4, 64, 32, 256, 256, 0, 1.0 / 16)
+    Wp1, _ = ops.lstm_pack_weights(W1.to(dev), U1.to(dev))
+    x1 = x1.to(dev)
+    ms = timed(lambda: ops.lstm_stacked(x1, Wp1), 10)
+    out.append({"config": "1: stacked LSTM fp32 D4 H256 N32 L64", "ms": ms,
+                "samples_steps_per_s": 32 * 64 / (ms * 1e-3), "bound": "latency (67 levels), fp32 on CUDA cores"})
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -133,6 +211,7 @@ def main():
     ap.add_argument("--layers-per-group", type=int, default=0)
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ftb200" else args.warmup
 
@@ -282,6 +361,9 @@ def main():
                 "kernel": "lstm_static_kernel<bf16> (persistent, CTA pairs, static tile ownership)",
                 "launches_per_step": launches / args.steps, "dominant_launches_per_step": 1,
                 "avg_launch_us": 1e3 * ms_per_step, "flops_per_launch": flops_per_step}
+    others = None
+    if world == 1 and not args.no_other_configs:
+        others = other_configs(ops, dense, dev, pk)
     cpu = None
     if not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
@@ -301,7 +383,7 @@ def main():
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_pinned.numel() * 2,
                 "d2h_bytes_per_step": out_pinned.numel() * 2},
-        "gpu_launches": int(launches), "clocks": clocks,
+        "gpu_launches": int(launches), "clocks": clocks, "other_configs": others,
     }))
     if world > 1:
         dist.destroy_process_group()
