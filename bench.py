@@ -246,17 +246,44 @@ def main():
     out_pinned = torch.empty(L, N, H, dtype=torch.bfloat16).pin_memory()
     gathered = torch.empty(world * L, N, H, dtype=torch.bfloat16, device=dev) if world > 1 else None
 
+    # Multi-GPU steps: the all-gather of step i's output runs on its own stream while step i+1's
+    # wavefront computes into the other hidden-state buffer; a step is complete when its gather is.
+    s_comm = torch.cuda.Stream(device=dev) if world > 1 else None
+    hs_pair = [hs, torch.empty_like(hs)] if world > 1 else [hs]
+    gathered_pair = [gathered, torch.empty_like(gathered)] if world > 1 else None
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_gathered = [torch.cuda.Event() for _ in range(2)]
+    res_state = {"i": 0}
+
     def step_resident():
-        ops.lstm_stacked(x_dev, Wp, None, hs, c, layers_per_group=args.layers_per_group, bn=args.bn)
+        if world == 1:
+            ops.lstm_stacked(x_dev, Wp, None, hs, c, layers_per_group=args.layers_per_group, bn=args.bn)
+            return
+        i = res_state["i"]
+        b = i & 1
+        cur = torch.cuda.current_stream()
+        if i >= 2:
+            cur.wait_event(ev_gathered[b])  # hs_pair[b] was read by the gather of step i-2
+        ops.lstm_stacked(x_dev, Wp, None, hs_pair[b], c, layers_per_group=args.layers_per_group, bn=args.bn)
+        ev_done[b].record(cur)
+        with torch.cuda.stream(s_comm):
+            s_comm.wait_event(ev_done[b])
+            dist.all_gather_into_tensor(gathered_pair[b], hs_pair[b][D - 1].reshape(L, N, H))
+            ev_gathered[b].record(s_comm)
+        res_state["i"] = i + 1
+
+    def drain_resident():
         if world > 1:
-            dist.all_gather_into_tensor(gathered, hs[D - 1].reshape(L, N, H))
+            cur = torch.cuda.current_stream()
+            for ev in ev_gathered:
+                cur.wait_event(ev)
 
     # End-to-end pipeline: every step copies its input from pinned host memory, runs the forward
     # through the public operator and copies the top layer's hidden states back to pinned host
     # memory; three streams and two buffer sets let step i's copies overlap step i+-1's compute.
     s_in, s_run, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
     x_buf = [torch.empty_like(x_dev) for _ in range(2)]
-    hs_buf = [hs, torch.empty_like(hs)]
+    hs_buf = hs_pair if world > 1 else [hs, torch.empty_like(hs)]
     out_buf = [out_pinned, torch.empty_like(out_pinned).pin_memory()]
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_run = [torch.cuda.Event() for _ in range(2)]
@@ -313,6 +340,7 @@ def main():
         e0.record()
         for _ in range(steps):
             fn()
+        drain_resident()
         e1.record()
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -325,6 +353,7 @@ def main():
         sampler.start()  # nvidia-smi needs a moment to start: launch it before the warm-up
     for _ in range(args.warmup):
         step_resident()
+    drain_resident()
     ops.check_status()
 
     n0 = lib.ftb_launch_count()
@@ -377,7 +406,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": "stacked LSTM D16 H1024 I1024 N256/GPU L100, bf16 weights/activations, fp32 cell state "
                                "(BASELINE config 4)", "global_batch": world * N, "seq_len": L,
-                   "parallelism": "batch-sharded x%d, weights replicated, all-gather of top-layer output" % world,
+                   "parallelism": "batch-sharded x%d, weights replicated, all-gather of top-layer output (on its own stream, overlapping the next step)" % world,
                    "cache": "per-step inputs exceed L2 (268 MB weights + 839 MB states vs 126 MB L2); no flush needed",
                    "layers_per_group": args.layers_per_group, "bn": args.bn},
         "roofline": roofline, "cpu_baseline": cpu,
