@@ -45,42 +45,49 @@ cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ 
   const int ty = threadIdx.x >> 4;  // 2 consecutive rows
   float acc[2][4] = {};
 
-  for (int s = 0; s < it.nseg; ++s) {
+  // K is walked in chunks of TK over the cell's segments.  The next chunk's global loads are
+  // issued into registers before the current chunk is multiplied out of shared memory, so their
+  // latency overlaps the arithmetic instead of preceding it (same summation order either way).
+  const int ld_r = threadIdx.x >> 3;        // row (A) / first column (W) this thread loads
+  const int ld_kq = (threadIdx.x & 7) * 4;  // its four consecutive k
+  const bool a_row_ok = m_tile * TM + ld_r < it.rows;
+  float4 va = make_float4(0.f, 0.f, 0.f, 0.f), vw0 = va, vw1 = va;
+  auto fetch = [&](int s, int k0) {
     const float* A = args.act[it.seg_map[s]];
     const int lda = args.ld_act[it.seg_map[s]];
     const int row0 = it.seg_row[s] + m_tile * TM;
-    const int klen = it.seg_kb[s] * 64;
     const float* W = args.w[it.w_map] + static_cast<size_t>(it.w_row0 + n_tile * TN) * args.ldw + it.seg_wk[s];
-    for (int k0 = 0; k0 < klen; k0 += TK) {
-      // A chunk: 32 rows x 32 k; one float4 per thread.
-      {
-        const int r = threadIdx.x >> 3;
-        const int kq = (threadIdx.x & 7) * 4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (m_tile * TM + r < it.rows)
-          v = *reinterpret_cast<const float4*>(A + static_cast<size_t>(row0 + r) * lda + k0 + kq);
-        sA[kq + 0][r] = v.x; sA[kq + 1][r] = v.y; sA[kq + 2][r] = v.z; sA[kq + 3][r] = v.w;
-      }
-      // W chunk: 64 columns x 32 k; two float4 per thread.
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int c = (threadIdx.x >> 3) + h * 32;
-        const int kq = (threadIdx.x & 7) * 4;
-        const float4 v = *reinterpret_cast<const float4*>(W + static_cast<size_t>(c) * args.ldw + k0 + kq);
-        sW[kq + 0][c] = v.x; sW[kq + 1][c] = v.y; sW[kq + 2][c] = v.z; sW[kq + 3][c] = v.w;
-      }
-      __syncthreads();
-#pragma unroll
-      for (int k = 0; k < TK; ++k) {
-        const float a0 = sA[k][2 * ty], a1 = sA[k][2 * ty + 1];
-        const float4 w = *reinterpret_cast<const float4*>(&sW[k][4 * tx]);
-        acc[0][0] = fmaf(a0, w.x, acc[0][0]); acc[0][1] = fmaf(a0, w.y, acc[0][1]);
-        acc[0][2] = fmaf(a0, w.z, acc[0][2]); acc[0][3] = fmaf(a0, w.w, acc[0][3]);
-        acc[1][0] = fmaf(a1, w.x, acc[1][0]); acc[1][1] = fmaf(a1, w.y, acc[1][1]);
-        acc[1][2] = fmaf(a1, w.z, acc[1][2]); acc[1][3] = fmaf(a1, w.w, acc[1][3]);
-      }
-      __syncthreads();
+    va = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (a_row_ok) va = *reinterpret_cast<const float4*>(A + static_cast<size_t>(row0 + ld_r) * lda + k0 + ld_kq);
+    vw0 = *reinterpret_cast<const float4*>(W + static_cast<size_t>(ld_r) * args.ldw + k0 + ld_kq);
+    vw1 = *reinterpret_cast<const float4*>(W + static_cast<size_t>(ld_r + 32) * args.ldw + k0 + ld_kq);
+  };
+  int s = 0, k0 = 0;
+  if (it.nseg > 0) fetch(0, 0);
+  while (s < it.nseg) {
+    sA[ld_kq + 0][ld_r] = va.x; sA[ld_kq + 1][ld_r] = va.y; sA[ld_kq + 2][ld_r] = va.z; sA[ld_kq + 3][ld_r] = va.w;
+    sW[ld_kq + 0][ld_r] = vw0.x; sW[ld_kq + 1][ld_r] = vw0.y; sW[ld_kq + 2][ld_r] = vw0.z; sW[ld_kq + 3][ld_r] = vw0.w;
+    sW[ld_kq + 0][ld_r + 32] = vw1.x; sW[ld_kq + 1][ld_r + 32] = vw1.y;
+    sW[ld_kq + 2][ld_r + 32] = vw1.z; sW[ld_kq + 3][ld_r + 32] = vw1.w;
+    __syncthreads();
+    int ns = s, nk0 = k0 + TK;
+    if (nk0 >= it.seg_kb[s] * 64) {
+      ++ns;
+      nk0 = 0;
     }
+    if (ns < it.nseg) fetch(ns, nk0);
+#pragma unroll
+    for (int k = 0; k < TK; ++k) {
+      const float a0 = sA[k][2 * ty], a1 = sA[k][2 * ty + 1];
+      const float4 w = *reinterpret_cast<const float4*>(&sW[k][4 * tx]);
+      acc[0][0] = fmaf(a0, w.x, acc[0][0]); acc[0][1] = fmaf(a0, w.y, acc[0][1]);
+      acc[0][2] = fmaf(a0, w.z, acc[0][2]); acc[0][3] = fmaf(a0, w.w, acc[0][3]);
+      acc[1][0] = fmaf(a1, w.x, acc[1][0]); acc[1][1] = fmaf(a1, w.y, acc[1][1]);
+      acc[1][2] = fmaf(a1, w.z, acc[1][2]); acc[1][3] = fmaf(a1, w.w, acc[1][3]);
+    }
+    __syncthreads();
+    s = ns;
+    k0 = nk0;
   }
 
   const int col0 = n_tile * TN + 4 * tx;

@@ -39,6 +39,8 @@ def main():
     ap.add_argument("--schedule", type=int, default=0)
     ap.add_argument("--pair", type=int, default=0)
     ap.add_argument("--min-len", type=int, default=1, help="varlen: lengths are uniform in [min-len, L]")
+    ap.add_argument("--graph", action="store_true",
+                    help="capture one call in a CUDA graph and time replays (schedules with one launch per level)")
     a = ap.parse_args()
     dt, dev = DT[a.dtype], torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(0)
@@ -92,6 +94,18 @@ def main():
     for _ in range(a.warmup):
         fn()
     torch.cuda.synchronize()
+    if a.graph:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()  # warm the side stream (workspace, lazy initialisation) before capturing
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(graph):
+            fn()
+        fn = graph.replay
+        fn()
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(a.iters):
