@@ -1,4 +1,4 @@
-"""Headline benchmark: stacked LSTM forward, BASELINE config 4 (depth 16, hidden 1024,
+"""Headline benchmark: stacked LSTM forward, benchmark config 4 (depth 16, hidden 1024,
 batch 256 per GPU, 100 steps, bf16 with fp32 cell state), metric samples*steps/s.
 
     python bench.py --gpus N --steps K --warmup W            # this library
@@ -118,14 +118,14 @@ def run_reference(args, rank):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "stacked LSTM D16 H1024 I1024 N256 L100 (BASELINE config 4)", "sample": sample_desc},
+        "config": {"workload": "stacked LSTM D16 H1024 I1024 N256 L100 (benchmark config 4)", "sample": sample_desc},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample_desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
 def other_configs(ops, dense, dev, pk):
-    """The path's other BASELINE configurations, each timed alone on the resident data with CUDA
+    """The path's other benchmark configurations, each timed alone on the resident data with CUDA
     events after 3 warm-up calls (rank 0, single-GPU runs only): the B2B GEMM against the HBM
     roofline, attention against the tensor roofline, and the latency-bound wavefronts as times."""
     import math
@@ -405,7 +405,7 @@ def main():
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": "stacked LSTM D16 H1024 I1024 N256/GPU L100, bf16 weights/activations, fp32 cell state "
-                               "(BASELINE config 4)", "global_batch": world * N, "seq_len": L,
+                               "(benchmark config 4)", "global_batch": world * N, "seq_len": L,
                    "parallelism": "batch-sharded x%d, weights replicated, all-gather of top-layer output (on its own stream, overlapping the next step)" % world,
                    "cache": "per-step inputs exceed L2 (268 MB weights + 839 MB states vs 126 MB L2); no flush needed",
                    "layers_per_group": args.layers_per_group, "bn": args.bn},

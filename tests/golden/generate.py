@@ -2,7 +2,7 @@
 eager frontend (kaleido.frontend, imported from the reference tree) on small
 seeded inputs.  Run once, where the reference tree is mounted:
 
-    python tests/golden/generate.py [/path/to/reference] [fixture-name ...]
+    python tests/golden/generate.py /path/to/reference [fixture-name ...]
 
 (with fixture names, e.g. ``stacked_lstm_varlen_small``, only those files are rewritten).
 
@@ -83,7 +83,9 @@ def load_reference_frontend(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/generate.py /path/to/reference [fixture-name ...]")
+    ref_root = sys.argv[1]
     only = set(sys.argv[2:])
 
     def save(name, **arrays):
@@ -145,7 +147,7 @@ def main():
                         b=b.numpy(), top=top.numpy())
     print("stacked small", top.shape)
 
-    # BASELINE config 1 at full size through the real frontend; inputs are
+    # benchmark config 1 at full size through the real frontend; inputs are
     # regenerated from the seed, the fixture keeps two samples of the output.
     if not only or "stacked_lstm_config1_samples" in only:
         x, W, U, b, top = run_stacked(4, 64, 32, 256, 0, 1.0 / 16, False)

@@ -90,7 +90,7 @@ def test_stacked_lstm_golden_small_fp32(ops, golden_dir):
 
 
 def test_stacked_lstm_config1_fp32(ops, golden_dir):
-    """BASELINE config 1 (D4 H256 I256 N32 L64, seed 0) against the oracle at full size and
+    """benchmark config 1 (D4 H256 I256 N32 L64, seed 0) against the oracle at full size and
     against the two samples the reference frontend produced."""
     x, W, U, _ = dense.make_lstm_inputs(4, 64, 32, 256, 256, 0, 1.0 / 16)
     hs, c = _run_stacked(ops, x, W, U, None)
@@ -171,7 +171,7 @@ def test_stacked_lstm_falls_back_when_cooperative_launch_is_refused(ops, monkeyp
 
 
 def test_stacked_lstm_config4_properties(ops):
-    """BASELINE config 4 at full size (D16 H1024 N256 L100 bf16).  The oracle needs minutes
+    """benchmark config 4 at full size (D16 H1024 N256 L100 bf16).  The oracle needs minutes
     there, so: (1) the first layers/steps depend only on earlier layers/steps and are checked
     against the oracle on that prefix; (2) samples are independent, so a half-batch run must
     reproduce the same rows bit for bit."""
@@ -270,7 +270,7 @@ def test_varlen_lstm_sequences_are_independent(ops):
 
 
 def test_varlen_lstm_config4_size_properties(ops):
-    """BASELINE config 4's shape (D16 H1024 L100 N256 bf16) with lengths uniform in [20, 100]:
+    """benchmark config 4's shape (D16 H1024 L100 N256 bf16) with lengths uniform in [20, 100]:
     the first layers and steps against the oracle, and batch independence, as for the rectangular case."""
     D, L, N, H = 16, 100, 256, 1024
     active, x, W, U, b = _varlen_inputs(D, L, N, H, H, 23, torch.bfloat16, min_len=20, w_bound=1.0 / 32)
@@ -369,7 +369,7 @@ def test_dilated_schedules_agree_bit_for_bit(ops):
 
 
 def test_dilated_config5a_prefix(ops):
-    """BASELINE config 5a shape (6 layers, dilations 1..32, H256, N256) on the first 64 steps
+    """benchmark config 5a shape (6 layers, dilations 1..32, H256, N256) on the first 64 steps
     (the recurrence up to step t only needs inputs up to t)."""
     dils = [1, 2, 4, 8, 16, 32]
     x, W, U, _ = dense.make_lstm_inputs(6, 512, 256, 256, 256, 4, 1.0 / 16, dtype=torch.float16)
@@ -455,7 +455,7 @@ def test_grid_schedules_agree_bit_for_bit(ops, shape):
 
 
 def test_grid_config5b_corner(ops):
-    """BASELINE config 5b shape (32x32 grid, H256, N64, fp16): the 6x6 corner of the grid only
+    """benchmark config 5b shape (32x32 grid, H256, N64, fp16): the 6x6 corner of the grid only
     depends on itself and is checked against the oracle; the rest must be finite and bounded."""
     X, Y, p = dense.make_grid_inputs(1, 32, 32, 64, 256, 4, 1.0 / 16, dtype=torch.float16)
     hx, hy = _run_grid(ops, X, Y, p)
@@ -476,7 +476,7 @@ def test_b2b_gemm(ops, dt, batch, M):
 
 
 def test_b2b_config2_full_size(ops):
-    """BASELINE config 2 (16 x [16384x128].[128x128].[128x128], fp16, seed 1): full oracle compare,
+    """benchmark config 2 (16 x [16384x128].[128x128].[128x128], fp16, seed 1): full oracle compare,
     plus exact linearity under a power-of-two scale of A."""
     A, B, C = dense.make_b2b_inputs(16, 16384, 128, 128, 128, 1)
     Ad, Bd, Cd = _dev(A, B, C)
@@ -528,7 +528,7 @@ def test_flash_attention_large_scores_rescale_path(ops):
 
 
 def test_flash_attention_config3_properties(ops):
-    """BASELINE config 3 at full size (B16 h16 S2048 d128 fp16, seed 2): oracle on two
+    """benchmark config 3 at full size (B16 h16 S2048 d128 fp16, seed 2): oracle on two
     (batch, head) slices; with V = 1 every output is 1 (softmax rows sum to one)."""
     q, k, v = dense.make_attention_inputs(16, 16, 2048, 128, 2)
     sc = 1.0 / math.sqrt(128.0)

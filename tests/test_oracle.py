@@ -22,7 +22,7 @@ def test_stacked_lstm_small_matches_reference_frontend(golden_dir):
 
 
 def test_stacked_lstm_config1_matches_reference_frontend(golden_dir):
-    """BASELINE config 1 at full size (D4, H256, N32, L64, seed 0): the fixture holds
+    """benchmark config 1 at full size (D4, H256, N32, L64, seed 0): the fixture holds
     two samples of the frontend's output; samples are independent."""
     g = _load(golden_dir, "stacked_lstm_config1_samples.npz")
     x, W, U, _ = dense.make_lstm_inputs(4, 64, 32, 256, 256, 0, 1.0 / 16)
