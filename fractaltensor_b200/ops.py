@@ -283,3 +283,17 @@ def gemm_nt(A, Bt, out=None, bn=0, pair=0):
         check(lib.ftb_gemm_nt(_ptr(A), _ptr(Bt), _ptr(out), M, N, K, _dtype_code(A), _tuning(bn=bn, pair=pair), _ptr(ws), ws.numel(),
                               _stream()), "ftb_gemm_nt")
     return out
+
+
+def online_softmax(x, out=None):
+    """Row-wise softmax of an fp32 matrix x [rows, width]: e^(max(x - m, -64)) / d per row."""
+    _req(x, "x", torch.float32)
+    if x.dim() != 2:
+        raise ValueError("online_softmax: expected a matrix, got shape %s" % (tuple(x.shape),))
+    if out is None:
+        out = torch.empty_like(x)
+    _req(out, "out", torch.float32)
+    rows, width = x.shape
+    with torch.cuda.device(x.device):
+        check(lib.ftb_online_softmax(_ptr(x), _ptr(out), rows, width, _stream()), "ftb_online_softmax")
+    return out

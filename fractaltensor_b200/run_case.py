@@ -20,7 +20,7 @@ DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["lstm", "varlen", "dilated", "grid", "b2b", "attn"])
+    ap.add_argument("case", choices=["lstm", "varlen", "dilated", "grid", "b2b", "attn", "softmax"])
     ap.add_argument("--D", type=int, default=16)
     ap.add_argument("--L", type=int, default=20)
     ap.add_argument("--N", type=int, default=256)
@@ -86,6 +86,15 @@ def main():
         def fn():
             turn[0] = (turn[0] + 1) % 3
             return ops.b2b_gemm(*sets[turn[0]])
+    elif a.case == "softmax":
+        # rows x width fp32; three input/output pairs in turn when a pair is smaller than 2 x L2
+        xs = [rnd(a.M, a.H) for _ in range(3)]
+        ys = [torch.empty_like(xs[0]) for _ in range(3)]
+        turn = [0]
+
+        def fn():
+            turn[0] = (turn[0] + 1) % 3
+            return ops.online_softmax(xs[turn[0]], ys[turn[0]])
     else:
         q, k, v = (rnd(a.B, a.heads, a.S, 128).to(dt) for _ in range(3))
         out = torch.empty_like(q)

@@ -172,6 +172,15 @@ int ftb_b2b_gemm(const void* A, const void* B, const void* C, void* Dout, int ba
 int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S, int d,
                        float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Row-wise softmax of an fp32 matrix x [rows, width] (row-major, contiguous) with the online
+ * (maximum, normaliser) reduction: y = e^(max(x - m, -64)) / d per row, m the row maximum, d the sum
+ * of e^(x - m).  Stands in for KeOnlineNormalizedSoftMax / OnlineNormalizedSoftmaxOp
+ * (kaleido/core/device/kernels/online_softmax.h:15-183,
+ * kaleido/core/operators/online_softmax_op.cu:13-38; the reference instantiates fp32 only and
+ * normalises along dimension 0 of its [height, width] view, i.e. over each row's `width`
+ * elements).  Needs no workspace. */
+int ftb_online_softmax(const float* x, float* y, int rows, int width, void* stream);
+
 /* Plain GEMM out[M,N] = A[M,K] . Bt[N,K]^T through the cell kernel's main loop
  * (support op; the reference's KeCuteGemm, kaleido/core/device/kernels/cutlass_wmma.h:115-181).
  * 16-bit dtypes: K % 64 == 0, N % 128 == 0.  fp32: K % 64 == 0, N % 64 == 0. */

@@ -202,6 +202,17 @@ def flash_attention_dense(q, k, v, scale=1.0, block=64):
     return o
 
 
+def online_softmax_dense(x):
+    """Row-wise softmax with the reference kernel's clamp.
+
+    Follows ReduceMD / MapRescale (kaleido/core/device/kernels/online_softmax.h:113-163): per row
+    m = max x, d = sum e^(x - m), output e^(max(x - m, -64)) / d.  x: [rows, width].
+    """
+    m = x.max(dim=1, keepdim=True).values
+    d = torch.exp(x - m).sum(dim=1, keepdim=True)
+    return torch.exp(torch.clamp(x - m, min=-64.0)) / d
+
+
 def attention_plain(q, k, v, scale=1.0):
     """softmax(scale * q k^T) v, the closed form the blockwise carry equals."""
     return torch.softmax((q @ k.transpose(-1, -2)) * scale, dim=-1) @ v

@@ -543,6 +543,32 @@ def test_flash_attention_config3_properties(ops):
     assert (ones.float() - 1).abs().max().item() <= 2e-3
 
 
+# ------------------------------------------------------------ online softmax
+@pytest.mark.parametrize("shape", [(2, 7), (2, 517), (2, 1027), (5, 4096), (3, 60000), (300, 128), (1, 1)])
+def test_online_softmax(ops, shape):
+    """The reference test's shapes (2x7, 2x517, 2x1027) and others: rows that fit the shared-memory
+    cache and rows that do not, widths that allow 16-byte accesses and widths that do not."""
+    g = torch.Generator().manual_seed(10)
+    x = torch.randn(*shape, generator=g) * 3
+    y = ops.online_softmax(x.cuda()).cpu()
+    ref = dense.online_softmax_dense(x)
+    assert (y - ref).abs().max().item() <= 1e-6
+    assert (y.sum(dim=1) - 1).abs().max().item() <= 1e-5
+
+
+def test_online_softmax_clamp_and_large_matrix(ops):
+    x = torch.tensor([[0.0, -100.0, -64.0, -63.0] * 2], dtype=torch.float32)
+    y = ops.online_softmax(x.cuda()).cpu()
+    ref = dense.online_softmax_dense(x)
+    assert torch.allclose(y, ref, rtol=1e-4, atol=0) and y[0, 1].item() > 0  # clamped, not flushed to 0
+    # 512 MB in and out: every row sums to one, rows are independent (a row alone gives the same bits)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    big = torch.randn(16384, 8192, device="cuda", generator=g)
+    out = ops.online_softmax(big)
+    assert (out.sum(dim=1) - 1).abs().max().item() <= 1e-4
+    assert torch.equal(ops.online_softmax(big[77:78].contiguous()), out[77:78])
+
+
 # ------------------------------------------------------------ model-level frontend
 def test_frontend_signatures(ops):
     from fractaltensor_b200 import frontend as fe

@@ -126,3 +126,18 @@ def test_seeded_inputs_are_deterministic():
     q2 = dense.make_attention_inputs(1, 1, 4, 4, 2)[0]
     assert torch.equal(q1, q2)
     assert abs(dense.make_b2b_inputs(1, 256, 128, 128, 128, 1)[0].float().std().item() - 1 / math.sqrt(128)) < 0.01
+
+
+def test_online_softmax_is_softmax_with_a_clamp():
+    """The reference checks its online softmax against its plain softmax (and rows against 1):
+    the same here, plus the clamp at x - max = -64 that only the online kernel has."""
+    g = torch.Generator().manual_seed(9)
+    for rows, width in ((2, 7), (2, 517), (2, 1027)):  # the reference test's shapes
+        x = torch.randn(rows, width, generator=g)
+        y = dense.online_softmax_dense(x)
+        assert torch.allclose(y, torch.softmax(x, dim=1), atol=1e-7)
+        assert torch.allclose(y.sum(dim=1), torch.ones(rows), atol=1e-5)
+    x = torch.tensor([[0.0, -100.0, -64.0]])
+    y = dense.online_softmax_dense(x)
+    d = 1.0 + math.exp(-100.0) + math.exp(-64.0)
+    assert abs(y[0, 1].item() - math.exp(-64.0) / d) < 1e-35 and y[0, 1].item() > 0
