@@ -192,6 +192,33 @@ def other_configs(ops, dense, dev, pk):
     out.append({"config": "5b: grid RNN 32x32 H256 N64 fp16", "ms": ms,
                 "cells_per_s": 32 * 32 * 64 / (ms * 1e-3), "bound": "latency (63 anti-diagonals)"})
 
+    # stand-alone online softmax, fp32 16384 x 4096 (three input/output pairs in turn, 1.6 GB > L2)
+    xs = [rnd(16384, 4096) for _ in range(3)]
+    ys = [torch.empty_like(xs[0]) for _ in range(3)]
+
+    def softmax():
+        turn[0] = (turn[0] + 1) % 3
+        ops.online_softmax(xs[turn[0]], ys[turn[0]])
+
+    ms = timed(softmax, 30)
+    nbytes = 2 * 16384 * 4096 * 4
+    out.append({"config": "online softmax fp32 16384x4096", "ms": ms, "bound": "hbm",
+                "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": pk["hbm"], "unit": "GB/s",
+                "frac": nbytes / (ms * 1e-3) / 1e9 / pk["hbm"], "cache": "three rotating buffer pairs of 537 MB"})
+    del xs, ys
+
+    # embedding lookup in front of config 4: 25 600 words, table 50 000 x 1024 bf16
+    table = rnd(50000, 1024).bfloat16()
+    ids = torch.randint(0, 50000, (25600,), device=dev, generator=g)
+    rows_out = torch.empty(25600, 1024, device=dev, dtype=torch.bfloat16)
+    ms = timed(lambda: ops.embedding_gather(table, ids, rows_out), 30)
+    nbytes = 25600 * (2 * 1024 * 2 + 8)
+    out.append({"config": "embedding lookup 25600 words, table 50000x1024 bf16", "ms": ms, "bound": "hbm",
+                "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": pk["hbm"], "unit": "GB/s",
+                "frac": nbytes / (ms * 1e-3) / 1e9 / pk["hbm"],
+                "cache": "105 MB per call: fits L2, so this is a launch- and latency-bound size"})
+    del table, ids, rows_out
+
     # config 1: stacked LSTM fp32 D4 H256 N32 L64 (CUDA cores; the reference's own CPU-runnable case)
     x1, W1, U1, _ = dense.make_lstm_inputs(4, 64, 32, 256, 256, 0, 1.0 / 16)
     Wp1, _ = ops.lstm_pack_weights(W1.to(dev), U1.to(dev))

@@ -10,9 +10,10 @@
 // The op is HBM-bound (8 bytes per element when the input is read once), so the
 // kernel is organised around one global read and one global write per element:
 // a CTA owns a row at a time, keeps it in shared memory between the reduction
-// and the rescale when it fits, moves 16 bytes per thread per access, and the
-// grid is a whole number of CTAs per SM looping over rows.  Rows that do not fit
-// in shared memory are read a second time (from L2 when the row is smaller than it).
+// and the rescale (the first 48 K floats of it when it is longer: only the rest is
+// read a second time), moves 16 bytes per thread per access, and the grid is a whole
+// number of CTAs per SM looping over rows.  Rows of up to 2048 floats take a warp each
+// and stay in registers: no block-wide synchronisation at all.
 #include <cfloat>
 
 #include "../../include/ftb200.h"
@@ -49,14 +50,15 @@ __device__ __forceinline__ void push(MD& s, float v) {
   s.m = m;
 }
 
-__global__ void __launch_bounds__(kSoftmaxThreads)
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
 online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int width, int cache_floats) {
   extern __shared__ float4 row_cache4[];
   float* row_cache = reinterpret_cast<float*>(row_cache4);
-  __shared__ float red_m[kSoftmaxThreads / 32], red_d[kSoftmaxThreads / 32];
+  __shared__ float red_m[32], red_d[32];
   __shared__ float final_m, final_d;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const bool cached = width <= cache_floats;
+  const int cached_floats = width < cache_floats ? width : cache_floats;  // prefix of the row kept on chip
   // 16-byte accesses need rows that start on a 16-byte boundary.
   const bool vec = (width & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
 
@@ -68,18 +70,20 @@ online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int ro
     s.d = 0.f;
     if (vec) {
       const float4* x4 = reinterpret_cast<const float4*>(xr);
-      for (int i = tid; i < width / 4; i += kSoftmaxThreads) {
-        const float4 v = __ldcs(x4 + i);  // streamed: read once
-        if (cached) row_cache4[i] = v;
+      for (int i = tid; i < width / 4; i += THREADS) {
+        // The cached part is read once (streamed); the tail is read again by the rescale.
+        const bool keep = 4 * i < cached_floats;
+        const float4 v = keep ? __ldcs(x4 + i) : x4[i];
+        if (keep) row_cache4[i] = v;
         push(s, v.x);
         push(s, v.y);
         push(s, v.z);
         push(s, v.w);
       }
     } else {
-      for (int i = tid; i < width; i += kSoftmaxThreads) {
+      for (int i = tid; i < width; i += THREADS) {
         const float v = xr[i];
-        if (cached) row_cache[i] = v;
+        if (i < cached_floats) row_cache[i] = v;
         push(s, v);
       }
     }
@@ -98,10 +102,10 @@ online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int ro
     __syncthreads();
     if (warp == 0) {
       MD t;
-      t.m = lane < kSoftmaxThreads / 32 ? red_m[lane] : -FLT_MAX;
-      t.d = lane < kSoftmaxThreads / 32 ? red_d[lane] : 0.f;
+      t.m = lane < THREADS / 32 ? red_m[lane] : -FLT_MAX;
+      t.d = lane < THREADS / 32 ? red_d[lane] : 0.f;
 #pragma unroll
-      for (int o = 4; o > 0; o >>= 1) {
+      for (int o = 16; o > 0; o >>= 1) {
         MD u;
         u.m = __shfl_xor_sync(0xffffffffu, t.m, o);
         u.d = __shfl_xor_sync(0xffffffffu, t.d, o);
@@ -116,10 +120,10 @@ online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int ro
     const float m = final_m;
     const float inv_d = 1.f / final_d;
     if (vec) {
-      const float4* src = cached ? row_cache4 : reinterpret_cast<const float4*>(xr);
+      const float4* x4 = reinterpret_cast<const float4*>(xr);
       float4* y4 = reinterpret_cast<float4*>(yr);
-      for (int i = tid; i < width / 4; i += kSoftmaxThreads) {
-        float4 v = src[i];
+      for (int i = tid; i < width / 4; i += THREADS) {
+        float4 v = 4 * i < cached_floats ? row_cache4[i] : __ldcs(x4 + i);
         v.x = exp_fast(fmaxf(v.x - m, kClamp)) * inv_d;
         v.y = exp_fast(fmaxf(v.y - m, kClamp)) * inv_d;
         v.z = exp_fast(fmaxf(v.z - m, kClamp)) * inv_d;
@@ -127,10 +131,58 @@ online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int ro
         __stcs(y4 + i, v);
       }
     } else {
-      const float* src = cached ? row_cache : xr;
-      for (int i = tid; i < width; i += kSoftmaxThreads) yr[i] = exp_fast(fmaxf(src[i] - m, kClamp)) * inv_d;
+      for (int i = tid; i < width; i += THREADS) {
+        const float v = i < cached_floats ? row_cache[i] : xr[i];
+        yr[i] = exp_fast(fmaxf(v - m, kClamp)) * inv_d;
+      }
     }
     __syncthreads();  // the cache and the reduction slots are reused by the next row
+  }
+}
+
+// Short rows (width % 4 == 0, up to 32 * 4 * kMaxV floats): one warp per row, the row in registers.
+constexpr int kMaxV = 16;
+__global__ void __launch_bounds__(kSoftmaxThreads)
+online_softmax_warp_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int width) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = kSoftmaxThreads / 32;
+  const int n4 = width / 4;
+  for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
+    const float4* x4 = reinterpret_cast<const float4*>(x + static_cast<size_t>(r) * width);
+    float4* y4 = reinterpret_cast<float4*>(y + static_cast<size_t>(r) * width);
+    float4 v[kMaxV];
+#pragma unroll
+    for (int j = 0; j < kMaxV; ++j)
+      if (j * 32 + lane < n4) v[j] = __ldcs(x4 + j * 32 + lane);
+    MD s;
+    s.m = -FLT_MAX;
+    s.d = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxV; ++j)
+      if (j * 32 + lane < n4) {
+        push(s, v[j].x);
+        push(s, v[j].y);
+        push(s, v[j].z);
+        push(s, v[j].w);
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      MD t;
+      t.m = __shfl_xor_sync(0xffffffffu, s.m, o);
+      t.d = __shfl_xor_sync(0xffffffffu, s.d, o);
+      s = merge(s, t);
+    }
+    const float m = s.m, inv_d = 1.f / s.d;
+#pragma unroll
+    for (int j = 0; j < kMaxV; ++j)
+      if (j * 32 + lane < n4) {
+        float4 o4;
+        o4.x = exp_fast(fmaxf(v[j].x - m, kClamp)) * inv_d;
+        o4.y = exp_fast(fmaxf(v[j].y - m, kClamp)) * inv_d;
+        o4.z = exp_fast(fmaxf(v[j].z - m, kClamp)) * inv_d;
+        o4.w = exp_fast(fmaxf(v[j].w - m, kClamp)) * inv_d;
+        __stcs(y4 + j * 32 + lane, o4);
+      }
   }
 }
 
@@ -145,23 +197,38 @@ extern "C" int ftb_online_softmax(const float* x, float* y, int rows, int width,
   if (static_cast<int64_t>(rows) * width > 0x7fffffffffLL) return FTB_ERR_ARG;
   int rc = check_device_sm100();
   if (rc) return rc;
-  // Row cache: the whole row when it fits in 192 KB of shared memory, else none.
+  const bool aligned16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  if (aligned16 && width % 4 == 0 && width <= 32 * 4 * kMaxV && rows >= 8) {
+    const int64_t ctas = (static_cast<int64_t>(rows) + kSoftmaxThreads / 32 - 1) / (kSoftmaxThreads / 32);
+    const int64_t full = static_cast<int64_t>(current_sm_count()) * 4;
+    online_softmax_warp_kernel<<<static_cast<int>(ctas < full ? ctas : full), kSoftmaxThreads, 0, stream>>>(x, y, rows,
+                                                                                                            width);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+  }
+  // Row cache: the row, or its first 48 K floats, in up to 192 KB of shared memory.
   constexpr int kMaxCacheFloats = 48 * 1024;
-  const int cache_floats = width <= kMaxCacheFloats ? ((width + 3) & ~3) : 0;
+  const int cache_floats = width <= kMaxCacheFloats ? ((width + 3) & ~3) : kMaxCacheFloats;
   const size_t smem = static_cast<size_t>(cache_floats) * sizeof(float);
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(online_softmax_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(online_softmax_kernel<kSoftmaxThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kMaxCacheFloats * static_cast<int>(sizeof(float))) != cudaSuccess ||
+        cudaFuncSetAttribute(online_softmax_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kMaxCacheFloats * static_cast<int>(sizeof(float))) != cudaSuccess)
       return FTB_ERR_LAUNCH;
     configured = true;
   }
-  // A whole number of CTAs per SM: as many as the row cache lets be resident (at most 8).
-  int per_sm = smem == 0 ? 8 : static_cast<int>((200 * 1024) / (smem + 1024));
+  // A whole number of CTAs per SM: as many as the row cache lets be resident (at most 8).  A cache
+  // that leaves room for one or two CTAs per SM gets CTAs of 1024 threads to keep loads in flight.
+  int per_sm = static_cast<int>((200 * 1024) / (smem + 1024));
   per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
   const int64_t want = static_cast<int64_t>(current_sm_count()) * per_sm;
   const int grid = static_cast<int>(rows < want ? rows : want);
-  online_softmax_kernel<<<grid, kSoftmaxThreads, smem, stream>>>(x, y, rows, width, cache_floats);
+  if (per_sm <= 2)
+    online_softmax_kernel<1024><<<grid, 1024, smem, stream>>>(x, y, rows, width, cache_floats);
+  else
+    online_softmax_kernel<kSoftmaxThreads><<<grid, kSoftmaxThreads, smem, stream>>>(x, y, rows, width, cache_floats);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }

@@ -30,6 +30,7 @@ enum Status : int {
   FTB_ERR_TIMEOUT_SLOT = 19,  // device: producer waited too long for a free stage
   FTB_ERR_TIMEOUT_DEP = 20,   // device: a cell waited too long for the cells it depends on
   FTB_ERR_TMEM_LAYOUT = 21,   // device: the two CTAs of a pair got different TMEM columns
+  FTB_ERR_INDEX = 22,         // device: an index was outside its table (the row was written as zeros)
 };
 
 #ifndef FTB_WAIT_TIMEOUT_NS

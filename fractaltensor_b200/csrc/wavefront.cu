@@ -369,6 +369,7 @@ const char* ftb_status_str(int code) {
     case FTB_ERR_TIMEOUT_SLOT: return "device wait ran out: no free pipeline stage";
     case FTB_ERR_TIMEOUT_DEP: return "device wait ran out: a cell's inputs never completed";
     case FTB_ERR_TMEM_LAYOUT: return "the two CTAs of a pair got different TMEM columns";
+    case FTB_ERR_INDEX: return "an index was outside its table";
     default: return "unknown status";
   }
 }

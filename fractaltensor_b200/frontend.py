@@ -8,6 +8,7 @@ over ``FractalTensor`` values (flat ``.data`` buffer plus nested ``.indices``):
     dilated_lstm(embs, Wss, Uss, bss)                  examples/dilated_rnn/dilated_rnn.py:16-41 (the fold in model())
     stacked_grid_rnns(src_encs, trg_encs, params)      examples/grid_rnn/grid_rnn.py:111-122
     flash_attention(qsss, ksss, vsss)                  examples/flash_attention/flash_attention.py:75-88
+    embed(words, embedding)                            examples/stacked_rnn/rnn_utils.py:80-90 (the lookup in front)
 
 The functions here keep those argument lists and return the same nested values,
 but run the whole nest as one fused wavefront on the GPU.  Arguments may be the
@@ -87,6 +88,23 @@ def _cuda(t, dtype=None):
     if not t.is_cuda:
         raise RuntimeError("inputs must already live on a CUDA device: there is no CPU path")
     return t if dtype is None else t.to(dtype)
+
+
+def embed(words, embedding, dtype=None):
+    """The lookup the RNN examples run first:
+    ``ops.map(lambda ws: ops.map(lambda word: ops.index(ops.slices(embedding, dim=0), word), ws), words)``.
+
+    words: a FractalTensor of integers in any nesting (batch-major [N][L_n] or time-major [L][n_t],
+    ragged or not); embedding: [V,H] tensor (or an object with .data).  Returns a FractalTensor with
+    the same nesting whose elements are the [1,H] rows, ready for stacked_lstm / stacked_lstm_time_major.
+    """
+    table = embedding.data if hasattr(embedding, "data") and not isinstance(embedding, torch.Tensor) else embedding
+    table = _cuda(table, dtype)
+    if table.dim() != 2:
+        table = table.reshape(-1, table.shape[-1])
+    ids = _cuda(words.data.reshape(-1)).to(torch.int64)
+    out = ops.embedding_gather(table.contiguous(), ids.contiguous())
+    return FractalTensor(out, words.indices, (1, table.shape[1]))
 
 
 def _is_ragged(x):

@@ -297,3 +297,21 @@ def online_softmax(x, out=None):
     with torch.cuda.device(x.device):
         check(lib.ftb_online_softmax(_ptr(x), _ptr(out), rows, width, _stream()), "ftb_online_softmax")
     return out
+
+
+def embedding_gather(table, ids, out=None):
+    """table: [V,H]; ids: int64 [T] (any nesting flattened) -> out [T,H] = table[ids]."""
+    _req(table, "table")
+    _req(ids, "ids", torch.int64)
+    if table.dim() != 2:
+        raise ValueError("embedding_gather: expected a [V,H] table, got shape %s" % (tuple(table.shape),))
+    V, H = table.shape
+    T = ids.numel()
+    if out is None:
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    _req(out, "out", table.dtype)
+    ws = workspace(table.device)
+    with torch.cuda.device(table.device):
+        check(lib.ftb_embedding_gather(_ptr(table), _ptr(ids), _ptr(out), T, V, H, _dtype_code(table), _ptr(ws),
+                                       ws.numel(), _stream()), "ftb_embedding_gather")
+    return out

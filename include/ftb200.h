@@ -172,6 +172,16 @@ int ftb_b2b_gemm(const void* A, const void* B, const void* C, void* Dout, int ba
 int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S, int d,
                        float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Embedding lookup out[t, :] = table[ids[t], :] for t < T.  Stands in for the lookup in front of
+ * the reference's RNN examples, ops.index(ops.slices(embedding, dim=0), word) mapped over a batch
+ * of word sequences (examples/stacked_rnn/rnn_utils.py:80-90): `ids` is the flat int64 buffer of
+ * the words FractalTensor in any nesting (batch-major or time-major, ragged or not), `out` the flat
+ * buffer of the resulting FractalTensor of [1, H] tensors in the same order.  table: [V, H] of
+ * `dtype`; ids: int64 [T] on the device; out: [T, H].  An id outside [0, V) gives a row of zeros
+ * and sets the (sticky) status word to 22. */
+int ftb_embedding_gather(const void* table, const long long* ids, void* out, long long T, long long V, int H,
+                         int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Row-wise softmax of an fp32 matrix x [rows, width] (row-major, contiguous) with the online
  * (maximum, normaliser) reduction: y = e^(max(x - m, -64)) / d per row, m the row maximum, d the sum
  * of e^(x - m).  Stands in for KeOnlineNormalizedSoftMax / OnlineNormalizedSoftmaxOp

@@ -213,6 +213,15 @@ def online_softmax_dense(x):
     return torch.exp(torch.clamp(x - m, min=-64.0)) / d
 
 
+def embedding_gather_dense(table, ids):
+    """One table row per word, in the order of the flat word buffer.
+
+    Follows ops.index(ops.slices(embedding, dim=0), word) mapped over a batch of word sequences
+    (examples/stacked_rnn/rnn_utils.py:80-90).  table: [V,H]; ids: int64 [T]; returns [T,H].
+    """
+    return table[ids.reshape(-1)]
+
+
 def attention_plain(q, k, v, scale=1.0):
     """softmax(scale * q k^T) v, the closed form the blockwise carry equals."""
     return torch.softmax((q @ k.transpose(-1, -2)) * scale, dim=-1) @ v

@@ -10,6 +10,7 @@ The model programs below are restated from the reference examples, calling the
 reference's real ``ops.map / scan / fold / reduce / dilated_map / zip / ...``:
   stacked   examples/stacked_rnn/stacked_lstm1.py:13-76
   varlen    examples/stacked_rnn/stacked_rnn.py:40-79 (time-major, length-sorted ragged batch)
+  embedding examples/stacked_rnn/rnn_utils.py:80-90 (the word lookup in front of the RNN)
   dilated   examples/dilated_rnn/dilated_rnn.py:16-41
   grid      examples/grid_rnn/grid_rnn.py:42-122
   attention examples/flash_attention/flash_attention.py:14-88
@@ -184,6 +185,23 @@ def main():
     save("stacked_lstm_varlen_small", active_rows=np.array(active), x=x.numpy(), W=W.numpy(), U=U.numpy(),
          b=b.numpy(), top=top.numpy())
     print("stacked varlen", active, top.shape)
+
+    # -------------------------------------------------------------- embedding lookup
+    def run_embedding(V, H, lens, seed):
+        g = torch.Generator().manual_seed(seed)
+        table = torch.randn(V, H, generator=g)
+        seqs = [[int(torch.randint(0, V, (1,), generator=g)) for _ in range(n)] for n in lens]
+        emb = Tensor((V, H), kaleido.float32, device="cpu")
+        emb.data = table.clone()
+        words = FractalTensor.from_pylist(seqs, "cpu")
+        embs = ops.map(lambda ws: ops.map(lambda word: ops.index(ops.slices(emb, dim=0), word), ws), words)
+        assert [len(i) for i in embs.indices] == lens
+        return table, words.data.clone(), embs.data.view(-1, H).clone()
+
+    lens = [3, 5, 1, 4]
+    table, ids, rows = run_embedding(23, 8, lens, 13)
+    save("embedding_small", table=table.numpy(), ids=ids.numpy(), lens=np.array(lens), rows=rows.numpy())
+    print("embedding", rows.shape)
 
     # ---------------------------------------------------------------------- dilated
     def run_dilated(D, L, N, H, seed, w_bound):

@@ -569,6 +569,63 @@ def test_online_softmax_clamp_and_large_matrix(ops):
     assert torch.equal(ops.online_softmax(big[77:78].contiguous()), out[77:78])
 
 
+# ---------------------------------------------------------- embedding lookup
+def test_embedding_golden(ops, golden_dir):
+    g = _load(golden_dir, "embedding_small.npz")
+    rows = ops.embedding_gather(g["table"].cuda(), g["ids"].cuda())
+    ops.check_status()
+    assert torch.equal(rows.cpu(), g["rows"])  # a copy: bit-exact
+
+
+@pytest.mark.parametrize("dt,V,H,T", [(torch.bfloat16, 5000, 1024, 25600), (torch.float32, 1000, 256, 2048),
+                                      (torch.float16, 77, 72, 1000), (torch.float32, 10, 3, 50), (torch.bfloat16, 4, 64, 1)])
+def test_embedding_gather(ops, dt, V, H, T):
+    """Rows of 16-byte multiples and others (H=72 fp16: 144 B; H=3 fp32: 12 B), repeated ids, one id."""
+    g = torch.Generator().manual_seed(14)
+    table = torch.randn(V, H, generator=g).to(dt)
+    ids = torch.randint(0, V, (T,), generator=g)
+    out = ops.embedding_gather(table.cuda(), ids.cuda())
+    ops.check_status()
+    assert torch.equal(out.cpu(), dense.embedding_gather_dense(table, ids))
+
+
+def test_embedding_out_of_range_id_is_reported(ops):
+    from fractaltensor_b200._lib import FtbError
+    table = torch.ones(8, 64).cuda()
+    ids = torch.tensor([1, 8, 2, -1]).cuda()
+    out = ops.embedding_gather(table, ids)
+    with pytest.raises(FtbError) as e:
+        ops.check_status()
+    assert e.value.code == 22
+    assert out[0].eq(1).all() and out[2].eq(1).all() and out[1].eq(0).all() and out[3].eq(0).all()
+    ops.embedding_gather(table, torch.tensor([0]).cuda())
+    ops.check_status()  # the word was cleared by the failed check
+
+
+def test_embed_then_ragged_lstm_through_the_frontend(ops):
+    """words -> embedding lookup -> stacked LSTM on a ragged batch, model-level signatures only."""
+    from fractaltensor_b200 import frontend
+    D, H, V = 2, 64, 50
+    lens = [4, 6, 2]
+    g = torch.Generator().manual_seed(15)
+    table = torch.randn(V, H, generator=g)
+    ids = [torch.randint(0, V, (n,), generator=g) for n in lens]
+    W = (torch.rand(D, 4, H, H, generator=g) * 2 - 1) / 8
+    U = (torch.rand(D, 4, H, H, generator=g) * 2 - 1) / 8
+    b = (torch.rand(D, 4, H, generator=g) * 2 - 1) / 8
+    words = frontend.FractalTensor(torch.cat(ids).cuda(), [list(range(n)) for n in lens], (1,))
+    embs = frontend.embed(words, table.cuda())
+    assert [len(i) for i in embs.indices] == lens and embs.element_shape == (1, H)
+    ft = lambda t, d: frontend.FractalTensor.from_dense(t.cuda(), d)
+    out = frontend.stacked_lstm(embs, ft(W, 2), ft(U, 2), ft(b.reshape(D, 4, 1, H), 2))
+    flat = out.data.reshape(-1, H).cpu()
+    pos = 0
+    for n, seq in zip(lens, ids):
+        rhs, _ = dense.stacked_lstm_dense(table[seq][:, None], W, U, b)
+        _assert_fp32(flat[pos:pos + n], rhs[-1][:, 0])
+        pos += n
+
+
 # ------------------------------------------------------------ model-level frontend
 def test_frontend_signatures(ops):
     from fractaltensor_b200 import frontend as fe

@@ -141,3 +141,10 @@ def test_online_softmax_is_softmax_with_a_clamp():
     y = dense.online_softmax_dense(x)
     d = 1.0 + math.exp(-100.0) + math.exp(-64.0)
     assert abs(y[0, 1].item() - math.exp(-64.0) / d) < 1e-35 and y[0, 1].item() > 0
+
+
+def test_embedding_lookup_matches_reference_frontend(golden_dir):
+    """ops.index(ops.slices(embedding, dim=0), word) mapped over a ragged batch of word sequences."""
+    g = _load(golden_dir, "embedding_small.npz")
+    rows = dense.embedding_gather_dense(g["table"], g["ids"])
+    assert torch.equal(rows, g["rows"])
