@@ -70,6 +70,7 @@ online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int ro
     s.d = 0.f;
     if (vec) {
       const float4* x4 = reinterpret_cast<const float4*>(xr);
+#pragma unroll 4
       for (int i = tid; i < width / 4; i += THREADS) {
         // The cached part is read once (streamed); the tail is read again by the rescale.
         const bool keep = 4 * i < cached_floats;
@@ -122,6 +123,7 @@ online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int ro
     if (vec) {
       const float4* x4 = reinterpret_cast<const float4*>(xr);
       float4* y4 = reinterpret_cast<float4*>(yr);
+#pragma unroll 4
       for (int i = tid; i < width / 4; i += THREADS) {
         float4 v = 4 * i < cached_floats ? row_cache4[i] : __ldcs(x4 + i);
         v.x = exp_fast(fmaxf(v.x - m, kClamp)) * inv_d;
