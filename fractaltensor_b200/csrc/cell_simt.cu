@@ -12,10 +12,12 @@ namespace ftb {
 
 namespace {
 
+// Small tiles: the fp32 configurations are latency-bound wavefronts of small cells, so what
+// counts is how many SMs a level reaches and how short one tile's K loop is.
 constexpr int TM = 32;   // rows per tile
-constexpr int TN = 64;   // accumulator columns per tile (16 LSTM units)
+constexpr int TN = 32;   // accumulator columns per tile (8 LSTM units)
 constexpr int TK = 32;   // K chunk
-constexpr int kSimtThreads = 256;
+constexpr int kSimtThreads = 128;
 
 struct SimtArgs {
   const float* act[kNumActMaps];
@@ -29,8 +31,8 @@ __device__ __forceinline__ float sigmoid_acc(float x) { return 1.f / (1.f + expf
 template <int EPI>
 __global__ void __launch_bounds__(kSimtThreads)
 cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ CellBatch batch) {
-  __shared__ float sA[TK][TM + 1];
-  __shared__ float sW[TK][TN + 4];
+  __shared__ __align__(16) float sA[TM][TK + 4];  // [row][k]: a thread reads four k of a row at once
+  __shared__ __align__(16) float sW[TK][TN + 4];  // [k][column]
 
   const int tile = blockIdx.x;
   int idx = 0;
@@ -41,34 +43,36 @@ cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ 
   const int n_tile = local / it.m_tiles;
   const int m_tile = local - n_tile * it.m_tiles;
 
-  const int tx = threadIdx.x & 15;  // 4 consecutive columns: one LSTM unit
-  const int ty = threadIdx.x >> 4;  // 2 consecutive rows
+  const int tx = threadIdx.x & 7;   // 4 consecutive columns: one LSTM unit
+  const int ty = threadIdx.x >> 3;  // 2 consecutive rows
   float acc[2][4] = {};
 
   // K is walked in chunks of TK over the cell's segments.  The next chunk's global loads are
   // issued into registers before the current chunk is multiplied out of shared memory, so their
   // latency overlaps the arithmetic instead of preceding it (same summation order either way).
-  const int ld_r = threadIdx.x >> 3;        // row (A) / first column (W) this thread loads
+  const int ld_r = threadIdx.x >> 3;        // first row (A) / column (W) this thread loads; second is +16
   const int ld_kq = (threadIdx.x & 7) * 4;  // its four consecutive k
-  const bool a_row_ok = m_tile * TM + ld_r < it.rows;
-  float4 va = make_float4(0.f, 0.f, 0.f, 0.f), vw0 = va, vw1 = va;
+  const bool a_ok0 = m_tile * TM + ld_r < it.rows, a_ok1 = m_tile * TM + ld_r + 16 < it.rows;
+  float4 va0 = make_float4(0.f, 0.f, 0.f, 0.f), va1 = va0, vw0 = va0, vw1 = va0;
   auto fetch = [&](int s, int k0) {
     const float* A = args.act[it.seg_map[s]];
     const int lda = args.ld_act[it.seg_map[s]];
     const int row0 = it.seg_row[s] + m_tile * TM;
     const float* W = args.w[it.w_map] + static_cast<size_t>(it.w_row0 + n_tile * TN) * args.ldw + it.seg_wk[s];
-    va = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (a_row_ok) va = *reinterpret_cast<const float4*>(A + static_cast<size_t>(row0 + ld_r) * lda + k0 + ld_kq);
+    va0 = va1 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (a_ok0) va0 = *reinterpret_cast<const float4*>(A + static_cast<size_t>(row0 + ld_r) * lda + k0 + ld_kq);
+    if (a_ok1) va1 = *reinterpret_cast<const float4*>(A + static_cast<size_t>(row0 + ld_r + 16) * lda + k0 + ld_kq);
     vw0 = *reinterpret_cast<const float4*>(W + static_cast<size_t>(ld_r) * args.ldw + k0 + ld_kq);
-    vw1 = *reinterpret_cast<const float4*>(W + static_cast<size_t>(ld_r + 32) * args.ldw + k0 + ld_kq);
+    vw1 = *reinterpret_cast<const float4*>(W + static_cast<size_t>(ld_r + 16) * args.ldw + k0 + ld_kq);
   };
   int s = 0, k0 = 0;
   if (it.nseg > 0) fetch(0, 0);
   while (s < it.nseg) {
-    sA[ld_kq + 0][ld_r] = va.x; sA[ld_kq + 1][ld_r] = va.y; sA[ld_kq + 2][ld_r] = va.z; sA[ld_kq + 3][ld_r] = va.w;
+    *reinterpret_cast<float4*>(&sA[ld_r][ld_kq]) = va0;
+    *reinterpret_cast<float4*>(&sA[ld_r + 16][ld_kq]) = va1;
     sW[ld_kq + 0][ld_r] = vw0.x; sW[ld_kq + 1][ld_r] = vw0.y; sW[ld_kq + 2][ld_r] = vw0.z; sW[ld_kq + 3][ld_r] = vw0.w;
-    sW[ld_kq + 0][ld_r + 32] = vw1.x; sW[ld_kq + 1][ld_r + 32] = vw1.y;
-    sW[ld_kq + 2][ld_r + 32] = vw1.z; sW[ld_kq + 3][ld_r + 32] = vw1.w;
+    sW[ld_kq + 0][ld_r + 16] = vw1.x; sW[ld_kq + 1][ld_r + 16] = vw1.y;
+    sW[ld_kq + 2][ld_r + 16] = vw1.z; sW[ld_kq + 3][ld_r + 16] = vw1.w;
     __syncthreads();
     int ns = s, nk0 = k0 + TK;
     if (nk0 >= it.seg_kb[s] * 64) {
@@ -77,13 +81,18 @@ cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ 
     }
     if (ns < it.nseg) fetch(ns, nk0);
 #pragma unroll
-    for (int k = 0; k < TK; ++k) {
-      const float a0 = sA[k][2 * ty], a1 = sA[k][2 * ty + 1];
-      const float4 w = *reinterpret_cast<const float4*>(&sW[k][4 * tx]);
-      acc[0][0] = fmaf(a0, w.x, acc[0][0]); acc[0][1] = fmaf(a0, w.y, acc[0][1]);
-      acc[0][2] = fmaf(a0, w.z, acc[0][2]); acc[0][3] = fmaf(a0, w.w, acc[0][3]);
-      acc[1][0] = fmaf(a1, w.x, acc[1][0]); acc[1][1] = fmaf(a1, w.y, acc[1][1]);
-      acc[1][2] = fmaf(a1, w.z, acc[1][2]); acc[1][3] = fmaf(a1, w.w, acc[1][3]);
+    for (int k4 = 0; k4 < TK; k4 += 4) {
+      const float4 r0 = *reinterpret_cast<const float4*>(&sA[2 * ty][k4]);
+      const float4 r1 = *reinterpret_cast<const float4*>(&sA[2 * ty + 1][k4]);
+      const float a0[4] = {r0.x, r0.y, r0.z, r0.w}, a1[4] = {r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 w = *reinterpret_cast<const float4*>(&sW[k4 + j][4 * tx]);
+        acc[0][0] = fmaf(a0[j], w.x, acc[0][0]); acc[0][1] = fmaf(a0[j], w.y, acc[0][1]);
+        acc[0][2] = fmaf(a0[j], w.z, acc[0][2]); acc[0][3] = fmaf(a0[j], w.w, acc[0][3]);
+        acc[1][0] = fmaf(a1[j], w.x, acc[1][0]); acc[1][1] = fmaf(a1[j], w.y, acc[1][1]);
+        acc[1][2] = fmaf(a1[j], w.z, acc[1][2]); acc[1][3] = fmaf(a1[j], w.w, acc[1][3]);
+      }
     }
     __syncthreads();
     s = ns;
@@ -120,8 +129,8 @@ cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ 
 
 }  // namespace
 
-// fp32 twin of launch_cell_gemm.  Tiles are 32 rows x 64 columns, so the
-// batch must have been tiled with m_tiles = ceil(rows / 32) and n_cols % 64 == 0.
+// fp32 twin of launch_cell_gemm.  Tiles are 32 rows x 32 columns, so the
+// batch must have been tiled with m_tiles = ceil(rows / 32) and n_cols % 32 == 0.
 int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* const* w, int ldw,
                      const CellBatch& batch, cudaStream_t stream) {
   SimtArgs a;

@@ -68,7 +68,7 @@ struct CellLauncher {
     return (rows + rows_per_tile() - 1) / rows_per_tile();
   }
   int w_box_rows() const { return pair ? bn / 2 : bn; }
-  int cols_per_tile() const { return dtype == FTB_F32 ? 64 : bn; }
+  int cols_per_tile() const { return dtype == FTB_F32 ? 32 : bn; }
 
   // Launches the cells of one level (any number; split into chunks).
   int run(std::vector<CellItem>& items) const {
