@@ -652,30 +652,58 @@ int ftb_lstm_stacked_varlen_fwd(const void* x, const void* Wp, const float* bias
   bool persistent = dtype != FTB_F32 && tune.schedule != 1 && (tune.schedule >= 2 || workspace_bytes >= lay.total);
   if (persistent) {
     if (workspace_bytes < lay.total) return FTB_ERR_WORKSPACE;
-    // Launch order: group by group, level by level (level = layer-in-group + step), so every
-    // cell comes after the two it reads.
-    std::vector<CellItem> order;
-    order.reserve(n_cells);
-    std::vector<int> index_of(n_cells, -1);
-    for (int g0 = 0; g0 < D; g0 += G) {
-      const int Lg = std::min(G, D - g0);
-      for (int m = 0; m < Lg + L - 1; ++m)
-        for (int l = g0; l < g0 + Lg; ++l) {
-          const int t = m - (l - g0);
-          if (t < 0 || t >= L) continue;
-          index_of[l * L + t] = static_cast<int>(order.size());
-          order.push_back(make_item(l, t));
-        }
-    }
-    std::vector<int32_t> deps(static_cast<size_t>(n_cells) * kMaxSeg * 2, -1);
-    for (int l = 0; l < D; ++l)
-      for (int t = 0; t < L; ++t) {
-        const int me = index_of[l * L + t];
-        if (l > 0) deps[(me * kMaxSeg + 0) * 2 + 0] = deps[(me * kMaxSeg + 0) * 2 + 1] = index_of[(l - 1) * L + t];
-        if (t > 0) deps[(me * kMaxSeg + 1) * 2 + 0] = deps[(me * kMaxSeg + 1) * 2 + 1] = index_of[l * L + t - 1];
+    // One persistent launch over the steps [t0, t1) of every layer.  Launch order: group by
+    // group, level by level (level = layer-in-group + step), so every cell comes after the two
+    // it reads; cells of earlier steps belong to an earlier launch on the stream and count as
+    // inputs.
+    auto run_range = [&](const CellLauncher& launcher, int t0, int t1) -> int {
+      const int Lr = t1 - t0;
+      std::vector<CellItem> order;
+      order.reserve(static_cast<size_t>(D) * Lr);
+      std::vector<int> index_of(static_cast<size_t>(D) * Lr, -1);
+      for (int g0 = 0; g0 < D; g0 += G) {
+        const int Lg = std::min(G, D - g0);
+        for (int m = 0; m < Lg + Lr - 1; ++m)
+          for (int l = g0; l < g0 + Lg; ++l) {
+            const int t = m - (l - g0);
+            if (t < 0 || t >= Lr) continue;
+            index_of[l * Lr + t] = static_cast<int>(order.size());
+            order.push_back(make_item(l, t0 + t));
+          }
       }
-    rc = run_persistent(cl, order, deps, static_cast<char*>(workspace), lay, workspace_bytes);
+      std::vector<int32_t> deps(order.size() * kMaxSeg * 2, -1);
+      for (int l = 0; l < D; ++l)
+        for (int t = 0; t < Lr; ++t) {
+          const int me = index_of[l * Lr + t];
+          if (l > 0)
+            deps[(me * kMaxSeg + 0) * 2 + 0] = deps[(me * kMaxSeg + 0) * 2 + 1] = index_of[(l - 1) * Lr + t];
+          if (t > 0) deps[(me * kMaxSeg + 1) * 2 + 0] = deps[(me * kMaxSeg + 1) * 2 + 1] = index_of[l * Lr + t - 1];
+        }
+      return run_persistent(launcher, order, deps, static_cast<char*>(workspace), lay, workspace_bytes);
+    };
+    // Once the batch has shrunk to one 128-row tile, a CTA pair would multiply 128 rows of
+    // padding with every weight tile.  From that step on the cells run as single CTAs on
+    // 128-column tiles (same bytes per CTA and K block, half the tensor work, twice the tiles):
+    // the time axis is cut there into two launches.  Only when the caller left the tile shape open.
+    int t_split = L;
+    if (cl.pair && tune.pair == 0 && tune.bn == 0 && tune.schedule == 0)
+      for (int t = 0; t < L; ++t)
+        if (active_rows[t] <= 128) {
+          t_split = t;
+          break;
+        }
+    rc = FTB_OK;
+    if (t_split > 0) rc = run_range(cl, 0, t_split);
+    if (rc == FTB_OK && t_split < L) {
+      CellLauncher single = cl;
+      single.pair = 0;
+      single.bn = 128;
+      rc = make_tmap_2d(&single.mapW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, single.w_box_rows(), 64);
+      if (rc) return rc;
+      rc = run_range(single, t_split, L);
+    }
     if (rc != FTB_ERR_LAUNCH || tune.schedule != 0) return rc;
+    // A refused cooperative launch falls back to one launch per level (which recomputes every cell).
   }
 
   std::vector<CellItem> items;
