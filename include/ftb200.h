@@ -160,7 +160,8 @@ int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* 
  * KeBack2BackGemm (kaleido/core/device/kernels/gemm.h:233-269,
  * cutlass_wmma.h:440-540).  A: [batch,M,K] row-major; B: [batch,N,K]
  * (column-major [K,N]); C: [batch,P,N] (column-major [N,P]); Dout: [batch,M,P].
- * K = N = P = 128, M % 128 == 0; dtype fp16 or bf16. */
+ * M % 128 == 0; K and P 64 or 128; N 128, 256 or 512, with B and C of one batch entry
+ * (N.(K+P) 16-bit elements) at most 128 KB; dtype fp16 or bf16. */
 int ftb_b2b_gemm(const void* A, const void* B, const void* C, void* Dout, int batch, int M, int N, int K, int P,
                  int dtype, void* workspace, size_t workspace_bytes, void* stream);
 

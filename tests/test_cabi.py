@@ -52,7 +52,8 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
     assert lib.ftb_lstm_stacked_fwd(one, one, z, one, one, 2, 1, 1, 128, 64, 2, None, one, 256, z) == 1
     # missing workspace
     assert lib.ftb_lstm_stacked_fwd(one, one, z, one, one, 1, 1, 1, 64, 64, 2, None, z, 0, z) == 3
-    assert lib.ftb_b2b_gemm(one, one, one, one, 1, 128, 64, 128, 128, 1, one, 256, z) == 1   # N != 128
+    assert lib.ftb_b2b_gemm(one, one, one, one, 1, 128, 64, 128, 128, 1, one, 256, z) == 1   # N not 128/256/512
+    assert lib.ftb_b2b_gemm(one, one, one, one, 1, 128, 512, 64, 128, 1, one, 256, z) == 1   # B, C too large for one SM
     assert lib.ftb_b2b_gemm(one, one, one, one, 1, 100, 128, 128, 128, 1, one, 256, z) == 1  # M % 128
     assert lib.ftb_b2b_gemm(one, one, one, one, 1, 128, 128, 128, 128, 0, one, 256, z) == 1  # fp32
     assert lib.ftb_flash_attn_fwd(one, one, one, one, 1, 1, 256, 64, 1.0, 1, one, 256, z) == 1  # d != 128

@@ -475,6 +475,22 @@ def test_b2b_gemm(ops, dt, batch, M):
     _assert_16(out, dense.b2b_gemm_dense(A, B, C).float(), tol=4e-3)
 
 
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [
+    (1, 8192, 256, 64, 64), (1, 8192, 512, 64, 64),   # shapes of the reference's own benchmark
+    (2, 256, 256, 64, 64), (3, 384, 256, 128, 128),   # two chunks of N; one B/C buffer pair only
+    (5, 128, 512, 64, 64), (2, 256, 128, 64, 128), (2, 256, 128, 128, 64), (4, 640, 256, 64, 128),
+])
+def test_b2b_gemm_shapes(ops, dt, shape):
+    """K and P of 64 or 128, N of 128, 256 or 512 (walked in chunks of 128), ranges that cross
+    batch entries with one or two B/C buffer pairs."""
+    batch, M, N, K, P = shape
+    A, B, C = dense.make_b2b_inputs(batch, M, N, K, P, 7, dtype=dt)
+    out = ops.b2b_gemm(*_dev(A, B, C))
+    ops.check_status()
+    _assert_16(out, dense.b2b_gemm_dense(A, B, C).float(), tol=6e-3)
+
+
 def test_b2b_config2_full_size(ops):
     """benchmark config 2 (16 x [16384x128].[128x128].[128x128], fp16, seed 1): full oracle compare,
     plus exact linearity under a power-of-two scale of A."""
