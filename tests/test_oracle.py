@@ -27,7 +27,8 @@ def test_stacked_lstm_config1_matches_reference_frontend(golden_dir):
     g = _load(golden_dir, "stacked_lstm_config1_samples.npz")
     x, W, U, _ = dense.make_lstm_inputs(4, 64, 32, 256, 256, 0, 1.0 / 16)
     idx = g["samples"].long()
-    hs, _ = dense.stacked_lstm_dense(x[:, idx], W, U)
+    # in float64: the fp32 evaluation on a multi-threaded host is not reproducible to this bound
+    hs, _ = dense.stacked_lstm_dense(x[:, idx].double(), W.double(), U.double())
     err = (hs[-1] - g["top"]).abs().max().item()
     assert err <= 1e-5 * g["top"].abs().max().item(), err
 
