@@ -1,0 +1,251 @@
+"""Second-order array combinators with the reference's signatures, dispatching whole programs.
+
+The reference's frontend runs ``ops.map / scan / fold / zip`` eagerly, one Python call per
+element (kaleido/frontend/operations/fractaltensor/functional/aggregate.py:28-112,
+apply_to_each.py:28-46, access.py:36-61).  Here a program written with the same combinators is
+*traced*: the outermost combinator that receives real FractalTensors runs the user's functions
+once on symbolic stand-ins, obtains the nest of combinators and the cell arithmetic as a tree,
+and compares it with the trees of the programs the library has fused kernels for.  On a match
+the whole nest runs as one wavefront on the GPU; anything else raises ``NotImplementedError``
+(there is no element-by-element fallback).
+
+Recognised so far: the stacked LSTM, batch-major (examples/stacked_rnn/stacked_lstm1.py:12-76)
+and time-major over a length-sorted ragged batch (examples/stacked_rnn/stacked_rnn.py:12-79).
+
+    from fractaltensor_b200 import operations as ops
+    out = ops.fold(lambda s, param: lstm_layer(s, *param), ops.zip(Wss, Uss, bss), initializer=embs)
+"""
+import builtins
+
+import torch
+
+from . import frontend
+
+__all__ = ["map", "scan", "fold", "zip", "repeat", "zeros", "sigmoid", "tanh"]
+
+
+# ----------------------------------------------------------------- symbolic values
+def _canon(op, a, b):
+    """Commutative operands in a fixed order, so that x*y and y*x trace to the same tree."""
+    return (op,) + tuple(sorted((a, b), key=repr))
+
+
+class SymTensor(object):
+    """Stand-in for a Tensor while a program is traced: records the arithmetic applied to it."""
+
+    def __init__(self, expr):
+        self.expr = expr
+
+    def __matmul__(self, other):
+        return SymTensor(("matmul", self.expr, _expr(other)))
+
+    def __add__(self, other):
+        return SymTensor(_canon("add", self.expr, _expr(other)))
+
+    __radd__ = __add__
+
+    def __mul__(self, other):
+        return SymTensor(_canon("mul", self.expr, _expr(other)))
+
+    __rmul__ = __mul__
+
+
+def _expr(v):
+    if isinstance(v, SymTensor):
+        return v.expr
+    raise NotImplementedError("only traced tensors can be combined inside a traced program, got %s" % type(v).__name__)
+
+
+class SymSeq(object):
+    """Stand-in for a FractalTensor: either unrolled (``items``: a short static list, e.g. the four
+    gates of a layer) or one representative element plus a tag that says where it comes from."""
+
+    def __init__(self, elem=None, items=None, tag=None):
+        self.elem, self.items, self.tag = elem, items, tag
+
+    @property
+    def length(self):
+        return len(self.items) if self.items is not None else ("len", self.tag)
+
+    def __len__(self):
+        if self.items is None:
+            raise NotImplementedError("the length of a traced sequence is symbolic; use .length")
+        return len(self.items)
+
+    def __getitem__(self, i):
+        if self.items is not None:
+            got = self.items[i]
+            return SymSeq(items=got) if isinstance(i, slice) else got
+        if isinstance(i, slice):
+            if i.start not in (None, 0) or i.step is not None:
+                raise NotImplementedError("only prefixes of a traced sequence can be sliced")
+            return SymSeq(elem=self.elem, tag=("prefix", self.tag, i.stop))
+        return self.elem  # any element of a traced sequence stands for all of them
+
+
+def _desc(v):
+    """Canonical, comparable description of a traced value."""
+    if isinstance(v, SymTensor):
+        return v.expr
+    if isinstance(v, SymSeq):
+        if v.items is not None:
+            return ("list",) + tuple(_desc(x) for x in v.items)
+        return ("seq", v.tag)
+    if isinstance(v, tuple):
+        return ("tuple",) + tuple(_desc(x) for x in v)
+    raise NotImplementedError("cannot trace a value of type %s" % type(v).__name__)
+
+
+def _is_sym(v):
+    return isinstance(v, (SymTensor, SymSeq)) or (isinstance(v, tuple) and len(v) > 0 and builtins.all(_is_sym(x) for x in v))
+
+
+def _split(results, make):
+    """A traced function that returns a tuple yields a tuple of sequences, like the reference."""
+    if isinstance(results, tuple):
+        return tuple(make(results[j], j) for j in range(len(results)))
+    return make(results, 0)
+
+
+# ------------------------------------------------------------------- combinators
+class _Zipped(object):
+    """zip of real FractalTensors, kept as is until the enclosing combinator dispatches."""
+
+    def __init__(self, xs):
+        self.xs = xs
+
+
+def zip(*xs):
+    if builtins.all(isinstance(x, SymSeq) for x in xs):
+        if builtins.all(x.items is not None for x in xs):
+            n = len(xs[0].items)
+            if builtins.any(len(x.items) != n for x in xs):
+                raise ValueError("zip of sequences of different lengths")
+            return SymSeq(items=[tuple(x.items[k] for x in xs) for k in range(n)])
+        if builtins.any(x.items is not None for x in xs):
+            raise NotImplementedError("zip of an unrolled and a traced sequence")
+        return SymSeq(elem=tuple(x.elem for x in xs), tag=("zip",) + tuple(x.tag for x in xs))
+    if builtins.any(isinstance(x, SymSeq) for x in xs):
+        raise NotImplementedError("zip of traced and real sequences")
+    return _Zipped(xs)
+
+
+def map(func, xs, **kwargs):
+    if kwargs:
+        raise NotImplementedError("map: keyword arguments are not supported")
+    if not isinstance(xs, SymSeq):
+        raise NotImplementedError("map over real data is only dispatched as part of a recognised program "
+                                  "(the outermost combinator of the stacked LSTM is fold)")
+    if xs.items is not None:
+        results = [func(it) for it in xs.items]
+        if isinstance(results[0], tuple):
+            return tuple(SymSeq(items=[r[j] for r in results]) for j in range(len(results[0])))
+        return SymSeq(items=results)
+    body = func(xs.elem)
+    bdesc = _desc(body)
+    return _split(body, lambda r, j: SymSeq(elem=r, tag=("map", xs.tag, bdesc, j)))
+
+
+def scan(func, xs, initializer=None, **kwargs):
+    if kwargs:
+        raise NotImplementedError("scan: keyword arguments are not supported")
+    if not isinstance(xs, SymSeq) or xs.items is not None:
+        raise NotImplementedError("scan over real data is only dispatched as part of a recognised program")
+    if initializer is None:
+        raise NotImplementedError("scan without an initializer")
+    init = initializer if isinstance(initializer, tuple) else (initializer,)
+
+    def state_like(v, j):
+        tag = ("state", xs.tag, j)
+        if isinstance(v, SymSeq):
+            return SymSeq(elem=SymTensor(("elem", tag)), tag=tag)
+        return SymTensor(tag)
+
+    state = tuple(state_like(v, j) for j, v in enumerate(init))
+    body = func(state if isinstance(initializer, tuple) else state[0], xs.elem)
+    idesc, bdesc = _desc(tuple(init)), _desc(body)
+    return _split(body, lambda r, j: SymSeq(elem=r, tag=("scan", xs.tag, idesc, bdesc, j)))
+
+
+def repeat(x, n):
+    return SymSeq(elem=x, tag=("repeat", _desc(x), n))
+
+
+def zeros(shape, device=None, dtype=None):
+    return SymTensor(("zeros",))
+
+
+def sigmoid(x):
+    return SymTensor(("sigmoid", _expr(x)))
+
+
+def tanh(x):
+    return SymTensor(("tanh", _expr(x)))
+
+
+# ------------------------------------------------------------ recognised programs
+def _gate(w, u, b, x, s):
+    return x @ w + s @ u + b
+
+
+def _cell(h_prev, c_prev, x, ws, us, bs):
+    pre = map(lambda p: _gate(*p, x, h_prev), zip(ws, us, bs))
+    g = map(sigmoid, pre[:3])
+    c = g[1] * c_prev + g[0] * tanh(pre[3])
+    return g[2] * tanh(c), c
+
+
+def _program_batch_major(embs, params):
+    """fold(depth) of map(batch) of scan(time): stacked_lstm1.py."""
+    def layer(xss, ws, us, bs):
+        hss, _ = map(lambda xs: scan(lambda st, x: _cell(*st, x, ws, us, bs), xs, initializer=(zeros(()), zeros(()))), xss)
+        return hss
+
+    return layer(embs, *params)
+
+
+def _program_time_major(embs, params):
+    """fold(depth) of scan(time) of map(sequences still running): stacked_rnn.py."""
+    def step(hs_prev, cs_prev, xs, ws, us, bs):
+        return map(lambda t: _cell(*t, ws, us, bs), zip(hs_prev[0:xs.length], cs_prev[0:xs.length], xs))
+
+    def layer(xss, ws, us, bs):
+        init = repeat(zeros(()), xss[0].length)
+        hss, _ = scan(lambda st, xs: step(*st, xs, ws, us, bs), xss, initializer=(init, init))
+        return hss
+
+    return layer(embs, *params)
+
+
+def _symbolic_inputs(n_params, gates):
+    seq = ("input", "state")
+    inner = ("elem", seq)
+    embs = SymSeq(tag=seq, elem=SymSeq(tag=inner, elem=SymTensor(("elem", inner))))
+    params = tuple(SymSeq(items=[SymTensor(("param", p, k)) for k in range(gates)]) for p in range(n_params))
+    return embs, params
+
+
+def _inner_length(ft):
+    idx = ft.indices
+    return len(idx[0]) if idx and isinstance(idx[0], list) else None
+
+
+def fold(func, xs, initializer=None, **kwargs):
+    """``ops.fold(lambda s, param: layer(s, *param), ops.zip(Wss, Uss, bss), initializer=embs)``."""
+    if kwargs:
+        raise NotImplementedError("fold: keyword arguments are not supported")
+    if isinstance(xs, SymSeq) or _is_sym(initializer):
+        raise NotImplementedError("a fold inside a traced program is not recognised")
+    if not isinstance(xs, _Zipped) or len(xs.xs) != 3 or initializer is None:
+        raise NotImplementedError("fold: expected ops.zip(Wss, Uss, bss) and an initializer (the stacked LSTM)")
+    Wss, Uss, bss = xs.xs
+    if builtins.any(_inner_length(p) != 4 for p in (Wss, Uss, bss)):
+        raise NotImplementedError("fold: the parameters are not [depth][4 gates] FractalTensors")
+    embs_sym, params_sym = _symbolic_inputs(3, 4)
+    traced = _desc(func(embs_sym, params_sym))
+    if traced == _desc(_program_batch_major(*_symbolic_inputs(3, 4))):
+        return frontend.stacked_lstm(initializer, Wss, Uss, bss)
+    if traced == _desc(_program_time_major(*_symbolic_inputs(3, 4))):
+        return frontend.stacked_lstm_time_major(initializer, Wss, Uss, bss)
+    raise NotImplementedError("this program is not one the library has a fused kernel for, and there is no "
+                              "element-by-element fallback")

@@ -645,6 +645,29 @@ def test_embed_then_ragged_lstm_through_the_frontend(ops):
         pos += n
 
 
+# ------------------------------------------------- traced programs (operations)
+def test_traced_programs_run_the_fused_wavefront(ops):
+    """The reference's two stacked-LSTM programs, written with the combinators of
+    fractaltensor_b200.operations, on real data: rectangular batch-major and ragged time-major."""
+    from fractaltensor_b200 import frontend, operations
+    from programs import user_programs
+    batch_major, time_major, _ = user_programs(operations)
+    D, H, N, L = 2, 64, 5, 6
+    x, W, U, b = dense.make_lstm_inputs(D, L, N, H, H, 17, 1.0 / 8, bias=True)
+    ft = lambda t, d: frontend.FractalTensor.from_dense(t.cuda(), d)
+    Wss, Uss, bss = ft(W, 2), ft(U, 2), ft(b.reshape(D, 4, 1, H), 2)
+    out = batch_major(ft(x.permute(1, 0, 2).reshape(N, L, 1, H), 2), Wss, Uss, bss)
+    rhs, _ = dense.stacked_lstm_dense(*_f32(x, W, U, b))
+    _assert_fp32(out.to_dense().reshape(N, L, H).permute(1, 0, 2), rhs[-1])
+    active = [5, 5, 3, 3, 2, 1]
+    packed = x.reshape(L * N, H)[:sum(active)].contiguous()
+    tm = frontend.FractalTensor(packed.cuda(), [list(range(n)) for n in active], (1, H))
+    out_tm = time_major(tm, Wss, Uss, bss)
+    assert [len(i) for i in out_tm.indices] == active
+    rv, _ = dense.stacked_lstm_varlen_dense(packed.double(), active, *_f32(W, U, b))
+    _assert_fp32(out_tm.data.reshape(-1, H).cpu(), rv[-1])
+
+
 # ------------------------------------------------------------ model-level frontend
 def test_frontend_signatures(ops):
     from fractaltensor_b200 import frontend as fe

@@ -91,3 +91,25 @@ def test_two_rank_shard_and_gather_gloo(n, dim):
     for p in procs:
         p.join(timeout=60)
     assert sorted(res) == [(0, True), (1, True)]
+
+
+# ----------------------------------------------------- program tracing and dispatch
+def test_programs_are_recognised_and_routed(monkeypatch):
+    from fractaltensor_b200 import operations as ops
+    calls = []
+    monkeypatch.setattr(frontend, "stacked_lstm", lambda *a: calls.append("batch") or "B")
+    monkeypatch.setattr(frontend, "stacked_lstm_time_major", lambda *a: calls.append("time") or "T")
+    embs = frontend.FractalTensor.from_dense(torch.zeros(2, 3, 1, 64), 2)
+    w = frontend.FractalTensor.from_dense(torch.zeros(2, 4, 64, 64), 2)
+    b = frontend.FractalTensor.from_dense(torch.zeros(2, 4, 1, 64), 2)
+    from programs import user_programs
+    batch_major, time_major, wrong_gates = user_programs(ops)
+    assert batch_major(embs, w, w, b) == "B"
+    assert time_major(embs, w, w, b) == "T"
+    assert calls == ["batch", "time"]
+    with pytest.raises(NotImplementedError, match="fused kernel"):
+        wrong_gates(embs, w, w, b)
+    assert calls == ["batch", "time"]
+    three_gates = frontend.FractalTensor.from_dense(torch.zeros(2, 3, 64, 64), 2)
+    with pytest.raises(NotImplementedError):
+        batch_major(embs, three_gates, three_gates, b)
