@@ -10,7 +10,9 @@ the whole nest runs as one wavefront on the GPU; anything else raises ``NotImple
 (there is no element-by-element fallback).
 
 Recognised so far: the stacked LSTM, batch-major (examples/stacked_rnn/stacked_lstm1.py:12-76)
-and time-major over a length-sorted ragged batch (examples/stacked_rnn/stacked_rnn.py:12-79).
+and time-major over a length-sorted ragged batch (examples/stacked_rnn/stacked_rnn.py:12-79), and
+blockwise attention with the online-softmax carry (examples/flash_attention/flash_attention.py:14-88,
+carry in (max, sum, out) order, optionally with the scores multiplied by a Python float).
 
     from fractaltensor_b200 import operations as ops
     out = ops.fold(lambda s, param: lstm_layer(s, *param), ops.zip(Wss, Uss, bss), initializer=embs)
@@ -21,7 +23,8 @@ import torch
 
 from . import frontend
 
-__all__ = ["map", "scan", "fold", "zip", "repeat", "zeros", "sigmoid", "tanh"]
+__all__ = ["map", "scan", "fold", "reduce", "zip", "repeat", "zeros", "full", "sigmoid", "tanh", "exp", "max", "sum",
+           "maximum"]
 
 
 # ----------------------------------------------------------------- symbolic values
@@ -45,9 +48,21 @@ class SymTensor(object):
     __radd__ = __add__
 
     def __mul__(self, other):
+        if isinstance(other, (int, float)):
+            return SymTensor(("scale", self.expr, float(other)))
         return SymTensor(_canon("mul", self.expr, _expr(other)))
 
     __rmul__ = __mul__
+
+    def __sub__(self, other):
+        return SymTensor(("sub", self.expr, _expr(other)))
+
+    def __truediv__(self, other):
+        return SymTensor(("div", self.expr, _expr(other)))
+
+    @property
+    def T(self):
+        return SymTensor(("transpose", self.expr))
 
 
 def _expr(v):
@@ -133,9 +148,10 @@ def zip(*xs):
 def map(func, xs, **kwargs):
     if kwargs:
         raise NotImplementedError("map: keyword arguments are not supported")
+    if isinstance(xs, _Zipped):
+        return _dispatch_attention(func, xs)
     if not isinstance(xs, SymSeq):
-        raise NotImplementedError("map over real data is only dispatched as part of a recognised program "
-                                  "(the outermost combinator of the stacked LSTM is fold)")
+        raise NotImplementedError("map over real data is only dispatched as part of a recognised program")
     if xs.items is not None:
         results = [func(it) for it in xs.items]
         if isinstance(results[0], tuple):
@@ -173,6 +189,39 @@ def repeat(x, n):
 
 def zeros(shape, device=None, dtype=None):
     return SymTensor(("zeros",))
+
+
+def full(shape, fill_value, device=None, dtype=None):
+    return SymTensor(("full", "lowest" if fill_value <= -3e38 else float(fill_value)))
+
+
+def exp(x):
+    return SymTensor(("exp", _expr(x)))
+
+
+def maximum(x, y):
+    return SymTensor(_canon("maximum", _expr(x), _expr(y)))
+
+
+def max(x, dim=-1, keepdim=False):
+    return SymTensor(("rowmax", _expr(x), dim, bool(keepdim)))
+
+
+def sum(x, dim=-1, keepdim=False):
+    return SymTensor(("rowsum", _expr(x), dim, bool(keepdim)))
+
+
+def reduce(func, xs, initializer=None, **kwargs):
+    """Like scan, but only the last state comes back (a tuple of tensors)."""
+    if kwargs:
+        raise NotImplementedError("reduce: keyword arguments are not supported")
+    if not isinstance(xs, SymSeq) or xs.items is not None or initializer is None:
+        raise NotImplementedError("reduce over real data is only dispatched as part of a recognised program")
+    init = initializer if isinstance(initializer, tuple) else (initializer,)
+    state = tuple(SymTensor(("state", xs.tag, j)) for j in range(len(init)))
+    body = func(state if isinstance(initializer, tuple) else state[0], xs.elem)
+    idesc, bdesc = _desc(tuple(init)), _desc(body)
+    return _split(body, lambda r, j: SymTensor(("reduce", xs.tag, idesc, bdesc, j)))
 
 
 def sigmoid(x):
@@ -215,6 +264,69 @@ def _program_time_major(embs, params):
         return hss
 
     return layer(embs, *params)
+
+
+def _program_attention(batch, scale):
+    """map(batch) of map(heads) of map(query blocks) of reduce(key/value blocks): flash_attention.py."""
+    def step(m_prev, l_prev, o_prev, q, k, v):
+        w = q @ k.T
+        if scale is not None:
+            w = w * scale
+        m_cur = max(w, dim=-1, keepdim=True)
+        e = exp(w - m_cur)
+        ev = e @ v
+        l_cur = sum(e, dim=-1, keepdim=True)
+        m_new = maximum(m_cur, m_prev)
+        r_prev, r_cur = exp(m_prev - m_new), exp(m_cur - m_new)
+        l_new = r_prev * l_prev + r_cur * l_cur
+        return m_new, l_new, (o_prev * l_prev * r_prev + r_cur * ev) / l_new
+
+    def block(q, ks, vs):
+        init = (full((), -3.5e38), zeros(()), zeros(()))
+        _, _, o = reduce(lambda st, kv: step(*st, q, *kv), zip(ks, vs), initializer=init)
+        return o
+
+    return map(lambda xss: map(lambda xs: map(lambda q: block(q, xs[1], xs[2]), xs[0]), zip(*xss)), batch)
+
+
+def _deep_input(name, depth):
+    tag = ("input", name)
+    def build(t, d):
+        return SymTensor(("elem", t)) if d == 0 else SymSeq(tag=t, elem=build(("elem", t), d - 1))
+    return build(tag, depth)
+
+
+def _find_scales(tree, out):
+    if isinstance(tree, tuple):
+        if len(tree) == 3 and tree[0] == "scale":
+            out.add(tree[2])
+        for x in tree:
+            _find_scales(x, out)
+    return out
+
+
+def _dispatch_attention(func, zipped):
+    def depth(ft):
+        d, x = 0, getattr(ft, "indices", None)
+        while isinstance(x, list):
+            d, x = d + 1, (x[0] if x else None)
+        return d
+
+    if len(zipped.xs) != 3 or builtins.any(depth(x) != 3 for x in zipped.xs):
+        raise NotImplementedError("map over real data: expected ops.zip(qsss, ksss, vsss) of depth-3 FractalTensors")
+
+    def batch():
+        return zip(*[_deep_input(n, 3) for n in ("q", "k", "v")])
+    traced = _desc(map(func, batch()))
+    scales = _find_scales(traced, set())
+    if len(scales) > 1:
+        raise NotImplementedError("more than one constant factor in the program")
+    scale = scales.pop() if scales else None
+    if traced == _desc(_program_attention(batch(), scale)):
+        q, k, v = zipped.xs
+        return frontend.flash_attention(q, k, v, scale=1.0 if scale is None else scale)
+    raise NotImplementedError("this program is not one the library has a fused kernel for, and there is no "
+                              "element-by-element fallback")
 
 
 def _symbolic_inputs(n_params, gates):

@@ -53,3 +53,38 @@ def user_programs(ops, H=64):
         return ops.fold(lambda s, param: layer(s, *param), ops.zip(Wss, Uss, bss), initializer=embs)
 
     return batch_major, time_major, wrong_gates
+
+
+def attention_program(ops, blk, d, scale=None):
+    """Blockwise attention with the online-softmax carry (examples/flash_attention/flash_attention.py),
+    the carry started in (max, sum, out) order."""
+    def attn_func(prev_maxes, prev_sums, prev_out, query, key, value):
+        attn_weights = query @ key.T
+        if scale is not None:
+            attn_weights = attn_weights * scale
+        cur_maxes = ops.max(attn_weights, dim=-1, keepdim=True)
+        exp_weights = ops.exp(attn_weights - cur_maxes)
+        exp_values = exp_weights @ value
+        cur_sums = ops.sum(exp_weights, dim=-1, keepdim=True)
+        new_maxes = ops.maximum(cur_maxes, prev_maxes)
+        renorm_prev = ops.exp(prev_maxes - new_maxes)
+        renorm_cur = ops.exp(cur_maxes - new_maxes)
+        new_sums = renorm_prev * prev_sums + renorm_cur * cur_sums
+        o = (prev_out * prev_sums * renorm_prev + renorm_cur * exp_values) / new_sums
+        return new_maxes, new_sums, o
+
+    def per_block_func(query, ks, vs):
+        init_sum = ops.zeros(shape=(blk, 1), device="cpu")
+        init_max = ops.full(shape=(blk, 1), fill_value=-3.4028234663852886e38, device="cpu")
+        init_o = ops.zeros(shape=(blk, d), device="cpu")
+        _, _, o = ops.reduce(lambda state, kvs: attn_func(*state, query, *kvs), ops.zip(ks, vs),
+                             initializer=(init_max, init_sum, init_o))
+        return o
+
+    def per_head_func(qs, ks, vs):
+        return ops.map(lambda q_: per_block_func(q_, ks, vs), qs)
+
+    def flash_attention(qsss, ksss, vsss):
+        return ops.map(lambda xss: ops.map(lambda xs: per_head_func(*xs), ops.zip(*xss)), ops.zip(qsss, ksss, vsss))
+
+    return flash_attention

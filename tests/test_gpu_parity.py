@@ -668,6 +668,15 @@ def test_traced_programs_run_the_fused_wavefront(ops):
     _assert_fp32(out_tm.data.reshape(-1, H).cpu(), rv[-1])
 
 
+def test_traced_attention_program(ops):
+    from fractaltensor_b200 import frontend, operations
+    from programs import attention_program
+    q, k, v = dense.make_attention_inputs(1, 2, 512, 128, 19)
+    to_ft = lambda t: frontend.FractalTensor.from_dense(t.reshape(1, 2, 8, 64, 128).cuda(), 3)
+    o = attention_program(operations, 64, 128, scale=0.1)(to_ft(q), to_ft(k), to_ft(v))
+    _assert_16(o.to_dense().reshape(1, 2, 512, 128), dense.attention_plain(*_f32(q, k, v), scale=0.1))
+
+
 # ------------------------------------------------------------ model-level frontend
 def test_frontend_signatures(ops):
     from fractaltensor_b200 import frontend as fe

@@ -113,3 +113,17 @@ def test_programs_are_recognised_and_routed(monkeypatch):
     three_gates = frontend.FractalTensor.from_dense(torch.zeros(2, 3, 64, 64), 2)
     with pytest.raises(NotImplementedError):
         batch_major(embs, three_gates, three_gates, b)
+
+
+def test_attention_program_is_recognised_with_its_scale(monkeypatch):
+    from fractaltensor_b200 import operations as ops
+    from programs import attention_program
+    seen = []
+    monkeypatch.setattr(frontend, "flash_attention", lambda q, k, v, scale=1.0: seen.append(scale) or "A")
+    t = frontend.FractalTensor.from_dense(torch.zeros(1, 2, 2, 64, 128), 3)
+    assert attention_program(ops, 64, 128)(t, t, t) == "A"
+    assert attention_program(ops, 64, 128, scale=0.125)(t, t, t) == "A"
+    assert seen == [1.0, 0.125]
+    shallow = frontend.FractalTensor.from_dense(torch.zeros(2, 2, 64, 128), 2)
+    with pytest.raises(NotImplementedError):
+        attention_program(ops, 64, 128)(shallow, shallow, shallow)
