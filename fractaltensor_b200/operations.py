@@ -12,7 +12,8 @@ the whole nest runs as one wavefront on the GPU; anything else raises ``NotImple
 Recognised so far: the stacked LSTM, batch-major (examples/stacked_rnn/stacked_lstm1.py:12-76)
 and time-major over a length-sorted ragged batch (examples/stacked_rnn/stacked_rnn.py:12-79), and
 blockwise attention with the online-softmax carry (examples/flash_attention/flash_attention.py:14-88,
-carry in (max, sum, out) order, optionally with the scores multiplied by a Python float).
+carry in (max, sum, out) order, optionally with the scores multiplied by a Python float), and the
+stacked dilated LSTM (examples/dilated_rnn/dilated_rnn.py:16-41, dilation 2**layer).
 
     from fractaltensor_b200 import operations as ops
     out = ops.fold(lambda s, param: lstm_layer(s, *param), ops.zip(Wss, Uss, bss), initializer=embs)
@@ -23,7 +24,7 @@ import torch
 
 from . import frontend
 
-__all__ = ["map", "scan", "fold", "reduce", "zip", "repeat", "zeros", "full", "sigmoid", "tanh", "exp", "max", "sum",
+__all__ = ["map", "scan", "fold", "reduce", "zip", "enumerate", "dilated_map", "repeat", "zeros", "full", "sigmoid", "tanh", "exp", "max", "sum",
            "maximum"]
 
 
@@ -123,6 +124,32 @@ def _split(results, make):
 
 
 # ------------------------------------------------------------------- combinators
+class SymInt(object):
+    """Stand-in for the position that ops.enumerate hands to the folded function."""
+
+    def __init__(self, expr):
+        self.expr = expr
+
+    def __rpow__(self, base):
+        return SymInt(("pow", base, self.expr))
+
+
+class _Enumerated(object):
+    """enumerate of real FractalTensors, kept until the enclosing combinator dispatches."""
+
+    def __init__(self, xs):
+        self.xs = xs
+
+
+def enumerate(*xs):
+    if builtins.any(isinstance(x, SymSeq) for x in xs):
+        raise NotImplementedError("enumerate of traced sequences")
+    return _Enumerated(xs)
+
+
+_seen = {}  # real parameter sets met inside the program being traced
+
+
 class _Zipped(object):
     """zip of real FractalTensors, kept as is until the enclosing combinator dispatches."""
 
@@ -150,6 +177,8 @@ def map(func, xs, **kwargs):
         raise NotImplementedError("map: keyword arguments are not supported")
     if isinstance(xs, _Zipped):
         return _dispatch_attention(func, xs)
+    if not isinstance(xs, SymSeq) and hasattr(xs, "indices") and hasattr(xs, "data"):
+        return _dispatch_dilated(func, xs)
     if not isinstance(xs, SymSeq):
         raise NotImplementedError("map over real data is only dispatched as part of a recognised program")
     if xs.items is not None:
@@ -177,10 +206,24 @@ def scan(func, xs, initializer=None, **kwargs):
             return SymSeq(elem=SymTensor(("elem", tag)), tag=tag)
         return SymTensor(tag)
 
-    state = tuple(state_like(v, j) for j, v in enumerate(init))
+    state = tuple(state_like(v, j) for j, v in builtins.enumerate(init))
     body = func(state if isinstance(initializer, tuple) else state[0], xs.elem)
     idesc, bdesc = _desc(tuple(init)), _desc(body)
     return _split(body, lambda r, j: SymSeq(elem=r, tag=("scan", xs.tag, idesc, bdesc, j)))
+
+
+def dilated_map(func, xs, dilation=1, **kwargs):
+    """func applied to each of the `dilation` interleaved sub-sequences of xs, results merged back."""
+    if kwargs:
+        raise NotImplementedError("dilated_map: keyword arguments are not supported")
+    if not isinstance(xs, SymSeq) or xs.items is not None:
+        raise NotImplementedError("dilated_map over real data is only dispatched as part of a recognised program")
+    d = dilation.expr if isinstance(dilation, SymInt) else int(dilation)
+    sub = SymSeq(elem=xs.elem, tag=("every", d, xs.tag))
+    body = func(sub)
+    bdesc = _desc(body)
+    return _split(body, lambda r, j: SymSeq(elem=r.elem if isinstance(r, SymSeq) else r,
+                                            tag=("dilated_map", xs.tag, d, bdesc, j)))
 
 
 def repeat(x, n):
@@ -329,6 +372,30 @@ def _dispatch_attention(func, zipped):
                               "element-by-element fallback")
 
 
+def _program_dilated(embs, enumerated):
+    """map(batch) of fold(layers) of dilated_map(scan(time)), dilation 2**layer: dilated_rnn.py."""
+    def layer(state, position, ws, us, bs):
+        h, _ = dilated_map(lambda xs: scan(lambda st, x: _cell(*st, x, ws, us, bs), xs, initializer=(zeros(()), zeros(()))),
+                           state, dilation=2 ** position)
+        return h
+
+    return map(lambda xs: fold(lambda s, p: layer(s, *p), enumerated, initializer=xs), embs)
+
+
+def _dispatch_dilated(func, embs):
+    def symbolic():
+        return _symbolic_inputs(3, 4)[0]
+
+    _seen.clear()
+    traced = _desc(map(func, symbolic()))
+    params = _seen.pop("enumerated", None)
+    if params is not None and traced == _desc(_program_dilated(symbolic(), params)):
+        Wss, Uss, bss = params.xs
+        return frontend.dilated_lstm(embs, Wss, Uss, bss)
+    raise NotImplementedError("this program is not one the library has a fused kernel for, and there is no "
+                              "element-by-element fallback")
+
+
 def _symbolic_inputs(n_params, gates):
     seq = ("input", "state")
     inner = ("elem", seq)
@@ -346,6 +413,15 @@ def fold(func, xs, initializer=None, **kwargs):
     """``ops.fold(lambda s, param: layer(s, *param), ops.zip(Wss, Uss, bss), initializer=embs)``."""
     if kwargs:
         raise NotImplementedError("fold: keyword arguments are not supported")
+    if isinstance(xs, _Enumerated) and isinstance(initializer, SymSeq):
+        # Inside a traced program: fold over (position, one layer's parameters) of real parameters.
+        if len(xs.xs) != 3 or builtins.any(_inner_length(p) != 4 for p in xs.xs):
+            raise NotImplementedError("fold: expected ops.enumerate(Wss, Uss, bss) of [depth][4 gates] parameters")
+        _seen["enumerated"] = xs
+        state = SymSeq(elem=initializer.elem, tag=("state", "fold"))
+        elem = (SymInt("position"),) + _symbolic_inputs(3, 4)[1]
+        body = func(state, elem)
+        return SymSeq(elem=body.elem, tag=("fold", _desc(initializer), _desc(body)))
     if isinstance(xs, SymSeq) or _is_sym(initializer):
         raise NotImplementedError("a fold inside a traced program is not recognised")
     if not isinstance(xs, _Zipped) or len(xs.xs) != 3 or initializer is None:

@@ -88,3 +88,30 @@ def attention_program(ops, blk, d, scale=None):
         return ops.map(lambda xss: ops.map(lambda xs: per_head_func(*xs), ops.zip(*xss)), ops.zip(qsss, ksss, vsss))
 
     return flash_attention
+
+
+def dilated_program(ops, H=64):
+    """The stacked dilated LSTM (examples/dilated_rnn/dilated_rnn.py): layer i scans 2**i interleaved
+    sub-sequences."""
+    def gate_f(w, u, b, x, s):
+        return x @ w + s @ u + b
+
+    def lstm_cell(h_prev, c_prev, input, ws, us, bs):
+        prev_gate = ops.map(lambda x: gate_f(*x, input, h_prev), ops.zip(ws, us, bs))
+        gate = ops.map(lambda x: ops.sigmoid(x), prev_gate[:3])
+        c = gate[1] * c_prev + gate[0] * ops.tanh(prev_gate[3])
+        h = gate[2] * ops.tanh(c)
+        return h, c
+
+    def dilated_layer(state, itr, Ws, Us, bs):
+        zeros = ops.zeros(shape=(1, H), device="cpu", dtype="float")
+        h, _ = ops.dilated_map(
+            lambda xs: ops.scan(lambda s, x: lstm_cell(*s, x, Ws, Us, bs), xs, initializer=(zeros, zeros)),
+            state, dilation=2 ** itr)
+        return h
+
+    def model(embs, Wss, Uss, bss):
+        itrs = ops.enumerate(Wss, Uss, bss)
+        return ops.map(lambda xs: ops.fold(lambda s, x: dilated_layer(s, *x), itrs, initializer=xs), embs)
+
+    return model

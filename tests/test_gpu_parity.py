@@ -668,6 +668,18 @@ def test_traced_programs_run_the_fused_wavefront(ops):
     _assert_fp32(out_tm.data.reshape(-1, H).cpu(), rv[-1])
 
 
+def test_traced_dilated_program(ops):
+    from fractaltensor_b200 import frontend, operations
+    from programs import dilated_program
+    D, L, N, H = 3, 11, 4, 64
+    x, W, U, b = dense.make_lstm_inputs(D, L, N, H, H, 18, 1.0 / 8, bias=True)
+    ft = lambda t, d: frontend.FractalTensor.from_dense(t.cuda(), d)
+    out = dilated_program(operations)(ft(x.permute(1, 0, 2).reshape(N, L, 1, H), 2), ft(W, 2), ft(U, 2),
+                                      ft(b.reshape(D, 4, 1, H), 2))
+    ref = dense.dilated_lstm_dense(*_f32(x, W, U), [1, 2, 4], b.double())
+    _assert_fp32(out.to_dense().reshape(N, L, H).permute(1, 0, 2), ref[-1])
+
+
 def test_traced_attention_program(ops):
     from fractaltensor_b200 import frontend, operations
     from programs import attention_program

@@ -127,3 +127,19 @@ def test_attention_program_is_recognised_with_its_scale(monkeypatch):
     shallow = frontend.FractalTensor.from_dense(torch.zeros(2, 2, 64, 128), 2)
     with pytest.raises(NotImplementedError):
         attention_program(ops, 64, 128)(shallow, shallow, shallow)
+
+
+def test_dilated_program_is_recognised(monkeypatch):
+    from fractaltensor_b200 import operations as ops
+    from programs import dilated_program
+    got = []
+    monkeypatch.setattr(frontend, "dilated_lstm", lambda embs, W, U, b: got.append((W, U, b)) or "D")
+    embs = frontend.FractalTensor.from_dense(torch.zeros(2, 8, 1, 64), 2)
+    w = frontend.FractalTensor.from_dense(torch.zeros(3, 4, 64, 64), 2)
+    u = frontend.FractalTensor.from_dense(torch.zeros(3, 4, 64, 64), 2)
+    b = frontend.FractalTensor.from_dense(torch.zeros(3, 4, 1, 64), 2)
+    assert dilated_program(ops)(embs, w, u, b) == "D"
+    assert got[0][0] is w and got[0][1] is u and got[0][2] is b
+    # a plain map over real data with some other body is not a known program
+    with pytest.raises(NotImplementedError):
+        ops.map(lambda xs: ops.map(lambda x: ops.tanh(x), xs), embs)
