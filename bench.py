@@ -421,7 +421,7 @@ def main():
     if world == 1 and not args.no_other_configs:
         others = other_configs(ops, dense, dev, pk)
     cpu = None
-    if not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline:  # timed on rank 0 of single-GPU runs only
         threads = os.cpu_count() or 1
         sample = 50
         rate, dt = cpu_port_rate(sample, threads)
