@@ -40,6 +40,7 @@ constexpr int kTileBytes = 2 * kHalfBytes;
 constexpr int kKVSlots = 5;
 constexpr int kThreads = 64 + 512;
 constexpr float kRescaleThreshold = 8.0f;
+constexpr int kCausalGroup = 16;   // (batch, head) entries whose CTAs are ordered longest first together
 
 // Shared memory, all dynamic so that the 1024-byte alignment of the swizzled tiles costs
 // no more than the bytes actually skipped: tiles, then the small control block.
@@ -84,11 +85,11 @@ __device__ unsigned long long g_fa_trace[2][32][8];
 #define FA_STAMP_MMA(tt, jj, k)
 #endif
 
-template <typename T>
+template <typename T, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                   const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, int S,
-                  float scale_log2, int* __restrict__ status) {
+                  int n_bh, int group, float scale_log2, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
 
   if (*reinterpret_cast<volatile int*>(status) != 0) return;
@@ -108,11 +109,25 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   volatile int* s_abort = &ctl.abort;
 
   const int pairs = S / 256;
-  const int bh = blockIdx.x / pairs;
-  const int qpair = blockIdx.x - bh * pairs;
+  int bh = blockIdx.x / pairs;
+  int qpair = blockIdx.x - bh * pairs;
+  if (kCausal) {
+    // A pair's run length grows with its position, so CTAs are handed out longest first: within
+    // a group of `group` (batch, head) entries all last pairs, then all pairs before them, ...
+    // The grid's last CTAs are then the shortest, and the group bounds the K/V set in flight.
+    const int per_group = group * pairs;
+    const int g = blockIdx.x / per_group;
+    const int r = blockIdx.x - g * per_group;
+    const int gsize = min(group, n_bh - g * group);
+    qpair = pairs - 1 - r / gsize;
+    bh = g * group + r % gsize;
+  }
   const int row_base = bh * S;            // first row of this (batch, head) in the flattened [B*heads*S, d] view
   const int q_row0 = row_base + qpair * 256;
-  const int n_kv = S / 128;
+  // Key/value blocks this CTA walks.  Causal (key index <= query index): query tile t of this pair
+  // ends at block 2*qpair + t, its diagonal block; tile 0 leaves the loop one block before tile 1.
+  const int n_kv = kCausal ? 2 * qpair + 2 : S / 128;
+  const int n_kv0 = kCausal ? n_kv - 1 : n_kv;  // tile 0's count
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&mapQ);
@@ -220,6 +235,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         if (!wait_slot(2 * j + 1)) break;            // V_j
         if (more && !wait_slot(2 * j + 2)) break;    // K_{j+1}
         for (int t = 0; t < 2 && ok; ++t) {
+          if (kCausal && t == 0 && j >= n_kv0) continue;
           // P_t(j) is in TMEM (and the softmax is done with S_t(j)).
           if (!mbar_wait(&ctl.p_full[t], j & 1, s_abort, status, FTB_ERR_TIMEOUT_EPI)) {
             ok = false;
@@ -230,7 +246,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
           issue_pv(t, j);
           // The tensor pipe runs MMAs in issue order: S_t(j+1) overwrites S_t / P_t only after
           // PV_t(j) has read P_t.
-          if (more) issue_s(t, j + 1);
+          if (more && (!kCausal || t == 1 || j + 1 < n_kv0)) issue_s(t, j + 1);
           FA_STAMP_MMA(t, j, 6);
         }
         if (!ok) break;
@@ -253,8 +269,9 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     uint64_t* pair = &ctl.pair_bar[t][q];
     float m_used = 0.f, l = 0.f;
     bool ok = true;
+    const int n_mine = t == 0 ? n_kv0 : n_kv;
 
-    for (int j = 0; j < n_kv && ok; ++j) {
+    for (int j = 0; j < n_mine && ok; ++j) {
       if (!__all_sync(0xffffffffu, mbar_wait(&ctl.s_full[t], j & 1, s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
         ok = false;
         break;
@@ -266,6 +283,13 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       tmem_ld32p(s_addr + 32, s + 32);
       tmem_ld_wait();
       FA_STAMP(t, j, 1);
+      if (kCausal && j == n_mine - 1) {
+        // Diagonal block: key h*64 + i is visible to query `row` when it is not after it.  Key 0 of
+        // the block is visible to every row, so the row maximum stays finite.
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (h * 64 + i > row) s[i] = 0xff800000u;  // -inf
+      }
 
       // Maximum of this half of the row: eight independent chains of three-input maxima.
       float mx8[8];
@@ -353,12 +377,12 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       *my_x = l;
       __syncwarp();
       if (lane == 0) mbar_arrive(pair);
-      ok = __all_sync(0xffffffffu, mbar_wait(pair, n_kv & 1, s_abort, status, FTB_ERR_TIMEOUT_EPI));
+      ok = __all_sync(0xffffffffu, mbar_wait(pair, n_mine & 1, s_abort, status, FTB_ERR_TIMEOUT_EPI));
       if (ok) l += *peer_x;
     }
     // Final: O_t / l -> 16-bit -> staging (the Q tile, dead once the last PV is done) -> TMA store.
     if (ok && __all_sync(0xffffffffu,
-                         mbar_wait(&ctl.pv_done[t], (n_kv - 1) & 1, s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
+                         mbar_wait(&ctl.pv_done[t], (n_mine - 1) & 1, s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
       tc_fence_after();
       const float inv_l = 1.f / l;
 #pragma unroll 1
@@ -403,17 +427,18 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   }
 }
 
-template <typename T>
-int launch(const CUtensorMap& mQ, const CUtensorMap& mK, const CUtensorMap& mV, const CUtensorMap& mO, int units,
+template <typename T, bool kCausal>
+int launch(const CUtensorMap& mQ, const CUtensorMap& mK, const CUtensorMap& mV, const CUtensorMap& mO, int n_bh,
            int S, float scale_log2, int* status, cudaStream_t stream) {
   static bool configured = false;
-  auto kfn = flash_attn_kernel<T>;
+  auto kfn = flash_attn_kernel<T, kCausal>;
   if (!configured) {
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
       return FTB_ERR_LAUNCH;
     configured = true;
   }
-  kfn<<<units, kThreads, kSmemBytes, stream>>>(mQ, mK, mV, mO, S, scale_log2, status);
+  const int group = kCausalGroup;
+  kfn<<<n_bh * (S / 256), kThreads, kSmemBytes, stream>>>(mQ, mK, mV, mO, S, n_bh, group, scale_log2, status);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
@@ -429,13 +454,14 @@ extern "C" int ftb_debug_fa_trace(unsigned long long* out) {
 }
 #endif
 
-extern "C" int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S,
-                                  int d, float scale, int dtype, void* workspace, size_t workspace_bytes,
-                                  void* stream_) {
+namespace {
+int flash_attn_entry(const void* q, const void* k, const void* v, void* o, int B, int heads, int S, int d,
+                     float scale, int dtype, bool causal, void* workspace, size_t workspace_bytes, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!q || !k || !v || !o || B <= 0 || heads <= 0 || S <= 0) return FTB_ERR_ARG;
   if (dtype != FTB_F16 && dtype != FTB_BF16) return FTB_ERR_ARG;
   if (d != 128 || S % 256 != 0) return FTB_ERR_ARG;
+  if (causal && !(scale > 0.f)) return FTB_ERR_ARG;  // masked scores are -inf times the scale
   const int64_t rows = static_cast<int64_t>(B) * heads * S;
   if (rows > 0x7fffffffLL) return FTB_ERR_ARG;
   if (workspace == nullptr || workspace_bytes < ftb_workspace_bytes()) return FTB_ERR_WORKSPACE;
@@ -450,8 +476,25 @@ extern "C" int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, v
   if ((rc = make_tmap_2d(&mK, k, dtype, rows, d, d, 128, 64))) return rc;
   if ((rc = make_tmap_2d(&mV, v, dtype, rows, d, d, 128, 64))) return rc;
   if ((rc = make_tmap_2d(&mO, o, dtype, rows, d, d, 128, 64))) return rc;
-  const int units = B * heads * (S / 256);
+  const int units = B * heads;
   const float scale_log2 = scale * 1.4426950408889634f;
-  if (dtype == FTB_F16) return launch<__half>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
-  return launch<__nv_bfloat16>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
+  if (causal) {
+    if (dtype == FTB_F16) return launch<__half, true>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
+    return launch<__nv_bfloat16, true>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
+  }
+  if (dtype == FTB_F16) return launch<__half, false>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
+  return launch<__nv_bfloat16, false>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
+}
+}  // namespace
+
+extern "C" int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S,
+                                  int d, float scale, int dtype, void* workspace, size_t workspace_bytes,
+                                  void* stream) {
+  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, false, workspace, workspace_bytes, stream);
+}
+
+extern "C" int ftb_flash_attn_causal_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads,
+                                         int S, int d, float scale, int dtype, void* workspace,
+                                         size_t workspace_bytes, void* stream) {
+  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, true, workspace, workspace_bytes, stream);
 }

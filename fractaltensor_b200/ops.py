@@ -248,8 +248,8 @@ def b2b_gemm(A, B, C, out=None):
     return out
 
 
-def flash_attention(q, k, v, scale=None, out=None):
-    """q,k,v: [B,heads,S,d] -> softmax(scale * q k^T) v, same shape."""
+def flash_attention(q, k, v, scale=None, out=None, causal=False):
+    """q,k,v: [B,heads,S,d] -> softmax(scale * q k^T) v, same shape; `causal`: keys 0..i for query i."""
     _req(q, "q")
     _req(k, "k", q.dtype)
     _req(v, "v", q.dtype)
@@ -263,8 +263,9 @@ def flash_attention(q, k, v, scale=None, out=None):
     _req(out, "out", q.dtype)
     ws = workspace(q.device)
     with torch.cuda.device(q.device):
-        check(lib.ftb_flash_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, heads, S, d, float(scale),
-                                     _dtype_code(q), _ptr(ws), ws.numel(), _stream()), "ftb_flash_attn_fwd")
+        name = "ftb_flash_attn_causal_fwd" if causal else "ftb_flash_attn_fwd"
+        check(getattr(lib, name)(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, heads, S, d, float(scale),
+                                 _dtype_code(q), _ptr(ws), ws.numel(), _stream()), name)
     return out
 
 

@@ -173,6 +173,15 @@ int ftb_b2b_gemm(const void* A, const void* B, const void* C, void* Dout, int ba
 int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S, int d,
                        float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same with a causal mask: query i attends to keys 0..i only (scores of later keys
+ * are -inf before the softmax).  The reference has no causal program; this is the
+ * blockwise program above with the key walk of each query tile cut at its diagonal
+ * block, as every other implementation of that example's algorithm defines it.
+ * Same shapes and types; scale > 0. */
+int ftb_flash_attn_causal_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S,
+                              int d, float scale, int dtype, void* workspace, size_t workspace_bytes,
+                              void* stream);
+
 /* Embedding lookup out[t, :] = table[ids[t], :] for t < T.  Stands in for the lookup in front of
  * the reference's RNN examples, ops.index(ops.slices(embedding, dim=0), word) mapped over a batch
  * of word sequences (examples/stacked_rnn/rnn_utils.py:80-90): `ids` is the flat int64 buffer of

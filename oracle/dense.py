@@ -222,9 +222,49 @@ def embedding_gather_dense(table, ids):
     return table[ids.reshape(-1)]
 
 
-def attention_plain(q, k, v, scale=1.0):
-    """softmax(scale * q k^T) v, the closed form the blockwise carry equals."""
-    return torch.softmax((q @ k.transpose(-1, -2)) * scale, dim=-1) @ v
+def attention_plain(q, k, v, scale=1.0, causal=False):
+    """softmax(scale * q k^T) v, the closed form the blockwise carry equals.
+
+    `causal`: query i sees keys 0..i (later scores are -inf before the softmax).  The reference
+    has no causal program, so this case has no vectors of the reference behind it.
+    """
+    w = (q @ k.transpose(-1, -2)) * scale
+    if causal:
+        S = q.shape[-2]
+        keep = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        w = w.masked_fill(~keep, float("-inf"))
+    return torch.softmax(w, dim=-1) @ v
+
+
+def flash_attention_causal_dense(q, k, v, scale=1.0, block=64):
+    """The blockwise carry of flash_attention_dense with the key walk of each query block cut
+    at its diagonal block and the later keys of that block masked to -inf."""
+    Bsz, heads, S, d = q.shape
+    out = torch.empty_like(q)
+    for i0 in range(0, S, block):
+        qi = q[:, :, i0:i0 + block]
+        m = q.new_full((Bsz, heads, qi.shape[2], 1), -torch.finfo(torch.float32).max)
+        l = q.new_zeros(Bsz, heads, qi.shape[2], 1)
+        o = q.new_zeros(Bsz, heads, qi.shape[2], d)
+        for j0 in range(0, i0 + block, block):
+            kj, vj = k[:, :, j0:j0 + block], v[:, :, j0:j0 + block]
+            w = (qi @ kj.transpose(-1, -2)) * scale
+            if j0 == i0:
+                n = w.shape[-1]
+                keep = torch.ones(qi.shape[2], n, dtype=torch.bool, device=q.device).tril()
+                w = w.masked_fill(~keep, float("-inf"))
+            cur_m = w.max(dim=-1, keepdim=True).values
+            e = torch.exp(w - cur_m)
+            ev = e @ vj
+            cur_l = e.sum(dim=-1, keepdim=True)
+            new_m = torch.maximum(cur_m, m)
+            r_prev = torch.exp(m - new_m)
+            r_cur = torch.exp(cur_m - new_m)
+            new_l = r_prev * l + r_cur * cur_l
+            o = (o * l * r_prev + r_cur * ev) / new_l
+            m, l = new_m, new_l
+        out[:, :, i0:i0 + block] = o
+    return out
 
 
 # ------------------------------------------------------------------ seeded inputs

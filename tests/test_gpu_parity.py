@@ -562,6 +562,46 @@ def test_flash_attention_config3_properties(ops):
     assert (ones.float() - 1).abs().max().item() <= 2e-3
 
 
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 1, 256), (1, 2, 512), (2, 3, 1280)])
+def test_flash_attention_causal(ops, dt, shape):
+    """Causal mask: the blockwise carry cut at the diagonal block, and the closed form."""
+    B, h, S = shape
+    q, k, v = dense.make_attention_inputs(B, h, S, 128, 21, dtype=dt)
+    sc = 1.0 / math.sqrt(128.0)
+    out = ops.flash_attention(*_dev(q, k, v), scale=sc, causal=True)
+    ops.check_status()
+    _assert_16(out, dense.flash_attention_causal_dense(*_f32(q, k, v), scale=sc, block=64))
+    _assert_16(out, dense.attention_plain(*_f32(q, k, v), scale=sc, causal=True))
+    # the first query sees key 0 only: its output is v[0]
+    assert (out[:, :, 0].float().cpu() - v[:, :, 0].float()).abs().max().item() <= 2e-3
+
+
+def test_flash_attention_causal_ignores_later_keys(ops):
+    """Full-size property (benchmark config 3 shape): changing keys and values after position
+    p leaves the outputs of queries 0..p unchanged, bit for bit."""
+    q, k, v = dense.make_attention_inputs(16, 16, 2048, 128, 2)
+    sc = 1.0 / math.sqrt(128.0)
+    qd, kd, vd = _dev(q, k, v)
+    out = ops.flash_attention(qd, kd, vd, scale=sc, causal=True)
+    p = 1000
+    k2, v2 = kd.clone(), vd.clone()
+    k2[:, :, p + 1:] = 7.0
+    v2[:, :, p + 1:] = -3.0
+    out2 = ops.flash_attention(qd, k2, v2, scale=sc, causal=True)
+    ops.check_status()
+    assert torch.equal(out[:, :, :p + 1], out2[:, :, :p + 1])
+    assert not torch.equal(out[:, :, p + 1:], out2[:, :, p + 1:])
+    ref = dense.attention_plain(q[3, 5].double(), k[3, 5].double(), v[3, 5].double(), sc, causal=True)
+    _assert_16(out[3, 5], ref)
+
+
+def test_flash_attention_causal_rejects_nonpositive_scale(ops):
+    q, k, v = dense.make_attention_inputs(1, 1, 256, 128, 2)
+    with pytest.raises(RuntimeError):
+        ops.flash_attention(*_dev(q, k, v), scale=0.0, causal=True)
+
+
 # ------------------------------------------------------------ online softmax
 @pytest.mark.parametrize("shape", [(2, 7), (2, 517), (2, 1027), (5, 4096), (3, 60000), (300, 128), (1, 1)])
 def test_online_softmax(ops, shape):

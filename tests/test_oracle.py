@@ -84,6 +84,16 @@ def test_flash_attention_matches_reference_frontend(golden_dir):
     assert (o - ref).abs().max().item() <= 2e-6
 
 
+def test_causal_attention_blockwise_equals_closed_form():
+    q, k, v = dense.make_attention_inputs(1, 2, 128, 16, 7, dtype=torch.float32)
+    ref = dense.attention_plain(q.double(), k.double(), v.double(), scale=0.25, causal=True)
+    for block in (16, 32, 128):
+        o = dense.flash_attention_causal_dense(q.double(), k.double(), v.double(), scale=0.25, block=block)
+        assert (o - ref).abs().max().item() <= 1e-12
+    # row 0 attends to key 0 only
+    assert torch.equal(ref[:, :, 0], v.double()[:, :, 0])
+
+
 def test_flash_attention_block_size_does_not_matter():
     q, k, v = dense.make_attention_inputs(1, 2, 128, 16, 7, dtype=torch.float32)
     a = dense.flash_attention_dense(q, k, v, scale=0.25, block=32)
