@@ -148,6 +148,27 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     }
     ctl.abort = 0;
     fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  // K0, V0, K1, V1, ... stream: tile n into ring slot n % kKVSlots.
+  auto load_kv = [&](int n) {
+    const int slot = n % kKVSlots;
+    uint8_t* dst = sKV + slot * kTileBytes;
+    const CUtensorMap* m = (n & 1) ? &mapV : &mapK;
+    const int r = row_base + (n >> 1) * 128;
+    mbar_arrive_expect_tx(&ctl.kv_full[slot], kTileBytes);
+    tma_load_2d(dst, m, &ctl.kv_full[slot], 0, r);
+    tma_load_2d(dst + kHalfBytes, m, &ctl.kv_full[slot], 64, r);
+  };
+  const int n_pre = min(kKVSlots, 2 * n_kv);
+  if (threadIdx.x == 0) {
+    // Q and the first pass over the (empty) ring are on their way while TMEM is allocated.
+    mbar_arrive_expect_tx(&ctl.q_full, 2 * kTileBytes);
+    for (int t = 0; t < 2; ++t) {
+      tma_load_2d(sQ + t * kTileBytes, &mapQ, &ctl.q_full, 0, q_row0 + t * 128);
+      tma_load_2d(sQ + t * kTileBytes + kHalfBytes, &mapQ, &ctl.q_full, 64, q_row0 + t * 128);
+    }
+    for (int n = 0; n < n_pre; ++n) load_kv(n);
   }
   if (warp == 1) {
     tmem_alloc(&ctl.tmem_base, 512);
@@ -164,21 +185,11 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(&ctl.q_full, 2 * kTileBytes);
-      for (int t = 0; t < 2; ++t) {
-        tma_load_2d(sQ + t * kTileBytes, &mapQ, &ctl.q_full, 0, q_row0 + t * 128);
-        tma_load_2d(sQ + t * kTileBytes + kHalfBytes, &mapQ, &ctl.q_full, 64, q_row0 + t * 128);
-      }
       int slot = 0;
-      uint32_t phase = 0;
-      for (int n = 0; n < 2 * n_kv; ++n) {  // K0, V0, K1, V1, ...
-        const int j = n >> 1;
-        const CUtensorMap* m = (n & 1) ? &mapV : &mapK;
+      uint32_t phase = 1;  // the first pass was issued above
+      for (int n = n_pre; n < 2 * n_kv; ++n) {
         if (!mbar_wait(&ctl.kv_empty[slot], phase ^ 1u, s_abort, status, FTB_ERR_TIMEOUT_SLOT)) break;
-        uint8_t* dst = sKV + slot * kTileBytes;
-        mbar_arrive_expect_tx(&ctl.kv_full[slot], kTileBytes);
-        tma_load_2d(dst, m, &ctl.kv_full[slot], 0, row_base + j * 128);
-        tma_load_2d(dst + kHalfBytes, m, &ctl.kv_full[slot], 64, row_base + j * 128);
+        load_kv(n);
         if (++slot == kKVSlots) {
           slot = 0;
           phase ^= 1u;
@@ -410,7 +421,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         tma_store_2d(&mapO, my_stage, 0, q_row0 + t * 128);
         tma_store_2d(&mapO, my_stage + kHalfBytes, 64, q_row0 + t * 128);
         tma_store_commit();
-        tma_store_wait<0>();
+        tma_store_wait_read<0>();  // the staging tile has been read; the writes land before the grid ends
       }
     }
   }
