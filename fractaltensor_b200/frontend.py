@@ -59,6 +59,19 @@ class FractalTensor(object):
     def to_dense(self):
         return _dense(self)
 
+    @property
+    def element_type(self):
+        """The type singleton of the stored numbers (types.float32, types.float16, types.bfloat16, ...)."""
+        from . import types
+        return types.torch_type_to_internal_type(self.data.dtype)
+
+    def astype(self, dtype):
+        """The same nesting with the numbers converted; dtype: a type singleton or a torch dtype."""
+        from . import types
+        if isinstance(dtype, types.Number):
+            dtype = types.internal_type_to_torch_type(dtype)
+        return FractalTensor(self.data.to(dtype), self.indices, self.element_shape)
+
 
 def _nest_dims(indices):
     """Lengths of a rectangular nesting; raises ValueError for a ragged one."""

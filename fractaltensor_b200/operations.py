@@ -13,7 +13,11 @@ Recognised so far: the stacked LSTM, batch-major (examples/stacked_rnn/stacked_l
 and time-major over a length-sorted ragged batch (examples/stacked_rnn/stacked_rnn.py:12-79), and
 blockwise attention with the online-softmax carry (examples/flash_attention/flash_attention.py:14-88,
 carry in (max, sum, out) order, optionally with the scores multiplied by a Python float), and the
-stacked dilated LSTM (examples/dilated_rnn/dilated_rnn.py:16-41, dilation 2**layer).
+stacked dilated LSTM (examples/dilated_rnn/dilated_rnn.py:16-41, dilation 2**layer), and the stacked
+grid RNN (examples/grid_rnn/grid_rnn.py:42-146: ``ops.product`` of the two sentences, two nested
+scans, ``ops.cat`` of the two incoming states, a tanh cell per direction; ``stacked_params`` a
+Python sequence of ((i2h, h2h, bias), (i2h, h2h, bias)) per layer; the call returns the top layer's
+(h_x, h_y) grids).
 
     from fractaltensor_b200 import operations as ops
     out = ops.fold(lambda s, param: lstm_layer(s, *param), ops.zip(Wss, Uss, bss), initializer=embs)
@@ -24,8 +28,8 @@ import torch
 
 from . import frontend
 
-__all__ = ["map", "scan", "fold", "reduce", "zip", "enumerate", "dilated_map", "repeat", "zeros", "full", "sigmoid", "tanh", "exp", "max", "sum",
-           "maximum"]
+__all__ = ["map", "scan", "fold", "reduce", "zip", "enumerate", "dilated_map", "product", "repeat", "zeros", "full", "cat",
+           "sigmoid", "tanh", "exp", "max", "sum", "maximum"]
 
 
 # ----------------------------------------------------------------- symbolic values
@@ -72,6 +76,20 @@ def _expr(v):
     raise NotImplementedError("only traced tensors can be combined inside a traced program, got %s" % type(v).__name__)
 
 
+_LEN_BASE = 1 << 40
+_len_codes = {}  # tag of a traced sequence -> the integer its len() answered with
+
+
+def _length_of(n):
+    """The symbolic length an integer from len(traced sequence) stands for; other values as they are."""
+    if isinstance(n, int) and n >= _LEN_BASE:
+        for tag, code in _len_codes.items():
+            if code == n:
+                return ("len", tag)
+        raise NotImplementedError("arithmetic on the length of a traced sequence")
+    return n
+
+
 class SymSeq(object):
     """Stand-in for a FractalTensor: either unrolled (``items``: a short static list, e.g. the four
     gates of a layer) or one representative element plus a tag that says where it comes from."""
@@ -84,9 +102,18 @@ class SymSeq(object):
         return len(self.items) if self.items is not None else ("len", self.tag)
 
     def __len__(self):
+        """len() must return an int: a traced sequence answers with a number that stands for its
+        (symbolic) length, which repeat() turns back into the sequence it was asked of."""
+        if self.items is not None:
+            return len(self.items)
+        if self.tag not in _len_codes:
+            _len_codes[self.tag] = _LEN_BASE + len(_len_codes)
+        return _len_codes[self.tag]
+
+    def __iter__(self):
         if self.items is None:
-            raise NotImplementedError("the length of a traced sequence is symbolic; use .length")
-        return len(self.items)
+            raise NotImplementedError("a traced sequence cannot be iterated or unpacked")
+        return iter(self.items)
 
     def __getitem__(self, i):
         if self.items is not None:
@@ -176,7 +203,7 @@ def map(func, xs, **kwargs):
     if kwargs:
         raise NotImplementedError("map: keyword arguments are not supported")
     if isinstance(xs, _Zipped):
-        return _dispatch_attention(func, xs)
+        return _dispatch_grid(func, xs) if len(xs.xs) == 2 else _dispatch_attention(func, xs)
     if not isinstance(xs, SymSeq) and hasattr(xs, "indices") and hasattr(xs, "data"):
         return _dispatch_dilated(func, xs)
     if not isinstance(xs, SymSeq):
@@ -227,7 +254,21 @@ def dilated_map(func, xs, dilation=1, **kwargs):
 
 
 def repeat(x, n):
-    return SymSeq(elem=x, tag=("repeat", _desc(x), n))
+    return SymSeq(elem=x, tag=("repeat", _desc(x), _length_of(n)))
+
+
+def product(xs, ys):
+    """Cartesian product as two grids: xss[i][j] = xs[j], yss[i][j] = ys[i]
+    (kaleido/frontend/operations/fractaltensor/access.py:207-247)."""
+    if not (isinstance(xs, SymSeq) and isinstance(ys, SymSeq)) or xs.items is not None or ys.items is not None:
+        raise NotImplementedError("product over real data is only dispatched as part of a recognised program")
+    xss = repeat(xs, ys.length)
+    yss = SymSeq(elem=repeat(ys.elem, xs.length), tag=("rows", ys.tag, xs.length))
+    return xss, yss
+
+
+def cat(tensors, dim=0):
+    return SymTensor(("cat", int(dim)) + tuple(_expr(t) for t in tensors))
 
 
 def zeros(shape, device=None, dtype=None):
@@ -396,6 +437,74 @@ def _dispatch_dilated(func, embs):
                               "element-by-element fallback")
 
 
+def _program_grid(pairs, stacked_params):
+    """map(sentence pairs) of fold(depth) of scan(rows) of scan(columns) of the two-direction tanh
+    cell on the src x trg grid: grid_rnn.py."""
+    def cell(own, both, i2h, h2h, bias):
+        return tanh(both @ i2h + own @ h2h + bias)
+
+    def point(carry, cur, px, py):
+        from_above, (x, y) = cur
+        both = cat([from_above, carry[1]], dim=1)
+        return cell(x, both, *px), cell(y, both, *py)
+
+    def row(carry, cur, px, py):
+        z = zeros(())
+        return scan(lambda c, p: point(c, p, px, py), zip(carry[0], zip(cur[0], cur[1])), initializer=(z, z))
+
+    def layer(grid, px, py):
+        z = repeat(zeros(()), len(grid[0][0]))
+        hx, hy = scan(lambda c, r: row(c, r, px, py), grid, initializer=(z, z))
+        return zip(hx, hy)
+
+    def pair(src, trg):
+        xss, yss = product(src, trg)
+        return fold(lambda g, p: layer(g, *p), stacked_params, initializer=zip(xss, yss))
+
+    return map(lambda st: pair(st[0], st[1]), pairs)
+
+
+def _dispatch_grid(func, zipped):
+    def depth(ft):
+        d, x = 0, getattr(ft, "indices", None)
+        while isinstance(x, list):
+            d, x = d + 1, (x[0] if x else None)
+        return d
+
+    if builtins.any(depth(x) != 2 for x in zipped.xs):
+        raise NotImplementedError("map over real data: expected ops.zip(src_encs, trg_encs) of depth-2 FractalTensors")
+
+    def pairs():
+        return zip(_deep_input("src", 2), _deep_input("trg", 2))
+
+    _seen.clear()
+    _len_codes.clear()
+    traced = _desc(map(func, pairs()))
+    params = _seen.pop("grid_params", None)
+    if params is not None and traced == _desc(_program_grid(pairs(), params)):
+        src, trg = zipped.xs
+        return frontend.stacked_grid_rnns(src, trg, params)
+    raise NotImplementedError("this program is not one the library has a fused kernel for, and there is no "
+                              "element-by-element fallback")
+
+
+def _like(v, tag):
+    """A fresh stand-in with the structure of v."""
+    if isinstance(v, tuple):
+        return tuple(_like(x, (tag, j)) for j, x in builtins.enumerate(v))
+    if isinstance(v, SymSeq):
+        return SymSeq(elem=_like(v.elem, ("elem", tag)), tag=tag)
+    return SymTensor(tag)
+
+
+def _is_grid_params(xs):
+    def is_cell(c):
+        return isinstance(c, (tuple, list)) and len(c) == 3
+
+    return (isinstance(xs, (tuple, list)) and len(xs) > 0 and
+            builtins.all(isinstance(b, (tuple, list)) and len(b) == 2 and is_cell(b[0]) and is_cell(b[1]) for b in xs))
+
+
 def _symbolic_inputs(n_params, gates):
     seq = ("input", "state")
     inner = ("elem", seq)
@@ -421,6 +530,15 @@ def fold(func, xs, initializer=None, **kwargs):
         state = SymSeq(elem=initializer.elem, tag=("state", "fold"))
         elem = (SymInt("position"),) + _symbolic_inputs(3, 4)[1]
         body = func(state, elem)
+        return SymSeq(elem=body.elem, tag=("fold", _desc(initializer), _desc(body)))
+    if _is_grid_params(xs) and isinstance(initializer, SymSeq):
+        # Inside a traced program: fold over the layers' (x-direction, y-direction) cell parameters.
+        _seen["grid_params"] = xs
+        state = _like(initializer, ("state", "fold"))
+        elem = tuple(tuple(SymTensor(("param", d, k)) for k in range(3)) for d in range(2))
+        body = func(state, elem)
+        if not isinstance(body, SymSeq):
+            raise NotImplementedError("fold: the folded function must return a sequence")
         return SymSeq(elem=body.elem, tag=("fold", _desc(initializer), _desc(body)))
     if isinstance(xs, SymSeq) or _is_sym(initializer):
         raise NotImplementedError("a fold inside a traced program is not recognised")

@@ -115,3 +115,60 @@ def dilated_program(ops, H=64):
         return ops.map(lambda xs: ops.fold(lambda s, x: dilated_layer(s, *x), itrs, initializer=xs), embs)
 
     return model
+
+
+def grid_program(ops, H):
+    """The stacked grid RNN as the example writes it (examples/grid_rnn/grid_rnn.py:42-146): a tanh
+    cell per direction on the concatenated (state from above, state from the left)."""
+    def vanilla_cell(state, cur, i2h, h2h, bias):
+        h = ops.tanh(cur @ i2h + state @ h2h + bias)
+        return h
+
+    def grid_cell(state, cur_input, block_params):
+        _, state_y = state
+        state_x, (x_t, y_t) = cur_input
+        rnn_param_x, rnn_param_y = block_params
+        s = ops.cat([state_x, state_y], dim=1)
+        h_x = vanilla_cell(x_t, s, *rnn_param_x)
+        h_y = vanilla_cell(y_t, s, *rnn_param_y)
+        return h_x, h_y
+
+    def direction_y(state, cur_input, block_params):
+        state_xs, _ = state
+        zero = ops.zeros(shape=(1, H), device="cpu")
+        ys = ops.scan(lambda s, x: grid_cell(s, x, block_params), ops.zip(state_xs, ops.zip(*cur_input)),
+                      initializer=(zero, zero))
+        return ys
+
+    def direction_x(state, block_params):
+        zeros = ops.repeat(ops.zeros(shape=(1, H), device="cpu"), len(state[0][0]))
+        ys1, ys2 = ops.scan(lambda s, x: direction_y(s, x, block_params), state, initializer=(zeros, zeros))
+        return ops.zip(ys1, ys2)
+
+    def stacked_grid_rnns(src_encs, trg_encs, stacked_params):
+        return ops.fold(lambda inputs, params: direction_x(inputs, params), stacked_params,
+                        initializer=ops.zip(*ops.product(src_encs, trg_encs)))
+
+    def model(src_encs, trg_encs, stacked_params):
+        return ops.map(lambda x: stacked_grid_rnns(*x, stacked_params), ops.zip(src_encs, trg_encs))
+
+    def wrong_state(src_encs, trg_encs, stacked_params):  # both cells fed the state from above twice
+        def bad_cell(state, cur_input, block_params):
+            state_x, (x_t, y_t) = cur_input
+            s = ops.cat([state_x, state_x], dim=1)
+            return vanilla_cell(x_t, s, *block_params[0]), vanilla_cell(y_t, s, *block_params[1])
+
+        def bad_y(state, cur_input, block_params):
+            zero = ops.zeros(shape=(1, H), device="cpu")
+            return ops.scan(lambda s, x: bad_cell(s, x, block_params), ops.zip(state[0], ops.zip(*cur_input)),
+                            initializer=(zero, zero))
+
+        def bad_x(state, block_params):
+            zeros = ops.repeat(ops.zeros(shape=(1, H), device="cpu"), len(state[0][0]))
+            ys1, ys2 = ops.scan(lambda s, x: bad_y(s, x, block_params), state, initializer=(zeros, zeros))
+            return ops.zip(ys1, ys2)
+
+        return ops.map(lambda x: ops.fold(lambda i, p: bad_x(i, p), stacked_params,
+                                          initializer=ops.zip(*ops.product(*x))), ops.zip(src_encs, trg_encs))
+
+    return model, wrong_state

@@ -720,6 +720,22 @@ def test_traced_dilated_program(ops):
     _assert_fp32(out.to_dense().reshape(N, L, H).permute(1, 0, 2), ref[-1])
 
 
+def test_traced_grid_program(ops):
+    from fractaltensor_b200 import frontend, operations
+    from programs import grid_program
+    D, A, B, N, H = 2, 4, 5, 3, 64
+    X, Y, p = dense.make_grid_inputs(D, A, B, N, H, 23, 1.0 / 8, bias=True)
+    src, trg = X[0], Y[:, 0]  # [B,N,H], [A,N,H]
+    ft = lambda t: frontend.FractalTensor.from_dense(t.permute(1, 0, 2).reshape(N, -1, 1, H).cuda(), 2)
+    cell = lambda d, k: (p["i2h_" + k][d].cuda(), p["h2h_" + k][d].cuda(), p["b_" + k][d].reshape(1, H).cuda())
+    params = [(cell(d, "x"), cell(d, "y")) for d in range(D)]
+    model, _ = grid_program(operations, H)
+    hx, hy = model(ft(src), ft(trg), params)
+    rx, ry = _grid_ref(X, Y, p)
+    _assert_fp32(hx.to_dense().reshape(N, A, B, H).permute(1, 2, 0, 3), rx[-1])
+    _assert_fp32(hy.to_dense().reshape(N, A, B, H).permute(1, 2, 0, 3), ry[-1])
+
+
 def test_traced_attention_program(ops):
     from fractaltensor_b200 import frontend, operations
     from programs import attention_program

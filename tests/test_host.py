@@ -143,3 +143,56 @@ def test_dilated_program_is_recognised(monkeypatch):
     # a plain map over real data with some other body is not a known program
     with pytest.raises(NotImplementedError):
         ops.map(lambda xs: ops.map(lambda x: ops.tanh(x), xs), embs)
+
+
+def test_grid_program_is_recognised(monkeypatch):
+    from fractaltensor_b200 import operations as ops
+    from programs import grid_program
+    got = []
+    monkeypatch.setattr(frontend, "stacked_grid_rnns", lambda s, t, p: got.append((s, t, p)) or "G")
+    src = frontend.FractalTensor.from_dense(torch.zeros(2, 5, 1, 64), 2)
+    trg = frontend.FractalTensor.from_dense(torch.zeros(2, 4, 1, 64), 2)
+    cell = lambda: (torch.zeros(128, 64), torch.zeros(64, 64), torch.zeros(1, 64))
+    params = [(cell(), cell()) for _ in range(3)]
+    model, wrong_state = grid_program(ops, 64)
+    assert model(src, trg, params) == "G"
+    assert got[0][0] is src and got[0][1] is trg and got[0][2] is params
+    with pytest.raises(NotImplementedError):
+        wrong_state(src, trg, params)
+    # initial column state sized by the number of rows instead of the row length: another program
+    def wrong_len(src_encs, trg_encs, stacked_params):
+        def layer(state, p):
+            z = ops.repeat(ops.zeros(shape=(1, 64)), len(state))
+            ys1, ys2 = ops.scan(lambda s, x: s, state, initializer=(z, z))
+            return ops.zip(ys1, ys2)
+        return ops.map(lambda x: ops.fold(layer, stacked_params, initializer=ops.zip(*ops.product(*x))),
+                       ops.zip(src_encs, trg_encs))
+    with pytest.raises(NotImplementedError):
+        wrong_len(src, trg, params)
+
+
+def test_element_type_singletons():
+    from fractaltensor_b200 import types as T
+    assert T.internal_type_to_torch_type(T.float32) is torch.float32
+    assert T.internal_type_to_torch_type(T.float16) is torch.float16
+    assert T.internal_type_to_torch_type(T.bfloat16) is torch.bfloat16
+    for name, want in (("float", T.float32), ("half", T.float16), ("bfloat16", T.bfloat16), ("int", T.int32)):
+        assert T.str_to_internal_type(name) is want
+    for t in (torch.float16, torch.bfloat16, torch.float32, torch.int32, torch.int64):
+        assert T.internal_type_to_torch_type(T.torch_type_to_internal_type(t)) is t
+    assert not T.float16.is_equal_type(T.bfloat16) and T.float16.is_equal_type(T.Real(16))
+    assert T.float16.byte == 16 and T.bfloat16.max > T.float16.max
+    assert T.pytype_to_internal_type(1) is T.int64 and T.pytype_to_internal_type(1.0) is T.float32
+    with pytest.raises(NotImplementedError):
+        T.str_to_internal_type("complex")
+    with pytest.raises(ValueError):
+        T.Real(32, brain=True)
+
+
+def test_fractal_tensor_element_type():
+    from fractaltensor_b200 import types as T
+    ft = frontend.FractalTensor.from_dense(torch.zeros(2, 3, 1, 8), 2)
+    assert ft.element_type is T.float32
+    half = ft.astype(T.bfloat16)
+    assert half.element_type is T.bfloat16 and half.indices == ft.indices and half.element_shape == (1, 8)
+    assert ft.astype(torch.float16).element_type is T.float16
