@@ -89,7 +89,7 @@ template <typename T, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                   const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, int S,
-                  int n_bh, int group, float scale_log2, int* __restrict__ status) {
+                  int n_bh, int group, int window, float scale_log2, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
 
   if (*reinterpret_cast<volatile int*>(status) != 0) return;
@@ -126,8 +126,19 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   const int q_row0 = row_base + qpair * 256;
   // Key/value blocks this CTA walks.  Causal (key index <= query index): query tile t of this pair
   // ends at block 2*qpair + t, its diagonal block; tile 0 leaves the loop one block before tile 1.
-  const int n_kv = kCausal ? 2 * qpair + 2 : S / 128;
-  const int n_kv0 = kCausal ? n_kv - 1 : n_kv;  // tile 0's count
+  // With a window W > 0 query i also leaves out keys at or before i - W, so a tile starts at the block
+  // of the first key its first row sees.  The CTA walks blocks [blk0, blk0 + n_kv); tile 0 takes part
+  // in iterations 0..last0 of that walk, tile 1 in first1..n_kv-1 (first1 is 0 or 1).
+  int blk0 = 0, n_kv = S / 128, first1 = 0, last0 = n_kv - 1;
+  if (kCausal) {
+    const int r0 = qpair * 256;
+    const int lo0 = window > 0 ? max(0, r0 - window + 1) >> 7 : 0;
+    const int lo1 = window > 0 ? max(0, r0 + 128 - window + 1) >> 7 : 0;
+    blk0 = lo0;
+    n_kv = 2 * qpair + 2 - lo0;
+    first1 = lo1 - lo0;
+    last0 = n_kv - 2;
+  }
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&mapQ);
@@ -155,7 +166,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     const int slot = n % kKVSlots;
     uint8_t* dst = sKV + slot * kTileBytes;
     const CUtensorMap* m = (n & 1) ? &mapV : &mapK;
-    const int r = row_base + (n >> 1) * 128;
+    const int r = row_base + (blk0 + (n >> 1)) * 128;
     mbar_arrive_expect_tx(&ctl.kv_full[slot], kTileBytes);
     tma_load_2d(dst, m, &ctl.kv_full[slot], 0, r);
     tma_load_2d(dst + kHalfBytes, m, &ctl.kv_full[slot], 64, r);
@@ -226,19 +237,19 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       // O_t += P_t(j) . V_j: A = P_t from TMEM (16 keys = 8 packed columns per step; the two
       // key halves start 64 columns apart); B = V, MN-major: 16 keys = two 8-row groups
       // (1024 B apart), the two 64-column halves of d are 16 KB apart.
-      auto issue_pv = [&](int t, int j) {
+      auto issue_pv = [&](int t, int j, bool first) {
         const uint32_t aV = aKV + ((2 * j + 1) % kKVSlots) * kTileBytes;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + (k >> 2) * 64 + (k & 3) * 8,
-                  make_sdesc_sw128(aV + k * 2048, kHalfBytes, 1024), idesc_pv, (j | k) != 0 ? 1u : 0u);
+                  make_sdesc_sw128(aV + k * 2048, kHalfBytes, 1024), idesc_pv, (!first || k != 0) ? 1u : 0u);
         umma_commit(&ctl.pv_done[t]);
       };
 
       if (ok) ok = wait_slot(0);
       if (ok) {
         issue_s(0, 0);
-        issue_s(1, 0);
+        if (first1 == 0) issue_s(1, 0);
         umma_commit(&ctl.kv_empty[0]);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
@@ -246,18 +257,21 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         if (!wait_slot(2 * j + 1)) break;            // V_j
         if (more && !wait_slot(2 * j + 2)) break;    // K_{j+1}
         for (int t = 0; t < 2 && ok; ++t) {
-          if (kCausal && t == 0 && j >= n_kv0) continue;
-          // P_t(j) is in TMEM (and the softmax is done with S_t(j)).
-          if (!mbar_wait(&ctl.p_full[t], j & 1, s_abort, status, FTB_ERR_TIMEOUT_EPI)) {
-            ok = false;
-            break;
+          const int first = t == 0 ? 0 : first1;
+          const int last = t == 0 ? last0 : n_kv - 1;
+          if (j >= first && j <= last) {
+            // P_t(j) is in TMEM (and the softmax is done with S_t(j)).
+            if (!mbar_wait(&ctl.p_full[t], (j - first) & 1, s_abort, status, FTB_ERR_TIMEOUT_EPI)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            FA_STAMP_MMA(t, j, 5);
+            issue_pv(t, j, j == first);
           }
-          tc_fence_after();
-          FA_STAMP_MMA(t, j, 5);
-          issue_pv(t, j);
           // The tensor pipe runs MMAs in issue order: S_t(j+1) overwrites S_t / P_t only after
           // PV_t(j) has read P_t.
-          if (more && (!kCausal || t == 1 || j + 1 < n_kv0)) issue_s(t, j + 1);
+          if (more && j + 1 >= first && j + 1 <= last) issue_s(t, j + 1);
           FA_STAMP_MMA(t, j, 6);
         }
         if (!ok) break;
@@ -280,10 +294,13 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     uint64_t* pair = &ctl.pair_bar[t][q];
     float m_used = 0.f, l = 0.f;
     bool ok = true;
-    const int n_mine = t == 0 ? n_kv0 : n_kv;
+    const int j_first = t == 0 ? 0 : first1;
+    const int j_last = t == 0 ? last0 : n_kv - 1;
+    const int n_mine = j_last - j_first + 1;
 
-    for (int j = 0; j < n_mine && ok; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&ctl.s_full[t], j & 1, s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
+    for (int j = j_first; j <= j_last && ok; ++j) {
+      const int it = j - j_first;  // this tile's block count so far: the phase of its barriers
+      if (!__all_sync(0xffffffffu, mbar_wait(&ctl.s_full[t], it & 1, s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
         ok = false;
         break;
       }
@@ -294,7 +311,16 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       tmem_ld32p(s_addr + 32, s + 32);
       tmem_ld_wait();
       FA_STAMP(t, j, 1);
-      if (kCausal && j == n_mine - 1) {
+      if (kCausal && window > 0) {
+        // Keys at or before row - window are outside the window: columns 0..thr of this thread's 64.
+        const int thr = qpair * 256 + t * 128 + row - window - (blk0 + j) * 128 - h * 64;
+        if (__any_sync(0xffffffffu, thr >= 0)) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (i <= thr) s[i] = 0xff800000u;  // -inf
+        }
+      }
+      if (kCausal && j == j_last) {
         // Diagonal block: key h*64 + i is visible to query `row` when it is not after it.  Key 0 of
         // the block is visible to every row, so the row maximum stays finite.
 #pragma unroll
@@ -318,13 +344,15 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       *my_x = mx;
       __syncwarp();
       if (lane == 0) mbar_arrive(pair);
-      if (!__all_sync(0xffffffffu, mbar_wait(pair, j & 1, s_abort, status, FTB_ERR_TIMEOUT_EPI))) {
+      if (!__all_sync(0xffffffffu, mbar_wait(pair, it & 1, s_abort, status, FTB_ERR_TIMEOUT_EPI))) {
         ok = false;
         break;
       }
       mx = fmaxf(mx, *peer_x);
-      const float m_new = mx * scale_log2;
-      if (j == 0) {
+      // With a window a row can have no visible key in its first block: the floor keeps 2^(s - m) at 0
+      // there instead of inf - inf, and the first real maximum rescales the (zero) accumulator by 0.
+      const float m_new = kCausal ? fmaxf(mx * scale_log2, -1e30f) : mx * scale_log2;
+      if (it == 0) {
         m_used = m_new;
       } else {
         // Both threads of a row see the same m_new and m_used, so both take the same branch.
@@ -332,7 +360,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         if (__any_sync(0xffffffffu, need)) {
           // O_t must be at rest: the PV MMA of the previous block has to be done.
           if (!__all_sync(0xffffffffu,
-                          mbar_wait(&ctl.pv_done[t], (j - 1) & 1, s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
+                          mbar_wait(&ctl.pv_done[t], (it - 1) & 1, s_abort, status, FTB_ERR_TIMEOUT_MMA))) {
             ok = false;
             break;
           }
@@ -440,7 +468,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 
 template <typename T, bool kCausal>
 int launch(const CUtensorMap& mQ, const CUtensorMap& mK, const CUtensorMap& mV, const CUtensorMap& mO, int n_bh,
-           int S, float scale_log2, int* status, cudaStream_t stream) {
+           int S, int window, float scale_log2, int* status, cudaStream_t stream) {
   static bool configured = false;
   auto kfn = flash_attn_kernel<T, kCausal>;
   if (!configured) {
@@ -449,7 +477,7 @@ int launch(const CUtensorMap& mQ, const CUtensorMap& mK, const CUtensorMap& mV, 
     configured = true;
   }
   const int group = kCausalGroup;
-  kfn<<<n_bh * (S / 256), kThreads, kSmemBytes, stream>>>(mQ, mK, mV, mO, S, n_bh, group, scale_log2, status);
+  kfn<<<n_bh * (S / 256), kThreads, kSmemBytes, stream>>>(mQ, mK, mV, mO, S, n_bh, group, window, scale_log2, status);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
@@ -467,12 +495,15 @@ extern "C" int ftb_debug_fa_trace(unsigned long long* out) {
 
 namespace {
 int flash_attn_entry(const void* q, const void* k, const void* v, void* o, int B, int heads, int S, int d,
-                     float scale, int dtype, bool causal, void* workspace, size_t workspace_bytes, void* stream_) {
+                     float scale, int dtype, bool causal, int window, void* workspace, size_t workspace_bytes,
+                     void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!q || !k || !v || !o || B <= 0 || heads <= 0 || S <= 0) return FTB_ERR_ARG;
   if (dtype != FTB_F16 && dtype != FTB_BF16) return FTB_ERR_ARG;
   if (d != 128 || S % 256 != 0) return FTB_ERR_ARG;
   if (causal && !(scale > 0.f)) return FTB_ERR_ARG;  // masked scores are -inf times the scale
+  if (window < 0) return FTB_ERR_ARG;
+  if (window >= S) window = 0;  // every earlier key is inside the window
   const int64_t rows = static_cast<int64_t>(B) * heads * S;
   if (rows > 0x7fffffffLL) return FTB_ERR_ARG;
   if (workspace == nullptr || workspace_bytes < ftb_workspace_bytes()) return FTB_ERR_WORKSPACE;
@@ -490,22 +521,30 @@ int flash_attn_entry(const void* q, const void* k, const void* v, void* o, int B
   const int units = B * heads;
   const float scale_log2 = scale * 1.4426950408889634f;
   if (causal) {
-    if (dtype == FTB_F16) return launch<__half, true>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
-    return launch<__nv_bfloat16, true>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
+    if (dtype == FTB_F16) return launch<__half, true>(mQ, mK, mV, mO, units, S, window, scale_log2, status, stream);
+    return launch<__nv_bfloat16, true>(mQ, mK, mV, mO, units, S, window, scale_log2, status, stream);
   }
-  if (dtype == FTB_F16) return launch<__half, false>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
-  return launch<__nv_bfloat16, false>(mQ, mK, mV, mO, units, S, scale_log2, status, stream);
+  if (dtype == FTB_F16) return launch<__half, false>(mQ, mK, mV, mO, units, S, 0, scale_log2, status, stream);
+  return launch<__nv_bfloat16, false>(mQ, mK, mV, mO, units, S, 0, scale_log2, status, stream);
 }
 }  // namespace
 
 extern "C" int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S,
                                   int d, float scale, int dtype, void* workspace, size_t workspace_bytes,
                                   void* stream) {
-  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, false, workspace, workspace_bytes, stream);
+  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, false, 0, workspace, workspace_bytes, stream);
 }
 
 extern "C" int ftb_flash_attn_causal_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads,
                                          int S, int d, float scale, int dtype, void* workspace,
                                          size_t workspace_bytes, void* stream) {
-  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, true, workspace, workspace_bytes, stream);
+  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, true, 0, workspace, workspace_bytes, stream);
+}
+
+extern "C" int ftb_flash_attn_window_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads,
+                                         int S, int d, int window, float scale, int dtype, void* workspace,
+                                         size_t workspace_bytes, void* stream) {
+  if (window <= 0) return FTB_ERR_ARG;
+  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, true, window, workspace, workspace_bytes,
+                          stream);
 }

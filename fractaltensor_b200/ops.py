@@ -248,8 +248,9 @@ def b2b_gemm(A, B, C, out=None):
     return out
 
 
-def flash_attention(q, k, v, scale=None, out=None, causal=False):
-    """q,k,v: [B,heads,S,d] -> softmax(scale * q k^T) v, same shape; `causal`: keys 0..i for query i."""
+def flash_attention(q, k, v, scale=None, out=None, causal=False, window=None):
+    """q,k,v: [B,heads,S,d] -> softmax(scale * q k^T) v, same shape; `causal`: keys 0..i for query i;
+    `window` (with causal): keys i-window+1..i."""
     _req(q, "q")
     _req(k, "k", q.dtype)
     _req(v, "v", q.dtype)
@@ -263,6 +264,13 @@ def flash_attention(q, k, v, scale=None, out=None, causal=False):
     _req(out, "out", q.dtype)
     ws = workspace(q.device)
     with torch.cuda.device(q.device):
+        if window is not None:
+            if not causal:
+                raise ValueError("flash_attention: a window needs causal=True (the window ends at the query)")
+            check(lib.ftb_flash_attn_window_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, heads, S, d, int(window),
+                                                float(scale), _dtype_code(q), _ptr(ws), ws.numel(), _stream()),
+                  "ftb_flash_attn_window_fwd")
+            return out
         name = "ftb_flash_attn_causal_fwd" if causal else "ftb_flash_attn_fwd"
         check(getattr(lib, name)(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, heads, S, d, float(scale),
                                  _dtype_code(q), _ptr(ws), ws.numel(), _stream()), name)

@@ -182,6 +182,16 @@ int ftb_flash_attn_causal_fwd(const void* q, const void* k, const void* v, void*
                               int d, float scale, int dtype, void* workspace, size_t workspace_bytes,
                               void* stream);
 
+/* Causal attention inside a sliding window: query i attends to keys i-window+1 .. i
+ * (window >= 1; window >= S is plain causal attention).  Each query tile starts its key
+ * walk at the block of the first key its first row sees.  The windowed part of the
+ * reference's sparse attention example (examples/sparse_attention/sparse_attention.py:44-46,
+ * ops.shifted_slide) is token-level, two-sided and dilated; this entry is the one-sided
+ * block form only. */
+int ftb_flash_attn_window_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S,
+                              int d, int window, float scale, int dtype, void* workspace,
+                              size_t workspace_bytes, void* stream);
+
 /* Embedding lookup out[t, :] = table[ids[t], :] for t < T.  Stands in for the lookup in front of
  * the reference's RNN examples, ops.index(ops.slices(embedding, dim=0), word) mapped over a batch
  * of word sequences (examples/stacked_rnn/rnn_utils.py:80-90): `ids` is the flat int64 buffer of

@@ -222,7 +222,7 @@ def embedding_gather_dense(table, ids):
     return table[ids.reshape(-1)]
 
 
-def attention_plain(q, k, v, scale=1.0, causal=False):
+def attention_plain(q, k, v, scale=1.0, causal=False, window=None):
     """softmax(scale * q k^T) v, the closed form the blockwise carry equals.
 
     `causal`: query i sees keys 0..i (later scores are -inf before the softmax).  The reference
@@ -232,6 +232,8 @@ def attention_plain(q, k, v, scale=1.0, causal=False):
     if causal:
         S = q.shape[-2]
         keep = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        if window is not None:  # keys i-window+1 .. i
+            keep &= ~torch.ones(S, S, dtype=torch.bool, device=q.device).tril(-int(window))
         w = w.masked_fill(~keep, float("-inf"))
     return torch.softmax(w, dim=-1) @ v
 

@@ -596,6 +596,40 @@ def test_flash_attention_causal_ignores_later_keys(ops):
     _assert_16(out[3, 5], ref)
 
 
+@pytest.mark.parametrize("window", [1, 5, 64, 127, 128, 129, 200, 256, 300, 511, 1000, 5000])
+def test_flash_attention_window(ops, window):
+    """Sliding window ending at the query: windows below, at and above the 128-key block and the
+    256-row CTA sizes, one that covers the whole sequence, and single-key attention (out = v)."""
+    B, h, S = 1, 2, 1280
+    q, k, v = dense.make_attention_inputs(B, h, S, 128, 22, dtype=torch.bfloat16)
+    sc = 1.0 / math.sqrt(128.0)
+    out = ops.flash_attention(*_dev(q, k, v), scale=sc, causal=True, window=window)
+    ops.check_status()
+    _assert_16(out, dense.attention_plain(*_f32(q, k, v), scale=sc, causal=True, window=window))
+    if window == 1:
+        assert (out.float().cpu() - v.float()).abs().max().item() <= 2e-3
+
+
+def test_flash_attention_window_ignores_keys_outside(ops):
+    """Full-size property: the outputs of queries p..p+99 do not change, bit for bit, when keys and
+    values before p-window+1 and after p+99 are replaced."""
+    q, k, v = dense.make_attention_inputs(16, 16, 2048, 128, 2)
+    sc = 1.0 / math.sqrt(128.0)
+    qd, kd, vd = _dev(q, k, v)
+    W, p = 300, 1100
+    out = ops.flash_attention(qd, kd, vd, scale=sc, causal=True, window=W)
+    k2, v2 = kd.clone(), vd.clone()
+    k2[:, :, :p - W + 1] = 5.0
+    v2[:, :, :p - W + 1] = 9.0
+    k2[:, :, p + 100:] = -5.0
+    v2[:, :, p + 100:] = 4.0
+    out2 = ops.flash_attention(qd, k2, v2, scale=sc, causal=True, window=W)
+    ops.check_status()
+    assert torch.equal(out[:, :, p:p + 100], out2[:, :, p:p + 100])
+    ref = dense.attention_plain(q[2, 9].double(), k[2, 9].double(), v[2, 9].double(), sc, causal=True, window=W)
+    _assert_16(out[2, 9], ref)
+
+
 def test_flash_attention_causal_rejects_nonpositive_scale(ops):
     q, k, v = dense.make_attention_inputs(1, 1, 256, 128, 2)
     with pytest.raises(RuntimeError):

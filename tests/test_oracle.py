@@ -92,6 +92,11 @@ def test_causal_attention_blockwise_equals_closed_form():
         assert (o - ref).abs().max().item() <= 1e-12
     # row 0 attends to key 0 only
     assert torch.equal(ref[:, :, 0], v.double()[:, :, 0])
+    # a window of one key: every query returns its own value; a window of S keys: plain causal
+    one = dense.attention_plain(q.double(), k.double(), v.double(), scale=0.25, causal=True, window=1)
+    assert (one - v.double()).abs().max().item() <= 1e-12
+    full = dense.attention_plain(q.double(), k.double(), v.double(), scale=0.25, causal=True, window=128)
+    assert torch.equal(full, ref)
 
 
 def test_flash_attention_block_size_does_not_matter():
