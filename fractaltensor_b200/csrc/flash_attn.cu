@@ -85,11 +85,11 @@ __device__ unsigned long long g_fa_trace[2][32][8];
 #define FA_STAMP_MMA(tt, jj, k)
 #endif
 
-template <typename T, bool kCausal>
+template <typename T, bool kMasked>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                   const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, int S,
-                  int n_bh, int group, int window, float scale_log2, int* __restrict__ status) {
+                  int n_bh, int group, int left, int right, float scale_log2, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
 
   if (*reinterpret_cast<volatile int*>(status) != 0) return;
@@ -111,7 +111,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   const int pairs = S / 256;
   int bh = blockIdx.x / pairs;
   int qpair = blockIdx.x - bh * pairs;
-  if (kCausal) {
+  if (kMasked) {
     // A pair's run length grows with its position, so CTAs are handed out longest first: within
     // a group of `group` (batch, head) entries all last pairs, then all pairs before them, ...
     // The grid's last CTAs are then the shortest, and the group bounds the K/V set in flight.
@@ -124,20 +124,22 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   }
   const int row_base = bh * S;            // first row of this (batch, head) in the flattened [B*heads*S, d] view
   const int q_row0 = row_base + qpair * 256;
-  // Key/value blocks this CTA walks.  Causal (key index <= query index): query tile t of this pair
-  // ends at block 2*qpair + t, its diagonal block; tile 0 leaves the loop one block before tile 1.
-  // With a window W > 0 query i also leaves out keys at or before i - W, so a tile starts at the block
-  // of the first key its first row sees.  The CTA walks blocks [blk0, blk0 + n_kv); tile 0 takes part
-  // in iterations 0..last0 of that walk, tile 1 in first1..n_kv-1 (first1 is 0 or 1).
+  // Key/value blocks this CTA walks.  Masked: query i sees keys i-left .. i+right (left < 0: no
+  // lower limit; causal attention is left < 0, right = 0).  A query tile walks from the block of the
+  // first key its first row sees to the block of the last key its last row sees.  The CTA walks the
+  // union, blocks [blk0, blk0 + n_kv); tile 0 takes part in iterations 0..last0 of that walk, tile 1
+  // in first1..n_kv-1 (tile 1 starts and ends at most one block after tile 0).
   int blk0 = 0, n_kv = S / 128, first1 = 0, last0 = n_kv - 1;
-  if (kCausal) {
+  if (kMasked) {
     const int r0 = qpair * 256;
-    const int lo0 = window > 0 ? max(0, r0 - window + 1) >> 7 : 0;
-    const int lo1 = window > 0 ? max(0, r0 + 128 - window + 1) >> 7 : 0;
+    const int lo0 = left >= 0 ? max(0, r0 - left) >> 7 : 0;
+    const int lo1 = left >= 0 ? max(0, r0 + 128 - left) >> 7 : 0;
+    const int hi0 = min(S / 128 - 1, (r0 + 127 + right) >> 7);
+    const int hi1 = min(S / 128 - 1, (r0 + 255 + right) >> 7);
     blk0 = lo0;
-    n_kv = 2 * qpair + 2 - lo0;
+    n_kv = hi1 - lo0 + 1;
     first1 = lo1 - lo0;
-    last0 = n_kv - 2;
+    last0 = hi0 - lo0;
   }
 
   if (threadIdx.x == 0) {
@@ -311,21 +313,23 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       tmem_ld32p(s_addr + 32, s + 32);
       tmem_ld_wait();
       FA_STAMP(t, j, 1);
-      if (kCausal && window > 0) {
-        // Keys at or before row - window are outside the window: columns 0..thr of this thread's 64.
-        const int thr = qpair * 256 + t * 128 + row - window - (blk0 + j) * 128 - h * 64;
-        if (__any_sync(0xffffffffu, thr >= 0)) {
+      if (kMasked) {
+        // This thread's 64 keys start at key0; its query is `mine`.  Columns below lo_col are before
+        // the window, columns above hi_col after it (for causal attention: after the query).
+        const int key0 = (blk0 + j) * 128 + h * 64;
+        const int mine = qpair * 256 + t * 128 + row;
+        const int lo_col = left >= 0 ? mine - left - key0 : 0;
+        const int hi_col = mine + right - key0;
+        if (__any_sync(0xffffffffu, lo_col > 0)) {
 #pragma unroll
           for (int i = 0; i < 64; ++i)
-            if (i <= thr) s[i] = 0xff800000u;  // -inf
+            if (i < lo_col) s[i] = 0xff800000u;  // -inf
         }
-      }
-      if (kCausal && j == j_last) {
-        // Diagonal block: key h*64 + i is visible to query `row` when it is not after it.  Key 0 of
-        // the block is visible to every row, so the row maximum stays finite.
+        if (__any_sync(0xffffffffu, hi_col < 63)) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (h * 64 + i > row) s[i] = 0xff800000u;  // -inf
+          for (int i = 0; i < 64; ++i)
+            if (i > hi_col) s[i] = 0xff800000u;
+        }
       }
 
       // Maximum of this half of the row: eight independent chains of three-input maxima.
@@ -349,9 +353,9 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         break;
       }
       mx = fmaxf(mx, *peer_x);
-      // With a window a row can have no visible key in its first block: the floor keeps 2^(s - m) at 0
+      // A row can have no visible key in a block of its tile's walk: the floor keeps 2^(s - m) at 0
       // there instead of inf - inf, and the first real maximum rescales the (zero) accumulator by 0.
-      const float m_new = kCausal ? fmaxf(mx * scale_log2, -1e30f) : mx * scale_log2;
+      const float m_new = kMasked ? fmaxf(mx * scale_log2, -1e30f) : mx * scale_log2;
       if (it == 0) {
         m_used = m_new;
       } else {
@@ -466,18 +470,18 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
   }
 }
 
-template <typename T, bool kCausal>
+template <typename T, bool kMasked>
 int launch(const CUtensorMap& mQ, const CUtensorMap& mK, const CUtensorMap& mV, const CUtensorMap& mO, int n_bh,
-           int S, int window, float scale_log2, int* status, cudaStream_t stream) {
+           int S, int left, int right, float scale_log2, int* status, cudaStream_t stream) {
   static bool configured = false;
-  auto kfn = flash_attn_kernel<T, kCausal>;
+  auto kfn = flash_attn_kernel<T, kMasked>;
   if (!configured) {
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
       return FTB_ERR_LAUNCH;
     configured = true;
   }
   const int group = kCausalGroup;
-  kfn<<<n_bh * (S / 256), kThreads, kSmemBytes, stream>>>(mQ, mK, mV, mO, S, n_bh, group, window, scale_log2, status);
+  kfn<<<n_bh * (S / 256), kThreads, kSmemBytes, stream>>>(mQ, mK, mV, mO, S, n_bh, group, left, right, scale_log2, status);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
@@ -495,15 +499,16 @@ extern "C" int ftb_debug_fa_trace(unsigned long long* out) {
 
 namespace {
 int flash_attn_entry(const void* q, const void* k, const void* v, void* o, int B, int heads, int S, int d,
-                     float scale, int dtype, bool causal, int window, void* workspace, size_t workspace_bytes,
-                     void* stream_) {
+                     float scale, int dtype, bool masked, int left, int right, void* workspace,
+                     size_t workspace_bytes, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!q || !k || !v || !o || B <= 0 || heads <= 0 || S <= 0) return FTB_ERR_ARG;
   if (dtype != FTB_F16 && dtype != FTB_BF16) return FTB_ERR_ARG;
   if (d != 128 || S % 256 != 0) return FTB_ERR_ARG;
-  if (causal && !(scale > 0.f)) return FTB_ERR_ARG;  // masked scores are -inf times the scale
-  if (window < 0) return FTB_ERR_ARG;
-  if (window >= S) window = 0;  // every earlier key is inside the window
+  if (masked && !(scale > 0.f)) return FTB_ERR_ARG;  // masked scores are -inf times the scale
+  if (masked && right < 0) return FTB_ERR_ARG;
+  if (left >= S) left = -1;  // every earlier key is inside the window
+  if (right > S) right = S;
   const int64_t rows = static_cast<int64_t>(B) * heads * S;
   if (rows > 0x7fffffffLL) return FTB_ERR_ARG;
   if (workspace == nullptr || workspace_bytes < ftb_workspace_bytes()) return FTB_ERR_WORKSPACE;
@@ -520,31 +525,40 @@ int flash_attn_entry(const void* q, const void* k, const void* v, void* o, int B
   if ((rc = make_tmap_2d(&mO, o, dtype, rows, d, d, 128, 64))) return rc;
   const int units = B * heads;
   const float scale_log2 = scale * 1.4426950408889634f;
-  if (causal) {
-    if (dtype == FTB_F16) return launch<__half, true>(mQ, mK, mV, mO, units, S, window, scale_log2, status, stream);
-    return launch<__nv_bfloat16, true>(mQ, mK, mV, mO, units, S, window, scale_log2, status, stream);
+  if (masked) {
+    if (dtype == FTB_F16)
+      return launch<__half, true>(mQ, mK, mV, mO, units, S, left, right, scale_log2, status, stream);
+    return launch<__nv_bfloat16, true>(mQ, mK, mV, mO, units, S, left, right, scale_log2, status, stream);
   }
-  if (dtype == FTB_F16) return launch<__half, false>(mQ, mK, mV, mO, units, S, 0, scale_log2, status, stream);
-  return launch<__nv_bfloat16, false>(mQ, mK, mV, mO, units, S, 0, scale_log2, status, stream);
+  if (dtype == FTB_F16) return launch<__half, false>(mQ, mK, mV, mO, units, S, -1, 0, scale_log2, status, stream);
+  return launch<__nv_bfloat16, false>(mQ, mK, mV, mO, units, S, -1, 0, scale_log2, status, stream);
 }
 }  // namespace
 
 extern "C" int ftb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S,
                                   int d, float scale, int dtype, void* workspace, size_t workspace_bytes,
                                   void* stream) {
-  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, false, 0, workspace, workspace_bytes, stream);
+  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, false, -1, 0, workspace, workspace_bytes, stream);
 }
 
 extern "C" int ftb_flash_attn_causal_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads,
                                          int S, int d, float scale, int dtype, void* workspace,
                                          size_t workspace_bytes, void* stream) {
-  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, true, 0, workspace, workspace_bytes, stream);
+  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, true, -1, 0, workspace, workspace_bytes, stream);
 }
 
 extern "C" int ftb_flash_attn_window_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads,
                                          int S, int d, int window, float scale, int dtype, void* workspace,
                                          size_t workspace_bytes, void* stream) {
   if (window <= 0) return FTB_ERR_ARG;
-  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, true, window, workspace, workspace_bytes,
+  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, true, window - 1, 0, workspace,
+                          workspace_bytes, stream);
+}
+
+extern "C" int ftb_flash_attn_local_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads,
+                                        int S, int d, int left, int right, float scale, int dtype,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+  if (left < 0 || right < 0) return FTB_ERR_ARG;
+  return flash_attn_entry(q, k, v, o, B, heads, S, d, scale, dtype, true, left, right, workspace, workspace_bytes,
                           stream);
 }

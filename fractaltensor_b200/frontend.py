@@ -244,15 +244,16 @@ def stacked_grid_rnns(src_encs, trg_encs, stacked_params, dtype=None):
     return to_ft(hx), to_ft(hy)
 
 
-def flash_attention(qsss, ksss, vsss, scale=1.0, dtype=None, causal=False, window=None):
+def flash_attention(qsss, ksss, vsss, scale=1.0, dtype=None, causal=False, window=None, local=None):
     """map(batch) of map(heads) of map(query blocks) of reduce(key/value blocks) of attn_func.
 
     q/k/v: [B][heads][blocks] of [block, d].  Returns the same nesting.  `causal`: the reduce of
     query block i runs over key/value blocks 0..i, the last one masked above its diagonal; `window`
-    (with causal) also drops the keys more than window-1 positions before the query.
+    (with causal) also drops the keys more than window-1 positions before the query; `local=(left,
+    right)` keeps keys i-left..i+right instead.
     """
     q, k, v = (_cuda(_dense(t), dtype) for t in (qsss, ksss, vsss))
     Bsz, heads, nblk, blk, d = q.shape
     flat = lambda t: t.reshape(Bsz, heads, nblk * blk, d).contiguous()
-    o = ops.flash_attention(flat(q), flat(k), flat(v), scale=scale, causal=causal, window=window)
+    o = ops.flash_attention(flat(q), flat(k), flat(v), scale=scale, causal=causal, window=window, local=local)
     return FractalTensor.from_dense(o.reshape(Bsz, heads, nblk, blk, d), 3)

@@ -248,9 +248,9 @@ def b2b_gemm(A, B, C, out=None):
     return out
 
 
-def flash_attention(q, k, v, scale=None, out=None, causal=False, window=None):
+def flash_attention(q, k, v, scale=None, out=None, causal=False, window=None, local=None):
     """q,k,v: [B,heads,S,d] -> softmax(scale * q k^T) v, same shape; `causal`: keys 0..i for query i;
-    `window` (with causal): keys i-window+1..i."""
+    `window` (with causal): keys i-window+1..i; `local=(left, right)`: keys i-left..i+right."""
     _req(q, "q")
     _req(k, "k", q.dtype)
     _req(v, "v", q.dtype)
@@ -264,6 +264,13 @@ def flash_attention(q, k, v, scale=None, out=None, causal=False, window=None):
     _req(out, "out", q.dtype)
     ws = workspace(q.device)
     with torch.cuda.device(q.device):
+        if local is not None:
+            if causal or window is not None:
+                raise ValueError("flash_attention: local=(left, right) stands alone")
+            check(lib.ftb_flash_attn_local_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, heads, S, d, int(local[0]),
+                                               int(local[1]), float(scale), _dtype_code(q), _ptr(ws), ws.numel(),
+                                               _stream()), "ftb_flash_attn_local_fwd")
+            return out
         if window is not None:
             if not causal:
                 raise ValueError("flash_attention: a window needs causal=True (the window ends at the query)")

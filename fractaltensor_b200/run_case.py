@@ -41,6 +41,7 @@ def main():
     ap.add_argument("--min-len", type=int, default=1, help="varlen: lengths are uniform in [min-len, L]")
     ap.add_argument("--causal", action="store_true", help="attn: keys 0..i for query i")
     ap.add_argument("--window", type=int, default=None, help="attn with --causal: keys i-window+1..i")
+    ap.add_argument("--local", type=int, nargs=2, default=None, help="attn: keys i-LEFT..i+RIGHT")
     ap.add_argument("--graph", action="store_true",
                     help="capture one call in a CUDA graph and time replays (schedules with one launch per level)")
     a = ap.parse_args()
@@ -100,7 +101,7 @@ def main():
     else:
         q, k, v = (rnd(a.B, a.heads, a.S, 128).to(dt) for _ in range(3))
         out = torch.empty_like(q)
-        fn = lambda: ops.flash_attention(q, k, v, scale=1 / math.sqrt(128), out=out, causal=a.causal, window=a.window)
+        fn = lambda: ops.flash_attention(q, k, v, scale=1 / math.sqrt(128), out=out, causal=a.causal, window=a.window, local=a.local)
 
     for _ in range(a.warmup):
         fn()

@@ -192,6 +192,14 @@ int ftb_flash_attn_window_fwd(const void* q, const void* k, const void* v, void*
                               int d, int window, float scale, int dtype, void* workspace,
                               size_t workspace_bytes, void* stream);
 
+/* Two-sided local attention: query i attends to keys i-left .. i+right (both >= 0, cut at
+ * the ends of the sequence).  left = right = w is the block form of a window of 2w+1 keys
+ * centred on the query, as ops.shifted_slide builds it with dilation 1
+ * (examples/sparse_attention/sparse_attention.py:44-46). */
+int ftb_flash_attn_local_fwd(const void* q, const void* k, const void* v, void* o, int B, int heads, int S,
+                             int d, int left, int right, float scale, int dtype, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
 /* Embedding lookup out[t, :] = table[ids[t], :] for t < T.  Stands in for the lookup in front of
  * the reference's RNN examples, ops.index(ops.slices(embedding, dim=0), word) mapped over a batch
  * of word sequences (examples/stacked_rnn/rnn_utils.py:80-90): `ids` is the flat int64 buffer of

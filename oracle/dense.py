@@ -222,14 +222,19 @@ def embedding_gather_dense(table, ids):
     return table[ids.reshape(-1)]
 
 
-def attention_plain(q, k, v, scale=1.0, causal=False, window=None):
+def attention_plain(q, k, v, scale=1.0, causal=False, window=None, local=None):
     """softmax(scale * q k^T) v, the closed form the blockwise carry equals.
 
     `causal`: query i sees keys 0..i (later scores are -inf before the softmax).  The reference
     has no causal program, so this case has no vectors of the reference behind it.
     """
     w = (q @ k.transpose(-1, -2)) * scale
-    if causal:
+    if local is not None:  # keys i-left .. i+right
+        S = q.shape[-2]
+        ones = torch.ones(S, S, dtype=torch.bool, device=q.device)
+        keep = ones.tril(int(local[1])) & ones.triu(-int(local[0]))
+        w = w.masked_fill(~keep, float("-inf"))
+    elif causal:
         S = q.shape[-2]
         keep = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
         if window is not None:  # keys i-window+1 .. i

@@ -610,6 +610,19 @@ def test_flash_attention_window(ops, window):
         assert (out.float().cpu() - v.float()).abs().max().item() <= 2e-3
 
 
+@pytest.mark.parametrize("local", [(0, 0), (2, 2), (0, 70), (63, 64), (127, 128), (128, 127), (200, 10), (10, 300),
+                                   (256, 256), (500, 129), (5000, 0), (0, 5000), (5000, 5000)])
+def test_flash_attention_local(ops, local):
+    """Two-sided window: edges inside, on and across the 128-key blocks and 256-row CTAs, one-sided
+    in either direction, and windows that cover the whole sequence (= unmasked attention)."""
+    B, h, S = 1, 2, 1280
+    q, k, v = dense.make_attention_inputs(B, h, S, 128, 24, dtype=torch.float16)
+    sc = 1.0 / math.sqrt(128.0)
+    out = ops.flash_attention(*_dev(q, k, v), scale=sc, local=local)
+    ops.check_status()
+    _assert_16(out, dense.attention_plain(*_f32(q, k, v), scale=sc, local=local))
+
+
 def test_flash_attention_window_ignores_keys_outside(ops):
     """Full-size property: the outputs of queries p..p+99 do not change, bit for bit, when keys and
     values before p-window+1 and after p+99 are replaced."""

@@ -97,6 +97,13 @@ def test_causal_attention_blockwise_equals_closed_form():
     assert (one - v.double()).abs().max().item() <= 1e-12
     full = dense.attention_plain(q.double(), k.double(), v.double(), scale=0.25, causal=True, window=128)
     assert torch.equal(full, ref)
+    # two-sided windows: (S, 0) is causal, (S, S) is unmasked, (w-1, 0) is the one-sided window w
+    qd, kd, vd = q.double(), k.double(), v.double()
+    assert torch.equal(dense.attention_plain(qd, kd, vd, scale=0.25, local=(128, 0)), ref)
+    assert torch.equal(dense.attention_plain(qd, kd, vd, scale=0.25, local=(128, 128)),
+                       dense.attention_plain(qd, kd, vd, scale=0.25))
+    assert torch.equal(dense.attention_plain(qd, kd, vd, scale=0.25, local=(6, 0)),
+                       dense.attention_plain(qd, kd, vd, scale=0.25, causal=True, window=7))
 
 
 def test_flash_attention_block_size_does_not_matter():
