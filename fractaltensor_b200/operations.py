@@ -401,6 +401,7 @@ def _dispatch_attention(func, zipped):
 
     def batch():
         return zip(*[_deep_input(n, 3) for n in ("q", "k", "v")])
+    _len_codes.clear()
     traced = _desc(map(func, batch()))
     scales = _find_scales(traced, set())
     if len(scales) > 1:
@@ -428,6 +429,7 @@ def _dispatch_dilated(func, embs):
         return _symbolic_inputs(3, 4)[0]
 
     _seen.clear()
+    _len_codes.clear()
     traced = _desc(map(func, symbolic()))
     params = _seen.pop("enumerated", None)
     if params is not None and traced == _desc(_program_dilated(symbolic(), params)):
@@ -548,6 +550,7 @@ def fold(func, xs, initializer=None, **kwargs):
     if builtins.any(_inner_length(p) != 4 for p in (Wss, Uss, bss)):
         raise NotImplementedError("fold: the parameters are not [depth][4 gates] FractalTensors")
     embs_sym, params_sym = _symbolic_inputs(3, 4)
+    _len_codes.clear()
     traced = _desc(func(embs_sym, params_sym))
     if traced == _desc(_program_batch_major(*_symbolic_inputs(3, 4))):
         return frontend.stacked_lstm(initializer, Wss, Uss, bss)

@@ -58,6 +58,11 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
     assert lib.ftb_b2b_gemm(one, one, one, one, 1, 128, 128, 128, 128, 0, one, 256, z) == 1  # fp32
     assert lib.ftb_flash_attn_fwd(one, one, one, one, 1, 1, 256, 64, 1.0, 1, one, 256, z) == 1  # d != 128
     assert lib.ftb_flash_attn_fwd(one, one, one, one, 1, 1, 100, 128, 1.0, 1, one, 256, z) == 1  # S % 256
+    assert lib.ftb_flash_attn_causal_fwd(one, one, one, one, 1, 1, 256, 128, 0.0, 1, one, 256, z) == 1  # scale <= 0
+    assert lib.ftb_flash_attn_causal_fwd(one, one, one, one, 1, 1, 100, 128, 1.0, 1, one, 256, z) == 1  # S % 256
+    assert lib.ftb_flash_attn_window_fwd(one, one, one, one, 1, 1, 256, 128, 0, 1.0, 1, one, 256, z) == 1  # window < 1
+    assert lib.ftb_flash_attn_local_fwd(one, one, one, one, 1, 1, 256, 128, -1, 0, 1.0, 1, one, 256, z) == 1  # left < 0
+    assert lib.ftb_flash_attn_local_fwd(one, one, one, one, 1, 1, 256, 128, 0, -2, 1.0, 1, one, 256, z) == 1  # right < 0
     assert lib.ftb_gemm_nt(one, one, one, 8, 128, 60, 1, None, one, 256, z) == 1  # K % 64
     rows = (ctypes.c_int * 3)(4, 5, 1)  # not sorted by decreasing length
     assert lib.ftb_lstm_stacked_varlen_fwd(one, one, z, one, one, rows, 1, 3, 64, 64, 1, None, one, 256, z) == 1
