@@ -1,5 +1,8 @@
-// Flash attention forward (non-causal) with online softmax for 16-bit inputs on
-// sm_100a, head dimension 128.
+// Flash attention forward with online softmax for 16-bit inputs on sm_100a, head
+// dimension 128: unmasked, and (second instantiation) masked to keys i-left..i+right
+// of query i, which covers causal attention (no lower limit, right = 0) and one- and
+// two-sided sliding windows.  A masked query tile only walks the key/value blocks its
+// rows can see; the blocks the window's edges cross are masked element by element.
 //
 // Follows the recurrence of attn_func (examples/flash_attention/flash_attention.py:14-44):
 // per key/value block, scores S = scale * q k^T, running row maximum m and row sum
