@@ -364,13 +364,9 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
 template <typename T, int KK, int PP, int NCH>
 int launch(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mC, const CUtensorMap& mD, const Shape& sh,
            uint32_t smem_bytes, int* status, int sm_count, cudaStream_t stream) {
-  static bool configured = false;
+  static std::atomic<unsigned long long> configured{0};
   auto kfn = b2b_gemm_kernel<T, KK, PP, NCH>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024) != cudaSuccess)
-      return FTB_ERR_LAUNCH;
-    configured = true;
-  }
+  if (!ensure_dynamic_smem(kfn, kSmemBudget + 1024, configured)) return FTB_ERR_LAUNCH;
   const int grid = sh.total_tiles < sm_count ? sh.total_tiles : sm_count;
   kfn<<<grid, kThreads, smem_bytes, stream>>>(mA, mB, mC, mD, sh, status);
   count_launch();

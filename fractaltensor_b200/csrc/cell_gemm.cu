@@ -163,8 +163,14 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(&tmem_base_s, C::kTmemCols);
-    tmem_relinquish();
+    // A kernel's tcgen05 instructions all use one .cta_group: pairs allocate as pairs.
+    if (PAIR) {
+      tmem_alloc_pair(&tmem_base_s, C::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&tmem_base_s, C::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -589,7 +595,10 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
       while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     }
     tc_fence_after();
-    tmem_dealloc(tmem_base, C::kTmemCols);
+    if (PAIR)
+      tmem_dealloc_pair(tmem_base, C::kTmemCols);
+    else
+      tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -597,13 +606,9 @@ template <typename T, int BN, int EPI, bool PERSIST, bool PAIR>
 int launch_one(const CUtensorMap* maps, const CUtensorMap& mapW, const CUtensorMap& mapC, const CellBatch& batch,
                const PlanView& plan, int* status, int sm_count, cudaStream_t stream) {
   using C = Cfg<BN, EPI, PAIR>;
-  static bool configured = false;
+  static std::atomic<unsigned long long> configured{0};
   auto kfn = cell_gemm_kernel<T, BN, EPI, PERSIST, PAIR>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
-      return FTB_ERR_LAUNCH;
-    configured = true;
-  }
+  if (!ensure_dynamic_smem(kfn, C::kSmemBytes, configured)) return FTB_ERR_LAUNCH;
   int grid = batch.total_tiles < sm_count ? batch.total_tiles : sm_count;
   if (PAIR) grid &= ~1;  // whole pairs only; tiles 2p and 2p+1 are the two halves of one row block
   if (grid <= 0) return FTB_OK;

@@ -476,13 +476,9 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 template <typename T, bool kMasked>
 int launch(const CUtensorMap& mQ, const CUtensorMap& mK, const CUtensorMap& mV, const CUtensorMap& mO, int n_bh,
            int S, int left, int right, float scale_log2, int* status, cudaStream_t stream) {
-  static bool configured = false;
+  static std::atomic<unsigned long long> configured{0};
   auto kfn = flash_attn_kernel<T, kMasked>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-      return FTB_ERR_LAUNCH;
-    configured = true;
-  }
+  if (!ensure_dynamic_smem(kfn, kSmemBytes, configured)) return FTB_ERR_LAUNCH;
   const int group = kCausalGroup;
   kfn<<<n_bh * (S / 256), kThreads, kSmemBytes, stream>>>(mQ, mK, mV, mO, S, n_bh, group, left, right, scale_log2, status);
   count_launch();

@@ -113,8 +113,9 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(&tmem_base_s, kTmemCols);
-    tmem_relinquish();
+    // Every tcgen05 instruction of this kernel is .cta_group::2, the allocation included.
+    tmem_alloc_pair(&tmem_base_s, kTmemCols);
+    tmem_relinquish_pair();
   }
   tc_fence_before();
   __syncthreads();
@@ -367,20 +368,16 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
       while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     }
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
 template <typename T>
 int launch(const CUtensorMap& mX, const CUtensorMap& mH, const CUtensorMap& mW, const StaticArgs& a, int grid,
            cudaStream_t stream) {
-  static bool configured = false;
+  static std::atomic<unsigned long long> configured{0};
   auto kfn = lstm_static_kernel<T>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-      return FTB_ERR_LAUNCH;
-    configured = true;
-  }
+  if (!ensure_dynamic_smem(kfn, kSmemBytes, configured)) return FTB_ERR_LAUNCH;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);

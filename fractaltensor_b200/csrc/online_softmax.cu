@@ -212,15 +212,12 @@ extern "C" int ftb_online_softmax(const float* x, float* y, int rows, int width,
   constexpr int kMaxCacheFloats = 48 * 1024;
   const int cache_floats = width <= kMaxCacheFloats ? ((width + 3) & ~3) : kMaxCacheFloats;
   const size_t smem = static_cast<size_t>(cache_floats) * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(online_softmax_kernel<kSoftmaxThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kMaxCacheFloats * static_cast<int>(sizeof(float))) != cudaSuccess ||
-        cudaFuncSetAttribute(online_softmax_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kMaxCacheFloats * static_cast<int>(sizeof(float))) != cudaSuccess)
-      return FTB_ERR_LAUNCH;
-    configured = true;
-  }
+  static std::atomic<unsigned long long> configured_a{0}, configured_b{0};
+  if (!ensure_dynamic_smem(online_softmax_kernel<kSoftmaxThreads>, kMaxCacheFloats * static_cast<int>(sizeof(float)),
+                           configured_a) ||
+      !ensure_dynamic_smem(online_softmax_kernel<1024>, kMaxCacheFloats * static_cast<int>(sizeof(float)),
+                           configured_b))
+    return FTB_ERR_LAUNCH;
   // A whole number of CTAs per SM: as many as the row cache lets be resident (at most 8).  A cache
   // that leaves room for one or two CTAs per SM gets CTAs of 1024 threads to keep loads in flight.
   int per_sm = static_cast<int>((200 * 1024) / (smem + 1024));

@@ -8,6 +8,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace ftb {
 
 enum DType : int { FTB_F32 = 0, FTB_F16 = 1, FTB_BF16 = 2 };
@@ -29,6 +31,24 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int dtype, uint64_t cols, u
 int check_device_sm100();
 
 int current_sm_count();
+
+// Opt-in to more than 48 KB of dynamic shared memory for kernel `kfn` on the CURRENT device.
+// The attribute belongs to each device's copy of the kernel, so `configured` (one static per
+// kernel instantiation) keeps one bit per device ordinal; devices past 63 are set up on every call.
+// Safe to call from several host threads.  Returns false when the runtime refuses.
+template <typename Kernel>
+inline bool ensure_dynamic_smem(Kernel kfn, int bytes, std::atomic<unsigned long long>& configured) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return false;
+  const unsigned long long bit = dev < 64 ? (1ull << dev) : 0ull;
+  if (bit != 0 && (configured.load(std::memory_order_acquire) & bit) != 0) return true;
+  if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  configured.fetch_or(bit, std::memory_order_release);
+  return true;
+}
 
 // Process-wide count of kernels this library has launched (reported by ftb_launch_count()).
 void count_launch(int n = 1);

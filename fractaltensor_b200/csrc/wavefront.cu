@@ -9,6 +9,7 @@
 // hyperplane as gather -> batched GEMM -> elementwise -> scatter.  Here a level
 // is one launch of a fused cell kernel that addresses the hyperplane in place.
 #include <algorithm>
+#include <initializer_list>
 #include <map>
 #include <mutex>
 #include <vector>
@@ -148,6 +149,13 @@ int begin_call(void* workspace, size_t workspace_bytes, cudaStream_t stream, int
 }
 
 bool valid_dtype(int dt) { return dt == FTB_F32 || dt == FTB_F16 || dt == FTB_BF16; }
+
+// Every kernel reads and writes 16 bytes at a time (the fp32 path as float4, the 16-bit path by TMA).
+bool aligned16(std::initializer_list<const void*> ptrs) {
+  for (const void* p : ptrs)
+    if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) return false;
+  return true;
+}
 
 // Optional tuning knobs of the wavefront entry points (0 = automatic).
 struct Tuning {
@@ -417,6 +425,7 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
   if (H <= 0 || I <= 0 || H % 64 != 0 || I % 64 != 0) return FTB_ERR_ARG;
   if (D > 1 && I != H) return FTB_ERR_ARG;
   if (static_cast<int64_t>(D) * L * N > 0x7fffffffLL) return FTB_ERR_ARG;
+  if (!aligned16({x, Wp, bias_p, hs, c})) return FTB_ERR_ALIGN;
   int* status = nullptr;
   int rc = begin_call(workspace, workspace_bytes, stream, &status);
   if (rc) return rc;
@@ -576,6 +585,7 @@ int ftb_lstm_stacked_varlen_fwd(const void* x, const void* Wp, const float* bias
   const int64_t T = off[L];
   const int N = active_rows[0];
   if (static_cast<int64_t>(D) * T > 0x7fffffffLL) return FTB_ERR_ARG;
+  if (!aligned16({x, Wp, bias_p, hs, c})) return FTB_ERR_ALIGN;
   int* status = nullptr;
   int rc = begin_call(workspace, workspace_bytes, stream, &status);
   if (rc) return rc;
@@ -742,6 +752,7 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
     max_dil = std::max(max_dil, dilations[l]);
   }
   if (static_cast<int64_t>(D) * L * N > 0x7fffffffLL) return FTB_ERR_ARG;
+  if (!aligned16({x, Wp, bias_p, hs, c})) return FTB_ERR_ALIGN;
   int* status = nullptr;
   int rc = begin_call(workspace, workspace_bytes, stream, &status);
   if (rc) return rc;
@@ -851,7 +862,10 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
           deps[(me * kMaxSeg + 1) * 2 + 0] = deps[(me * kMaxSeg + 1) * 2 + 1] = prev;
         }
       }
-    return run_persistent(cl, order, deps, static_cast<char*>(workspace), lay, workspace_bytes);
+    rc = run_persistent(cl, order, deps, static_cast<char*>(workspace), lay, workspace_bytes);
+    // A refused cooperative launch falls back to one launch per level, as in the other entries;
+    // an explicitly requested persistent schedule reports the refusal.
+    if (rc != FTB_ERR_LAUNCH || tune.schedule != 0) return rc;
   }
   for (auto& kv : levels) {
     rc = cl.run(kv.second);
@@ -873,6 +887,7 @@ int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* 
     return FTB_ERR_ARG;
   if (H <= 0 || H % 64 != 0) return FTB_ERR_ARG;
   if (static_cast<int64_t>(D) * A * B * N > 0x7fffffffLL) return FTB_ERR_ARG;
+  if (!aligned16({X, Y, Wpx, Wpy, bias_x, bias_y, hx, hy})) return FTB_ERR_ALIGN;
   int* status = nullptr;
   int rc = begin_call(workspace, workspace_bytes, stream, &status);
   if (rc) return rc;
@@ -1014,6 +1029,7 @@ int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, i
   if (!A || !Bt || !out || M <= 0 || N <= 0 || K <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
   if (K % 64 != 0) return FTB_ERR_ARG;
   if (dtype == FTB_F32 ? (N % 64 != 0) : (N % 128 != 0)) return FTB_ERR_ARG;
+  if (!aligned16({A, Bt, out})) return FTB_ERR_ALIGN;
   int* status = nullptr;
   int rc = begin_call(workspace, workspace_bytes, stream, &status);
   if (rc) return rc;
@@ -1106,7 +1122,10 @@ int ftb_lstm_stacked_fwd_noalloc(const void* x, const void* Wp, const float* bia
   int t[FTB_TUNING_INTS] = {0, 0, 0, 0, 0, 0};
   if (tuning != nullptr)
     for (int i = 0; i < FTB_TUNING_INTS; ++i) t[i] = tuning[i];
-  t[2] = 2;  // persistent schedule: the only one whose host side builds nothing on the heap
+  // A single-launch schedule: their host side builds nothing on the heap (the one-launch-per-level
+  // schedule keeps its cell lists in std::vector).  2 = generic persistent kernel, 3 = static tile
+  // ownership; anything else the caller asked for becomes 2.
+  if (t[2] != 3) t[2] = 2;
   return ftb_lstm_stacked_fwd(x, Wp, bias_p, hs, c, D, L, N, I, H, dtype, t, scratch, FTB_STATIC_SCRATCH_BYTES,
                               stream);
 }

@@ -38,6 +38,17 @@ def _req(t, name, dtype=None):
     return t
 
 
+def _req_like(t, name, dtype, shape, ref):
+    """A caller-supplied buffer or parameter: the C side builds its addresses from the problem sizes,
+    not from the buffer, so shape, dtype and device are checked here."""
+    _req(t, name, dtype)
+    if tuple(t.shape) != tuple(shape):
+        raise ValueError("%s must have shape %s, got %s" % (name, tuple(shape), tuple(t.shape)))
+    if t.device != ref.device:
+        raise ValueError("%s lives on %s, the inputs on %s" % (name, t.device, ref.device))
+    return t
+
+
 def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
 
@@ -104,16 +115,16 @@ def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0, 
     L, N, I = x.shape
     D, H4, K = Wp.shape
     H = H4 // 4
-    if K != I + H:
+    if K != I + H or H4 != 4 * H or Wp.device != x.device:
         raise ValueError("Wp %s does not match x %s" % (tuple(Wp.shape), tuple(x.shape)))
     if bias_p is not None:
-        _req(bias_p, "bias_p", torch.float32)
+        _req_like(bias_p, "bias_p", torch.float32, (D, 4 * H), x)
     if hs is None:
         hs = torch.empty(D, L, N, H, dtype=x.dtype, device=x.device)
     if c is None:
         c = torch.empty(D, N, H, dtype=torch.float32, device=x.device)
-    _req(hs, "hs", x.dtype)
-    _req(c, "c", torch.float32)
+    _req_like(hs, "hs", x.dtype, (D, L, N, H), x)
+    _req_like(c, "c", torch.float32, (D, N, H), x)
     ws = workspace(x.device, lib.ftb_lstm_stacked_workspace_bytes(D, L, N, H))
     with torch.cuda.device(x.device):
         check(lib.ftb_lstm_stacked_fwd(_ptr(x), _ptr(Wp), _ptr(bias_p), _ptr(hs), _ptr(c), D, L, N, I, H,
@@ -140,18 +151,18 @@ def lstm_stacked_varlen(x, active_rows, Wp, bias_p=None, hs=None, c=None, layers
     T, I = x.shape
     D, H4, K = Wp.shape
     H = H4 // 4
-    if K != I + H or T != sum(active_rows):
+    if K != I + H or H4 != 4 * H or T != sum(active_rows) or Wp.device != x.device:
         raise ValueError("Wp %s / active_rows (sum %d) do not match x %s" % (tuple(Wp.shape), sum(active_rows),
                                                                            tuple(x.shape)))
     if bias_p is not None:
-        _req(bias_p, "bias_p", torch.float32)
+        _req_like(bias_p, "bias_p", torch.float32, (D, 4 * H), x)
     N = active_rows[0]
     if hs is None:
         hs = torch.empty(D, T, H, dtype=x.dtype, device=x.device)
     if c is None:
         c = torch.empty(D, N, H, dtype=torch.float32, device=x.device)
-    _req(hs, "hs", x.dtype)
-    _req(c, "c", torch.float32)
+    _req_like(hs, "hs", x.dtype, (D, T, H), x)
+    _req_like(c, "c", torch.float32, (D, N, H), x)
     rows = (ctypes.c_int * L)(*active_rows)
     ws = workspace(x.device, lib.ftb_lstm_stacked_varlen_workspace_bytes(D, L))
     with torch.cuda.device(x.device):
@@ -167,15 +178,17 @@ def lstm_dilated(x, Wp, dilations, bias_p=None, hs=None, c=None, bn=0, pair=0, s
     _req(Wp, "Wp", x.dtype)
     L, N, H = x.shape
     D = Wp.shape[0]
-    if tuple(Wp.shape) != (D, 4 * H, 2 * H) or len(dilations) != D:
+    if tuple(Wp.shape) != (D, 4 * H, 2 * H) or len(dilations) != D or Wp.device != x.device:
         raise ValueError("Wp %s / dilations do not match x %s" % (tuple(Wp.shape), tuple(x.shape)))
     if bias_p is not None:
-        _req(bias_p, "bias_p", torch.float32)
+        _req_like(bias_p, "bias_p", torch.float32, (D, 4 * H), x)
     md = max(int(d) for d in dilations)
     if hs is None:
         hs = torch.empty(D, L, N, H, dtype=x.dtype, device=x.device)
     if c is None:
         c = torch.empty(D, md * N, H, dtype=torch.float32, device=x.device)
+    _req_like(hs, "hs", x.dtype, (D, L, N, H), x)
+    _req_like(c, "c", torch.float32, (D, md * N, H), x)
     dil = (ctypes.c_int * D)(*[int(d) for d in dilations])
     ws = workspace(x.device, lib.ftb_lstm_dilated_workspace_bytes(D, L))
     with torch.cuda.device(x.device):
@@ -214,7 +227,7 @@ def grid_rnn(X, Y, Wpx, Wpy, bias_x=None, bias_y=None, schedule=0):
         raise ValueError("grid_rnn: inconsistent shapes")
     for b in (bias_x, bias_y):
         if b is not None:
-            _req(b, "bias", torch.float32)
+            _req_like(b, "bias", torch.float32, (D, H), X)
     hx = torch.empty(D, A, B, N, H, dtype=X.dtype, device=X.device)
     hy = torch.empty_like(hx)
     # The library picks the persistent schedule when the workspace has room for its tables.
@@ -240,7 +253,7 @@ def b2b_gemm(A, B, C, out=None):
         raise ValueError("b2b_gemm: inconsistent shapes")
     if out is None:
         out = torch.empty(batch, M, P, dtype=A.dtype, device=A.device)
-    _req(out, "out", A.dtype)
+    _req_like(out, "out", A.dtype, (batch, M, P), A)
     ws = workspace(A.device)
     with torch.cuda.device(A.device):
         check(lib.ftb_b2b_gemm(_ptr(A), _ptr(B), _ptr(C), _ptr(out), batch, M, N, K, P, _dtype_code(A), _ptr(ws),
@@ -261,7 +274,7 @@ def flash_attention(q, k, v, scale=None, out=None, causal=False, window=None, lo
         scale = 1.0
     if out is None:
         out = torch.empty_like(q)
-    _req(out, "out", q.dtype)
+    _req_like(out, "out", q.dtype, q.shape, q)
     ws = workspace(q.device)
     with torch.cuda.device(q.device):
         if local is not None:
@@ -294,6 +307,7 @@ def gemm_nt(A, Bt, out=None, bn=0, pair=0):
         raise ValueError("gemm_nt: inner dimensions differ")
     if out is None:
         out = torch.empty(M, N, dtype=A.dtype, device=A.device)
+    _req_like(out, "out", A.dtype, (M, N), A)
     ws = workspace(A.device)
     with torch.cuda.device(A.device):
         check(lib.ftb_gemm_nt(_ptr(A), _ptr(Bt), _ptr(out), M, N, K, _dtype_code(A), _tuning(bn=bn, pair=pair), _ptr(ws), ws.numel(),
@@ -308,7 +322,7 @@ def online_softmax(x, out=None):
         raise ValueError("online_softmax: expected a matrix, got shape %s" % (tuple(x.shape),))
     if out is None:
         out = torch.empty_like(x)
-    _req(out, "out", torch.float32)
+    _req_like(out, "out", torch.float32, x.shape, x)
     rows, width = x.shape
     with torch.cuda.device(x.device):
         check(lib.ftb_online_softmax(_ptr(x), _ptr(out), rows, width, _stream()), "ftb_online_softmax")
@@ -325,7 +339,7 @@ def embedding_gather(table, ids, out=None):
     T = ids.numel()
     if out is None:
         out = torch.empty(T, H, dtype=table.dtype, device=table.device)
-    _req(out, "out", table.dtype)
+    _req_like(out, "out", table.dtype, (T, H), table)
     ws = workspace(table.device)
     with torch.cuda.device(table.device):
         check(lib.ftb_embedding_gather(_ptr(table), _ptr(ids), _ptr(out), T, V, H, _dtype_code(table), _ptr(ws),

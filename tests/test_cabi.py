@@ -75,6 +75,23 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
     assert lib.ftb_lstm_dilated_fwd(one, one, z, one, one, dil, 2, 4, 1, 64, 1, None, one, 256, z) == 1  # dilation 0
 
 
+def test_misaligned_pointers_are_rejected_without_a_device(lib):
+    """Every kernel moves 16 bytes at a time (float4 on the fp32 path, TMA on the 16-bit path): a
+    pointer off a 16-byte boundary is answered with FTB_ERR_ALIGN (2) before any launch."""
+    z = ctypes.c_void_p(0)
+    ok, off = ctypes.c_void_p(4096), ctypes.c_void_p(4096 + 4)
+    for dtype in (0, 1, 2):
+        assert lib.ftb_lstm_stacked_fwd(off, ok, z, ok, ok, 1, 1, 1, 64, 64, dtype, None, ok, 256, z) == 2
+        assert lib.ftb_lstm_stacked_fwd(ok, ok, z, off, ok, 1, 1, 1, 64, 64, dtype, None, ok, 256, z) == 2
+        assert lib.ftb_lstm_stacked_fwd(ok, ok, off, ok, ok, 1, 1, 1, 64, 64, dtype, None, ok, 256, z) == 2
+    dil = (ctypes.c_int * 1)(1)
+    assert lib.ftb_lstm_dilated_fwd(ok, off, z, ok, ok, dil, 1, 4, 1, 64, 0, None, ok, 256, z) == 2
+    assert lib.ftb_grid_rnn_fwd(ok, ok, ok, ok, z, z, ok, off, 1, 2, 2, 1, 64, 0, ok, 256, z) == 2
+    assert lib.ftb_gemm_nt(ok, ok, off, 8, 128, 64, 0, None, ok, 256, z) == 2
+    rows = (ctypes.c_int * 2)(2, 1)
+    assert lib.ftb_lstm_stacked_varlen_fwd(ok, ok, z, ok, off, rows, 1, 2, 64, 64, 0, None, ok, 256, z) == 2
+
+
 def test_no_fallback_when_library_is_missing(monkeypatch, tmp_path):
     from fractaltensor_b200 import _lib
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))

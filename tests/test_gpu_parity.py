@@ -811,3 +811,89 @@ def test_frontend_signatures(ops):
     o = fe.flash_attention(blk(q), blk(k), blk(v), scale=0.1)
     assert o.depth == 3 and o.element_shape == (64, 128)
     _assert_16(o.to_dense().reshape(1, 2, 256, 128), dense.attention_plain(*_f32(q, k, v), scale=0.1))
+
+
+# ------------------------------------------ refused cooperative launches, argument checks
+def test_dilated_grid_varlen_fall_back_when_cooperative_launch_is_refused(ops, monkeypatch):
+    """The three other wavefront entries survive a refused cooperative launch (host-side injection,
+    the device is never touched by the refused call) by running one launch per level, bit for bit."""
+    dils = [1, 2, 4]
+    x, W, U, b = dense.make_lstm_inputs(3, 12, 64, 128, 128, 6, 1.0 / 8, dtype=torch.float16, bias=True)
+    xd, Wd, Ud, bd = _dev(x, W, U, b)
+    Wp, bp = ops.lstm_pack_weights(Wd, Ud, bd)
+    ref_d, _ = ops.lstm_dilated(xd, Wp, dils, bp)
+    X, Y, p = dense.make_grid_inputs(2, 4, 5, 32, 128, 6, 1.0 / 8, dtype=torch.bfloat16, bias=True)
+    ref_gx, ref_gy = _run_grid(ops, X, Y, p)
+    active, xv, Wv, Uv, bv = _varlen_inputs(2, 6, 150, 128, 128, 21, torch.bfloat16)
+    ref_v, ref_vc = _run_varlen(ops, active, xv, Wv, Uv, bv)
+    ops.check_status()
+    monkeypatch.setenv("FTB_REFUSE_COOPERATIVE", "1")
+    hs, _ = ops.lstm_dilated(xd, Wp, dils, bp)
+    ops.check_status()
+    assert torch.equal(hs, ref_d)
+    gx, gy = _run_grid(ops, X, Y, p)
+    assert torch.equal(gx, ref_gx) and torch.equal(gy, ref_gy)
+    hv, cv = _run_varlen(ops, active, xv, Wv, Uv, bv)
+    assert torch.equal(hv, ref_v) and torch.equal(cv, ref_vc)
+    with pytest.raises(RuntimeError):
+        ops.lstm_dilated(xd, Wp, dils, bp, schedule=2)
+
+
+def test_output_buffers_and_parameters_are_validated(ops):
+    """The C side derives every address from the problem sizes, so a buffer of the wrong shape,
+    dtype or device must stop in Python, not as an out-of-bounds write on the device."""
+    D, L, N, H = 2, 3, 64, 64
+    x = torch.zeros(L, N, H, dtype=torch.bfloat16, device="cuda")
+    Wp = torch.zeros(D, 4 * H, 2 * H, dtype=torch.bfloat16, device="cuda")
+    good_hs = torch.empty(D, L, N, H, dtype=torch.bfloat16, device="cuda")
+    good_c = torch.empty(D, N, H, dtype=torch.float32, device="cuda")
+    with pytest.raises(ValueError):
+        ops.lstm_stacked(x, Wp, hs=torch.empty(D, L, N - 1, H, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):
+        ops.lstm_stacked(x, Wp, hs=good_hs, c=torch.empty(D, N, H + 64, dtype=torch.float32, device="cuda"))
+    with pytest.raises(TypeError):
+        ops.lstm_stacked(x, Wp, hs=good_hs.float(), c=good_c)
+    with pytest.raises(ValueError):
+        ops.lstm_stacked(x, Wp, bias_p=torch.zeros(D, 2 * H, dtype=torch.float32, device="cuda"))
+    with pytest.raises(ValueError):
+        ops.lstm_dilated(x, Wp, [1, 2], hs=torch.empty(D, L, N, 2 * H, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):
+        ops.lstm_dilated(x, Wp, [1, 2], c=torch.empty(D, N, H, dtype=torch.float32, device="cuda"))  # needs max_dil*N rows
+    with pytest.raises(ValueError):
+        ops.lstm_stacked_varlen(x.reshape(L * N, H), [N] * L, Wp, hs=good_hs)
+    A = torch.zeros(1, 128, 128, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        ops.b2b_gemm(A, A, A, out=torch.empty(1, 256, 128, dtype=torch.float16, device="cuda"))
+    q = torch.zeros(1, 1, 256, 128, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        ops.flash_attention(q, q, q, out=torch.empty(1, 1, 512, 128, dtype=torch.float16, device="cuda"))
+    with pytest.raises(ValueError):
+        ops.gemm_nt(A[0], A[0], out=torch.empty(128, 256, dtype=torch.float16, device="cuda"))
+    with pytest.raises(ValueError):
+        ops.online_softmax(torch.zeros(4, 8, device="cuda"), out=torch.empty(4, 9, device="cuda"))
+    ops.lstm_stacked(x, Wp, hs=good_hs, c=good_c)
+    ops.check_status()
+
+
+@pytest.mark.skipif(torch.cuda.is_available() and torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_drives_two_devices(ops):
+    """The opt-in to large dynamic shared memory is per device: every kernel family called first on
+    cuda:0 and then on cuda:1 from the same process gives the same bits on both."""
+    x, W, U, b = dense.make_lstm_inputs(2, 4, 256, 256, 256, 3, 1.0 / 8, dtype=torch.bfloat16, bias=True)
+    A, B, C = dense.make_b2b_inputs(2, 256, 128, 128, 128, 1)
+    q, k, v = dense.make_attention_inputs(1, 2, 512, 128, 2)
+    xs = torch.randn(64, 4096)
+    outs = []
+    for idx in (0, 1):
+        dev = torch.device("cuda", idx)
+        with torch.cuda.device(dev):
+            Wp, bp = ops.lstm_pack_weights(W.to(dev), U.to(dev), b.to(dev))
+            hs, _ = ops.lstm_stacked(x.to(dev), Wp, bp)
+            hs2, _ = ops.lstm_stacked(x.to(dev), Wp, bp, schedule=2, pair=1)
+            o_b2b = ops.b2b_gemm(A.to(dev), B.to(dev), C.to(dev))
+            o_att = ops.flash_attention(q.to(dev), k.to(dev), v.to(dev), scale=0.088)
+            o_sm = ops.online_softmax(xs.to(dev))
+            ops.check_status(dev)
+            outs.append([t.cpu() for t in (hs, hs2, o_b2b, o_att, o_sm)])
+    for a, b_ in zip(*outs):
+        assert torch.equal(a, b_)

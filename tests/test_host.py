@@ -196,3 +196,53 @@ def test_fractal_tensor_element_type():
     half = ft.astype(T.bfloat16)
     assert half.element_type is T.bfloat16 and half.indices == ft.indices and half.element_shape == (1, 8)
     assert ft.astype(torch.float16).element_type is T.float16
+
+
+REFERENCE_ROOT = os.environ.get("FTB_REFERENCE_ROOT", "/root/reference")
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE_ROOT, "kaleido")),
+                    reason="the reference tree is not mounted on this machine")
+def test_reference_fractaltensor_objects_are_accepted_as_they_are():
+    """The reference's own kaleido.FractalTensor objects (built with the loader of
+    tests/golden/generate.py, which imports the reference frontend from its tree) go straight into
+    the model-level entry points: their flat buffer and nesting are read into the dense view the
+    kernels take, and the call then stops at the device check because the data lives on the CPU."""
+    sys_path = list(__import__("sys").path)
+    try:
+        from golden import generate
+        kaleido, _ = generate.load_reference_frontend(REFERENCE_ROOT)
+        from kaleido import FractalTensor, FractalTensorStorage, TensorStorage
+    finally:
+        __import__("sys").path[:] = sys_path
+
+    def ft(data, shape, indices):
+        depth = 1 if not isinstance(indices[0], list) else 2
+        st = TensorStorage(list(shape), kaleido.float32, device="cpu")
+        x = FractalTensor(FractalTensorStorage(st) if depth == 2 else st)
+        x.indices = indices
+        x.data = data.clone()
+        return x
+
+    D, L, N, H = 2, 5, 3, 64
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(N, L, 1, H, generator=g)
+    W = torch.randn(D, 4, H, H, generator=g)
+    b = torch.randn(D, 4, 1, H, generator=g)
+    embs = ft(x.reshape(N * L, 1, H), (1, H), [list(range(L)) for _ in range(N)])
+    Wss = ft(W.reshape(D * 4, H, H), (H, H), [list(range(4)) for _ in range(D)])
+    bss = ft(b.reshape(D * 4, 1, H), (1, H), [list(range(4)) for _ in range(D)])
+    assert type(embs).__module__.startswith("kaleido.")
+    # the dense views the entry points compute from the reference objects
+    assert torch.equal(frontend._dense(embs), x)
+    assert torch.equal(frontend._dense(Wss), W)
+    assert torch.equal(frontend._dense(bss), b)
+    assert not frontend._is_ragged(embs)
+    for fn in (frontend.stacked_lstm, frontend.stacked_lstm_time_major, frontend.dilated_lstm):
+        with pytest.raises(RuntimeError, match="no CPU path"):
+            fn(embs, Wss, Wss, bss)
+    # a ragged reference object is routed to the variable-length entry, not densified
+    ragged = ft(x.reshape(N * L, 1, H)[:12], (1, H), [list(range(5)), list(range(4)), list(range(3))])
+    assert frontend._is_ragged(ragged)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        frontend.stacked_lstm(ragged, Wss, Wss, bss)

@@ -43,10 +43,18 @@ def test_noalloc_entry_matches_regular_entry_twice_in_a_row():
 
         hs = torch.full((D, L, N, H), float("nan"), dtype=torch.bfloat16, device="cuda")
         c = torch.full((D, N, H), float("nan"), dtype=torch.float32, device="cuda")
+        if call == 0:
+            # The first call on a device looks the scratch array's address up; measure the second.
+            rc, _ = _call_noalloc(lib, xd, Wp, bp, hs, c, D, L, N, H, H, 2)
+            assert rc == 0, lib.ftb_status_str(rc)
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]  # the driver's view: sees a cudaMalloc made inside the library too
         rc, scratch = _call_noalloc(lib, xd, Wp, bp, hs, c, D, L, N, H, H, 2)
         assert rc == 0, lib.ftb_status_str(rc)
+        torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
         status = ctypes.c_int(-1)
         assert scratch.value
         assert lib.ftb_read_status(scratch, ctypes.byref(status), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
