@@ -31,6 +31,10 @@ bool lstm_static_supported(int dtype, int D, int N, int I, int H, int G, int sm_
 int launch_lstm_static(int dtype, const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
                        int N, int I, int H, int G, int* done, int* status, unsigned long long* trace,
                        cudaStream_t stream);
+bool lstm_wmajor_supported(int dtype, int D, int N, int I, int H, int G, int sm_count);
+int launch_lstm_wmajor(int dtype, const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
+                       int N, int I, int H, int G, int resident, int* done, int* status, unsigned long long* trace,
+                       cudaStream_t stream);
 int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* const* w, int ldw,
                      const CellBatch& batch, cudaStream_t stream);
 int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I, int H, int dtype,
@@ -159,7 +163,7 @@ bool aligned16(std::initializer_list<const void*> ptrs) {
 
 // Optional tuning knobs of the wavefront entry points (0 = automatic).
 struct Tuning {
-  int layers_per_group = 0, bn = 0, schedule = 0, skew = 0, pair = 0, fine_deps = 0;
+  int layers_per_group = 0, bn = 0, schedule = 0, skew = 0, pair = 0, fine_deps = 0, resident = 0;
   explicit Tuning(const int* t) {
     if (t != nullptr) {
       layers_per_group = t[0];
@@ -168,6 +172,7 @@ struct Tuning {
       skew = t[3];
       pair = t[4];
       fine_deps = t[5];
+      resident = t[6];
     }
   }
   // pair: 0 = automatic (pairs when a cell has more than 128 rows), 1 = never, 2 = always.
@@ -485,6 +490,23 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
     char* ws = static_cast<char*>(workspace);
     // Static tile ownership (schedule 3, and the automatic choice when it applies): CTA pairs
     // keep their slice of a layer, cell state in registers, for a whole sweep over time.
+    // Weights-major static ownership (schedule 4, and the automatic choice for batches of at most
+    // 128 sequences): the batch is the N side of the MMA, so a small batch wastes no tensor work.
+    const bool can_wmajor = lstm_wmajor_supported(dtype, D, N, I, H, G, cl.sm_count);
+    if (schedule == 4 && !can_wmajor) return FTB_ERR_ARG;
+    if (schedule == 4 || (schedule == 0 && can_wmajor && tune.pair == 0 && bn == 0 && !tune.fine_deps)) {
+      // tuning[6]: 0 = as many recurrent weight blocks on chip as fit, -1 = none, n = n blocks
+      const int resident = tune.resident == 0 ? -1 : (tune.resident < 0 ? 0 : tune.resident);
+      unsigned long long* trace = nullptr;
+#ifdef FTB_TRACE
+      trace = reinterpret_cast<unsigned long long*>(ws + lay.trace);
+#endif
+      // one flag per (cell, tile), in the per-tile counter area (at least 4H/128 ints per cell)
+      rc = launch_lstm_wmajor(dtype, x, Wp, bias_p, hs, c, D, L, N, I, H, G, resident,
+                              reinterpret_cast<int*>(ws + lay.tile_done), status, trace, stream);
+      if (rc != FTB_ERR_LAUNCH || schedule != 0) return rc;
+      goto level_schedule;
+    }
     const bool can_static = tune.pair != 1 && (bn == 0 || bn == 256) && !tune.fine_deps &&
                             lstm_static_supported(dtype, D, N, I, H, G, cl.sm_count);
     if (schedule == 3 && !can_static) return FTB_ERR_ARG;

@@ -71,8 +71,9 @@ def workspace(device, nbytes=0):
     return ws
 
 
-def _tuning(layers_per_group=0, bn=0, schedule=0, skew=0, pair=0, fine_deps=0):
-    return (ctypes.c_int * 6)(int(layers_per_group), int(bn), int(schedule), int(skew), int(pair), int(fine_deps))
+def _tuning(layers_per_group=0, bn=0, schedule=0, skew=0, pair=0, fine_deps=0, resident=0):
+    return (ctypes.c_int * 7)(int(layers_per_group), int(bn), int(schedule), int(skew), int(pair), int(fine_deps),
+                              int(resident))
 
 
 def check_status(device=None):
@@ -106,10 +107,12 @@ def lstm_pack_weights(W, U, bias=None):
 
 
 def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0, schedule=0, skew=0, pair=0,
-                 fine_deps=0):
+                 fine_deps=0, resident=0):
     """x: [L,N,I]; Wp: [D,4H,I+H] -> (hs [D,L,N,H], c fp32 [D,N,H]).
-    schedule: 0 auto, 1 one launch per anti-diagonal, 2 one persistent kernel; pair: 0 auto, 1 single CTAs,
-    2 CTA pairs."""
+    schedule: 0 auto, 1 one launch per anti-diagonal, 2 one persistent kernel, 3 static tile ownership
+    (CTA pairs on 256 batch rows), 4 static tile ownership with the batch on the N side of the MMA
+    (at most 128 sequences; `resident`: recurrent weight blocks kept on chip, 0 auto, -1 none);
+    pair: 0 auto, 1 single CTAs, 2 CTA pairs."""
     _req(x, "x")
     _req(Wp, "Wp", x.dtype)
     L, N, I = x.shape
@@ -128,8 +131,9 @@ def lstm_stacked(x, Wp, bias_p=None, hs=None, c=None, layers_per_group=0, bn=0, 
     ws = workspace(x.device, lib.ftb_lstm_stacked_workspace_bytes(D, L, N, H))
     with torch.cuda.device(x.device):
         check(lib.ftb_lstm_stacked_fwd(_ptr(x), _ptr(Wp), _ptr(bias_p), _ptr(hs), _ptr(c), D, L, N, I, H,
-                                       _dtype_code(x), _tuning(layers_per_group, bn, schedule, skew, pair, fine_deps), _ptr(ws),
-                                       ws.numel(),
+                                       _dtype_code(x),
+                                       _tuning(layers_per_group, bn, schedule, skew, pair, fine_deps, resident),
+                                       _ptr(ws), ws.numel(),
                                        _stream()), "ftb_lstm_stacked_fwd")
     return hs, c
 

@@ -65,14 +65,24 @@ int ftb_lstm_pack_weights(const void* W, const void* U, const void* bias, void* 
  *                        in the workspace (16-bit dtypes only); 3 = persistent with static
  *                        tile ownership (stacked LSTM: every CTA pair keeps its slice of a
  *                        layer, cell state in registers, over a whole sweep; needs a layer
- *                        group's tiles to fit on the device; the automatic choice when so)
+ *                        group's tiles to fit on the device; the automatic choice when so and
+ *                        the batch exceeds 128 sequences); 4 = static tile ownership with the
+ *                        weights as the M side of the MMA and the batch (at most 128 sequences)
+ *                        as its N side, cell state in registers, recurrent weights resident in
+ *                        tensor memory (stacked LSTM; the automatic choice for such batches: it
+ *                        is the kernel a batch of 256 sharded over 2, 4 or 8 GPUs runs); every
+ *                        schedule gives the same bits
  *  [3] skew              persistent schedule: layer j of a group runs `skew` levels
  *                        behind layer j-1
  *  [4] pair              1 = single CTAs, 2 = CTA pairs (tcgen05 cta_group::2) on
  *                        256-row blocks; automatic = pairs when a cell has > 128 rows
  *  [5] fine_deps         persistent schedule: 1 = each K block waits only for the producer
- *                        tile that holds its columns; otherwise a cell waits for whole cells */
-#define FTB_TUNING_INTS 6
+ *                        tile that holds its columns; otherwise a cell waits for whole cells
+ *  [6] resident          weights-major schedule: 64-wide K blocks of each CTA's recurrent weights
+ *                        kept in tensor memory for a whole sweep over time; 0 = as many as fit
+ *                        beside the accumulators (14, 12 or 8 for batches up to 32, 64 or 128),
+ *                        -1 = none (stream everything), n = at most n */
+#define FTB_TUNING_INTS 7
 
 /* Stacked LSTM forward as a depth x time wavefront.
  * Stands in for stacked_lstm() (examples/stacked_rnn/stacked_lstm1.py:66-76) and

@@ -150,6 +150,32 @@ def test_stacked_lstm_schedules_agree_bit_for_bit(ops, shape, kw):
     _assert_16(h, rhs)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 1, 32, 64, 64), (2, 4, 20, 128, 128), (3, 5, 64, 256, 256), (2, 4, 128, 512, 512),
+                                   (5, 9, 100, 256, 256), (1, 4, 50, 192, 64), (4, 6, 32, 1024, 1024), (2, 3, 1, 64, 64),
+                                   (3, 4, 33, 1088, 1088), (6, 3, 128, 128, 128)])
+def test_stacked_lstm_weights_major_schedule(ops, dt, shape):
+    """The small-batch kernel (weights on the M side of the MMA, batch of at most 128 on the N side): the
+    same bits as one launch per level, whatever part of the recurrent weights stays in tensor memory;
+    it is also what the automatic choice runs for such batches."""
+    D, L, N, I, H = shape
+    x, W, U, b = dense.make_lstm_inputs(D, L, N, I, H, 3, 1.0 / 8, dtype=dt, bias=True)
+    ref_h, ref_c = _run_stacked(ops, x, W, U, b, schedule=1, pair=1)
+    for kw in ({"schedule": 4}, {"schedule": 4, "resident": -1}, {"schedule": 4, "resident": 3},
+               {"schedule": 4, "layers_per_group": 1}, {}):
+        h, c = _run_stacked(ops, x, W, U, b, **kw)
+        assert torch.equal(h, ref_h) and torch.equal(c, ref_c), kw
+    rhs, rc = dense.stacked_lstm_dense(*_f32(x, W, U, b))
+    _assert_16(ref_h, rhs)
+    _assert_16(ref_c, rc)
+
+
+def test_stacked_lstm_weights_major_schedule_rejects_large_batches(ops):
+    x, W, U, b = dense.make_lstm_inputs(2, 3, 129, 64, 64, 3, 1.0 / 8, dtype=torch.bfloat16, bias=True)
+    with pytest.raises(RuntimeError):
+        _run_stacked(ops, x, W, U, b, schedule=4)
+
+
 def test_stacked_lstm_falls_back_when_cooperative_launch_is_refused(ops, monkeypatch):
     """The automatic schedule must survive a refused cooperative launch (host-side injection: the
     launcher answers FTB_ERR_LAUNCH without touching the device) by running one launch per level;
@@ -171,6 +197,15 @@ def test_stacked_lstm_falls_back_when_cooperative_launch_is_refused(ops, monkeyp
     for sched in (2, 3):
         with pytest.raises(RuntimeError):
             _run_stacked(ops, x, W, U, b, schedule=sched)
+    # the small-batch kernel falls back the same way
+    xs = x[:, :64].contiguous()
+    monkeypatch.delenv("FTB_REFUSE_COOPERATIVE")
+    ref_s, _ = _run_stacked(ops, xs, W, U, b)
+    monkeypatch.setenv("FTB_REFUSE_COOPERATIVE", "1")
+    h_s, _ = _run_stacked(ops, xs, W, U, b)
+    assert torch.equal(h_s, ref_s)
+    with pytest.raises(RuntimeError):
+        _run_stacked(ops, xs, W, U, b, schedule=4)
 
 
 def test_stacked_lstm_config4_properties(ops):
