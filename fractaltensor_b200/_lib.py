@@ -38,6 +38,9 @@ SIGNATURES = {
     "ftb_flash_attn_local_fwd": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp]),
     "ftb_embedding_gather": (_i, [_vp, _vp, _vp, ctypes.c_longlong, ctypes.c_longlong, _i, _i, _vp, _sz, _vp]),
     "ftb_online_softmax": (_i, [_vp, _vp, _i, _i, _vp]),
+    "ftb_projection_padded_cols": (_i, [_i]),
+    "ftb_projection_pack": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "ftb_lstm_project_softmax": (_i, [_vp, _vp, _vp, ctypes.c_longlong, _i, _i, _i, _vp, _sz, _vp]),
     "ftb_gemm_nt": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, ctypes.POINTER(_i), _vp, _sz, _vp]),
 }
 

@@ -21,6 +21,7 @@ enum Epilogue : int {
   EPI_STORE = 0,  // out = acc
   EPI_LSTM = 1,   // columns are gate-interleaved (i,f,o,g per unit): c = f*c + i*g, h = o*tanh(c)
   EPI_TANH = 2,   // out = tanh(acc + bias)
+  EPI_STORE_F32 = 3,  // out = acc as fp32 (16-bit inputs; one launch per level, single CTAs only)
 };
 
 struct CellItem {

@@ -493,7 +493,14 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
               }
               v[j] = x;
             }
-            *reinterpret_cast<uint4*>(out_row + col0 + 8 * g) = pack8<T>(v);
+            if (EPI == EPI_STORE_F32) {
+              float4* of = reinterpret_cast<float4*>(reinterpret_cast<float*>(it->out) +
+                                                     static_cast<size_t>(row) * batch.ld_out + col0 + 8 * g);
+              of[0] = make_float4(v[0], v[1], v[2], v[3]);
+              of[1] = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+              *reinterpret_cast<uint4*>(out_row + col0 + 8 * g) = pack8<T>(v);
+            }
           }
         }
         tc_fence_before();
@@ -666,6 +673,10 @@ int launch_epi(int epi, const CUtensorMap* maps, const CUtensorMap& mapW, const 
       return launch_one<T, BN, EPI_LSTM, PERSIST, PAIR>(maps, mapW, mapC, batch, plan, status, sm_count, stream);
     case EPI_TANH:
       return launch_one<T, BN, EPI_TANH, PERSIST, PAIR>(maps, mapW, mapC, batch, plan, status, sm_count, stream);
+    case EPI_STORE_F32:
+      if constexpr (!PERSIST && !PAIR)
+        return launch_one<T, BN, EPI_STORE_F32, false, false>(maps, mapW, mapC, batch, plan, status, sm_count, stream);
+      return FTB_ERR_ARG;
     default: return FTB_ERR_ARG;
   }
 }

@@ -52,7 +52,8 @@ __device__ __forceinline__ void push(MD& s, float v) {
 
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
-online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int width, int cache_floats) {
+online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int width, int ld,
+                      int cache_floats) {
   extern __shared__ float4 row_cache4[];
   float* row_cache = reinterpret_cast<float*>(row_cache4);
   __shared__ float red_m[32], red_d[32];
@@ -60,11 +61,11 @@ online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int ro
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int cached_floats = width < cache_floats ? width : cache_floats;  // prefix of the row kept on chip
   // 16-byte accesses need rows that start on a 16-byte boundary.
-  const bool vec = (width & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  const bool vec = ((width | ld) & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
 
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-    const float* xr = x + static_cast<size_t>(r) * width;
-    float* yr = y + static_cast<size_t>(r) * width;
+    const float* xr = x + static_cast<size_t>(r) * ld;
+    float* yr = y + static_cast<size_t>(r) * ld;
     MD s;
     s.m = -FLT_MAX;
     s.d = 0.f;
@@ -145,13 +146,13 @@ online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int ro
 // Short rows (width % 4 == 0, up to 32 * 4 * kMaxV floats): one warp per row, the row in registers.
 constexpr int kMaxV = 16;
 __global__ void __launch_bounds__(kSoftmaxThreads)
-online_softmax_warp_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int width) {
+online_softmax_warp_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int width, int ld) {
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = kSoftmaxThreads / 32;
   const int n4 = width / 4;
   for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
-    const float4* x4 = reinterpret_cast<const float4*>(x + static_cast<size_t>(r) * width);
-    float4* y4 = reinterpret_cast<float4*>(y + static_cast<size_t>(r) * width);
+    const float4* x4 = reinterpret_cast<const float4*>(x + static_cast<size_t>(r) * ld);
+    float4* y4 = reinterpret_cast<float4*>(y + static_cast<size_t>(r) * ld);
     float4 v[kMaxV];
 #pragma unroll
     for (int j = 0; j < kMaxV; ++j)
@@ -193,23 +194,26 @@ online_softmax_warp_kernel(const float* __restrict__ x, float* __restrict__ y, i
 
 using namespace ftb;
 
-extern "C" int ftb_online_softmax(const float* x, float* y, int rows, int width, void* stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (!x || !y || rows <= 0 || width <= 0) return FTB_ERR_ARG;
-  if (static_cast<int64_t>(rows) * width > 0x7fffffffffLL) return FTB_ERR_ARG;
+namespace ftb {
+// Softmax over the first `width` floats of each row of x (rows `ld` floats apart), written to the
+// same positions of y; x == y is allowed when a row fits the on-chip cache (width <= 48 K floats).
+int online_softmax_rows(const float* x, float* y, int rows, int width, int ld, cudaStream_t stream) {
+  if (!x || !y || rows <= 0 || width <= 0 || ld < width) return FTB_ERR_ARG;
+  if (static_cast<int64_t>(rows) * ld > 0x7fffffffffLL) return FTB_ERR_ARG;
   int rc = check_device_sm100();
   if (rc) return rc;
   const bool aligned16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
-  if (aligned16 && width % 4 == 0 && width <= 32 * 4 * kMaxV && rows >= 8) {
+  if (aligned16 && ((width | ld) & 3) == 0 && width <= 32 * 4 * kMaxV && rows >= 8) {
     const int64_t ctas = (static_cast<int64_t>(rows) + kSoftmaxThreads / 32 - 1) / (kSoftmaxThreads / 32);
     const int64_t full = static_cast<int64_t>(current_sm_count()) * 4;
     online_softmax_warp_kernel<<<static_cast<int>(ctas < full ? ctas : full), kSoftmaxThreads, 0, stream>>>(x, y, rows,
-                                                                                                            width);
+                                                                                                            width, ld);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
   }
   // Row cache: the row, or its first 48 K floats, in up to 192 KB of shared memory.
   constexpr int kMaxCacheFloats = 48 * 1024;
+  if (x == y && width > kMaxCacheFloats) return FTB_ERR_ARG;
   const int cache_floats = width <= kMaxCacheFloats ? ((width + 3) & ~3) : kMaxCacheFloats;
   const size_t smem = static_cast<size_t>(cache_floats) * sizeof(float);
   static std::atomic<unsigned long long> configured_a{0}, configured_b{0};
@@ -225,9 +229,14 @@ extern "C" int ftb_online_softmax(const float* x, float* y, int rows, int width,
   const int64_t want = static_cast<int64_t>(current_sm_count()) * per_sm;
   const int grid = static_cast<int>(rows < want ? rows : want);
   if (per_sm <= 2)
-    online_softmax_kernel<1024><<<grid, 1024, smem, stream>>>(x, y, rows, width, cache_floats);
+    online_softmax_kernel<1024><<<grid, 1024, smem, stream>>>(x, y, rows, width, ld, cache_floats);
   else
-    online_softmax_kernel<kSoftmaxThreads><<<grid, kSoftmaxThreads, smem, stream>>>(x, y, rows, width, cache_floats);
+    online_softmax_kernel<kSoftmaxThreads><<<grid, kSoftmaxThreads, smem, stream>>>(x, y, rows, width, ld, cache_floats);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+}
+}  // namespace ftb
+
+extern "C" int ftb_online_softmax(const float* x, float* y, int rows, int width, void* stream_) {
+  return ftb::online_softmax_rows(x, y, rows, width, width, static_cast<cudaStream_t>(stream_));
 }

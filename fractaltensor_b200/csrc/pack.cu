@@ -83,6 +83,15 @@ int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* b
   return FTB_OK;
 }
 
+// P: [H, V] (x @ P orientation) -> Pt: [Vp, H] K-major, row v = column v of P, rows V..Vp-1 zero.
+int pack_projection(const void* P, void* Pt, int H, int V, int Vp, int dtype, cudaStream_t s) {
+  const size_t es = dtype_size(dtype);
+  if (cudaMemsetAsync(Pt, 0, static_cast<size_t>(Vp) * H * es, s) != cudaSuccess) return FTB_ERR_LAUNCH;
+  // pack_matrix with one "gate": out[u * ldo + k] = in[k][u] for k < K = H, u < V
+  if (es == 4) return pack_matrix<float>(static_cast<const float*>(P), static_cast<float*>(Pt), 1, H, V, H, 0, s);
+  return pack_matrix<uint16_t>(static_cast<const uint16_t*>(P), static_cast<uint16_t*>(Pt), 1, H, V, H, 0, s);
+}
+
 int pack_grid(const void* i2h, const void* h2h, void* Wp, int H, int dtype, cudaStream_t s) {
   int rc;
   if (dtype_size(dtype) == 4) {

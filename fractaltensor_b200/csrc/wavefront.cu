@@ -40,6 +40,8 @@ int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const 
 int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I, int H, int dtype,
               cudaStream_t s);
 int pack_grid(const void* i2h, const void* h2h, void* Wp, int H, int dtype, cudaStream_t s);
+int pack_projection(const void* P, void* Pt, int H, int V, int Vp, int dtype, cudaStream_t s);
+int online_softmax_rows(const float* x, float* y, int rows, int width, int ld, cudaStream_t stream);
 
 namespace {
 
@@ -1084,6 +1086,53 @@ int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, i
   items[0].rows = M;
   items[0].out = out;
   return cl.run(items);
+}
+
+int ftb_projection_padded_cols(int V) { return V <= 0 ? 0 : ((V + 127) / 128) * 128; }
+
+int ftb_projection_pack(const void* P, void* Pt, int H, int V, int dtype, void* stream) {
+  if (!P || !Pt || H <= 0 || V <= 0 || (dtype != FTB_F16 && dtype != FTB_BF16)) return FTB_ERR_ARG;
+  if (!aligned16({P, Pt})) return FTB_ERR_ALIGN;
+  return pack_projection(P, Pt, H, V, ftb_projection_padded_cols(V), dtype, static_cast<cudaStream_t>(stream));
+}
+
+int ftb_lstm_project_softmax(const void* h, const void* Pt, float* probs, long long T, int V, int H, int dtype,
+                             void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!h || !Pt || !probs || T <= 0 || T > 0x7fffffffLL || V <= 0 || H <= 0 || H % 64 != 0) return FTB_ERR_ARG;
+  if (dtype != FTB_F16 && dtype != FTB_BF16) return FTB_ERR_ARG;
+  if (V > 48 * 1024) return FTB_ERR_ARG;  // the softmax runs in place on rows that fit its on-chip row cache
+  if (!aligned16({h, Pt, probs})) return FTB_ERR_ALIGN;
+  const int Vp = ftb_projection_padded_cols(V);
+  if (static_cast<int64_t>(T) * Vp > 0x7fffffffffLL) return FTB_ERR_ARG;
+  int* status = nullptr;
+  int rc = begin_call(workspace, workspace_bytes, stream, &status);
+  if (rc) return rc;
+  // 1. logits = h . Pt^T, fp32, written straight into `probs` (row stride Vp)
+  CellLauncher cl;
+  cl.dtype = dtype;
+  cl.epi = EPI_STORE_F32;
+  cl.n_cols = Vp;
+  cl.ld_out = Vp;
+  cl.status = status;
+  cl.stream = stream;
+  cl.sm_count = current_sm_count();
+  cl.bn = (Vp % 256 == 0) ? 256 : 128;
+  cl.pair = 0;
+  rc = make_tmap_2d(&cl.maps[0], h, dtype, static_cast<uint64_t>(T), H, H, 128, 64);
+  if (rc) return rc;
+  cl.maps[1] = cl.maps[2] = cl.maps[3] = cl.maps[0];
+  rc = make_tmap_2d(&cl.mapW, Pt, dtype, Vp, H, H, cl.w_box_rows(), 64);
+  if (rc) return rc;
+  cl.mapC = cl.maps[0];
+  std::vector<CellItem> items(1, blank_item());
+  add_seg(items[0], 0, 0, H, 0);
+  items[0].rows = static_cast<int32_t>(T);
+  items[0].out = probs;
+  rc = cl.run(items);
+  if (rc) return rc;
+  // 2. softmax over the first V logits of every row, in place, one read and one write per logit
+  return online_softmax_rows(probs, probs, static_cast<int>(T), V, Vp, stream);
 }
 
 // ------------------------------------------------------------------------------

@@ -120,6 +120,24 @@ def embed(words, embedding, dtype=None):
     return FractalTensor(out, words.indices, (1, table.shape[1]))
 
 
+def project_softmax(hs, prev_softmax_proj):
+    """The vocabulary projection behind the recurrent layers: softmax(h @ prev_softmax_proj) for every
+    word position (prev_softmax_proj [H, vocab], examples/stacked_rnn/rnn_utils.py:45-50).
+
+    hs: the FractalTensor of [1,H] hidden states a stacked_lstm call returned (any nesting, ragged or
+    not); prev_softmax_proj: [H,V] tensor (or an object with .data).  Returns a FractalTensor with the
+    same nesting whose elements are the [1,V] fp32 probability rows."""
+    P = prev_softmax_proj.data if hasattr(prev_softmax_proj, "data") and not isinstance(prev_softmax_proj, torch.Tensor) \
+        else prev_softmax_proj
+    h = _cuda(hs.data if not isinstance(hs, torch.Tensor) else hs)
+    H = P.shape[0]
+    P = _cuda(P, h.dtype).reshape(H, -1).contiguous()
+    probs = ops.lstm_project_softmax(h.reshape(-1, H).contiguous(), ops.projection_pack(P), P.shape[1])
+    if isinstance(hs, torch.Tensor):
+        return probs
+    return FractalTensor(probs.contiguous(), hs.indices, (1, P.shape[1]))
+
+
 def _is_ragged(x):
     if isinstance(x, torch.Tensor):
         return False

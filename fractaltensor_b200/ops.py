@@ -333,6 +333,38 @@ def online_softmax(x, out=None):
     return out
 
 
+def projection_pack(P):
+    """P: [H,V] (x @ P orientation) -> Pt [Vp,H], one K-major row per vocabulary entry, Vp = V rounded up to 128."""
+    _req(P, "P")
+    if P.dim() != 2 or P.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("projection_pack: expected a 16-bit [H,V] matrix")
+    H, V = P.shape
+    Pt = torch.empty(lib.ftb_projection_padded_cols(V), H, dtype=P.dtype, device=P.device)
+    with torch.cuda.device(P.device):
+        check(lib.ftb_projection_pack(_ptr(P), _ptr(Pt), H, V, _dtype_code(P), _stream()), "ftb_projection_pack")
+    return Pt
+
+
+def lstm_project_softmax(h, Pt, V, out=None):
+    """h: [..., H] hidden states (flattened to [T,H]); Pt from projection_pack; V the vocabulary size
+    -> fp32 probabilities [T,V] = softmax(h . P) per row (a view of a [T,Vp] buffer)."""
+    _req(h, "h")
+    _req(Pt, "Pt", h.dtype)
+    H = h.shape[-1]
+    T = h.numel() // H
+    Vp = lib.ftb_projection_padded_cols(int(V))
+    if tuple(Pt.shape) != (Vp, H) or Pt.device != h.device:
+        raise ValueError("lstm_project_softmax: Pt %s does not match h %s and V=%d" % (tuple(Pt.shape), tuple(h.shape), V))
+    if out is None:
+        out = torch.empty(T, Vp, dtype=torch.float32, device=h.device)
+    _req_like(out, "out", torch.float32, (T, Vp), h)
+    ws = workspace(h.device)
+    with torch.cuda.device(h.device):
+        check(lib.ftb_lstm_project_softmax(_ptr(h), _ptr(Pt), _ptr(out), T, int(V), H, _dtype_code(h), _ptr(ws),
+                                           ws.numel(), _stream()), "ftb_lstm_project_softmax")
+    return out[:, :V]
+
+
 def embedding_gather(table, ids, out=None):
     """table: [V,H]; ids: int64 [T] (any nesting flattened) -> out [T,H] = table[ids]."""
     _req(table, "table")

@@ -229,6 +229,21 @@ int ftb_embedding_gather(const void* table, const long long* ids, void* out, lon
  * elements).  Needs no workspace. */
 int ftb_online_softmax(const float* x, float* y, int rows, int width, void* stream);
 
+/* The projection onto the vocabulary that follows the recurrent layers in the reference's RNN
+ * examples (prev_softmax_proj [H, vocab], examples/stacked_rnn/rnn_utils.py:39-62): for every word
+ * position, probs = softmax(h . P) over the vocabulary.
+ * ftb_projection_pack: P [H,V] (the reference's x @ P orientation) -> Pt [Vp,H] K-major, one row per
+ * vocabulary entry, Vp = ftb_projection_padded_cols(V) = V rounded up to 128, padding rows zero.
+ * ftb_lstm_project_softmax: h [T,H] = the top layer's hidden states in any flat order (the hs[D-1]
+ * of a wavefront entry point as it is); probs (out): fp32 [T,Vp], row t holds softmax(h[t] . P) in its
+ * first V columns (columns V..Vp-1 hold 0).  One tcgen05 GEMM writes the fp32 logits into `probs`
+ * and the online softmax (ftb_online_softmax's kernel, same clamp) normalises them in place: each
+ * logit is written once, read once and written once.  H % 64 == 0; V <= 49152; dtype fp16 or bf16. */
+int ftb_projection_padded_cols(int V);
+int ftb_projection_pack(const void* P, void* Pt, int H, int V, int dtype, void* stream);
+int ftb_lstm_project_softmax(const void* h, const void* Pt, float* probs, long long T, int V, int H, int dtype,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* Plain GEMM out[M,N] = A[M,K] . Bt[N,K]^T through the cell kernel's main loop
  * (support op; the reference's KeCuteGemm, kaleido/core/device/kernels/cutlass_wmma.h:115-181).
  * 16-bit dtypes: K % 64 == 0, N % 128 == 0.  fp32: K % 64 == 0, N % 64 == 0. */

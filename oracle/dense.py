@@ -213,6 +213,14 @@ def online_softmax_dense(x):
     return torch.exp(torch.clamp(x - m, min=-64.0)) / d
 
 
+def project_softmax_dense(h, P):
+    """softmax(h @ P) per row: the vocabulary projection the reference's RNN examples declare behind
+    the recurrent layers (prev_softmax_proj [H, vocab], examples/stacked_rnn/rnn_utils.py:45-50),
+    with the reference frontend's own softmax (ops.softmax = torch.nn.functional.softmax,
+    kaleido/frontend/operations/tensor/arithmetic/reduction.py:24-29).  h: [T,H]; P: [H,V]."""
+    return torch.softmax(h @ P, dim=-1)
+
+
 def embedding_gather_dense(table, ids):
     """One table row per word, in the order of the flat word buffer.
 

@@ -11,6 +11,7 @@ reference's real ``ops.map / scan / fold / reduce / dilated_map / zip / ...``:
   stacked   examples/stacked_rnn/stacked_lstm1.py:13-76
   varlen    examples/stacked_rnn/stacked_rnn.py:40-79 (time-major, length-sorted ragged batch)
   embedding examples/stacked_rnn/rnn_utils.py:80-90 (the word lookup in front of the RNN)
+  projection examples/stacked_rnn/rnn_utils.py:45-50 (prev_softmax_proj behind the RNN: softmax(h @ P))
   dilated   examples/dilated_rnn/dilated_rnn.py:16-41
   grid      examples/grid_rnn/grid_rnn.py:42-122
   attention examples/flash_attention/flash_attention.py:14-88
@@ -202,6 +203,26 @@ def main():
     table, ids, rows = run_embedding(23, 8, lens, 13)
     save("embedding_small", table=table.numpy(), ids=ids.numpy(), lens=np.array(lens), rows=rows.numpy())
     print("embedding", rows.shape)
+
+    # ------------------------------------------------- projection onto the vocabulary
+    def run_projection(H, V, lens, seed):
+        """softmax(h @ prev_softmax_proj) for every word position of a ragged batch of hidden states,
+        with the reference's Tensor @ and ops.softmax; the projection is drawn with torch.rand as
+        create_params() draws it (examples/stacked_rnn/rnn_utils.py:45-50)."""
+        g = torch.Generator().manual_seed(seed)
+        T = sum(lens)
+        h = torch.rand(T, 1, H, generator=g) * 2 - 1
+        proj = Tensor((H, V), kaleido.float32, device="cpu")
+        proj.data = torch.rand(H, V, generator=g)
+        hs = ft(h, (1, H), [list(range(n)) for n in lens])
+        probs = ops.map(lambda seq: ops.map(lambda hv: ops.softmax(hv @ proj, 1), seq), hs)
+        assert [len(i) for i in probs.indices] == lens
+        return h.reshape(T, H), proj.data.clone(), probs.data.view(T, V).clone()
+
+    lens = [3, 5, 1, 4]
+    h, proj, probs = run_projection(64, 200, lens, 17)
+    save("projection_small", h=h.numpy(), proj=proj.numpy(), lens=np.array(lens), probs=probs.numpy())
+    print("projection", probs.shape)
 
     # ---------------------------------------------------------------------- dilated
     def run_dilated(D, L, N, H, seed, w_bound):

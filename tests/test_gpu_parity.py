@@ -932,3 +932,65 @@ def test_one_process_drives_two_devices(ops):
             outs.append([t.cpu() for t in (hs, hs2, o_b2b, o_att, o_sm)])
     for a, b_ in zip(*outs):
         assert torch.equal(a, b_)
+
+
+# ------------------------------------------------- projection onto the vocabulary
+def test_projection_softmax_golden(ops, golden_dir):
+    """The reference frontend's softmax(h @ prev_softmax_proj) on a ragged batch (fixture made with the
+    reference's own Tensor @ and ops.softmax); 16-bit inputs, fp32 accumulation and fp32 softmax."""
+    g = _load(golden_dir, "projection_small.npz")
+    for dt in (torch.float16, torch.bfloat16):
+        h, P = g["h"].to(dt), g["proj"].to(dt)
+        probs = ops.lstm_project_softmax(h.cuda(), ops.projection_pack(P.cuda()), P.shape[1])
+        ops.check_status()
+        ref = dense.project_softmax_dense(h.double(), P.double())
+        assert probs.shape == ref.shape
+        _assert_16(probs, ref)
+        assert (probs.sum(dim=1) - 1).abs().max().item() <= 1e-3
+        # against the fixture itself (fp32 inputs there): the 16-bit rounding of h and P is all that differs
+        _assert_16(probs, g["probs"].double())
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("T,H,V", [(1, 64, 7), (37, 128, 517), (300, 256, 5000), (2560, 1024, 5000), (129, 64, 128),
+                                   (9, 192, 33000)])
+def test_projection_softmax(ops, dt, T, H, V):
+    g = torch.Generator().manual_seed(T + V)
+    h = (torch.rand(T, H, generator=g) * 2 - 1).to(dt)
+    P = (torch.rand(H, V, generator=g) / math.sqrt(H)).to(dt)
+    probs = ops.lstm_project_softmax(h.cuda(), ops.projection_pack(P.cuda()), V)
+    ops.check_status()
+    ref = dense.project_softmax_dense(h.double(), P.double())
+    err = (probs.double().cpu() - ref).abs().max().item()
+    assert err <= TOL16 * ref.max().item() + 1e-6, err   # relative to the largest probability of the matrix
+    assert (probs.sum(dim=1) - 1).abs().max().item() <= 1e-3
+    assert torch.equal(probs.argmax(dim=1).cpu(), ref.argmax(dim=1)) or err <= 1e-4
+
+
+def test_embed_lstm_projection_chain(ops):
+    """The language-model pipeline of the reference's RNN examples end to end through the model-level
+    signatures: word lookup -> stacked LSTM (ragged batch) -> projection onto the vocabulary -> softmax."""
+    from fractaltensor_b200 import frontend
+    D, H, V = 2, 64, 300
+    lens = [5, 2, 7, 3]
+    g = torch.Generator().manual_seed(31)
+    table = torch.randn(V, H, generator=g)
+    W = (torch.rand(D, 4, H, H, generator=g) * 2 - 1) / 8
+    U = (torch.rand(D, 4, H, H, generator=g) * 2 - 1) / 8
+    b = (torch.rand(D, 4, H, generator=g) * 2 - 1) / 8
+    P = torch.rand(H, V, generator=g)
+    ids = [torch.randint(0, V, (n,), generator=g) for n in lens]
+    words = frontend.FractalTensor(torch.cat(ids).cuda(), [list(range(n)) for n in lens], ())
+    ft = lambda t, d: frontend.FractalTensor.from_dense(t.cuda(), d)
+    embs = frontend.embed(words, table.cuda())
+    hs = frontend.stacked_lstm(embs, ft(W, 2), ft(U, 2), ft(b.reshape(D, 4, 1, H), 2))
+    probs = frontend.project_softmax(hs.astype(torch.bfloat16), P.cuda())
+    ops.check_status()
+    assert [len(i) for i in probs.indices] == lens and probs.element_shape == (1, V)
+    flat = probs.data.reshape(-1, V).cpu()
+    pos = 0
+    for n, seq in zip(lens, ids):
+        rhs, _ = dense.stacked_lstm_dense(table[seq][:, None].double(), W.double(), U.double(), b.double())
+        ref = dense.project_softmax_dense(rhs[-1][:, 0], P.double())
+        _assert_16(flat[pos:pos + n], ref)
+        pos += n

@@ -171,3 +171,13 @@ def test_embedding_lookup_matches_reference_frontend(golden_dir):
     g = _load(golden_dir, "embedding_small.npz")
     rows = dense.embedding_gather_dense(g["table"], g["ids"])
     assert torch.equal(rows, g["rows"])
+
+
+def test_projection_softmax_matches_reference_frontend(golden_dir):
+    """softmax(h @ prev_softmax_proj) per word position, as the reference's Tensor @ and ops.softmax
+    compute it on a ragged batch of hidden states."""
+    g = _load(golden_dir, "projection_small.npz")
+    out = dense.project_softmax_dense(g["h"], g["proj"])
+    assert out.shape == g["probs"].shape
+    assert (out - g["probs"]).abs().max().item() <= 1e-6
+    assert (out.sum(dim=1) - 1).abs().max().item() <= 1e-5
