@@ -30,6 +30,7 @@ SIGNATURES = {
     "ftb_lstm_dilated_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_i), _i, _i, _i, _i, _i, ctypes.POINTER(_i), _vp, _sz, _vp]),
     "ftb_grid_pack_weights": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "ftb_grid_rnn_workspace_bytes": (_sz, [_i, _i, _i]),
+    "ftb_grid_rnn_tables_bytes": (_sz, [_i, _i, _i]),
     "ftb_grid_rnn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "ftb_b2b_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "ftb_flash_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp]),

@@ -1,0 +1,833 @@
+// Latency-bound recurrences with small hidden size (H <= 256): the dilated stacked LSTM
+// and the 2-D grid RNN, one thread-block cluster per chain of dependent steps.
+//
+// These programs are chains of small cells: 512 dependent steps of [256 x 512].[512 x 1024]
+// in the first layer of the dilated LSTM, 63 anti-diagonals of [64 x 768].[768 x 256] cells
+// in the grid.  Run as a generic wavefront, every dependent level costs a trip through
+// global memory (store, fence, flag, poll, TMA load: 6-9 us) plus a re-read of the layer's
+// weights from L2.  Here
+//   * the weights never move: a cluster of CL CTAs owns one chain (one layer and batch slice of
+//     the dilated LSTM; one grid row and batch slice of the grid RNN), CTA r of the cluster owns
+//     128 packed weight rows (32 LSTM units x 4 gates, or 128 tanh units) for the whole launch,
+//     and that slice of the weights sits in tensor memory as the A operand of every MMA
+//     ("recurrent weights resident on chip");
+//   * the batch is the N side of the MMA (NB = 128 or 64 columns per slice);
+//   * the state a chain hands to its own next step -- h(t) of a layer with dilation 1, h_y of
+//     the grid cell to the left -- never leaves the cluster: each CTA writes its units into a
+//     staging tile and copies it with one bulk shared-memory-to-shared-memory copy per peer into
+//     the next step's B operand in every CTA of the cluster (distributed shared memory),
+//     completion counted on the receiver's mbarrier.  The receiving layout is the un-swizzled
+//     K-major core-matrix layout, in which one CTA's units are one contiguous block;
+//   * everything that crosses chains (the layer below, the grid row above, a layer's own state
+//     `dilation` >= 2 steps back) goes through global memory with one release flag per
+//     (cell, tile), polled by a whole warp, and TMA loads; those consumers run a few steps behind
+//     their producers, so this latency adds to the pipeline's depth, not to every step.  The
+//     global flag is published by a warp of its own, off the chain.
+// Same arithmetic in the same order as the cell kernels of the generic wavefront (input first,
+// then the recurrent state(s)): the results are bit-identical.
+//
+// Roles: warp 0 producer of the TMA-fed operand blocks, warp 1 MMA issuer (owns TMEM), warp 2
+// flag publisher, warp 3 idle, warps 4..11 epilogue.  tcgen05 cta_group::1; no multicast loads;
+// cooperative cluster launch (a chain waits for flags of other clusters).
+//
+// Programs: dilated_layer()/model() (examples/dilated_rnn/dilated_rnn.py:16-41) in place of
+// DilatedLstmRegion1/2 (kaleido/core/device/kernels/lstm/dilated_lstm/region{1,2}.h), and
+// stacked_grid_rnns() (examples/grid_rnn/grid_rnn.py:42-122) in place of the grid regions
+// (benchmarks/rnn/fractaltensor/grid_lstm/regions/region{1..8}.h).
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace ftb {
+
+namespace {
+
+constexpr int BK = 64;
+constexpr int kEpiWarps = 8;
+constexpr int kFirstEpiWarp = 4;
+constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
+constexpr uint32_t kStageBytes = 16384;
+constexpr int kMaxLayers = 16;
+
+enum ClusterMode : int { kDilated = 0, kGrid = 1 };
+
+#ifdef FTB_TRACE
+// Debug builds: globaltimer stamps of CTA rank 0 of every cluster, [cluster][step][16].
+__device__ unsigned long long* g_cluster_trace = nullptr;
+#define FTB_CL_STAMP(i, s) \
+  if (g_cluster_trace != nullptr && rank == 0) g_cluster_trace[(static_cast<size_t>(cid) * n_steps + (i)) * 16 + (s)] = globaltimer_ns()
+#else
+#define FTB_CL_STAMP(i, s)
+#endif
+
+struct ClusterArgs {
+  int D, L, N, H;  // layers, steps of a chain (dilated: time steps; grid: B), batch, hidden size
+  int A;           // grid: rows of the grid (chains per layer and slice); dilated: 1
+  int S;           // batch slices of NB columns
+  int CL;          // CTAs per cluster
+  int max_dil;
+  int dil[kMaxLayers];
+  const void* W0;       // dilated: Wp [D,4H,2H]; grid: Wpx [D,H,3H]
+  const void* W1;       // grid: Wpy
+  const float* bias0;   // dilated: bias_p [D,4H]; grid: bias_x [D,H]   (or nullptr)
+  const float* bias1;   // grid: bias_y
+  void* out0;           // dilated: hs [D,L,N,H]; grid: hx [D,A,B,N,H]
+  void* out1;           // grid: hy
+  float* c;             // dilated: fp32 [D, max_dil*N, H]
+  int* flags;           // [cells][CL], zero before the launch
+  int* status;
+};
+
+// One TMA-fed operand segment of a step: activation rows `row`.. of tensor map `map`, nkb 64-wide K
+// blocks, multiplied with the weight K blocks wkb0.. of this CTA's tile; flags to wait for first.
+struct Segment {
+  int map, row, nkb, wkb0;
+  const int* flags;  // nullptr: an input of the call
+  int nflags;
+};
+struct StepPlan {
+  int nseg;
+  Segment seg[2];
+  bool self;       // the cluster's own previous output is an operand (through shared memory)
+  int self_wkb0, self_nkb;
+};
+
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Whole-warp bounded wait until the n flags at `flags` are all non-zero (lane i polls flags i, i+32, ...).
+__device__ __forceinline__ bool warp_wait_flags(const int* flags, int n, int lane, volatile int* s_abort, int* g_status) {
+  uint64_t t0 = 0;
+  uint32_t it = 0;
+  for (;;) {
+    bool ready = true;
+    for (int i = lane; i < n; i += 32) ready = ready && (ld_acquire_gpu(flags + i) != 0);
+    if (__all_sync(0xffffffffu, ready)) return true;
+    if (((++it) & 0x3F) == 0) {
+      if (t0 == 0) t0 = globaltimer_ns();
+      const bool give_up = *s_abort != 0 || globaltimer_ns() - t0 > FTB_WAIT_TIMEOUT_NS;
+      if (__any_sync(0xffffffffu, give_up)) {
+        if (lane == 0 && *s_abort == 0) {
+          *s_abort = 1;
+          atomicCAS(g_status, 0, FTB_ERR_TIMEOUT_DEP);
+        }
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, volatile int* s_abort, int* g_status,
+                                                int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  for (;;) {
+    __nanosleep(32);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (((++it) & 0x3F) == 0) {
+      if (*s_abort) return false;
+      if (globaltimer_ns() - t0 > FTB_WAIT_TIMEOUT_NS) {
+        *s_abort = 1;
+        atomicCAS(g_status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+// Shared-memory operand descriptor for an un-swizzled K-major tile: core matrices of 8 rows x 16 B
+// stored contiguously (128 B); `lbo` = bytes between the two 16-byte K chunks of an MMA's K = 16,
+// `sbo` = bytes between consecutive 8-row groups.
+__device__ __forceinline__ uint64_t make_sdesc_plain(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  return d;
+}
+
+// Bulk copy from this CTA's shared memory into a peer's; completion (bytes) counted on the peer's mbarrier.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, uint32_t src_addr, uint32_t bytes,
+                                                  uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   dst_cluster_addr),
+               "r"(src_addr), "r"(bytes), "r"(bar_cluster_addr)
+               : "memory");
+}
+
+// Arrives, once the MMAs issued so far by this thread are done, on the mbarrier at the same
+// shared-memory offset in every CTA of the cluster whose bit is set in `mask`.
+__device__ __forceinline__ void umma_commit_to(uint64_t* bar, uint16_t mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
+
+__device__ __forceinline__ void quad_transpose(float& a0, float& a1, float& a2, float& a3, int lane) {
+  const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
+  float r;
+  r = __shfl_xor_sync(0xffffffffu, b0 ? a0 : a1, 1);
+  if (b0) a0 = r; else a1 = r;
+  r = __shfl_xor_sync(0xffffffffu, b0 ? a2 : a3, 1);
+  if (b0) a2 = r; else a3 = r;
+  r = __shfl_xor_sync(0xffffffffu, b1 ? a0 : a2, 2);
+  if (b1) a0 = r; else a2 = r;
+  r = __shfl_xor_sync(0xffffffffu, b1 ? a1 : a3, 2);
+  if (b1) a1 = r; else a3 = r;
+}
+
+template <typename T>
+__device__ __forceinline__ T to_elem(float v);
+template <>
+__device__ __forceinline__ __half to_elem<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 to_elem<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// What this CTA multiplies at step `i` of its chain.  Every role calls it with the same arguments.
+//   dilated: chain = (layer l, slice s), step = time step t.
+//   grid:    chain = (layer d, row a, slice s), step = column b.
+template <int MODE, int NB>
+__device__ __forceinline__ StepPlan plan_step(const ClusterArgs& a, int layer, int row_a, int slice, int rank, int i) {
+  StepPlan p;
+  p.nseg = 0;
+  p.self = false;
+  p.self_wkb0 = p.self_nkb = 0;
+  const int kbh = a.H / BK;
+  if (MODE == kDilated) {
+    const int d = a.dil[layer];
+    Segment& x = p.seg[p.nseg++];
+    x.nkb = kbh;
+    x.wkb0 = 0;
+    if (layer == 0) {
+      x.map = 0;
+      x.row = i * a.N + slice * NB;
+      x.flags = nullptr;
+      x.nflags = 0;
+    } else {
+      x.map = 1;
+      x.row = ((layer - 1) * a.L + i) * a.N + slice * NB;
+      x.flags = a.flags + (((layer - 1) * a.L + i) * a.S + slice) * a.CL;
+      x.nflags = a.CL;
+    }
+    if (i >= d) {
+      if (d == 1) {
+        p.self = true;
+        p.self_wkb0 = kbh;
+        p.self_nkb = kbh;
+      } else {
+        Segment& h = p.seg[p.nseg++];
+        h.map = 1;
+        h.row = (layer * a.L + i - d) * a.N + slice * NB;
+        h.nkb = kbh;
+        h.wkb0 = kbh;
+        h.flags = a.flags + ((layer * a.L + i - d) * a.S + slice) * a.CL;
+        h.nflags = a.CL;
+      }
+    }
+  } else {
+    // packed K order of a grid cell: [state_x | state_y | input]; issue order: input, state_x, state_y
+    const bool ydir = rank >= a.CL / 2;
+    const int cell = (layer * a.A + row_a) * a.L + i;  // a.L = B
+    Segment& in = p.seg[p.nseg++];
+    in.nkb = kbh;
+    in.wkb0 = 2 * kbh;
+    if (layer == 0) {
+      in.map = ydir ? 1 : 0;
+      in.row = ((row_a * a.L + i) * a.N) + slice * NB;
+      in.flags = nullptr;
+      in.nflags = 0;
+    } else {
+      const int below = ((layer - 1) * a.A + row_a) * a.L + i;
+      in.map = ydir ? 3 : 2;
+      in.row = below * a.N + slice * NB;
+      in.flags = a.flags + (below * a.S + slice) * a.CL + (ydir ? a.CL / 2 : 0);
+      in.nflags = a.CL / 2;
+    }
+    if (row_a > 0) {
+      const int up = (layer * a.A + row_a - 1) * a.L + i;
+      Segment& sx = p.seg[p.nseg++];
+      sx.map = 2;
+      sx.row = up * a.N + slice * NB;
+      sx.nkb = kbh;
+      sx.wkb0 = 0;
+      sx.flags = a.flags + (up * a.S + slice) * a.CL;  // the x-direction tiles come first
+      sx.nflags = a.CL / 2;
+    }
+    if (i > 0) {
+      p.self = true;
+      p.self_wkb0 = kbh;
+      p.self_nkb = kbh;
+    }
+    (void)cell;
+  }
+  return p;
+}
+
+template <typename T, int MODE, int NB>
+__global__ void __launch_bounds__(kThreads, 1)
+rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+                   const __grid_constant__ CUtensorMap map2, const __grid_constant__ CUtensorMap map3,
+                   const ClusterArgs a) {
+  constexpr int kBlocksPerStage = 128 / NB;        // [NB x 64] 16-bit blocks per 16 KB stage
+  constexpr uint32_t kBlockBytes = NB * BK * 2;
+  constexpr int kRing = MODE == kDilated ? 4 : 8;  // stages of the TMA-fed ring when the chain also uses the self slots
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t ring_full[12], ring_empty[12];
+  __shared__ uint64_t self_full[2];   // the slot holds the whole previous output (bytes counted)
+  __shared__ uint64_t self_free[2];   // producers only: every CTA of the cluster has multiplied the slot's contents
+  __shared__ uint64_t stg_ready;      // the eight epilogue warps have written the step's staging tile
+  __shared__ int out_issued;          // epilogue warps that have issued a step's global stores, summed over steps
+  __shared__ uint64_t tfull_bar[2], tempty_bar[2];
+  __shared__ uint64_t res_full;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  int* status = a.status;
+
+  // Which chain this cluster runs.
+  const int cid = blockIdx.x / a.CL;
+  int layer, row_a, slice;
+  if (MODE == kDilated) {
+    layer = cid / a.S;
+    slice = cid - layer * a.S;
+    row_a = 0;
+  } else {
+    slice = cid % a.S;
+    const int ra = cid / a.S;
+    layer = ra / a.A;
+    row_a = ra - layer * a.A;
+  }
+  const int kbh = a.H / BK;
+  const int n_wkb = MODE == kDilated ? 2 * kbh : 3 * kbh;  // K blocks of this CTA's weight tile, all in TMEM
+  const int K = n_wkb * BK;
+  // Does the chain hand its own output to its next step through the cluster's shared memory?
+  const bool self_chain = MODE == kGrid ? true : (a.dil[layer] == 1);
+  // Units of the self operand this CTA produces: dilated: 32 of H; grid: 128 of H, y-direction tiles only.
+  const bool self_producer = self_chain && (MODE == kDilated || rank >= a.CL / 2);
+  const int self_units = MODE == kDilated ? 32 : 128;
+  const int self_first_chunk = (MODE == kDilated ? rank : rank - a.CL / 2) * (self_units / 8);
+  const uint16_t producer_mask = static_cast<uint16_t>(MODE == kDilated ? ((1u << a.CL) - 1u)
+                                                                        : (((1u << a.CL) - 1u) & ~((1u << (a.CL / 2)) - 1u)));
+  const uint32_t self_slot_bytes = static_cast<uint32_t>(a.H / 8) * NB * 16;  // H units x NB rows, 16-bit
+  const uint32_t stage_tile_bytes = static_cast<uint32_t>(self_units / 8) * NB * 16;
+  // Shared memory: [self slot 0][self slot 1][staging 0][staging 1][ring ...] or, for chains without a
+  // self operand, the ring alone (12 stages).
+  uint8_t* s_self = smem;
+  uint8_t* s_stg = s_self + (self_chain ? 2 * self_slot_bytes : 0);
+  uint8_t* s_ring = s_stg + (self_chain ? 2 * stage_tile_bytes : 0);
+  const int n_ring = self_chain ? kRing : 12;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&map0);
+    prefetch_tmap(&map1);
+    prefetch_tmap(&map2);
+    prefetch_tmap(&map3);
+    for (int i = 0; i < 12; ++i) {
+      mbar_init(&ring_full[i], 1);
+      mbar_init(&ring_empty[i], 1);
+    }
+    mbar_init(&self_full[0], 1);
+    mbar_init(&self_full[1], 1);
+    mbar_init(&self_free[0], a.CL);
+    mbar_init(&self_free[1], a.CL);
+    mbar_init(&stg_ready, kEpiWarps);
+    out_issued = 0;
+    mbar_init(&tfull_bar[0], 1);
+    mbar_init(&tfull_bar[1], 1);
+    mbar_init(&tempty_bar[0], kEpiWarps);
+    mbar_init(&tempty_bar[1], kEpiWarps);
+    mbar_init(&res_full, kEpiWarps);
+    s_abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  // Peers copy into this CTA's shared memory and arrive on its barriers: nobody starts before all are set up.
+  cluster_sync_all();
+  const uint32_t tmem_base = tmem_base_s;
+  const uint32_t tmem_w = tmem_base + 2 * NB;  // the weight tile sits behind the two accumulators
+
+  const CUtensorMap* maps[4] = {&map0, &map1, &map2, &map3};
+  const int n_steps = a.L;
+  const int my_flag_cell0 = MODE == kDilated ? (layer * a.L) : ((layer * a.A + row_a) * a.L);
+
+  if (warp == 0) {
+    // ------------------------------------------ producer of the TMA-fed operand blocks
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int i = 0; i < n_steps && ok; ++i) {
+      const StepPlan p = plan_step<MODE, NB>(a, layer, row_a, slice, rank, i);
+      for (int s = 0; s < p.nseg && ok; ++s) {
+        const Segment& sg = p.seg[s];
+        if (sg.flags != nullptr && !warp_wait_flags(sg.flags, sg.nflags, lane, &s_abort, status)) {
+          ok = false;
+          break;
+        }
+        bool fine = true;
+        if (lane == 0) {
+          FTB_CL_STAMP(i, 7 + 2 * s);
+          if (sg.flags != nullptr) fence_proxy_async_all();  // other CTAs' plain stores -> this thread's TMA loads
+          for (int kb0 = 0; kb0 < sg.nkb && fine; kb0 += kBlocksPerStage) {
+            const int nb = min(kBlocksPerStage, sg.nkb - kb0);
+            fine = mbar_wait(&ring_empty[stage], phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT);
+            if (!fine) break;
+            mbar_arrive_expect_tx(&ring_full[stage], nb * kBlockBytes);
+            for (int b = 0; b < nb; ++b)
+              tma_load_2d(s_ring + stage * kStageBytes + b * kBlockBytes, maps[sg.map], &ring_full[stage],
+                          (kb0 + b) * BK, sg.row);
+            if (++stage == n_ring) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          FTB_CL_STAMP(i, 8 + 2 * s);
+        }
+        ok = __all_sync(0xffffffffu, fine);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(128, NB, Fmt<T>::kind, 0, 0);
+      const uint64_t ring_desc0 = make_sdesc_sw128(smem_u32(s_ring), 16, 1024);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = mbar_wait(&res_full, 0, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
+      tc_fence_after();
+      for (int i = 0; i < n_steps && ok; ++i) {
+        const StepPlan p = plan_step<MODE, NB>(a, layer, row_a, slice, rank, i);
+        const int acc = i & 1;
+        ok = mbar_wait(&tempty_bar[acc], ((i >> 1) & 1) ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_EPI);
+        if (!ok) break;
+        tc_fence_after();
+        FTB_CL_STAMP(i, 0);
+        const uint32_t d_tmem = tmem_base + acc * NB;
+        uint32_t accumulate = 0;  // the first MMA of a step overwrites the accumulator
+        for (int s = 0; s < p.nseg && ok; ++s) {
+          const Segment& sg = p.seg[s];
+          for (int kb = 0; kb < sg.nkb; ++kb) {
+            const int ab = kb % kBlocksPerStage;
+            if (ab == 0) {
+              ok = mbar_wait(&ring_full[stage], phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
+              if (!ok) break;
+              if (kb == 0) { FTB_CL_STAMP(i, 12 + s); }
+            }
+            const uint64_t bd = ring_desc0 + static_cast<uint64_t>((stage * kStageBytes + ab * kBlockBytes) >> 4);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) {
+              umma_ts(d_tmem, tmem_w + (sg.wkb0 + kb) * 32 + kk * 8, bd + 2 * kk, idesc, accumulate);
+              accumulate = 1;
+            }
+            if (ab == kBlocksPerStage - 1 || kb == sg.nkb - 1) {
+              umma_commit(&ring_empty[stage]);
+              if (++stage == n_ring) {
+                stage = 0;
+                phase ^= 1u;
+              }
+            }
+          }
+        }
+        if (!ok) break;
+        FTB_CL_STAMP(i, 1);
+        if (p.self) {
+          // The cluster's own output of step i-1, copied by its producers into slot (i-1) & 1 of every CTA.
+          const int slot = (i - 1) & 1;
+          mbar_arrive_expect_tx(&self_full[slot], self_slot_bytes);
+          ok = mbar_wait(&self_full[slot], ((i - 1) >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
+          if (!ok) break;
+          FTB_CL_STAMP(i, 2);
+          const uint32_t sb = smem_u32(s_self + slot * self_slot_bytes);
+          for (int j = 0; j < p.self_nkb * (BK / 16); ++j) {
+            // K = 16 is two 16-byte chunks, NB * 16 bytes apart; 8-row groups are 128 bytes apart
+            const uint64_t bd = make_sdesc_plain(sb + static_cast<uint32_t>(2 * j) * NB * 16, NB * 16, 128);
+            umma_ts(d_tmem, tmem_w + p.self_wkb0 * 32 + j * 8, bd, idesc, accumulate);
+            accumulate = 1;
+          }
+          umma_commit_to(&self_free[slot], producer_mask);
+        }
+        umma_commit(&tfull_bar[acc]);
+        FTB_CL_STAMP(i, 3);
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------------------------------------------------- flag publisher
+    // The epilogue warps count themselves in `out_issued` once their plain stores of a step's outputs are issued;
+    // this thread orders them before one release store per step, off the chain's critical path.
+    // (A running count, not an mbarrier: this thread may fall more than one step behind.)
+    if (lane == 0) {
+      volatile int* issued = &out_issued;
+      for (int i = 0; i < n_steps; ++i) {
+        const int want = kEpiWarps * (i + 1);
+        if (*issued < want) {
+          const uint64_t t0 = globaltimer_ns();
+          uint32_t it = 0;
+          while (*issued < want) {
+            __nanosleep(64);
+            if (((++it) & 0x3F) == 0 && (s_abort || globaltimer_ns() - t0 > FTB_WAIT_TIMEOUT_NS)) break;
+          }
+          if (*issued < want) {
+            if (!s_abort) {
+              s_abort = 1;
+              atomicCAS(status, 0, FTB_ERR_TIMEOUT_EPI);
+            }
+            break;
+          }
+        }
+        __threadfence_block();
+        fence_proxy_async_all();
+        st_release_gpu(a.flags + ((my_flag_cell0 + i) * a.S + slice) * a.CL + rank, 1);
+        FTB_CL_STAMP(i, 11);
+      }
+    }
+  } else if (warp >= kFirstEpiWarp) {
+    // ---------------------------------------------------------------- epilogue
+    constexpr int kCols = NB / 2;  // batch columns per warp
+    constexpr int kChunk = 32;
+    constexpr int kChunks = kCols / kChunk;
+    const int q = warp & 3;
+    const int half = (warp - kFirstEpiWarp) >> 2;
+    const int r_loc = q * 32 + lane;  // row of the 128-row tile = TMEM lane
+    const int et = threadIdx.x - kFirstEpiWarp * 32;
+    // Resident weights -> TMEM: thread r copies its packed weight row, two 16-bit values per 32-bit
+    // column (the layout of an A operand in tensor memory); the two warps of a quadrant alternate K blocks.
+    {
+      const T* wbase;
+      if (MODE == kDilated) {
+        wbase = reinterpret_cast<const T*>(a.W0) + (static_cast<size_t>(layer) * 4 * a.H + rank * 128 + r_loc) * K;
+      } else {
+        const bool ydir = rank >= a.CL / 2;
+        const int tile = ydir ? rank - a.CL / 2 : rank;
+        wbase = reinterpret_cast<const T*>(ydir ? a.W1 : a.W0) + (static_cast<size_t>(layer) * a.H + tile * 128 + r_loc) * K;
+      }
+      const uint4* wrow = reinterpret_cast<const uint4*>(wbase);
+      for (int kb = half; kb < n_wkb; kb += 2) {
+        uint32_t v[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 x4 = __ldg(wrow + kb * 8 + i);
+          v[4 * i + 0] = x4.x; v[4 * i + 1] = x4.y; v[4 * i + 2] = x4.z; v[4 * i + 3] = x4.w;
+        }
+        tmem_st32(tmem_w + (static_cast<uint32_t>(q * 32) << 16) + kb * 32, v);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&res_full);
+    }
+
+    // Per-thread constants of the two epilogues.
+    const int gate = lane & 3;
+    int unit;            // hidden unit this thread produces (dilated: after the quad transpose)
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float bias1 = 0.f;
+    T* out_base;         // + row * H + unit
+    if (MODE == kDilated) {
+      unit = rank * 32 + (r_loc >> 2);
+      if (a.bias0 != nullptr)
+        bias4 = __ldg(reinterpret_cast<const float4*>(a.bias0 + static_cast<size_t>(layer) * 4 * a.H + rank * 128) + (r_loc >> 2));
+      out_base = reinterpret_cast<T*>(a.out0);
+    } else {
+      const bool ydir = rank >= a.CL / 2;
+      const int tile = ydir ? rank - a.CL / 2 : rank;
+      unit = tile * 128 + r_loc;
+      const float* bp = ydir ? a.bias1 : a.bias0;
+      if (bp != nullptr) bias1 = __ldg(bp + static_cast<size_t>(layer) * a.H + unit);
+      out_base = reinterpret_cast<T*>(ydir ? a.out1 : a.out0);
+    }
+    const int dil = MODE == kDilated ? a.dil[layer] : 1;
+    constexpr int kOwn = kCols / 4;
+    float creg[kOwn];
+#pragma unroll
+    for (int i = 0; i < kOwn; ++i) creg[i] = 0.f;
+    const int n_valid = min(NB, a.N - slice * NB);  // batch columns of this slice that exist
+    // Position of unit `u_local` (this CTA's numbering) inside the staging tile / the self operand:
+    // chunk (u_local / 8) of NB rows x 16 bytes, then row n, then the unit's 2 bytes.
+    const int u_local = MODE == kDilated ? (r_loc >> 2) : r_loc;
+    const uint32_t stg_unit_off = static_cast<uint32_t>(u_local >> 3) * NB * 16 + (u_local & 7) * 2;
+
+    bool ok = true;
+    for (int i = 0; i < n_steps && ok; ++i) {
+      const int acc = i & 1;
+      // first output row of this step's cell in its [.., N, H] buffer
+      size_t cell_row;
+      if (MODE == kDilated) cell_row = (static_cast<size_t>(layer) * a.L + i) * a.N + slice * NB;
+      else cell_row = (static_cast<size_t>((layer * a.A + row_a)) * a.L + i) * a.N + slice * NB;
+      // cell state of a layer with dilation > 1 lives in global memory between the steps that share it
+      float* c_rows = nullptr;
+      if (MODE == kDilated && dil > 1)
+        c_rows = a.c + (static_cast<size_t>(layer) * a.max_dil + (i % dil)) * a.N * a.H + static_cast<size_t>(slice) * NB * a.H;
+      if (MODE == kDilated && dil > 1 && i >= dil) {
+#pragma unroll
+        for (int ci = 0; ci < kOwn; ++ci) {
+          const int n = half * kCols + (ci / (kChunk / 4)) * kChunk + 4 * (ci % (kChunk / 4)) + gate;
+          creg[ci] = n < n_valid ? __ldcg(c_rows + static_cast<size_t>(n) * a.H + unit) : 0.f;
+        }
+      } else if (MODE == kDilated && dil > 1) {
+#pragma unroll
+        for (int ci = 0; ci < kOwn; ++ci) creg[ci] = 0.f;
+      }
+      {
+        bool mine = true;
+        if (lane == 0) mine = mbar_wait_sleep(&tfull_bar[acc], (i >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA);
+        if (!__all_sync(0xffffffffu, mine)) {
+          ok = false;
+          break;
+        }
+      }
+      tc_fence_after();
+      if (warp == kFirstEpiWarp && lane == 0) { FTB_CL_STAMP(i, 4); }
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * NB + half * kCols;
+      uint8_t* stg = s_stg + (i & 1) * stage_tile_bytes + stg_unit_off;
+#pragma unroll
+      for (int ch = 0; ch < kChunks; ++ch) {
+        float v[kChunk];
+        {
+          uint32_t r[kChunk];
+          tmem_ld32(taddr + ch * kChunk, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < kChunk; ++k) v[k] = __uint_as_float(r[k]);
+        }
+        if (MODE == kDilated) {
+#pragma unroll
+          for (int kq = 0; kq < kChunk / 4; ++kq) {
+            quad_transpose(v[4 * kq], v[4 * kq + 1], v[4 * kq + 2], v[4 * kq + 3], lane);
+            const float gi = v[4 * kq + 0] + bias4.x;
+            const float gf = v[4 * kq + 1] + bias4.y;
+            const float go = v[4 * kq + 2] + bias4.z;
+            const float gc = v[4 * kq + 3] + bias4.w;
+            const int ci = ch * (kChunk / 4) + kq;
+            const float c_new = sigmoid_fast(gf) * creg[ci] + sigmoid_fast(gi) * tanh_fast(gc);
+            creg[ci] = c_new;
+            const T h_new = to_elem<T>(sigmoid_fast(go) * tanh_fast(c_new));
+            const int n = half * kCols + ch * kChunk + 4 * kq + gate;
+            if (n < n_valid) out_base[(cell_row + n) * a.H + unit] = h_new;
+            if (self_producer) *reinterpret_cast<T*>(stg + n * 16) = h_new;
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < kChunk; ++k) {
+            const T h_new = to_elem<T>(tanh_fast(v[k] + bias1));
+            const int n = half * kCols + ch * kChunk + k;
+            if (n < n_valid) out_base[(cell_row + n) * a.H + unit] = h_new;
+            if (self_producer) *reinterpret_cast<T*>(stg + n * 16) = h_new;
+          }
+        }
+      }
+      if (MODE == kDilated && (dil > 1 || i == n_steps - 1)) {
+        float* c_out = dil > 1 ? c_rows : a.c + static_cast<size_t>(layer) * a.max_dil * a.N * a.H + static_cast<size_t>(slice) * NB * a.H;
+#pragma unroll
+        for (int ci = 0; ci < kOwn; ++ci) {
+          const int n = half * kCols + (ci / (kChunk / 4)) * kChunk + 4 * (ci % (kChunk / 4)) + gate;
+          if (n < n_valid) c_out[static_cast<size_t>(n) * a.H + unit] = creg[ci];
+        }
+      }
+      if (warp == kFirstEpiWarp && lane == 0) { FTB_CL_STAMP(i, 5); }
+      tc_fence_before();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (self_producer && i + 1 < n_steps) {
+        // Hand the step's output to the cluster: staging tile complete -> one bulk copy per peer, once
+        // every CTA has multiplied what the destination slot held before (two steps ago).
+        fence_proxy_async_smem();  // plain shared-memory stores -> the bulk copy's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&stg_ready);
+        if (et < a.CL) {
+          bool go = mbar_wait(&stg_ready, i & 1, &s_abort, status, FTB_ERR_TIMEOUT_EPI);
+          if (go && i >= 2) go = mbar_wait(&self_free[i & 1], ((i - 2) >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_EPI);
+          if (go) {
+            const uint32_t src = smem_u32(s_stg + (i & 1) * stage_tile_bytes);
+            const uint32_t dst =
+                smem_u32(s_self + (i & 1) * self_slot_bytes) + static_cast<uint32_t>(self_first_chunk) * NB * 16;
+            bulk_copy_to_peer(map_to_cta(dst, et), src, stage_tile_bytes, map_to_cta(smem_u32(&self_full[i & 1]), et));
+            if (et == 0) { FTB_CL_STAMP(i, 6); }
+          }
+        }
+      }
+      // the step's global outputs are issued: let the publisher release the flag
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        atomicAdd(&out_issued, 1);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  // No CTA of the cluster may leave while a peer can still copy into it or signal its barriers.
+  cluster_sync_all();
+  if (warp == 1) {
+    if (s_abort) {
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename T, int MODE, int NB>
+int launch(const CUtensorMap* m, const ClusterArgs& a, int grid, uint32_t smem_bytes, cudaStream_t stream) {
+  static std::atomic<unsigned long long> configured{0};
+  auto kfn = rnn_cluster_kernel<T, MODE, NB>;
+  // the largest request of this instantiation (static shared memory comes on top of it)
+  constexpr int kMaxDynamic = 226 * 1024;
+  if (smem_bytes > static_cast<uint32_t>(kMaxDynamic) || !ensure_dynamic_smem(kfn, kMaxDynamic, configured))
+    return FTB_ERR_LAUNCH;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  attrs[na].id = cudaLaunchAttributeClusterDimension;
+  attrs[na].val.clusterDim.x = a.CL;
+  attrs[na].val.clusterDim.y = 1;
+  attrs[na].val.clusterDim.z = 1;
+  ++na;
+  // FTB_NO_COOPERATIVE=1 drops the cooperative attribute (profilers that cannot replay cooperative
+  // launches); residency then rests on the grid fitting an otherwise idle device, and the bounded
+  // waits turn a violated assumption into a status code.
+  static const bool no_coop = [] {
+    const char* e = getenv("FTB_NO_COOPERATIVE");
+    return e != nullptr && e[0] == '1';
+  }();
+  // FTB_REFUSE_COOPERATIVE=1 answers as if the driver had refused the launch (host-side failure
+  // injection for the tests of the fallback to the generic wavefront).
+  {
+    const char* e = getenv("FTB_REFUSE_COOPERATIVE");
+    if (e != nullptr && e[0] == '1') return FTB_ERR_LAUNCH;
+  }
+  if (!no_coop) {
+    attrs[na].id = cudaLaunchAttributeCooperative;
+    attrs[na].val.cooperative = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kfn, m[0], m[1], m[2], m[3], a);
+  if (err != cudaSuccess) {
+    if (getenv("FTB_VERBOSE") != nullptr) fprintf(stderr, "rnn_cluster launch: %s\n", cudaGetErrorString(err));
+    cudaGetLastError();
+    return FTB_ERR_LAUNCH;
+  }
+  count_launch();
+  return FTB_OK;
+}
+
+uint32_t smem_for(bool any_self, int H, int NB, int self_units, int ring_self) {
+  // worst case over the chains of the launch
+  uint32_t with_self = 2u * (H / 8) * NB * 16 + 2u * (self_units / 8) * NB * 16 + ring_self * kStageBytes;
+  uint32_t without = 12u * kStageBytes;
+  return (any_self ? std::max(with_self, without) : without) + 1024;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ dilated LSTM
+constexpr int kDilatedNB = 128;
+
+bool lstm_dilated_cluster_supported(int dtype, int D, int N, int H, int sm_count) {
+  if (dtype != FTB_F16 && dtype != FTB_BF16) return false;
+  if (H != 64 && H != 128 && H != 256) return false;  // 4H / 128 = 2, 4 or 8 CTAs per cluster
+  if (D < 1 || D > kMaxLayers || N < 1) return false;
+  const int S = (N + kDilatedNB - 1) / kDilatedNB;
+  return S <= 8 && D * S * (4 * H / 128) <= sm_count;
+}
+
+size_t lstm_dilated_cluster_flag_ints(int D, int L) { return static_cast<size_t>(D) * L * 8 * 8; }
+
+// x: [L,N,H]; Wp: [D,4H,2H]; hs: [D,L,N,H]; c: [D, max_dil*N, H]; flags: D*L*S*CL ints (zeroed here).
+int launch_lstm_dilated_cluster(int dtype, const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
+                                const int* dilations, int D, int L, int N, int H, int* flags, int* status,
+                                cudaStream_t stream) {
+  ClusterArgs a = {};
+  a.D = D; a.L = L; a.N = N; a.H = H; a.A = 1;
+  a.S = (N + kDilatedNB - 1) / kDilatedNB;
+  a.CL = 4 * H / 128;
+  a.max_dil = 1;
+  bool any_self = false;
+  for (int l = 0; l < D; ++l) {
+    a.dil[l] = dilations[l];
+    a.max_dil = std::max(a.max_dil, dilations[l]);
+    any_self = any_self || dilations[l] == 1;
+  }
+  a.W0 = Wp; a.bias0 = bias_p; a.out0 = hs; a.c = c; a.flags = flags; a.status = status;
+  CUtensorMap m[4];
+  int rc;
+  if ((rc = make_tmap_2d(&m[0], x, dtype, static_cast<uint64_t>(L) * N, H, H, kDilatedNB, 64))) return rc;
+  if ((rc = make_tmap_2d(&m[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, kDilatedNB, 64))) return rc;
+  m[2] = m[1];
+  m[3] = m[1];
+  const size_t n_flags = static_cast<size_t>(D) * L * a.S * a.CL;
+  if (cudaMemsetAsync(flags, 0, sizeof(int) * n_flags, stream) != cudaSuccess) return FTB_ERR_LAUNCH;
+  const int grid = D * a.S * a.CL;
+  const uint32_t smem = smem_for(any_self, H, kDilatedNB, 32, 4);
+  if (dtype == FTB_F16) return launch<__half, kDilated, kDilatedNB>(m, a, grid, smem, stream);
+  return launch<__nv_bfloat16, kDilated, kDilatedNB>(m, a, grid, smem, stream);
+}
+
+// --------------------------------------------------------------------- grid RNN
+constexpr int kGridNB = 64;
+
+bool grid_rnn_cluster_supported(int dtype, int D, int A, int B, int N, int H, int sm_count) {
+  if (dtype != FTB_F16 && dtype != FTB_BF16) return false;
+  if (H != 128 && H != 256) return false;  // 2 * H / 128 = 2 or 4 CTAs per cluster; 3H/64 K blocks fit TMEM
+  if (D < 1 || A < 1 || B < 1 || N < 1) return false;
+  const int S = (N + kGridNB - 1) / kGridNB;
+  return D * A * S * (2 * H / 128) <= sm_count;
+}
+
+// X,Y: [A,B,N,H]; Wpx,Wpy: [D,H,3H]; hx,hy: [D,A,B,N,H]; flags: D*A*B*S*CL ints (zeroed here).
+int launch_grid_rnn_cluster(int dtype, const void* X, const void* Y, const void* Wpx, const void* Wpy,
+                            const float* bias_x, const float* bias_y, void* hx, void* hy, int D, int A, int B, int N,
+                            int H, int* flags, int* status, cudaStream_t stream) {
+  ClusterArgs a = {};
+  a.D = D; a.L = B; a.N = N; a.H = H; a.A = A;
+  a.S = (N + kGridNB - 1) / kGridNB;
+  a.CL = 2 * H / 128;
+  a.max_dil = 1;
+  a.W0 = Wpx; a.W1 = Wpy; a.bias0 = bias_x; a.bias1 = bias_y; a.out0 = hx; a.out1 = hy; a.flags = flags; a.status = status;
+  CUtensorMap m[4];
+  int rc;
+  const uint64_t grid_rows = static_cast<uint64_t>(A) * B * N;
+  if ((rc = make_tmap_2d(&m[0], X, dtype, grid_rows, H, H, kGridNB, 64))) return rc;
+  if ((rc = make_tmap_2d(&m[1], Y, dtype, grid_rows, H, H, kGridNB, 64))) return rc;
+  if ((rc = make_tmap_2d(&m[2], hx, dtype, grid_rows * D, H, H, kGridNB, 64))) return rc;
+  if ((rc = make_tmap_2d(&m[3], hy, dtype, grid_rows * D, H, H, kGridNB, 64))) return rc;
+  const size_t n_flags = static_cast<size_t>(D) * A * B * a.S * a.CL;
+  if (cudaMemsetAsync(flags, 0, sizeof(int) * n_flags, stream) != cudaSuccess) return FTB_ERR_LAUNCH;
+  const int grid = D * A * a.S * a.CL;
+  const uint32_t smem = smem_for(true, H, kGridNB, 128, 8);
+  if (dtype == FTB_F16) return launch<__half, kGrid, kGridNB>(m, a, grid, smem, stream);
+  return launch<__nv_bfloat16, kGrid, kGridNB>(m, a, grid, smem, stream);
+}
+
+}  // namespace ftb
+
+#ifdef FTB_TRACE
+extern "C" int ftb_debug_set_cluster_trace(unsigned long long* buf) {
+  return cudaMemcpyToSymbol(ftb::g_cluster_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 1;
+}
+#endif
+

@@ -35,6 +35,15 @@ bool lstm_wmajor_supported(int dtype, int D, int N, int I, int H, int G, int sm_
 int launch_lstm_wmajor(int dtype, const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
                        int N, int I, int H, int G, int resident, int* done, int* status, unsigned long long* trace,
                        cudaStream_t stream);
+bool lstm_dilated_cluster_supported(int dtype, int D, int N, int H, int sm_count);
+size_t lstm_dilated_cluster_flag_ints(int D, int L);
+int launch_lstm_dilated_cluster(int dtype, const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
+                                const int* dilations, int D, int L, int N, int H, int* flags, int* status,
+                                cudaStream_t stream);
+bool grid_rnn_cluster_supported(int dtype, int D, int A, int B, int N, int H, int sm_count);
+int launch_grid_rnn_cluster(int dtype, const void* X, const void* Y, const void* Wpx, const void* Wpy,
+                            const float* bias_x, const float* bias_y, void* hx, void* hy, int D, int A, int B, int N,
+                            int H, int* flags, int* status, cudaStream_t stream);
 int launch_cell_simt(int epi, const float* const* act, const int* ld_act, const float* const* w, int ldw,
                      const CellBatch& batch, cudaStream_t stream);
 int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* bias_p, int D, int I, int H, int dtype,
@@ -814,6 +823,24 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
     if (rc) return rc;
   }
 
+  // Cluster schedule (schedule 4, and the automatic choice when it applies): one thread-block
+  // cluster per (layer, batch slice), weights resident in tensor memory, the state of a layer with
+  // dilation 1 handed on through the cluster's shared memory.  Its flags sit behind the tables of
+  // the generic persistent schedule in the workspace.
+  {
+    const size_t flags_off = plan_layout(D * L, 0).total;
+    const size_t need = flags_off + sizeof(int) * lstm_dilated_cluster_flag_ints(D, L);
+    const bool can = lstm_dilated_cluster_supported(dtype, D, N, H, cl.sm_count) && tune.pair == 0 && bn == 0;
+    if (tune.schedule == 4 && (!can || workspace_bytes < need)) return can ? FTB_ERR_WORKSPACE : FTB_ERR_ARG;
+    if ((tune.schedule == 4 || tune.schedule == 0) && can && workspace_bytes >= need) {
+      rc = launch_lstm_dilated_cluster(dtype, x, Wp, bias_p, hs, c, dilations, D, L, N, H,
+                                       reinterpret_cast<int*>(static_cast<char*>(workspace) + flags_off), status,
+                                       stream);
+      // a refused cooperative cluster launch falls back to the generic wavefront
+      if (rc != FTB_ERR_LAUNCH || tune.schedule != 0) return rc;
+    }
+  }
+
   // Layer l advances in steps of dilations[l] consecutive timesteps: those
   // timesteps only depend on the step before (same layer) and on the layer
   // below, so one step is one cell of batch dilation*N.  Earliest-start levels.
@@ -900,7 +927,8 @@ int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, voi
 
 size_t ftb_lstm_dilated_workspace_bytes(int D, int L) {
   if (D <= 0 || L <= 0) return kWorkspaceBytes;
-  return plan_layout(D * L, 0).total;
+  // tables of the generic persistent schedule, then the flags of the cluster schedule
+  return plan_layout(D * L, 0).total + sizeof(int) * lstm_dilated_cluster_flag_ints(D, L);
 }
 
 int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* Wpy, const float* bias_x,
@@ -992,6 +1020,15 @@ int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* 
   const int n_items = 2 * D * A * B;
   const int levels = (D - 1) + (A - 1) + (B - 1) + 1;
   const PlanLayout lay = plan_layout(n_items, 0);
+  // Cluster schedule (the choice when it applies and the workspace has room for its flags behind the
+  // tables): one thread-block cluster per grid row and batch slice, weights resident in tensor
+  // memory, h_y handed to the next column through the cluster's shared memory.
+  if (grid_rnn_cluster_supported(dtype, D, A, B, N, H, cl.sm_count) &&
+      workspace_bytes >= ftb_grid_rnn_workspace_bytes(D, A, B)) {
+    rc = launch_grid_rnn_cluster(dtype, X, Y, Wpx, Wpy, bias_x, bias_y, hx, hy, D, A, B, N, H,
+                                 reinterpret_cast<int*>(static_cast<char*>(workspace) + lay.total), status, stream);
+    if (rc != FTB_ERR_LAUNCH) return rc;  // a refused cooperative cluster launch falls back to the generic wavefront
+  }
   const bool persistent = dtype != FTB_F32 && workspace_bytes >= lay.total;
   if (persistent) {
     // One cooperative launch for the whole grid: items in level order, each K segment waiting
@@ -1041,9 +1078,17 @@ int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* 
   return FTB_OK;
 }
 
-size_t ftb_grid_rnn_workspace_bytes(int D, int A, int B) {
+size_t ftb_grid_rnn_tables_bytes(int D, int A, int B) {
   if (D <= 0 || A <= 0 || B <= 0) return kWorkspaceBytes;
   return plan_layout(2 * D * A * B, 0).total;
+}
+
+size_t ftb_grid_rnn_workspace_bytes(int D, int A, int B) {
+  if (D <= 0 || A <= 0 || B <= 0) return kWorkspaceBytes;
+  // tables of the generic persistent schedule, then the flags of the cluster schedule: one per cell,
+  // batch slice and CTA of a cluster; clusters x CTAs never exceed the SM count (taken as <= 256)
+  const size_t per_column = std::max<size_t>(static_cast<size_t>(D) * A * 4, 256);
+  return plan_layout(2 * D * A * B, 0).total + sizeof(int) * per_column * B;
 }
 
 int ftb_gemm_nt(const void* A, const void* Bt, void* out, int M, int N, int K, int dtype, const int* tuning,

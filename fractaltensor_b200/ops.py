@@ -177,7 +177,9 @@ def lstm_stacked_varlen(x, active_rows, Wp, bias_p=None, hs=None, c=None, layers
 
 
 def lstm_dilated(x, Wp, dilations, bias_p=None, hs=None, c=None, bn=0, pair=0, schedule=0):
-    """x: [L,N,H]; Wp: [D,4H,2H]; dilations: D ints -> (hs [D,L,N,H], c fp32 [D,max_dil*N,H])."""
+    """x: [L,N,H]; Wp: [D,4H,2H]; dilations: D ints -> (hs [D,L,N,H], c fp32 [D,max_dil*N,H]).
+    schedule: 0 auto, 1 one launch per level, 2 generic persistent kernel, 4 cluster kernel (H of 64, 128
+    or 256: weights resident in tensor memory, one thread-block cluster per layer and batch slice)."""
     _req(x, "x")
     _req(Wp, "Wp", x.dtype)
     L, N, H = x.shape
@@ -220,7 +222,8 @@ def grid_pack_weights(i2h, h2h):
 
 def grid_rnn(X, Y, Wpx, Wpy, bias_x=None, bias_y=None, schedule=0):
     """X,Y: [A,B,N,H]; Wpx,Wpy: [D,H,3H]; bias fp32 [D,H] -> (hx, hy) each [D,A,B,N,H].
-    schedule: 0 auto (one persistent kernel for 16-bit inputs), 1 one launch per anti-diagonal."""
+    schedule: 0 auto (16-bit inputs: the cluster kernel where it applies, else the generic persistent
+    kernel), 1 one launch per anti-diagonal, 2 the generic persistent kernel."""
     _req(X, "X")
     _req(Y, "Y", X.dtype)
     _req(Wpx, "Wpx", X.dtype)
@@ -234,9 +237,10 @@ def grid_rnn(X, Y, Wpx, Wpy, bias_x=None, bias_y=None, schedule=0):
             _req_like(b, "bias", torch.float32, (D, H), X)
     hx = torch.empty(D, A, B, N, H, dtype=X.dtype, device=X.device)
     hy = torch.empty_like(hx)
-    # The library picks the persistent schedule when the workspace has room for its tables.
+    # The library picks the schedule by the room the workspace offers: status word only -> one launch
+    # per level; the tables -> generic persistent kernel; tables and flags -> cluster kernel.
     ws = workspace(X.device, 0 if schedule == 1 else lib.ftb_grid_rnn_workspace_bytes(D, A, B))
-    ws_bytes = lib.ftb_workspace_bytes() if schedule == 1 else ws.numel()
+    ws_bytes = {1: lib.ftb_workspace_bytes(), 2: lib.ftb_grid_rnn_tables_bytes(D, A, B)}.get(schedule, ws.numel())
     with torch.cuda.device(X.device):
         check(lib.ftb_grid_rnn_fwd(_ptr(X), _ptr(Y), _ptr(Wpx), _ptr(Wpy), _ptr(bias_x), _ptr(bias_y), _ptr(hx),
                                    _ptr(hy), D, A, B, N, H, _dtype_code(X), _ptr(ws), ws_bytes, _stream()),

@@ -138,8 +138,13 @@ int ftb_lstm_stacked_varlen_fwd(const void* x, const void* Wp, const float* bias
  * and DilatedLstmRegion1/2 (kaleido/core/device/kernels/lstm/dilated_lstm/region{1,2}.h).
  * x: [L,N,H]; hs (out): [D,L,N,H]; c (scratch/out): fp32 [D, max_dilation*N, H].
  * `dilations` is a HOST array of D ints.  With ftb_lstm_dilated_workspace_bytes(D, L) bytes of
- * workspace (16-bit dtypes) the whole wavefront runs as one persistent launch; its schedule
- * tables are copied from host memory on `stream`, so that form is not for stream capture. */
+ * workspace (16-bit dtypes) the whole forward pass is one launch.  For H of 64, 128 or 256 that is the
+ * cluster schedule (tuning[2] = 4, and the automatic choice): one thread-block cluster per layer and
+ * slice of 128 sequences, each CTA's slice of the weights resident in tensor memory for the whole
+ * launch, the state of a layer with dilation 1 handed to its next step through the cluster's
+ * shared memory.  Otherwise (or with tuning[2] = 2) it is the generic persistent wavefront, whose
+ * schedule tables are copied from host memory on `stream`, so that form is not for stream capture.
+ * All schedules give the same bits. */
 size_t ftb_lstm_dilated_workspace_bytes(int D, int L);
 int ftb_lstm_dilated_fwd(const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
                          const int* dilations, int D, int L, int N, int H, int dtype, const int* tuning,
@@ -158,9 +163,16 @@ int ftb_grid_pack_weights(const void* i2h, const void* h2h, void* Wp, int H, int
  * Wpx,Wpy: [D,H,3H] from ftb_grid_pack_weights; bias_x,bias_y: fp32 [D,H] or NULL;
  * hx,hy (out): [D,A,B,N,H].  state_x = hx[a-1][b], state_y = hy[a][b-1].
  * Both directions of a level run in one launch.  With ftb_grid_rnn_workspace_bytes(D, A, B)
- * bytes of workspace (16-bit dtypes) the whole grid runs as one persistent launch whose
- * schedule tables are copied from host memory on `stream`; with less, one launch per level. */
+ * bytes of workspace (16-bit dtypes) the whole grid runs as one launch: for H of 128 or 256 and
+ * D*A*ceil(N/64)*(H/64) <= the SM count, the cluster schedule (one thread-block cluster per grid
+ * row and slice of 64 sequences walks the columns; weights resident in tensor memory; h_y handed to
+ * the next column through the cluster's shared memory; h_x of the row above through global flags);
+ * otherwise, or with a workspace of at least ftb_grid_rnn_tables_bytes(D, A, B) but less than
+ * ftb_grid_rnn_workspace_bytes(D, A, B) bytes, the generic persistent wavefront, whose schedule
+ * tables are copied from host memory on `stream`; with less than that, one launch per level.
+ * All schedules give the same bits. */
 size_t ftb_grid_rnn_workspace_bytes(int D, int A, int B);
+size_t ftb_grid_rnn_tables_bytes(int D, int A, int B);
 int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* Wpy, const float* bias_x,
                      const float* bias_y, void* hx, void* hy, int D, int A, int B, int N, int H, int dtype,
                      void* workspace, size_t workspace_bytes, void* stream);
