@@ -27,7 +27,8 @@
 // then the recurrent state(s)): the results are bit-identical.
 //
 // Roles: warp 0 producer of the TMA-fed operand blocks, warp 1 MMA issuer (owns TMEM), warp 2
-// flag publisher, warp 3 idle, warps 4..11 epilogue.  tcgen05 cta_group::1; no multicast loads;
+// output store and flag publisher, warp 3 idle, warps 4.. epilogue (16 for the LSTM cell, 8 for the
+// tanh cell).  tcgen05 cta_group::1; no multicast loads;
 // cooperative cluster launch (a chain waits for flags of other clusters).
 //
 // Programs: dilated_layer()/model() (examples/dilated_rnn/dilated_rnn.py:16-41) in place of
@@ -46,9 +47,11 @@ namespace ftb {
 namespace {
 
 constexpr int BK = 64;
-constexpr int kEpiWarps = 8;
 constexpr int kFirstEpiWarp = 4;
-constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
+// Epilogue warps: four per TMEM lane quadrant for the LSTM cell (five MUFU operations and a quad
+// transpose per element: latency-bound with fewer), two for the tanh cell.
+__host__ __device__ constexpr int epi_warps(int mode) { return mode == 0 ? 16 : 8; }
+__host__ __device__ constexpr int cta_threads(int mode) { return 32 * (kFirstEpiWarp + epi_warps(mode)); }
 constexpr uint32_t kStageBytes = 16384;
 constexpr int kMaxLayers = 16;
 
@@ -271,20 +274,30 @@ __device__ __forceinline__ StepPlan plan_step(const ClusterArgs& a, int layer, i
   return p;
 }
 
+// map0..map3: activation inputs (boxes of NB rows x 64 columns, 128-byte swizzle).  mapO0/mapO1:
+// outputs (dilated: hs; grid: hx, hy) as un-swizzled boxes of NB rows x this CTA's units; mapT0/mapT1:
+// the same with the row count of the last, partial batch slice.
 template <typename T, int MODE, int NB>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(cta_threads(MODE), 1)
 rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                    const __grid_constant__ CUtensorMap map2, const __grid_constant__ CUtensorMap map3,
+                   const __grid_constant__ CUtensorMap mapO0, const __grid_constant__ CUtensorMap mapO1,
+                   const __grid_constant__ CUtensorMap mapT0, const __grid_constant__ CUtensorMap mapT1,
                    const ClusterArgs a) {
+  constexpr int kEpiWarps = epi_warps(MODE);
+  constexpr int kSub = kEpiWarps / 4;              // epilogue warps per TMEM lane quadrant
   constexpr int kBlocksPerStage = 128 / NB;        // [NB x 64] 16-bit blocks per 16 KB stage
   constexpr uint32_t kBlockBytes = NB * BK * 2;
-  constexpr int kRing = MODE == kDilated ? 4 : 8;  // stages of the TMA-fed ring when the chain also uses the self slots
+  constexpr int kRing = MODE == kDilated ? 4 : 6;  // stages of the TMA-fed ring when the chain also uses the self slots
+  constexpr int kOutUnits = MODE == kDilated ? 32 : 128;                   // units this CTA produces
+  constexpr uint32_t kOutTileBytes = static_cast<uint32_t>(NB) * kOutUnits * 2;  // row-major [NB][units] staging
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t ring_full[12], ring_empty[12];
+  __shared__ uint64_t ring_full[12], ring_empty[12];  // up to 12 ring stages
   __shared__ uint64_t self_full[2];   // the slot holds the whole previous output (bytes counted)
   __shared__ uint64_t self_free[2];   // producers only: every CTA of the cluster has multiplied the slot's contents
   __shared__ uint64_t stg_ready;      // the eight epilogue warps have written the step's staging tile
-  __shared__ int out_issued;          // epilogue warps that have issued a step's global stores, summed over steps
+  __shared__ int out_issued;          // epilogue warps that have staged a step's outputs, summed over steps
+  __shared__ int out_stored;          // steps whose output staging tile the publisher has finished reading
   __shared__ uint64_t tfull_bar[2], tempty_bar[2];
   __shared__ uint64_t res_full;
   __shared__ uint32_t tmem_base_s;
@@ -322,11 +335,12 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
                                                                         : (((1u << a.CL) - 1u) & ~((1u << (a.CL / 2)) - 1u)));
   const uint32_t self_slot_bytes = static_cast<uint32_t>(a.H / 8) * NB * 16;  // H units x NB rows, 16-bit
   const uint32_t stage_tile_bytes = static_cast<uint32_t>(self_units / 8) * NB * 16;
-  // Shared memory: [self slot 0][self slot 1][staging 0][staging 1][ring ...] or, for chains without a
-  // self operand, the ring alone (12 stages).
+  // Shared memory: [self slot 0][self slot 1][staging 0][staging 1][output tile 0][output tile 1][ring ...];
+  // chains without a self operand have the output tiles and a longer ring only.
   uint8_t* s_self = smem;
   uint8_t* s_stg = s_self + (self_chain ? 2 * self_slot_bytes : 0);
-  uint8_t* s_ring = s_stg + (self_chain ? 2 * stage_tile_bytes : 0);
+  uint8_t* s_out = s_stg + (self_chain ? 2 * stage_tile_bytes : 0);  // two row-major output tiles for the TMA stores
+  uint8_t* s_ring = s_out + 2 * kOutTileBytes;
   const int n_ring = self_chain ? kRing : 12;
 
   if (threadIdx.x == 0) {
@@ -334,6 +348,10 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
     prefetch_tmap(&map1);
     prefetch_tmap(&map2);
     prefetch_tmap(&map3);
+    prefetch_tmap(&mapO0);
+    prefetch_tmap(&mapO1);
+    prefetch_tmap(&mapT0);
+    prefetch_tmap(&mapT1);
     for (int i = 0; i < 12; ++i) {
       mbar_init(&ring_full[i], 1);
       mbar_init(&ring_empty[i], 1);
@@ -344,6 +362,7 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
     mbar_init(&self_free[1], a.CL);
     mbar_init(&stg_ready, kEpiWarps);
     out_issued = 0;
+    out_stored = 0;
     mbar_init(&tfull_bar[0], 1);
     mbar_init(&tfull_bar[1], 1);
     mbar_init(&tempty_bar[0], kEpiWarps);
@@ -383,8 +402,9 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
         }
         bool fine = true;
         if (lane == 0) {
+          // (Producers write their outputs with TMA stores and consumers read them with TMA loads: both
+          // sides are in the async proxy, so the flag's release/acquire is all the ordering there is.)
           FTB_CL_STAMP(i, 7 + 2 * s);
-          if (sg.flags != nullptr) fence_proxy_async_all();  // other CTAs' plain stores -> this thread's TMA loads
           for (int kb0 = 0; kb0 < sg.nkb && fine; kb0 += kBlocksPerStage) {
             const int nb = min(kBlocksPerStage, sg.nkb - kb0);
             fine = mbar_wait(&ring_empty[stage], phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT);
@@ -468,12 +488,18 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
       }
     }
   } else if (warp == 2) {
-    // ---------------------------------------------------------- flag publisher
-    // The epilogue warps count themselves in `out_issued` once their plain stores of a step's outputs are issued;
-    // this thread orders them before one release store per step, off the chain's critical path.
+    // ------------------------------------------------ output store and flag publisher
+    // The epilogue warps count themselves in `out_issued` once their part of a step's output tile is
+    // staged in shared memory; this thread writes the tile to global memory with one TMA store, waits
+    // for it to complete and releases the step's flag -- all of it off the chain's critical path.
     // (A running count, not an mbarrier: this thread may fall more than one step behind.)
     if (lane == 0) {
       volatile int* issued = &out_issued;
+      volatile int* stored = &out_stored;
+      const int n_valid = min(NB, a.N - slice * NB);
+      const bool ydir = MODE == kGrid && rank >= a.CL / 2;
+      const CUtensorMap* om = n_valid == NB ? (ydir ? &mapO1 : &mapO0) : (ydir ? &mapT1 : &mapT0);
+      const int unit0 = MODE == kDilated ? rank * 32 : (ydir ? rank - a.CL / 2 : rank) * 128;
       for (int i = 0; i < n_steps; ++i) {
         const int want = kEpiWarps * (i + 1);
         if (*issued < want) {
@@ -492,22 +518,25 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
           }
         }
         __threadfence_block();
-        fence_proxy_async_all();
+        const int cell_row = (MODE == kDilated ? (layer * a.L + i) : ((layer * a.A + row_a) * a.L + i)) * a.N + slice * NB;
+        tma_store_2d(om, s_out + (i & 1) * kOutTileBytes, unit0, cell_row);
+        tma_store_commit();
+        tma_store_wait_read<0>();
+        *stored = i + 1;  // the tile may be overwritten (two steps from now)
+        tma_store_wait<0>();
         st_release_gpu(a.flags + ((my_flag_cell0 + i) * a.S + slice) * a.CL + rank, 1);
         FTB_CL_STAMP(i, 11);
       }
     }
   } else if (warp >= kFirstEpiWarp) {
     // ---------------------------------------------------------------- epilogue
-    constexpr int kCols = NB / 2;  // batch columns per warp
-    constexpr int kChunk = 32;
-    constexpr int kChunks = kCols / kChunk;
+    constexpr int kCols = NB / kSub;  // batch columns per warp (32 in both modes)
+    static_assert(kCols == 32, "an epilogue warp takes 32 accumulator columns");
     const int q = warp & 3;
-    const int half = (warp - kFirstEpiWarp) >> 2;
+    const int sub = (warp - kFirstEpiWarp) >> 2;
     const int r_loc = q * 32 + lane;  // row of the 128-row tile = TMEM lane
-    const int et = threadIdx.x - kFirstEpiWarp * 32;
     // Resident weights -> TMEM: thread r copies its packed weight row, two 16-bit values per 32-bit
-    // column (the layout of an A operand in tensor memory); the two warps of a quadrant alternate K blocks.
+    // column (the layout of an A operand in tensor memory); the warps of a quadrant alternate K blocks.
     {
       const T* wbase;
       if (MODE == kDilated) {
@@ -518,7 +547,7 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
         wbase = reinterpret_cast<const T*>(ydir ? a.W1 : a.W0) + (static_cast<size_t>(layer) * a.H + tile * 128 + r_loc) * K;
       }
       const uint4* wrow = reinterpret_cast<const uint4*>(wbase);
-      for (int kb = half; kb < n_wkb; kb += 2) {
+      for (int kb = sub; kb < n_wkb; kb += kSub) {
         uint32_t v[32];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -535,41 +564,37 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
 
     // Per-thread constants of the two epilogues.
     const int gate = lane & 3;
-    int unit;            // hidden unit this thread produces (dilated: after the quad transpose)
+    int unit;        // hidden unit this thread produces (dilated: after the quad transpose)
+    int u_local;     // the same, counted inside this CTA's tile
     float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
     float bias1 = 0.f;
-    T* out_base;         // + row * H + unit
     if (MODE == kDilated) {
-      unit = rank * 32 + (r_loc >> 2);
+      u_local = r_loc >> 2;
+      unit = rank * 32 + u_local;
       if (a.bias0 != nullptr)
-        bias4 = __ldg(reinterpret_cast<const float4*>(a.bias0 + static_cast<size_t>(layer) * 4 * a.H + rank * 128) + (r_loc >> 2));
-      out_base = reinterpret_cast<T*>(a.out0);
+        bias4 = __ldg(reinterpret_cast<const float4*>(a.bias0 + static_cast<size_t>(layer) * 4 * a.H + rank * 128) + u_local);
     } else {
       const bool ydir = rank >= a.CL / 2;
-      const int tile = ydir ? rank - a.CL / 2 : rank;
-      unit = tile * 128 + r_loc;
+      u_local = r_loc;
+      unit = (ydir ? rank - a.CL / 2 : rank) * 128 + r_loc;
       const float* bp = ydir ? a.bias1 : a.bias0;
       if (bp != nullptr) bias1 = __ldg(bp + static_cast<size_t>(layer) * a.H + unit);
-      out_base = reinterpret_cast<T*>(ydir ? a.out1 : a.out0);
     }
     const int dil = MODE == kDilated ? a.dil[layer] : 1;
-    constexpr int kOwn = kCols / 4;
+    constexpr int kOwn = kCols / 4;  // LSTM: (unit, batch column) elements per thread
     float creg[kOwn];
 #pragma unroll
     for (int i = 0; i < kOwn; ++i) creg[i] = 0.f;
     const int n_valid = min(NB, a.N - slice * NB);  // batch columns of this slice that exist
-    // Position of unit `u_local` (this CTA's numbering) inside the staging tile / the self operand:
-    // chunk (u_local / 8) of NB rows x 16 bytes, then row n, then the unit's 2 bytes.
-    const int u_local = MODE == kDilated ? (r_loc >> 2) : r_loc;
+    // Where this thread's unit sits (a) in the self operand / its staging tile: 16-byte chunk
+    // (u_local / 8) of NB rows, then row n, then the unit's 2 bytes; (b) in the row-major output tile.
     const uint32_t stg_unit_off = static_cast<uint32_t>(u_local >> 3) * NB * 16 + (u_local & 7) * 2;
+    const uint32_t out_unit_off = static_cast<uint32_t>(u_local) * 2;
+    volatile int* stored = &out_stored;
 
     bool ok = true;
     for (int i = 0; i < n_steps && ok; ++i) {
       const int acc = i & 1;
-      // first output row of this step's cell in its [.., N, H] buffer
-      size_t cell_row;
-      if (MODE == kDilated) cell_row = (static_cast<size_t>(layer) * a.L + i) * a.N + slice * NB;
-      else cell_row = (static_cast<size_t>((layer * a.A + row_a)) * a.L + i) * a.N + slice * NB;
       // cell state of a layer with dilation > 1 lives in global memory between the steps that share it
       float* c_rows = nullptr;
       if (MODE == kDilated && dil > 1)
@@ -577,7 +602,7 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
       if (MODE == kDilated && dil > 1 && i >= dil) {
 #pragma unroll
         for (int ci = 0; ci < kOwn; ++ci) {
-          const int n = half * kCols + (ci / (kChunk / 4)) * kChunk + 4 * (ci % (kChunk / 4)) + gate;
+          const int n = sub * kCols + 4 * ci + gate;
           creg[ci] = n < n_valid ? __ldcg(c_rows + static_cast<size_t>(n) * a.H + unit) : 0.f;
         }
       } else if (MODE == kDilated && dil > 1) {
@@ -585,8 +610,17 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
         for (int ci = 0; ci < kOwn; ++ci) creg[ci] = 0.f;
       }
       {
+        // one polling lane per warp, sleeping between polls; the others wait at the warp vote
         bool mine = true;
-        if (lane == 0) mine = mbar_wait_sleep(&tfull_bar[acc], (i >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA);
+        if (lane == 0) {
+          mine = mbar_wait_sleep(&tfull_bar[acc], (i >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA);
+          // the output tile of two steps ago must have left shared memory
+          if (mine && *stored < i - 1) {
+            const uint64_t t0 = globaltimer_ns();
+            while (*stored < i - 1 && !s_abort && globaltimer_ns() - t0 < FTB_WAIT_TIMEOUT_NS) __nanosleep(64);
+            mine = *stored >= i - 1;
+          }
+        }
         if (!__all_sync(0xffffffffu, mine)) {
           ok = false;
           break;
@@ -594,74 +628,86 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
       }
       tc_fence_after();
       if (warp == kFirstEpiWarp && lane == 0) { FTB_CL_STAMP(i, 4); }
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * NB + half * kCols;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * NB + sub * kCols;
       uint8_t* stg = s_stg + (i & 1) * stage_tile_bytes + stg_unit_off;
+      uint8_t* outp = s_out + (i & 1) * kOutTileBytes + out_unit_off;
+      float v[kCols];
+      {
+        uint32_t r[kCols];
+        tmem_ld32(taddr, r);
+        tmem_ld_wait();
 #pragma unroll
-      for (int ch = 0; ch < kChunks; ++ch) {
-        float v[kChunk];
-        {
-          uint32_t r[kChunk];
-          tmem_ld32(taddr + ch * kChunk, r);
-          tmem_ld_wait();
+        for (int k = 0; k < kCols; ++k) v[k] = __uint_as_float(r[k]);
+      }
+      // the accumulator is in registers: the MMA issuer may reuse it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (MODE == kDilated) {
 #pragma unroll
-          for (int k = 0; k < kChunk; ++k) v[k] = __uint_as_float(r[k]);
+        for (int kq = 0; kq < kCols / 4; ++kq) {
+          quad_transpose(v[4 * kq], v[4 * kq + 1], v[4 * kq + 2], v[4 * kq + 3], lane);
+          const float gi = v[4 * kq + 0] + bias4.x;
+          const float gf = v[4 * kq + 1] + bias4.y;
+          const float go = v[4 * kq + 2] + bias4.z;
+          const float gc = v[4 * kq + 3] + bias4.w;
+          const float c_new = sigmoid_fast(gf) * creg[kq] + sigmoid_fast(gi) * tanh_fast(gc);
+          creg[kq] = c_new;
+          const T h_new = to_elem<T>(sigmoid_fast(go) * tanh_fast(c_new));
+          const int n = sub * kCols + 4 * kq + gate;
+          *reinterpret_cast<T*>(outp + n * (kOutUnits * 2)) = h_new;
+          if (self_producer) *reinterpret_cast<T*>(stg + n * 16) = h_new;
         }
-        if (MODE == kDilated) {
+      } else {
 #pragma unroll
-          for (int kq = 0; kq < kChunk / 4; ++kq) {
-            quad_transpose(v[4 * kq], v[4 * kq + 1], v[4 * kq + 2], v[4 * kq + 3], lane);
-            const float gi = v[4 * kq + 0] + bias4.x;
-            const float gf = v[4 * kq + 1] + bias4.y;
-            const float go = v[4 * kq + 2] + bias4.z;
-            const float gc = v[4 * kq + 3] + bias4.w;
-            const int ci = ch * (kChunk / 4) + kq;
-            const float c_new = sigmoid_fast(gf) * creg[ci] + sigmoid_fast(gi) * tanh_fast(gc);
-            creg[ci] = c_new;
-            const T h_new = to_elem<T>(sigmoid_fast(go) * tanh_fast(c_new));
-            const int n = half * kCols + ch * kChunk + 4 * kq + gate;
-            if (n < n_valid) out_base[(cell_row + n) * a.H + unit] = h_new;
-            if (self_producer) *reinterpret_cast<T*>(stg + n * 16) = h_new;
-          }
-        } else {
-#pragma unroll
-          for (int k = 0; k < kChunk; ++k) {
-            const T h_new = to_elem<T>(tanh_fast(v[k] + bias1));
-            const int n = half * kCols + ch * kChunk + k;
-            if (n < n_valid) out_base[(cell_row + n) * a.H + unit] = h_new;
-            if (self_producer) *reinterpret_cast<T*>(stg + n * 16) = h_new;
-          }
+        for (int k = 0; k < kCols; ++k) {
+          const T h_new = to_elem<T>(tanh_fast(v[k] + bias1));
+          const int n = sub * kCols + k;
+          *reinterpret_cast<T*>(outp + n * (kOutUnits * 2)) = h_new;
+          if (self_producer) *reinterpret_cast<T*>(stg + n * 16) = h_new;
         }
       }
       if (MODE == kDilated && (dil > 1 || i == n_steps - 1)) {
         float* c_out = dil > 1 ? c_rows : a.c + static_cast<size_t>(layer) * a.max_dil * a.N * a.H + static_cast<size_t>(slice) * NB * a.H;
 #pragma unroll
         for (int ci = 0; ci < kOwn; ++ci) {
-          const int n = half * kCols + (ci / (kChunk / 4)) * kChunk + 4 * (ci % (kChunk / 4)) + gate;
+          const int n = sub * kCols + 4 * ci + gate;
           if (n < n_valid) c_out[static_cast<size_t>(n) * a.H + unit] = creg[ci];
         }
       }
       if (warp == kFirstEpiWarp && lane == 0) { FTB_CL_STAMP(i, 5); }
-      tc_fence_before();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      fence_proxy_async_smem();  // plain shared-memory stores -> the bulk copies' and the TMA store's reads
+      __syncwarp();
+      if (warp == kFirstEpiWarp && lane == 0) { FTB_CL_STAMP(i, 14); }
       if (self_producer && i + 1 < n_steps) {
-        // Hand the step's output to the cluster: staging tile complete -> one bulk copy per peer, once
-        // every CTA has multiplied what the destination slot held before (two steps ago).
-        fence_proxy_async_smem();  // plain shared-memory stores -> the bulk copy's reads
-        __syncwarp();
+        // Hand the step's output to every CTA of the cluster, once all of them have multiplied what the
+        // destination slot held before (two steps ago).
+        // Once all epilogue warps have staged their parts, the tile goes to every CTA of the cluster by
+        // bulk copies issued side by side by different warps.  (Measured: the SM's copy engine moves
+        // about 64 KB in 1.3-2 us however the tile is cut -- 128 copies of 512 B, 32 of 2 KB or 8 of
+        // 8 KB -- so the hand-off is bound by the bytes every CTA must receive, not by the slicing.)
         if (lane == 0) mbar_arrive(&stg_ready);
-        if (et < a.CL) {
+        const uint32_t kPiece = MODE == kGrid ? stage_tile_bytes : 2048u;
+        const int n_pieces = static_cast<int>(stage_tile_bytes / kPiece);
+        const int n_copies = n_pieces * a.CL;
+        const int per_warp = (n_copies + kEpiWarps - 1) / kEpiWarps;
+        const int ci = (warp - kFirstEpiWarp) * per_warp + lane;
+        if (lane < per_warp && ci < n_copies) {
           bool go = mbar_wait(&stg_ready, i & 1, &s_abort, status, FTB_ERR_TIMEOUT_EPI);
+          if (warp == kFirstEpiWarp && lane == 0) { FTB_CL_STAMP(i, 15); }
           if (go && i >= 2) go = mbar_wait(&self_free[i & 1], ((i - 2) >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_EPI);
           if (go) {
-            const uint32_t src = smem_u32(s_stg + (i & 1) * stage_tile_bytes);
-            const uint32_t dst =
-                smem_u32(s_self + (i & 1) * self_slot_bytes) + static_cast<uint32_t>(self_first_chunk) * NB * 16;
-            bulk_copy_to_peer(map_to_cta(dst, et), src, stage_tile_bytes, map_to_cta(smem_u32(&self_full[i & 1]), et));
-            if (et == 0) { FTB_CL_STAMP(i, 6); }
+            const int peer = ci / n_pieces;
+            const uint32_t off = static_cast<uint32_t>(ci - peer * n_pieces) * kPiece;
+            const uint32_t src = smem_u32(s_stg + (i & 1) * stage_tile_bytes) + off;
+            const uint32_t dst = smem_u32(s_self + (i & 1) * self_slot_bytes) +
+                                 static_cast<uint32_t>(self_first_chunk) * NB * 16 + off;
+            bulk_copy_to_peer(map_to_cta(dst, peer), src, kPiece, map_to_cta(smem_u32(&self_full[i & 1]), peer));
+            if (warp == kFirstEpiWarp && lane == 0) { FTB_CL_STAMP(i, 6); }
           }
         }
       }
-      // the step's global outputs are issued: let the publisher release the flag
+      // this warp's part of the output tile is staged: count it in for the publisher
       __syncwarp();
       if (lane == 0) {
         __threadfence_block();
@@ -695,7 +741,7 @@ int launch(const CUtensorMap* m, const ClusterArgs& a, int grid, uint32_t smem_b
     return FTB_ERR_LAUNCH;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(cta_threads(MODE));
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
@@ -725,7 +771,7 @@ int launch(const CUtensorMap* m, const ClusterArgs& a, int grid, uint32_t smem_b
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, kfn, m[0], m[1], m[2], m[3], a);
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kfn, m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], a);
   if (err != cudaSuccess) {
     if (getenv("FTB_VERBOSE") != nullptr) fprintf(stderr, "rnn_cluster launch: %s\n", cudaGetErrorString(err));
     cudaGetLastError();
@@ -735,10 +781,11 @@ int launch(const CUtensorMap* m, const ClusterArgs& a, int grid, uint32_t smem_b
   return FTB_OK;
 }
 
-uint32_t smem_for(bool any_self, int H, int NB, int self_units, int ring_self) {
-  // worst case over the chains of the launch
-  uint32_t with_self = 2u * (H / 8) * NB * 16 + 2u * (self_units / 8) * NB * 16 + ring_self * kStageBytes;
-  uint32_t without = 12u * kStageBytes;
+uint32_t smem_for(bool any_self, int H, int NB, int self_units, int out_units, int ring_self) {
+  // worst case over the chains of the launch; must agree with the kernel's carve-up
+  const uint32_t out_tiles = 2u * NB * out_units * 2;
+  const uint32_t with_self = 2u * (H / 8) * NB * 16 + 2u * (self_units / 8) * NB * 16 + out_tiles + ring_self * kStageBytes;
+  const uint32_t without = out_tiles + 12u * kStageBytes;
   return (any_self ? std::max(with_self, without) : without) + 1024;
 }
 
@@ -773,16 +820,22 @@ int launch_lstm_dilated_cluster(int dtype, const void* x, const void* Wp, const 
     any_self = any_self || dilations[l] == 1;
   }
   a.W0 = Wp; a.bias0 = bias_p; a.out0 = hs; a.c = c; a.flags = flags; a.status = status;
-  CUtensorMap m[4];
+  CUtensorMap m[8];
   int rc;
   if ((rc = make_tmap_2d(&m[0], x, dtype, static_cast<uint64_t>(L) * N, H, H, kDilatedNB, 64))) return rc;
   if ((rc = make_tmap_2d(&m[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, kDilatedNB, 64))) return rc;
   m[2] = m[1];
   m[3] = m[1];
+  // output boxes: NB (or the last slice's) rows x the 32 units of a CTA, un-swizzled
+  const int tail = N - (a.S - 1) * kDilatedNB;
+  if ((rc = make_tmap_2d(&m[4], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, kDilatedNB, 32, false))) return rc;
+  if ((rc = make_tmap_2d(&m[6], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, tail, 32, false))) return rc;
+  m[5] = m[4];
+  m[7] = m[6];
   const size_t n_flags = static_cast<size_t>(D) * L * a.S * a.CL;
   if (cudaMemsetAsync(flags, 0, sizeof(int) * n_flags, stream) != cudaSuccess) return FTB_ERR_LAUNCH;
   const int grid = D * a.S * a.CL;
-  const uint32_t smem = smem_for(any_self, H, kDilatedNB, 32, 4);
+  const uint32_t smem = smem_for(any_self, H, kDilatedNB, 32, 32, 4);
   if (dtype == FTB_F16) return launch<__half, kDilated, kDilatedNB>(m, a, grid, smem, stream);
   return launch<__nv_bfloat16, kDilated, kDilatedNB>(m, a, grid, smem, stream);
 }
@@ -808,17 +861,23 @@ int launch_grid_rnn_cluster(int dtype, const void* X, const void* Y, const void*
   a.CL = 2 * H / 128;
   a.max_dil = 1;
   a.W0 = Wpx; a.W1 = Wpy; a.bias0 = bias_x; a.bias1 = bias_y; a.out0 = hx; a.out1 = hy; a.flags = flags; a.status = status;
-  CUtensorMap m[4];
+  CUtensorMap m[8];
   int rc;
   const uint64_t grid_rows = static_cast<uint64_t>(A) * B * N;
   if ((rc = make_tmap_2d(&m[0], X, dtype, grid_rows, H, H, kGridNB, 64))) return rc;
   if ((rc = make_tmap_2d(&m[1], Y, dtype, grid_rows, H, H, kGridNB, 64))) return rc;
   if ((rc = make_tmap_2d(&m[2], hx, dtype, grid_rows * D, H, H, kGridNB, 64))) return rc;
   if ((rc = make_tmap_2d(&m[3], hy, dtype, grid_rows * D, H, H, kGridNB, 64))) return rc;
+  // output boxes: NB (or the last slice's) rows x the 128 units of a CTA, un-swizzled
+  const int tail = N - (a.S - 1) * kGridNB;
+  if ((rc = make_tmap_2d(&m[4], hx, dtype, grid_rows * D, H, H, kGridNB, 128, false))) return rc;
+  if ((rc = make_tmap_2d(&m[5], hy, dtype, grid_rows * D, H, H, kGridNB, 128, false))) return rc;
+  if ((rc = make_tmap_2d(&m[6], hx, dtype, grid_rows * D, H, H, tail, 128, false))) return rc;
+  if ((rc = make_tmap_2d(&m[7], hy, dtype, grid_rows * D, H, H, tail, 128, false))) return rc;
   const size_t n_flags = static_cast<size_t>(D) * A * B * a.S * a.CL;
   if (cudaMemsetAsync(flags, 0, sizeof(int) * n_flags, stream) != cudaSuccess) return FTB_ERR_LAUNCH;
   const int grid = D * A * a.S * a.CL;
-  const uint32_t smem = smem_for(true, H, kGridNB, 128, 8);
+  const uint32_t smem = smem_for(true, H, kGridNB, 128, 128, 6);
   if (dtype == FTB_F16) return launch<__half, kGrid, kGridNB>(m, a, grid, smem, stream);
   return launch<__nv_bfloat16, kGrid, kGridNB>(m, a, grid, smem, stream);
 }

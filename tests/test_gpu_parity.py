@@ -482,7 +482,7 @@ def test_grid_schedules_agree_bit_for_bit(ops, shape):
     n0 = _lib.lib.ftb_launch_count()
     hx1, hy1 = _run_grid(ops, X, Y, p, schedule=1)
     n1 = _lib.lib.ftb_launch_count()
-    hx2, hy2 = _run_grid(ops, X, Y, p)
+    hx2, hy2 = _run_grid(ops, X, Y, p, schedule=2)
     n2 = _lib.lib.ftb_launch_count()
     assert torch.equal(hx1, hx2) and torch.equal(hy1, hy2)
     # both runs pack the weights (two launches); levels: one launch each; persistent: one in all
@@ -994,3 +994,76 @@ def test_embed_lstm_projection_chain(ops):
         ref = dense.project_softmax_dense(rhs[-1][:, 0], P.double())
         _assert_16(flat[pos:pos + n], ref)
         pos += n
+
+
+# ------------------------------------- cluster kernels of the dilated LSTM and the grid RNN
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("case", [
+    (1, 3, 32, 256, [1]), (1, 9, 128, 256, [1]), (2, 8, 128, 256, [1, 2]), (3, 19, 200, 256, [1, 2, 4]),
+    (3, 7, 32, 64, [2, 2, 3]), (4, 24, 256, 128, [1, 2, 4, 8]), (2, 5, 1, 128, [1, 1]), (3, 40, 300, 256, [4, 1, 2]),
+])
+def test_dilated_cluster_schedule(ops, dt, case):
+    """The cluster kernel (weights in tensor memory, the state of dilation-1 layers through the cluster's
+    shared memory, everything else through global flags): the same bits as one launch per level, for
+    batches that fill, underfill and overflow the 128-sequence slices, and it is the automatic choice."""
+    D, L, N, H, dils = case
+    x, W, U, b = dense.make_lstm_inputs(D, L, N, H, H, 4, 1.0 / 8, dtype=dt, bias=True)
+    xd, Wd, Ud, bd = _dev(x, W, U, b)
+    Wp, bp = ops.lstm_pack_weights(Wd, Ud, bd)
+    ref, ref_c = ops.lstm_dilated(xd, Wp, dils, bp, schedule=1)
+    ops.check_status()
+    for kw in ({"schedule": 4}, {}, {"schedule": 2}):
+        hs, c = ops.lstm_dilated(xd, Wp, dils, bp, **kw)
+        ops.check_status()
+        assert torch.equal(hs, ref), kw
+        for l, d in enumerate(dils):  # layer l keeps one cell state per interleaved sub-sequence: d * N rows
+            assert torch.equal(c[l, :d * N], ref_c[l, :d * N]), (kw, l)
+    _assert_16(ref, dense.dilated_lstm_dense(*_f32(x, W, U), dils, b.double()))
+
+
+def test_dilated_cluster_schedule_needs_its_shapes(ops):
+    x, W, U, b = dense.make_lstm_inputs(2, 4, 32, 192, 192, 4, 1.0 / 8, dtype=torch.float16, bias=True)
+    xd, Wd, Ud, bd = _dev(x, W, U, b)
+    Wp, bp = ops.lstm_pack_weights(Wd, Ud, bd)
+    with pytest.raises(RuntimeError):
+        ops.lstm_dilated(xd, Wp, [1, 2], bp, schedule=4)   # H = 192 is not 64, 128 or 256
+    hs, _ = ops.lstm_dilated(xd, Wp, [1, 2], bp)            # the automatic choice falls back to the generic wavefront
+    ops.check_status()
+    _assert_16(hs, dense.dilated_lstm_dense(*_f32(x, W, U), [1, 2], b.double()))
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 1, 4, 64, 256), (1, 3, 4, 16, 256), (2, 3, 4, 64, 128), (1, 9, 7, 64, 256),
+                                   (1, 5, 6, 100, 256), (1, 32, 2, 3, 256), (3, 2, 5, 64, 128)])
+def test_grid_cluster_schedule(ops, dt, shape):
+    """The cluster kernel of the grid RNN (one cluster per grid row and batch slice; h_y to the next column
+    through the cluster's shared memory, h_x of the row above through global flags): the same bits as
+    one launch per anti-diagonal and as the generic persistent kernel."""
+    D, A, B, N, H = shape
+    X, Y, p = dense.make_grid_inputs(D, A, B, N, H, 6, 1.0 / 8, dtype=dt, bias=True)
+    hx1, hy1 = _run_grid(ops, X, Y, p, schedule=1)
+    hx2, hy2 = _run_grid(ops, X, Y, p, schedule=2)
+    hx0, hy0 = _run_grid(ops, X, Y, p)
+    assert torch.equal(hx1, hx2) and torch.equal(hy1, hy2)
+    assert torch.equal(hx1, hx0) and torch.equal(hy1, hy0)
+    rx, ry = _grid_ref(X, Y, p)
+    _assert_16(hx0, rx)
+    _assert_16(hy0, ry)
+
+
+def test_cluster_kernels_launch_once(ops):
+    """One kernel launch for the whole forward pass (plus the clearing of the flags, a memset)."""
+    from fractaltensor_b200 import _lib
+    x, W, U, _ = dense.make_lstm_inputs(3, 16, 128, 256, 256, 4, 1.0 / 8, dtype=torch.float16)
+    Wp, _ = ops.lstm_pack_weights(W.cuda(), U.cuda())
+    xd = x.cuda()
+    n0 = _lib.lib.ftb_launch_count()
+    ops.lstm_dilated(xd, Wp, [1, 2, 4], schedule=4)
+    assert _lib.lib.ftb_launch_count() - n0 == 1
+    X, Y, p = dense.make_grid_inputs(1, 6, 6, 64, 256, 6, 1.0 / 8, dtype=torch.float16)
+    Wpx = ops.grid_pack_weights(p["i2h_x"].cuda(), p["h2h_x"].cuda())
+    Wpy = ops.grid_pack_weights(p["i2h_y"].cuda(), p["h2h_y"].cuda())
+    n0 = _lib.lib.ftb_launch_count()
+    ops.grid_rnn(X.cuda(), Y.cuda(), Wpx, Wpy)
+    ops.check_status()
+    assert _lib.lib.ftb_launch_count() - n0 == 1
