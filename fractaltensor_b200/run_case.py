@@ -1,6 +1,9 @@
 """Runs one operator of the hot path once (or a few times) on seeded synthetic inputs.
 
     python -m fractaltensor_b200.run_case lstm --D 16 --L 20 --N 256 --H 1024 --dtype bf16 --iters 2
+    python -m fractaltensor_b200.run_case lstm --D 16 --L 20 --N 32 --H 1024      # a batch shard: the small-batch kernel
+    python -m fractaltensor_b200.run_case dilated --D 6 --L 128 --N 256 --H 256 --dtype fp16
+    python -m fractaltensor_b200.run_case grid --D 1 --A 32 --N 64 --H 256 --dtype fp16
     python -m fractaltensor_b200.run_case varlen --D 16 --L 100 --N 256 --H 1024 --min-len 20
     python -m fractaltensor_b200.run_case b2b --batch 16 --M 16384
     python -m fractaltensor_b200.run_case attn --B 4 --heads 16 --S 2048
@@ -38,6 +41,7 @@ def main():
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--schedule", type=int, default=0)
     ap.add_argument("--pair", type=int, default=0)
+    ap.add_argument("--resident", type=int, default=0, help="lstm, small-batch kernel: recurrent weight blocks kept in TMEM")
     ap.add_argument("--min-len", type=int, default=1, help="varlen: lengths are uniform in [min-len, L]")
     ap.add_argument("--causal", action="store_true", help="attn: keys 0..i for query i")
     ap.add_argument("--window", type=int, default=None, help="attn with --causal: keys i-window+1..i")
@@ -56,7 +60,7 @@ def main():
         hs = torch.empty(a.D, a.L, a.N, a.H, dtype=dt, device=dev)
         c = torch.empty(a.D, a.N, a.H, device=dev)
         fn = lambda: ops.lstm_stacked(x, Wp, None, hs, c, layers_per_group=a.layers_per_group, bn=a.bn,
-                                      schedule=a.schedule, pair=a.pair)
+                                      schedule=a.schedule, pair=a.pair, resident=a.resident)
     elif a.case == "varlen":
         lens = torch.randint(a.min_len, a.L + 1, (a.N,), generator=torch.Generator().manual_seed(0))
         lens[0] = a.L
@@ -73,7 +77,7 @@ def main():
         x = rnd(a.L, a.N, a.H).to(dt)
         Wp, _ = ops.lstm_pack_weights(uni(1 / 16, a.D, 4, a.H, a.H).to(dt), uni(1 / 16, a.D, 4, a.H, a.H).to(dt))
         dil = [2 ** l for l in range(a.D)]
-        fn = lambda: ops.lstm_dilated(x, Wp, dil, bn=a.bn)
+        fn = lambda: ops.lstm_dilated(x, Wp, dil, bn=a.bn, schedule=a.schedule)
     elif a.case == "grid":
         X, Y = rnd(a.A, a.A, a.N, a.H).to(dt), rnd(a.A, a.A, a.N, a.H).to(dt)
         Wpx = ops.grid_pack_weights(uni(1 / 16, a.D, 2 * a.H, a.H).to(dt), uni(1 / 16, a.D, a.H, a.H).to(dt))
