@@ -177,6 +177,14 @@ def cpu_other_configs(threads):
     dt = time.perf_counter() - t0
     out["5b"] = {"value": 32 * 32 * 64 / dt, "unit": "cells*samples/s", "cores": threads, "kind": "port",
                  "sample": "the whole configuration, fp32 (%.2f s)" % dt}
+    # sparse attention: 2 of the 32 (batch, head) pairs at sequence 4096
+    q, k, v = (torch.rand(1, 2, 4096, 64, generator=g) for _ in range(3))
+    pos = torch.randint(0, 4096, (1, 2, 4090, 3), generator=g, dtype=torch.int32)
+    t0 = time.perf_counter()
+    dense.sparse_attention_dense(q * 0.125, k, v, pos, 5, 2, 3)
+    dt = time.perf_counter() - t0
+    out["sparse"] = {"value": 2 * 4096 / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
+                     "sample": "2 of 32 (batch, head) pairs, fp32 (%.2f s)" % dt}
     return out
 
 
@@ -312,6 +320,23 @@ def other_configs(ops, dev, pk, cpu):
     out.append(hbm_entry("embedding lookup 25600 words, table 50000x1024 bf16", ms, 25600 * (2 * 1024 * 2 + 8),
                          cache="105 MB per call: fits L2, so this is a launch- and latency-bound size"))
     del table, ids, rows_out
+
+    # token-level sparse attention at the size the example names for real use: batch 2, 16 heads of 64,
+    # sequence 4096, window 5 dilation 2, 3 random keys, 3 + 3 global tokens, fp32 (three rotating sets)
+    sa = [[rnd(2, 16, 4096, 64) for _ in range(3)] + [torch.empty(2, 16, 4096, 64, device=dev)] for _ in range(3)]
+    pos = torch.randint(0, 4096, (2, 16, 4090, 3), device=dev, generator=g, dtype=torch.int32)
+
+    def sparse():
+        turn[0] = (turn[0] + 1) % 3
+        q_, k_, v_, o_ = sa[turn[0]]
+        ops.sparse_attention(q_, k_, v_, pos, 5, 2, 3, scale=0.125, out=o_)
+
+    ms = timed(sparse, 30)
+    out.append(hbm_entry("sparse attention fp32 B2 h16 S4096 d64, window 5 dilation 2, 3 random, 6 global", ms,
+                         4 * 2 * 16 * 4096 * 64 * 4 + 2 * 16 * 4090 * 3 * 4,
+                         cache="three rotating q/k/v/o sets of 134 MB", tokens_per_s=2 * 16 * 4096 / (ms * 1e-3),
+                         cpu_baseline=cpu.get("sparse")))
+    del sa, pos
 
     # config 1: stacked LSTM fp32 D4 H256 N32 L64 (CUDA cores; the reference's own CPU-runnable case)
     x1, W1, U1 = lstm_inputs(4, 64, 32, 256, 256, 0, 1.0 / 16, torch.float32)

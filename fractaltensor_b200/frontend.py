@@ -9,6 +9,7 @@ over ``FractalTensor`` values (flat ``.data`` buffer plus nested ``.indices``):
     stacked_grid_rnns(src_encs, trg_encs, params)      examples/grid_rnn/grid_rnn.py:111-122
     flash_attention(qsss, ksss, vsss)                  examples/flash_attention/flash_attention.py:75-88
     embed(words, embedding)                            examples/stacked_rnn/rnn_utils.py:80-90 (the lookup in front)
+    sparse_attention(query, key, value, random_attn)   examples/sparse_attention/sparse_attention.py:41-76, 109-114
 
 The functions here keep those argument lists and return the same nested values,
 but run the whole nest as one fused wavefront on the GPU.  Arguments may be the
@@ -275,3 +276,30 @@ def flash_attention(qsss, ksss, vsss, scale=1.0, dtype=None, causal=False, windo
     flat = lambda t: t.reshape(Bsz, heads, nblk * blk, d).contiguous()
     o = ops.flash_attention(flat(q), flat(k), flat(v), scale=scale, causal=causal, window=window, local=local)
     return FractalTensor.from_dense(o.reshape(Bsz, heads, nblk, blk, d), 3)
+
+
+def sparse_attention(query_proj, key_proj, value_proj, random_attn, window_size=5, dilation=2, n_global=3,
+                     scale=1.0, as_shipped=False, dtype=None):
+    """per_head_attn mapped over heads and batch: the last ``ops.map`` of multihead_sparse_attention
+    (examples/sparse_attention/sparse_attention.py:109-114), or one head (lines 41-76).
+
+    query_proj / key_proj / value_proj: FractalTensors of [1, d] tokens nested [S] (one head),
+    [heads][S] or [B][heads][S]; random_attn: the same nesting of [1, R] integer tensors, S - 2 *
+    n_global of them per head.  Returns the attention vectors in the nesting of query_proj.
+    `as_shipped=True` runs the softmax dimension the example's ``ops.softmax(x)`` calls really use
+    (dimension 0); the default normalises over the keys."""
+    q, k, v = (_cuda(_dense(t), dtype) for t in (query_proj, key_proj, value_proj))
+    pos = _cuda(_dense(random_attn)).to(torch.int32)
+    depth = q.dim() - 2            # element shape is [1, d]
+    if depth < 1 or depth > 3:
+        raise ValueError("sparse_attention: expected a nesting [S], [heads][S] or [B][heads][S]")
+    S, d = q.shape[depth - 1], q.shape[-1]
+    lead = tuple(q.shape[:depth - 1])
+    heads_total = 1
+    for n in lead:
+        heads_total *= n
+    flat = lambda t: t.reshape(1, heads_total, S, d).contiguous()
+    o = ops.sparse_attention(flat(q), flat(k), flat(v), pos.reshape(1, heads_total, S - 2 * n_global, -1).contiguous(),
+                             window_size=window_size, dilation=dilation, n_global=n_global, scale=scale,
+                             as_shipped=as_shipped)
+    return FractalTensor.from_dense(o.reshape(*lead, S, 1, d), depth)

@@ -305,6 +305,48 @@ def flash_attention(q, k, v, scale=None, out=None, causal=False, window=None, lo
     return out
 
 
+def sparse_attention(q, k, v, rand_pos, window_size=5, dilation=2, n_global=3, scale=1.0, as_shipped=False,
+                     out=None):
+    """Token-level sparse attention (examples/sparse_attention/sparse_attention.py:41-76).
+
+    q, k, v: [B, heads, S, d] (fp32, fp16 or bf16; d 32, 64, 128 or 256); rand_pos: int32
+    [B, heads, S - 2 * n_global, R].  The first and last `n_global` tokens attend to each other;
+    token i in between attends to the `window_size` keys at i - half + j * dilation (wrapped as
+    ops.shifted_slide wraps them) and to the keys at rand_pos[..., i - n_global, :].
+    `as_shipped=True` reproduces the softmax dimension the example actually runs with (dim 0:
+    windowed tokens get the plain sum of their values, the global block is normalised over the
+    queries); False normalises over the keys."""
+    _req(q, "q")
+    _req(k, "k", q.dtype)
+    _req(v, "v", q.dtype)
+    if q.dim() != 4 or tuple(k.shape) != tuple(q.shape) or tuple(v.shape) != tuple(q.shape):
+        raise ValueError("sparse_attention: q, k, v must be [B, heads, S, d] of one shape")
+    B, heads, S, d = q.shape
+    inner = S - 2 * int(n_global)
+    if inner < 0:
+        raise ValueError("sparse_attention: 2 * n_global exceeds the sequence length")
+    if rand_pos is None:
+        R = 0
+    else:
+        if rand_pos.dtype != torch.int32 or not rand_pos.is_cuda or not rand_pos.is_contiguous():
+            raise ValueError("sparse_attention: rand_pos must be a contiguous int32 CUDA tensor")
+        if rand_pos.dim() != 4 or tuple(rand_pos.shape[:3]) != (B, heads, inner):
+            raise ValueError("sparse_attention: rand_pos must be [B, heads, S - 2 * n_global, R]")
+        if rand_pos.device != q.device:
+            raise ValueError("sparse_attention: rand_pos is on another device")
+        R = rand_pos.shape[3]
+    if out is None:
+        out = torch.empty_like(q)
+    _req_like(out, "out", q.dtype, q.shape, q)
+    ws = workspace(q.device)
+    with torch.cuda.device(q.device):
+        check(lib.ftb_sparse_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(rand_pos) if R else None, _ptr(out), B, heads,
+                                      S, d, int(window_size), int(dilation), int(n_global), R, float(scale),
+                                      1 if as_shipped else 0, _dtype_code(q), _ptr(ws), ws.numel(), _stream()),
+              "ftb_sparse_attn_fwd")
+    return out
+
+
 def gemm_nt(A, Bt, out=None, bn=0, pair=0):
     """A: [M,K]; Bt: [N,K] -> A @ Bt^T."""
     _req(A, "A")

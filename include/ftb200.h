@@ -222,6 +222,27 @@ int ftb_flash_attn_local_fwd(const void* q, const void* k, const void* v, void* 
                              int d, int left, int right, float scale, int dtype, void* workspace,
                              size_t workspace_bytes, void* stream);
 
+/* Token-level sparse attention: dilated window + random + global keys, per head.  Stands in for
+ * per_head_attn / sparse_attn (examples/sparse_attention/sparse_attention.py:24-76).  The first and
+ * last n_global tokens of a head attend to each other only.  Every other token i attends to the
+ * `window` (odd) keys at i - half + j * dilation, half = (window - 1) * dilation / 2, wrapped as
+ * ops.shifted_slide wraps them (a position x < 0 becomes x + S - 1, x >= S becomes x - S;
+ * kaleido/frontend/operations/fractaltensor/access.py:389-410), and to the keys at the R positions
+ * rand_pos[b, head, i - n_global, :].  The example uses window 5, dilation 2, n_global 3, R 3,
+ * d 64, scale 1, fp32.
+ * q, k, v, o: [B, heads, S, d] of `dtype` (fp32, fp16 or bf16; the arithmetic is fp32), d 32, 64,
+ * 128 or 256; rand_pos: int32 [B, heads, S - 2 * n_global, R] on the device (NULL when R = 0);
+ * window + R <= 64, 2 * n_global <= min(S, 64), half < S.  A random position outside [0, S) is
+ * read as 0 and sets the (sticky) status word to 22.
+ * as_shipped: the example calls ops.softmax without a dimension, and the reference's softmax then
+ * normalises dimension 0 (kaleido/frontend/operations/tensor/arithmetic/reduction.py:26): every
+ * weight of a windowed token becomes 1 (the output is the sum of the gathered values) and the
+ * global block is normalised over the queries.  Non-zero reproduces exactly what that program
+ * returns; 0 gives softmax(scale * q.k^T) over the keys. */
+int ftb_sparse_attn_fwd(const void* q, const void* k, const void* v, const int* rand_pos, void* o, int B,
+                        int heads, int S, int d, int window, int dilation, int n_global, int R, float scale,
+                        int as_shipped, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Embedding lookup out[t, :] = table[ids[t], :] for t < T.  Stands in for the lookup in front of
  * the reference's RNN examples, ops.index(ops.slices(embedding, dim=0), word) mapped over a batch
  * of word sequences (examples/stacked_rnn/rnn_utils.py:80-90): `ids` is the flat int64 buffer of

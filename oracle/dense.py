@@ -221,6 +221,49 @@ def project_softmax_dense(h, P):
     return torch.softmax(h @ P, dim=-1)
 
 
+def sparse_attention_dense(q, k, v, rand_pos, window_size=5, dilation=2, n_global=3, as_shipped=False):
+    """Token-level sparse attention of one head: windowed + random + global keys.
+
+    Follows per_head_attn / sparse_attn (examples/sparse_attention/sparse_attention.py:24-76):
+    the first and last `n_global` tokens attend to each other only,
+    ``softmax(g_query @ g_key.T) @ g_value``; every other token i attends to the `window_size` keys
+    of ops.shifted_slide(window_size, dilation) centred on it, i.e. positions
+    range(i - half, i + half + 1, dilation) with half = ((window_size - 1) * (dilation - 1) +
+    window_size) // 2, wrapped the way ShiftedSlide._ids wraps them (x < 0 -> x + S - 1;
+    x >= S -> x - S; kaleido/frontend/operations/fractaltensor/access.py:389-410), plus the
+    positions rand_pos[i - n_global]; no scale on the scores.
+
+    `as_shipped`: the example calls ``ops.softmax(x)`` without a dimension, and the reference's
+    softmax defaults to dim = 0 (kaleido/frontend/operations/tensor/arithmetic/reduction.py:26):
+    on the [1, W + R] score row of a windowed token that normalises over a single element (every
+    weight becomes 1: the output is the plain sum of the selected values), and on the global
+    block it normalises over the queries instead of the keys.  True reproduces exactly that (it
+    is what the golden vector holds); False is the attention the example describes, softmax over
+    the keys.
+    q, k, v: [..., S, d]; rand_pos: integer [..., S - 2 * n_global, R].  Returns [..., S, d].
+    """
+    S = q.shape[-2]
+    half = ((window_size - 1) * (dilation - 1) + window_size) // 2
+    out = torch.empty_like(q)
+    gidx = list(range(n_global)) + list(range(S - n_global, S))
+    gq, gk, gv = q[..., gidx, :], k[..., gidx, :], v[..., gidx, :]
+    out[..., gidx, :] = torch.softmax(gq @ gk.transpose(-1, -2), dim=-2 if as_shipped else -1) @ gv
+
+    def wrap(x):
+        return x + S - 1 if x < 0 else (x - S if x >= S else x)
+
+    for i in range(n_global, S - n_global):
+        win = torch.tensor([wrap(x) for x in range(i - half, i + half + 1, dilation)], dtype=torch.long)
+        pos = rand_pos[..., i - n_global, :].long()
+        idx = torch.cat([win.expand(*pos.shape[:-1], win.numel()), pos], dim=-1)  # [..., W + R]
+        gather = lambda t: torch.gather(t, -2, idx[..., None].expand(*idx.shape, t.shape[-1]))
+        ks, vs = gather(k), gather(v)
+        s_row = q[..., i:i + 1, :] @ ks.transpose(-1, -2)
+        w = torch.ones_like(s_row) if as_shipped else torch.softmax(s_row, dim=-1)
+        out[..., i:i + 1, :] = w @ vs
+    return out
+
+
 def embedding_gather_dense(table, ids):
     """One table row per word, in the order of the flat word buffer.
 

@@ -12,6 +12,7 @@ reference's real ``ops.map / scan / fold / reduce / dilated_map / zip / ...``:
   varlen    examples/stacked_rnn/stacked_rnn.py:40-79 (time-major, length-sorted ragged batch)
   embedding examples/stacked_rnn/rnn_utils.py:80-90 (the word lookup in front of the RNN)
   projection examples/stacked_rnn/rnn_utils.py:45-50 (prev_softmax_proj behind the RNN: softmax(h @ P))
+  sparse    examples/sparse_attention/sparse_attention.py:41-76 (per_head_attn: window + random + global keys)
   dilated   examples/dilated_rnn/dilated_rnn.py:16-41
   grid      examples/grid_rnn/grid_rnn.py:42-122
   attention examples/flash_attention/flash_attention.py:14-88
@@ -223,6 +224,47 @@ def main():
     h, proj, probs = run_projection(64, 200, lens, 17)
     save("projection_small", h=h.numpy(), proj=proj.numpy(), lens=np.array(lens), probs=probs.numpy())
     print("projection", probs.shape)
+
+    # ------------------------------------------------- token-level sparse attention
+    def run_sparse_attention(S, d, R, seed, window_size=5, dilation=2):
+        """per_head_attn of examples/sparse_attention/sparse_attention.py:41-76 for one head: windowed
+        (ops.shifted_slide), random and global attention, with the reference's own operations."""
+        g = torch.Generator().manual_seed(seed)
+        def seq(t):
+            return ft(t.reshape(S, 1, d), (1, d), list(range(S)))
+        qd, kd, vd = (torch.rand(S, d, generator=g) for _ in range(3))
+        query, key, value = seq(qd), seq(kd), seq(vd)
+        pos = torch.stack([torch.randperm(S, generator=g)[:R] for _ in range(S - 6)])
+        rts = []
+        for r in range(S - 6):
+            t = Tensor((1, R), kaleido.int32, device="cpu")
+            t.data = pos[r].to(torch.int32)
+            rts.append(t)
+        random_attn_pos = FractalTensor.from_tensors(*rts)
+
+        def sparse_attn(query_token, w_keys, r_keys, w_values, r_values):
+            ks = ops.flatten(w_keys.join(r_keys)).T
+            vs = ops.flatten(w_values.join(r_values))
+            return ops.softmax(query_token @ ks) @ vs
+
+        windowed_key, windowed_value = ops.shifted_slide(ops.zip(key, value), window_size=window_size,
+                                                         dilation=dilation)
+        random_key, random_value = ops.map(lambda ids: (key[ids], value[ids]), random_attn_pos)
+        _, g_query, g_key, g_value = ops.filter(lambda x: (x[0] < 3 or x[0] >= query.length - 3),
+                                                ops.enumerate(query, key, value))
+        g_query, g_key, g_value = ops.flatten(g_query), ops.flatten(g_key), ops.flatten(g_value)
+        v1 = ops.slices(ops.softmax(g_query @ g_key.T) @ g_value, dim=0)
+        _, s_query, s_key, s_value = ops.filter(lambda x: x[0] >= 3 and x[0] < query.length - 3,
+                                                ops.enumerate(query, windowed_key, windowed_value))
+        v2 = ops.map(lambda x: sparse_attn(*x), ops.zip(s_query, s_key, random_key, s_value, random_value))
+        start, end = ops.split(v1, 2)
+        attn = start.join(v2).join(end)
+        return qd, kd, vd, pos, attn.data.reshape(S, d).clone()
+
+    q, k, v, pos, out = run_sparse_attention(16, 64, 3, 19)
+    save("sparse_attention_small", q=q.numpy(), k=k.numpy(), v=v.numpy(), rand_pos=pos.numpy(), out=out.numpy(),
+         window_size=5, dilation=2)
+    print("sparse attention", out.shape)
 
     # ---------------------------------------------------------------------- dilated
     def run_dilated(D, L, N, H, seed, w_bound):

@@ -64,6 +64,16 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
     assert lib.ftb_flash_attn_local_fwd(one, one, one, one, 1, 1, 256, 128, -1, 0, 1.0, 1, one, 256, z) == 1  # left < 0
     assert lib.ftb_flash_attn_local_fwd(one, one, one, one, 1, 1, 256, 128, 0, -2, 1.0, 1, one, 256, z) == 1  # right < 0
     assert lib.ftb_gemm_nt(one, one, one, 8, 128, 60, 1, None, one, 256, z) == 1  # K % 64
+    sp = lambda **kw: lib.ftb_sparse_attn_fwd(
+        one, one, one, kw.get("pos", one), one, 1, 1, kw.get("S", 16), kw.get("d", 64), kw.get("window", 5),
+        kw.get("dilation", 2), kw.get("ng", 3), kw.get("R", 3), 1.0, 0, 0, one, 256, z)
+    assert sp(window=4) == 1          # even windows are not defined by ops.shifted_slide
+    assert sp(dilation=0) == 1
+    assert sp(d=48) == 1
+    assert sp(ng=9) == 1              # 2 * n_global > S
+    assert sp(window=9, dilation=4) == 1   # half = 16 >= S: the wrap is a single step
+    assert sp(window=63, dilation=1, S=128, R=2) == 1  # more than 64 keys per token
+    assert sp(pos=z) == 1             # R > 0 without positions
     rows = (ctypes.c_int * 3)(4, 5, 1)  # not sorted by decreasing length
     assert lib.ftb_lstm_stacked_varlen_fwd(one, one, z, one, one, rows, 1, 3, 64, 64, 1, None, one, 256, z) == 1
     rows = (ctypes.c_int * 3)(4, 2, 0)  # a step without sequences
@@ -90,6 +100,7 @@ def test_misaligned_pointers_are_rejected_without_a_device(lib):
     assert lib.ftb_gemm_nt(ok, ok, off, 8, 128, 64, 0, None, ok, 256, z) == 2
     rows = (ctypes.c_int * 2)(2, 1)
     assert lib.ftb_lstm_stacked_varlen_fwd(ok, ok, z, ok, off, rows, 1, 2, 64, 64, 0, None, ok, 256, z) == 2
+    assert lib.ftb_sparse_attn_fwd(ok, off, ok, ok, ok, 1, 1, 16, 64, 5, 2, 3, 3, 1.0, 0, 0, ok, 256, z) == 2
 
 
 def test_no_fallback_when_library_is_missing(monkeypatch, tmp_path):

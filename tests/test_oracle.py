@@ -181,3 +181,23 @@ def test_projection_softmax_matches_reference_frontend(golden_dir):
     assert out.shape == g["probs"].shape
     assert (out - g["probs"]).abs().max().item() <= 1e-6
     assert (out.sum(dim=1) - 1).abs().max().item() <= 1e-5
+
+
+def test_sparse_attention_matches_reference_frontend(golden_dir):
+    """per_head_attn of the sparse attention example run through the reference's own shifted_slide,
+    filter, join, split and softmax (window 5, dilation 2, 3 random keys, 3 + 3 global tokens).  The
+    fixture holds what that program returns, which normalises dimension 0 (as_shipped)."""
+    g = _load(golden_dir, "sparse_attention_small.npz")
+    ws, dil = int(g["window_size"]), int(g["dilation"])
+    out = dense.sparse_attention_dense(g["q"], g["k"], g["v"], g["rand_pos"], ws, dil, as_shipped=True)
+    assert out.shape == g["out"].shape
+    assert (out - g["out"]).abs().max().item() <= 1e-6
+    # the attention the example describes: a convex combination of the gathered values per token
+    att = dense.sparse_attention_dense(g["q"], g["k"], g["v"], g["rand_pos"], ws, dil)
+    assert att.min().item() >= g["v"].min().item() - 1e-6 and att.max().item() <= g["v"].max().item() + 1e-6
+    # windowed tokens of the shipped form are plain sums of window + R value rows
+    S = g["q"].shape[0]
+    i, half = 5, (ws - 1) * dil // 2
+    rows = [x + S - 1 if x < 0 else (x - S if x >= S else x) for x in range(i - half, i + half + 1, dil)]
+    rows += g["rand_pos"][i - 3].tolist()
+    assert torch.allclose(g["out"][i], g["v"][rows].sum(dim=0), atol=1e-5)
