@@ -10,24 +10,33 @@
 //     kaleido/frontend/operations/fractaltensor/access.py:389-410) -- joined with the keys at
 //     the R positions rand_pos[i - n_global]                       (lines 24-38, 51-55, 66-71)
 //
-// This is gather work bound by memory, not a contraction: per token window + R key rows and as
-// many value rows of d elements, nearly all of them L1/L2 hits because neighbouring tokens
-// share window rows.  Algorithmic HBM traffic per head is one pass over q, k, v and the output,
-// 4 * S * d * element size bytes, plus 4 * R bytes of positions per token.  A group of d / 8
-// lanes owns a token (a warp works on 32 / (d / 8) consecutive tokens at a time): lane l of the
-// group holds elements [8 l, 8 l + 8) of the query, of each gathered row and of the output; the
-// scores are dot products reduced over the group's lanes by shuffles, which every lane of the
-// group ends up holding, and the softmax is carried across steps of four keys as (max, sum,
-// weighted values).  Rows move as 16-byte loads; the grid is a whole number of CTAs per SM
-// striding over (head, token).
+// This is gather work bound by memory, not a contraction.  Algorithmic HBM traffic per head is one
+// pass over q, k, v and the output, 4 * S * d * element size bytes, plus 4 * R bytes of positions
+// per token.
 //
-// `as_shipped`: the example calls ops.softmax(x) without a dimension and the reference's
-// softmax normalises dimension 0 by default
-// (kaleido/frontend/operations/tensor/arithmetic/reduction.py:26).  On the [1, window + R]
-// score row of a windowed token that is a single element, so every weight is 1 and the output
-// is the plain sum of the gathered values; on the global block it normalises each key's column
-// over the queries.  as_shipped != 0 reproduces that bit of behaviour (it is what the
-// reference's frontend returns); 0 normalises over the keys.
+// A group of d / 8 lanes owns a token (a warp works on 32 / (d / 8) tokens at a time): each lane
+// holds 8 elements of the query, of each gathered row and of the output; the scores are dot
+// products reduced over the group's lanes by shuffles, which every lane of the group ends up
+// holding, and the softmax is carried across steps of four keys as (max, sum, weighted values).
+//
+// Tiled kernel (the default): a persistent CTA walks tiles of TT consecutive tokens of one head.
+// The key and value rows the tile's windows can touch, positions [t0 - half, t0 + TT + half), are
+// contiguous in memory, and so are the tile's queries: three bulk asynchronous copies bring them
+// into shared memory under an mbarrier, for the next tile while the current one is computed (two
+// stages).  The tile's random positions are fetched into registers one tile ahead and parked in
+// shared memory.  Window rows, queries and positions then cost shared-memory latency; only the R
+// random rows per token (and window positions that wrap around the ends of the sequence) are
+// gathered from global memory, 16 bytes per lane.
+// Direct kernel (fallback when a tile does not fit in shared memory or R > 16): the same token
+// routine with every row gathered from global memory.
+//
+// `as_shipped`: the example calls ops.softmax(x) without a dimension and the reference's softmax
+// normalises dimension 0 by default
+// (kaleido/frontend/operations/tensor/arithmetic/reduction.py:26).  On the [1, window + R] score
+// row of a windowed token that is a single element, so every weight is 1 and the output is the
+// plain sum of the gathered values; on the global block it normalises each key's column over the
+// queries.  as_shipped != 0 reproduces that (it is what the reference's frontend returns);
+// 0 normalises over the keys.
 #include "../../include/ftb200.h"
 #include "ptx.cuh"
 #include "tmap.h"
@@ -39,67 +48,262 @@ namespace ftb {
 namespace {
 
 constexpr int kSparseThreads = 256;
-constexpr int kMaxKeys = 64;  // window + R, and 2 * n_global
+constexpr int kMaxKeys = 64;    // window + R, and 2 * n_global
+constexpr int kEPL = 8;         // elements of a row per lane
+constexpr int kCH = 4;          // keys per step: their rows are all requested before the first score is reduced
+constexpr int kPosRegs = 4;     // tiled kernel: random positions of the next tile held per thread
+constexpr int kMaxTileSmem = 110 * 1024;  // two stages; leaves room for two CTAs per SM
 
-template <typename T> __device__ __forceinline__ float to_f32(T x);
-template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
-template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
-template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
-template <typename T> __device__ __forceinline__ T from_f32(float x);
-template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
-template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
-template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+// 8 elements of a row owned by lane `gl` of a group of LPT lanes, moved as 16-byte pieces: piece c
+// of the lane is the 16 bytes at (c * LPT + gl) * 16, so that one load instruction of the group
+// covers a contiguous stretch of the row.
+template <typename T> struct Pieces { static constexpr int n = sizeof(T) * kEPL / 16; };
 
-// EPL elements of a row, owned by one lane, moved as 16-byte (or smaller) vectors.
-template <typename T, int EPL>
-struct alignas((sizeof(T) * EPL > 16) ? 16 : sizeof(T) * EPL) Frag {
-  T v[EPL];
-};
-
-template <typename T, int EPL>
-__device__ __forceinline__ void load_row(const T* __restrict__ row, int lane, float (&out)[EPL]) {
-  const Frag<T, EPL> f = reinterpret_cast<const Frag<T, EPL>*>(row)[lane];
+__device__ __forceinline__ void unpack16(const uint4& w, float* out, float) {
+  out[0] = __uint_as_float(w.x);
+  out[1] = __uint_as_float(w.y);
+  out[2] = __uint_as_float(w.z);
+  out[3] = __uint_as_float(w.w);
+}
+__device__ __forceinline__ void unpack16(const uint4& w, float* out, __half) {
+  const uint32_t r[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) out[e] = to_f32<T>(f.v[e]);
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&r[i]));
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void unpack16(const uint4& w, float* out, __nv_bfloat16) {
+  const uint32_t r[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(r[i] << 16);
+    out[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack16(const float* in, float) {
+  return make_uint4(__float_as_uint(in[0]), __float_as_uint(in[1]), __float_as_uint(in[2]), __float_as_uint(in[3]));
+}
+__device__ __forceinline__ uint4 pack16(const float* in, __half) {
+  uint32_t r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h = __floats2half2_rn(in[2 * i], in[2 * i + 1]);
+    r[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(r[0], r[1], r[2], r[3]);
+}
+__device__ __forceinline__ uint4 pack16(const float* in, __nv_bfloat16) {
+  uint32_t r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+    r[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(r[0], r[1], r[2], r[3]);
+}
+
+template <typename T, int LPT>
+__device__ __forceinline__ void load_row_global(const T* __restrict__ row, int gl, float (&out)[kEPL]) {
+#pragma unroll
+  for (int c = 0; c < Pieces<T>::n; ++c) {
+    const uint4 w = __ldg(reinterpret_cast<const uint4*>(row) + c * LPT + gl);
+    unpack16(w, out + c * (kEPL / Pieces<T>::n), T());
+  }
+}
+template <typename T, int LPT>
+__device__ __forceinline__ void load_row_shared(const T* row, int gl, float (&out)[kEPL]) {
+#pragma unroll
+  for (int c = 0; c < Pieces<T>::n; ++c) {
+    uint4 w;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                 : "r"(smem_u32(reinterpret_cast<const uint4*>(row) + c * LPT + gl)));
+    unpack16(w, out + c * (kEPL / Pieces<T>::n), T());
+  }
+}
+template <typename T, int LPT>
+__device__ __forceinline__ void store_row_global(T* row, int gl, const float (&in)[kEPL]) {
+#pragma unroll
+  for (int c = 0; c < Pieces<T>::n; ++c)
+    __stcs(reinterpret_cast<uint4*>(row) + c * LPT + gl, pack16(in + c * (kEPL / Pieces<T>::n), T()));
 }
 
 // Dot product of two rows spread over the LPT lanes of a token's group; every lane of the group
 // gets the sum.  `mask` names the group's lanes, so groups of one warp may diverge.
-template <int EPL, int LPT>
-__device__ __forceinline__ float group_dot(const float (&a)[EPL], const float (&b)[EPL], unsigned mask) {
+template <int LPT>
+__device__ __forceinline__ float group_dot(const float (&a)[kEPL], const float (&b)[kEPL], unsigned mask) {
   float s = 0.f;
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) s = fmaf(a[e], b[e], s);
+  for (int e = 0; e < kEPL; ++e) s = fmaf(a[e], b[e], s);
 #pragma unroll
   for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(mask, s, o);
   return s;
+}
+
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 struct SparseArgs {
   long long heads_total;  // B * heads
   int S, window, dilation, n_global, R, as_shipped;
   float scale;
+  // tiled kernel
+  int TT;              // tokens per tile
+  int tiles_per_head;  // ceil(S / TT)
+  int stage_bytes;     // K rows | V rows | queries | positions of one stage
 };
 
-constexpr int kEPL = 8;  // elements of a row per lane: 16 bytes of a 16-bit type, 32 of fp32
+// Where the rows of one token's head come from: global memory, and for the tiled kernel the stage
+// that holds rows [lo, hi) of K and V.
+template <typename T>
+struct Rows {
+  const T* kh;  // the head's keys, values, queries in global memory
+  const T* vh;
+  const T* qh;
+  const T* sk;  // shared memory (tiled kernel): key / value rows lo .. hi - 1
+  const T* sv;
+  int lo, hi;   // lo = hi = 0 for the direct kernel
+};
 
+// One token: query row `qv` already loaded, `pos_of(r)` gives the position of random key r.
+// `interior` (tiled kernel, the same for every token of a tile): no token of the tile is a global
+// one and no window position wraps, so window rows are in the stage and random rows are gathered
+// from global memory -- which of the two a key is then depends on its number only, and the warp
+// does not diverge over it.
+template <typename T, int LPT, typename PosFn>
+__device__ __forceinline__ void attend_token(const SparseArgs& a, const Rows<T>& rw, int i, int gl, unsigned gmask,
+                                             bool interior,
+                                             const float (&qv)[kEPL], PosFn pos_of, T* __restrict__ out_row,
+                                             int* __restrict__ status) {
+  constexpr int d = kEPL * LPT;
+  constexpr int CH = kCH;
+  const int S = a.S, ng = a.n_global, G = 2 * a.n_global;
+  const int half = (a.window - 1) * a.dilation / 2;
+  const bool global_tok = i < ng || i >= S - ng;
+  const int nk = global_tok ? G : a.window + a.R;
+  const bool use_scores = !a.as_shipped || global_tok;
+  const float scale2 = a.scale * 1.4426950408889634f;  // scores in the base-2 domain: exp(x) = 2^(x log2 e)
+
+  float acc[kEPL];
+#pragma unroll
+  for (int e = 0; e < kEPL; ++e) acc[e] = 0.f;
+  float m = -INFINITY, z = 0.f;
+
+  for (int j0 = 0; j0 < nk; j0 += CH) {
+    int p[CH];
+#pragma unroll
+    for (int u = 0; u < CH; ++u) {
+      const int j = j0 + u < nk ? j0 + u : nk - 1;  // the tail repeats the last key with weight 0
+      int x;
+      if (global_tok) {
+        x = j < ng ? j : S - G + j;
+      } else if (j < a.window) {
+        x = i - half + j * a.dilation;
+        x = x < 0 ? x + S - 1 : (x >= S ? x - S : x);
+      } else {
+        x = pos_of(j - a.window);
+        if (x < 0 || x >= S) {
+          if (gl == 0) atomicCAS(status, 0, FTB_ERR_INDEX);
+          x = 0;
+        }
+      }
+      p[u] = x;
+    }
+    float kv[CH][kEPL], vv[CH][kEPL];
+#pragma unroll
+    for (int u = 0; u < CH; ++u) {
+      const bool staged = interior ? ((j0 + u < nk ? j0 + u : nk - 1) < a.window) : (p[u] >= rw.lo && p[u] < rw.hi);
+      if (staged) {
+        if (use_scores) load_row_shared<T, LPT>(rw.sk + (p[u] - rw.lo) * d, gl, kv[u]);
+        load_row_shared<T, LPT>(rw.sv + (p[u] - rw.lo) * d, gl, vv[u]);
+      } else {
+        if (use_scores) load_row_global<T, LPT>(rw.kh + static_cast<long long>(p[u]) * d, gl, kv[u]);
+        load_row_global<T, LPT>(rw.vh + static_cast<long long>(p[u]) * d, gl, vv[u]);
+      }
+    }
+
+    if (!use_scores) {
+      // as shipped, windowed token: every weight is 1
+#pragma unroll
+      for (int u = 0; u < CH; ++u) {
+        const float wu = j0 + u < nk ? 1.f : 0.f;
+#pragma unroll
+        for (int e = 0; e < kEPL; ++e) acc[e] = fmaf(wu, vv[u][e], acc[e]);
+      }
+    } else if (a.as_shipped) {
+      // as shipped, global token: for key j the weight of query i is exp(s_ij) over the sum of
+      // exp(s_i'j) across the global queries i' (a softmax down the column of key j).
+#pragma unroll
+      for (int u = 0; u < CH; ++u) {
+        if (j0 + u >= nk) continue;
+        const float s_own = group_dot<LPT>(qv, kv[u], gmask) * a.scale;
+        float cm = -INFINITY, cz = 0.f;
+        for (int jj = 0; jj < G; ++jj) {
+          float q2[kEPL];
+          load_row_global<T, LPT>(rw.qh + static_cast<long long>(jj < ng ? jj : S - G + jj) * d, gl, q2);
+          const float s = group_dot<LPT>(q2, kv[u], gmask) * a.scale;
+          const float m2 = fmaxf(cm, s);
+          cz = cz * expf(cm - m2) + expf(s - m2);
+          cm = m2;
+        }
+        const float wu = expf(s_own - cm) / cz;
+#pragma unroll
+        for (int e = 0; e < kEPL; ++e) acc[e] = fmaf(wu, vv[u][e], acc[e]);
+      }
+    } else {
+      // softmax over the keys, carried across steps as (max, sum, weighted values)
+      float sc[CH];
+      float m2 = m;
+#pragma unroll
+      for (int u = 0; u < CH; ++u) {
+        const float s = group_dot<LPT>(qv, kv[u], gmask) * scale2;  // every lane of the group holds it
+        sc[u] = j0 + u < nk ? s : -INFINITY;
+        m2 = fmaxf(m2, sc[u]);
+      }
+      const float keep = exp2_fast(m - m2);  // 0 on the first step (m = -inf, m2 finite)
+      z *= keep;
+#pragma unroll
+      for (int e = 0; e < kEPL; ++e) acc[e] *= keep;
+#pragma unroll
+      for (int u = 0; u < CH; ++u) {
+        const float wu = exp2_fast(sc[u] - m2);
+        z += wu;
+#pragma unroll
+        for (int e = 0; e < kEPL; ++e) acc[e] = fmaf(wu, vv[u][e], acc[e]);
+      }
+      m = m2;
+    }
+  }
+  const float inv = a.as_shipped ? 1.f : 1.f / z;
+#pragma unroll
+  for (int e = 0; e < kEPL; ++e) acc[e] *= inv;
+  store_row_global<T, LPT>(out_row, gl, acc);
+}
+
+template <int LPT>
+__device__ __forceinline__ unsigned group_mask(int lane) {
+  return LPT == 32 ? 0xffffffffu : (((1u << (LPT & 31)) - 1u) << (lane - lane % LPT));
+}
+
+// ------------------------------------------------------------------ direct kernel
 template <typename T, int LPT>
 __global__ void __launch_bounds__(kSparseThreads)
 sparse_attn_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                    const int* __restrict__ rand_pos, T* __restrict__ o, SparseArgs a, int* __restrict__ status) {
-  constexpr int EPL = kEPL;
-  constexpr int d = EPL * LPT;
+  constexpr int d = kEPL * LPT;
   constexpr int TPW = 32 / LPT;  // tokens a warp works on at a time, one per group of LPT lanes
-  // Keys per step: their key and value rows are all requested before the first score is reduced, so
-  // a token costs two dependent memory round trips (positions and query, then the rows).
-  constexpr int CH = 4;
   const int lane = threadIdx.x & 31;
   const int gl = lane % LPT;
-  const unsigned gmask = LPT == 32 ? 0xffffffffu : (((1u << (LPT & 31)) - 1u) << (lane - gl));
+  const unsigned gmask = group_mask<LPT>(lane);
   const long long warp = (static_cast<long long>(blockIdx.x) * kSparseThreads + threadIdx.x) >> 5;
   const long long n_warps = (static_cast<long long>(gridDim.x) * kSparseThreads) >> 5;
   const int S = a.S, ng = a.n_global, G = 2 * a.n_global;
-  const int half = (a.window - 1) * a.dilation / 2;
   const long long total = a.heads_total * S;
   const bool small = total <= 0xffffffffLL;
 
@@ -109,116 +313,182 @@ sparse_attn_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
     const long long head = small ? static_cast<long long>(static_cast<unsigned>(item) / static_cast<unsigned>(S))
                                  : item / S;
     const int i = static_cast<int>(item - head * S);
-    const T* kh = k + head * S * d;
-    const T* vh = v + head * S * d;
-    const T* qh = q + head * S * d;
-    const bool global_tok = i < ng || i >= S - ng;
-    const int nk = global_tok ? G : a.window + a.R;
-    const int* rp = rand_pos + (head * (S - G) + (i - ng)) * a.R - a.window;  // indexed by key number; read for j >= window only
-    const bool use_scores = !a.as_shipped || global_tok;
+    Rows<T> rw;
+    rw.kh = k + head * S * d;
+    rw.vh = v + head * S * d;
+    rw.qh = q + head * S * d;
+    rw.sk = rw.sv = nullptr;
+    rw.lo = rw.hi = 0;
+    const int* rp = rand_pos + (head * (S - G) + (i - ng)) * a.R;  // read for windowed tokens only
+    float qv[kEPL];
+    load_row_global<T, LPT>(rw.qh + static_cast<long long>(i) * d, gl, qv);
+    attend_token<T, LPT>(a, rw, i, gl, gmask, false, qv, [&](int r) { return __ldg(rp + r); },
+                         o + (head * S + i) * d, status);
+  }
+}
 
-    float qv[EPL];
-    load_row<T, EPL>(qh + static_cast<long long>(i) * d, gl, qv);
+// ------------------------------------------------------------------ tiled kernel
+template <typename T, int LPT>
+__global__ void __launch_bounds__(kSparseThreads)
+sparse_attn_tile_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                        const int* __restrict__ rand_pos, T* __restrict__ o, SparseArgs a, int* __restrict__ status) {
+  constexpr int d = kEPL * LPT;
+  constexpr int TPW = 32 / LPT;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full[2];
+  __shared__ int s_abort;
 
-    float acc[EPL];
+  const int tid = threadIdx.x, lane = tid & 31, gl = lane % LPT;
+  const unsigned gmask = group_mask<LPT>(lane);
+  const int S = a.S, ng = a.n_global, G = 2 * a.n_global, TT = a.TT;
+  const int half = (a.window - 1) * a.dilation / 2;
+  const int rows_max = TT + 2 * half;
+  const long long n_tiles = a.heads_total * a.tiles_per_head;
+
+  auto stage_k = [&](int s) { return reinterpret_cast<T*>(smem + static_cast<size_t>(s) * a.stage_bytes); };
+  auto stage_v = [&](int s) { return stage_k(s) + static_cast<size_t>(rows_max) * d; };
+  auto stage_q = [&](int s) { return stage_v(s) + static_cast<size_t>(rows_max) * d; };
+  auto stage_pos = [&](int s) { return reinterpret_cast<int*>(stage_q(s) + static_cast<size_t>(TT) * d); };
+
+  struct Tile {
+    long long head;
+    int t0, nt, lo, hi;
+  };
+  auto tile_of = [&](long long t) {
+    Tile x;
+    x.head = t / a.tiles_per_head;
+    x.t0 = static_cast<int>(t - x.head * a.tiles_per_head) * TT;
+    x.nt = min(TT, S - x.t0);
+    x.lo = max(0, x.t0 - half);
+    x.hi = min(S, x.t0 + x.nt + half);
+    return x;
+  };
+  // Thread 0: the three bulk copies of a tile into stage s.
+  auto issue = [&](const Tile& x, int s) {
+    const uint32_t kv_bytes = static_cast<uint32_t>(x.hi - x.lo) * d * sizeof(T);
+    const uint32_t q_bytes = static_cast<uint32_t>(x.nt) * d * sizeof(T);
+    mbar_arrive_expect_tx(&full[s], 2 * kv_bytes + q_bytes);
+    bulk_load_1d(stage_k(s), k + (x.head * S + x.lo) * d, kv_bytes, &full[s]);
+    bulk_load_1d(stage_v(s), v + (x.head * S + x.lo) * d, kv_bytes, &full[s]);
+    bulk_load_1d(stage_q(s), q + (x.head * S + x.t0) * d, q_bytes, &full[s]);
+  };
+  // Every thread: its share of the tile's random positions (entry e = token * R + r of the tile).
+  auto fetch_pos = [&](const Tile& x, int (&pre)[kPosRegs]) {
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
-    float m = -INFINITY, z = 0.f;
-
-    for (int j0 = 0; j0 < nk; j0 += CH) {
-      int p[CH];
-#pragma unroll
-      for (int u = 0; u < CH; ++u) {
-        const int j = j0 + u < nk ? j0 + u : nk - 1;  // the tail repeats the last key with weight 0
-        int x;
-        if (global_tok) {
-          x = j < ng ? j : S - G + j;
-        } else if (j < a.window) {
-          x = i - half + j * a.dilation;
-          x = x < 0 ? x + S - 1 : (x >= S ? x - S : x);
-        } else {
-          x = rp[j];  // the same address in every lane of the group: one broadcast read
-          if (x < 0 || x >= S) {
-            if (gl == 0) atomicCAS(status, 0, FTB_ERR_INDEX);
-            x = 0;
-          }
-        }
-        p[u] = x;
+    for (int u = 0; u < kPosRegs; ++u) {
+      const int e = tid + u * kSparseThreads;
+      int val = 0;
+      if (e < x.nt * a.R) {
+        const int i = x.t0 + e / a.R;
+        if (i >= ng && i < S - ng) val = __ldg(rand_pos + (x.head * (S - G) + (i - ng)) * a.R + e % a.R);
       }
-      float kv[CH][EPL], vv[CH][EPL];
-      if (use_scores) {
-#pragma unroll
-        for (int u = 0; u < CH; ++u) load_row<T, EPL>(kh + static_cast<long long>(p[u]) * d, gl, kv[u]);
-      }
-#pragma unroll
-      for (int u = 0; u < CH; ++u) load_row<T, EPL>(vh + static_cast<long long>(p[u]) * d, gl, vv[u]);
-
-      if (!use_scores) {
-        // as shipped, windowed token: every weight is 1
-#pragma unroll
-        for (int u = 0; u < CH; ++u) {
-          const float wu = j0 + u < nk ? 1.f : 0.f;
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) acc[e] = fmaf(wu, vv[u][e], acc[e]);
-        }
-      } else if (a.as_shipped) {
-        // as shipped, global token: for key j the weight of query i is exp(s_ij) over the sum of
-        // exp(s_i'j) across the global queries i' (a softmax down the column of key j).
-#pragma unroll
-        for (int u = 0; u < CH; ++u) {
-          if (j0 + u >= nk) continue;
-          const float s_own = group_dot<EPL, LPT>(qv, kv[u], gmask) * a.scale;
-          float cm = -INFINITY, cz = 0.f;
-          for (int jj = 0; jj < G; ++jj) {
-            float q2[EPL];
-            load_row<T, EPL>(qh + static_cast<long long>(jj < ng ? jj : S - G + jj) * d, gl, q2);
-            const float s = group_dot<EPL, LPT>(q2, kv[u], gmask) * a.scale;
-            const float m2 = fmaxf(cm, s);
-            cz = cz * expf(cm - m2) + expf(s - m2);
-            cm = m2;
-          }
-          const float wu = expf(s_own - cm) / cz;
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) acc[e] = fmaf(wu, vv[u][e], acc[e]);
-        }
-      } else {
-        // softmax over the keys, carried across steps as (max, sum, weighted values)
-        float sc[CH];
-        float m2 = m;
-#pragma unroll
-        for (int u = 0; u < CH; ++u) {
-          const float s = group_dot<EPL, LPT>(qv, kv[u], gmask) * a.scale;  // every lane of the group holds it
-          sc[u] = j0 + u < nk ? s : -INFINITY;
-          m2 = fmaxf(m2, sc[u]);
-        }
-        const float keep = expf(m - m2);  // 0 on the first step (m = -inf, m2 finite)
-        z *= keep;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[e] *= keep;
-#pragma unroll
-        for (int u = 0; u < CH; ++u) {
-          const float wu = expf(sc[u] - m2);
-          z += wu;
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) acc[e] = fmaf(wu, vv[u][e], acc[e]);
-        }
-        m = m2;
-      }
+      pre[u] = val;
     }
-    const float inv = a.as_shipped ? 1.f : 1.f / z;
-    Frag<T, EPL> out;
+  };
+  auto park_pos = [&](int s, const int (&pre)[kPosRegs]) {
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) out.v[e] = from_f32<T>(acc[e] * inv);
-    reinterpret_cast<Frag<T, EPL>*>(o + (head * S + i) * d)[gl] = out;
+    for (int u = 0; u < kPosRegs; ++u) {
+      const int e = tid + u * kSparseThreads;
+      if (e < TT * a.R) stage_pos(s)[e] = pre[u];
+    }
+  };
+
+  if (tid == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    s_abort = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  long long tile = blockIdx.x;
+  if (tile >= n_tiles) return;
+  {
+    const Tile x = tile_of(tile);
+    if (tid == 0) issue(x, 0);
+    int pre[kPosRegs];
+    fetch_pos(x, pre);
+    park_pos(0, pre);
+  }
+  __syncthreads();
+
+  for (int it = 0; tile < n_tiles; tile += gridDim.x, ++it) {
+    const int s = it & 1;
+    const Tile x = tile_of(tile);
+    const long long next = tile + gridDim.x;
+    int pre[kPosRegs];
+    if (next < n_tiles) {
+      // stage s ^ 1 was last read in the previous round; the barrier that closed it orders those
+      // reads before these writes
+      const Tile y = tile_of(next);
+      if (tid == 0) issue(y, s ^ 1);
+      fetch_pos(y, pre);
+    }
+    if (!mbar_wait(&full[s], (it >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) break;
+
+    Rows<T> rw;
+    rw.kh = k + x.head * S * d;
+    rw.vh = v + x.head * S * d;
+    rw.qh = q + x.head * S * d;
+    rw.sk = stage_k(s);
+    rw.sv = stage_v(s);
+    rw.lo = x.lo;
+    rw.hi = x.hi;
+    const int* sp = stage_pos(s);
+    // no global token in the tile and no window position that wraps
+    const bool interior = x.t0 >= ng && x.t0 + x.nt <= S - ng && x.t0 - half >= 0 && x.t0 + x.nt - 1 + half < S;
+    for (int tok = (tid >> 5) * TPW + lane / LPT; tok < x.nt; tok += (kSparseThreads / 32) * TPW) {
+      const int i = x.t0 + tok;
+      float qv[kEPL];
+      load_row_shared<T, LPT>(stage_q(s) + tok * d, gl, qv);
+      attend_token<T, LPT>(a, rw, i, gl, gmask, interior, qv, [&](int r) { return sp[tok * a.R + r]; },
+                           o + (x.head * S + i) * d, status);
+    }
+    if (next < n_tiles) park_pos(s ^ 1, pre);
+    __syncthreads();
   }
 }
 
 template <typename T, int LPT>
-int launch_sparse(const void* q, const void* k, const void* v, const int* rand_pos, void* o, const SparseArgs& a,
+int launch_sparse(const void* q, const void* k, const void* v, const int* rand_pos, void* o, SparseArgs a,
                   int* status, cudaStream_t stream) {
+  constexpr int d = kEPL * LPT;
+  const int half = (a.window - 1) * a.dilation / 2;
+  // Tiled kernel: the largest tile of 64, 32 or 16 tokens whose two stages fit.
+  int TT = 0, stage = 0;
+  if (a.R <= 16) {
+    for (int t = 64; t >= 16; t >>= 1) {
+      if (t * a.R > kPosRegs * kSparseThreads) continue;
+      const long long rows = static_cast<long long>(t) + 2 * half;
+      const long long bytes = (2 * rows + t) * d * static_cast<long long>(sizeof(T)) + ((t * a.R * 4 + 15) / 16) * 16;
+      if (2 * bytes <= kMaxTileSmem) {
+        TT = t;
+        stage = static_cast<int>(bytes);
+        break;
+      }
+    }
+  }
+  if (TT > 0) {
+    static std::atomic<unsigned long long> configured{0};
+    auto kfn = sparse_attn_tile_kernel<T, LPT>;
+    if (ensure_dynamic_smem(kfn, kMaxTileSmem, configured)) {
+      a.TT = TT;
+      a.tiles_per_head = (a.S + TT - 1) / TT;
+      a.stage_bytes = stage;
+      const long long n_tiles = a.heads_total * a.tiles_per_head;
+      const long long full = static_cast<long long>(current_sm_count()) * 2;  // two CTAs per SM, persistent
+      const int grid = static_cast<int>(n_tiles < full ? n_tiles : full);
+      kfn<<<grid, kSparseThreads, 2 * stage, stream>>>(static_cast<const T*>(q), static_cast<const T*>(k),
+                                                       static_cast<const T*>(v), rand_pos, static_cast<T*>(o), a,
+                                                       status);
+      count_launch();
+      return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+    }
+  }
+  a.TT = a.tiles_per_head = a.stage_bytes = 0;
   const long long warps_needed = (a.heads_total * a.S + 32 / LPT - 1) / (32 / LPT);
   const long long ctas_needed = (warps_needed * 32 + kSparseThreads - 1) / kSparseThreads;
-  const long long full = static_cast<long long>(current_sm_count()) * 8;  // 8 CTAs of 256 threads per SM
+  const long long full = static_cast<long long>(current_sm_count()) * 8;
   const int grid = static_cast<int>(ctas_needed < full ? ctas_needed : full);
   sparse_attn_kernel<T, LPT><<<grid, kSparseThreads, 0, stream>>>(
       static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), rand_pos, static_cast<T*>(o), a,
@@ -273,6 +543,7 @@ extern "C" int ftb_sparse_attn_fwd(const void* q, const void* k, const void* v, 
   a.R = R;
   a.as_shipped = as_shipped ? 1 : 0;
   a.scale = scale;
+  a.TT = a.tiles_per_head = a.stage_bytes = 0;
   int* status = static_cast<int*>(workspace);  // sticky, as for the other single-kernel entry points
   switch (dtype) {
     case FTB_F32: return launch_sparse_d<float>(d, q, k, v, rand_pos, o, a, status, stream);

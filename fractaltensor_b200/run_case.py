@@ -7,6 +7,7 @@
     python -m fractaltensor_b200.run_case varlen --D 16 --L 100 --N 256 --H 1024 --min-len 20
     python -m fractaltensor_b200.run_case b2b --batch 16 --M 16384
     python -m fractaltensor_b200.run_case attn --B 4 --heads 16 --S 2048
+    python -m fractaltensor_b200.run_case sparse_attn --B 2 --heads 16 --S 4096 --dtype fp32
 
 A small, fixed workload to put under a profiler or to time by hand; prints the
 average time per call measured with CUDA events.
@@ -23,7 +24,7 @@ DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["lstm", "varlen", "dilated", "grid", "b2b", "attn", "softmax"])
+    ap.add_argument("case", choices=["lstm", "varlen", "dilated", "grid", "b2b", "attn", "softmax", "sparse_attn"])
     ap.add_argument("--D", type=int, default=16)
     ap.add_argument("--L", type=int, default=20)
     ap.add_argument("--N", type=int, default=256)
@@ -46,6 +47,8 @@ def main():
     ap.add_argument("--causal", action="store_true", help="attn: keys 0..i for query i")
     ap.add_argument("--window", type=int, default=None, help="attn with --causal: keys i-window+1..i")
     ap.add_argument("--local", type=int, nargs=2, default=None, help="attn: keys i-LEFT..i+RIGHT")
+    ap.add_argument("--head-dim", type=int, default=64, help="sparse_attn: elements per head")
+    ap.add_argument("--as-shipped", action="store_true", help="sparse_attn: the softmax dimension of the shipped example")
     ap.add_argument("--graph", action="store_true",
                     help="capture one call in a CUDA graph and time replays (schedules with one launch per level)")
     a = ap.parse_args()
@@ -102,6 +105,18 @@ def main():
         def fn():
             turn[0] = (turn[0] + 1) % 3
             return ops.online_softmax(xs[turn[0]], ys[turn[0]])
+    elif a.case == "sparse_attn":
+        # window 5, dilation 2, 3 random keys, 3 + 3 global tokens as in the example; three q/k/v/o sets in turn
+        sets = [[rnd(a.B, a.heads, a.S, a.head_dim).to(dt) for _ in range(3)] for _ in range(3)]
+        outs = [torch.empty_like(s_[0]) for s_ in sets]
+        pos = torch.randint(0, a.S, (a.B, a.heads, a.S - 6, 3), device=dev, generator=g, dtype=torch.int32)
+        turn = [0]
+
+        def fn():
+            turn[0] = (turn[0] + 1) % 3
+            q, k, v = sets[turn[0]]
+            return ops.sparse_attention(q, k, v, pos, 5, 2, 3, scale=1 / math.sqrt(a.head_dim),
+                                        as_shipped=a.as_shipped, out=outs[turn[0]])
     else:
         q, k, v = (rnd(a.B, a.heads, a.S, 128).to(dt) for _ in range(3))
         out = torch.empty_like(q)
