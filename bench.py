@@ -185,6 +185,17 @@ def cpu_other_configs(threads):
     dt = time.perf_counter() - t0
     out["sparse"] = {"value": 2 * 4096 / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
                      "sample": "2 of 32 (batch, head) pairs, fp32 (%.2f s)" % dt}
+    # attention RNN: 8 of the 64 sequences
+    Hr = 512
+    wr = [(torch.rand(Hr, Hr, generator=g) * 2 - 1) / math.sqrt(Hr) for _ in range(4)]
+    zb = torch.zeros(1, Hr)
+    t0 = time.perf_counter()
+    dense.rnn_attention_dense(torch.randn(8 * 50, Hr, generator=g), torch.randn(8 * 50, Hr, generator=g), [50] * 8,
+                              [50] * 8, wr[0], wr[1], zb, wr[2], wr[3], zb, torch.rand(Hr, 1, generator=g),
+                              torch.rand(Hr, 1, generator=g))
+    dt = time.perf_counter() - t0
+    out["rnn_attention"] = {"value": 8 * 100 / dt, "unit": UNIT, "cores": threads, "kind": "port",
+                            "sample": "8 of 64 sequences, 50 + 50 steps, fp32 (%.2f s)" % dt}
     return out
 
 
@@ -337,6 +348,20 @@ def other_configs(ops, dev, pk, cpu):
                          cache="three rotating q/k/v/o sets of 134 MB", tokens_per_s=2 * 16 * 4096 / (ms * 1e-3),
                          cpu_baseline=cpu.get("sparse")))
     del sa, pos
+
+    # attention RNN at the example's hidden size (512), batch 64, 50 source and 50 target positions, bf16
+    Hr, Nr, Lr = 512, 64, 50
+    rp = [uni(1 / math.sqrt(Hr), Hr, Hr).bfloat16() for _ in range(4)]
+    Wps, Wpt = ops.rnn_pack_weights(rp[0], rp[1]), ops.rnn_pack_weights(rp[2], rp[3])
+    xs_, ys_ = rnd(Lr, Nr, Hr).bfloat16(), rnd(Lr, Nr, Hr).bfloat16()
+    ep, dp = torch.rand(Hr, device=dev, generator=g).bfloat16(), torch.rand(Hr, device=dev, generator=g).bfloat16()
+    ms = timed(lambda: ops.rnn_attention(xs_, ys_, Wps, Wpt, None, None, ep, dp), 10)
+    out.append(tensor_entry("attention RNN bf16 H512 N64, 50 source + 50 target steps", ms,
+                            2 * Lr * Nr * 2 * (2 * Hr) * Hr, samples_steps_per_s=Nr * 2 * Lr / (ms * 1e-3),
+                            note="one launch per source step, two per target step: 151 dependent launches; "
+                                 "latency-bound, the tensor roofline is quoted for context",
+                            cpu_baseline=cpu.get("rnn_attention")))
+    del rp, Wps, Wpt, xs_, ys_
 
     # config 1: stacked LSTM fp32 D4 H256 N32 L64 (CUDA cores; the reference's own CPU-runnable case)
     x1, W1, U1 = lstm_inputs(4, 64, 32, 256, 256, 0, 1.0 / 16, torch.float32)

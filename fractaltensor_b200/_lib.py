@@ -37,6 +37,8 @@ SIGNATURES = {
     "ftb_flash_attn_causal_fwd": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp]),
     "ftb_flash_attn_window_fwd": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp]),
     "ftb_flash_attn_local_fwd": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp]),
+    "ftb_rnn_pack_weights": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "ftb_rnn_attention_fwd": (_i, [_vp] * 13 + [_i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "ftb_sparse_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _sz, _vp]),
     "ftb_embedding_gather": (_i, [_vp, _vp, _vp, ctypes.c_longlong, ctypes.c_longlong, _i, _i, _vp, _sz, _vp]),
     "ftb_online_softmax": (_i, [_vp, _vp, _i, _i, _vp]),

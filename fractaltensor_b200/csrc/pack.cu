@@ -106,4 +106,19 @@ int pack_grid(const void* i2h, const void* h2h, void* Wp, int H, int dtype, cuda
   return rc;
 }
 
+// Tanh RNN cell: Wp[u, k] = W[k, u] for k < I, U[k - I, u] for the H recurrent inputs behind them.
+int pack_rnn(const void* W, const void* U, void* Wp, int I, int H, int dtype, cudaStream_t s) {
+  int rc;
+  if (dtype_size(dtype) == 4) {
+    rc = pack_matrix<float>(static_cast<const float*>(W), static_cast<float*>(Wp), 1, I, H, I + H, 0, s);
+    if (rc) return rc;
+    rc = pack_matrix<float>(static_cast<const float*>(U), static_cast<float*>(Wp), 1, H, H, I + H, I, s);
+  } else {
+    rc = pack_matrix<uint16_t>(static_cast<const uint16_t*>(W), static_cast<uint16_t*>(Wp), 1, I, H, I + H, 0, s);
+    if (rc) return rc;
+    rc = pack_matrix<uint16_t>(static_cast<const uint16_t*>(U), static_cast<uint16_t*>(Wp), 1, H, H, I + H, I, s);
+  }
+  return rc;
+}
+
 }  // namespace ftb

@@ -50,6 +50,12 @@ int pack_lstm(const void* W, const void* U, const void* bias, void* Wp, float* b
               cudaStream_t s);
 int pack_grid(const void* i2h, const void* h2h, void* Wp, int H, int dtype, cudaStream_t s);
 int pack_projection(const void* P, void* Pt, int H, int V, int Vp, int dtype, cudaStream_t s);
+int pack_rnn(const void* W, const void* U, void* Wp, int I, int H, int dtype, cudaStream_t s);
+int rnn_attention_max_src_len();
+int launch_enc_scores(int dtype, const void* enc, const void* proj, float* scores, long long n_rows, int H,
+                      cudaStream_t stream);
+int launch_attn_step(int dtype, const void* enc, const float* enc_scores, const void* dec_t, const void* dec_proj,
+                     const int* src_lens, void* out_t, int Ls, int N, int H, cudaStream_t stream);
 int online_softmax_rows(const float* x, float* y, int rows, int width, int ld, cudaStream_t stream);
 
 namespace {
@@ -1073,6 +1079,105 @@ int ftb_grid_rnn_fwd(const void* X, const void* Y, const void* Wpx, const void* 
         }
       }
     rc = cl.run(items);
+    if (rc) return rc;
+  }
+  return FTB_OK;
+}
+
+int ftb_rnn_pack_weights(const void* W, const void* U, void* Wp, int I, int H, int dtype, void* stream) {
+  if (!W || !U || !Wp || I <= 0 || H <= 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
+  return pack_rnn(W, U, Wp, I, H, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int ftb_rnn_attention_fwd(const void* src, const void* trg, const void* Wp_src, const void* Wp_trg,
+                          const float* bias_src, const float* bias_trg, const void* enc_proj, const void* dec_proj,
+                          const int* src_lens, void* enc, float* enc_scores, void* dec, void* out, int Ls, int Lt,
+                          int N, int H, int dtype, void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!src || !trg || !Wp_src || !Wp_trg || !enc_proj || !dec_proj || !enc || !enc_scores || !dec || !out)
+    return FTB_ERR_ARG;
+  if (Ls <= 0 || Lt <= 0 || N <= 0 || H <= 0 || H % 64 != 0 || !valid_dtype(dtype)) return FTB_ERR_ARG;
+  if (Ls > rnn_attention_max_src_len()) return FTB_ERR_ARG;
+  if (static_cast<int64_t>(std::max(Ls, Lt)) * N > 0x7fffffffLL) return FTB_ERR_ARG;
+  if (!aligned16({src, trg, Wp_src, Wp_trg, bias_src, bias_trg, enc, dec, out})) return FTB_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(enc_scores) & 3) != 0 || (reinterpret_cast<uintptr_t>(src_lens) & 3) != 0)
+    return FTB_ERR_ALIGN;
+  int* status = nullptr;
+  int rc = begin_call(workspace, workspace_bytes, stream, &status);
+  if (rc) return rc;
+
+  const int K = 2 * H;
+  const size_t es = dtype_size(dtype);
+  // One launch context for both cells: activation buffers 0..3 = src, trg, enc, out (the attention
+  // vectors, which are the decoder's recurrent input); weight buffer 0 = encoder, 1 = decoder.
+  CellLauncher cl;
+  cl.dtype = dtype;
+  cl.epi = EPI_TANH;
+  cl.n_cols = H;
+  cl.ld_out = H;
+  cl.ld_c = H;
+  cl.status = status;
+  cl.stream = stream;
+  cl.sm_count = current_sm_count();
+  if (dtype == FTB_F32) {
+    cl.act[0] = static_cast<const float*>(src);
+    cl.act[1] = static_cast<const float*>(trg);
+    cl.act[2] = static_cast<const float*>(enc);
+    cl.act[3] = static_cast<const float*>(out);
+    cl.ld_act[0] = cl.ld_act[1] = cl.ld_act[2] = cl.ld_act[3] = H;
+    cl.w = static_cast<const float*>(Wp_src);
+    cl.w2 = static_cast<const float*>(Wp_trg);
+    cl.ldw = K;
+  } else {
+    cl.bn = pick_bn(H, 128);
+    if (cl.bn == 0) return FTB_ERR_ARG;
+    const uint64_t src_rows = static_cast<uint64_t>(Ls) * N, trg_rows = static_cast<uint64_t>(Lt) * N;
+    rc = make_tmap_2d(&cl.maps[0], src, dtype, src_rows, H, H, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.maps[1], trg, dtype, trg_rows, H, H, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.maps[2], enc, dtype, src_rows, H, H, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.maps[3], out, dtype, trg_rows, H, H, 128, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.mapW, Wp_src, dtype, H, K, K, cl.bn, 64);
+    if (rc) return rc;
+    rc = make_tmap_2d(&cl.mapC, Wp_trg, dtype, H, K, K, cl.bn, 64);
+    if (rc) return rc;
+  }
+
+  std::vector<CellItem> items(1);
+  // Encoder: e_j = tanh(x_j W + e_{j-1} U + b), one level per source position.
+  for (int j = 0; j < Ls; ++j) {
+    CellItem it = blank_item();
+    add_seg(it, 0, static_cast<int64_t>(j) * N, H, 0);
+    if (j > 0) add_seg(it, 2, static_cast<int64_t>(j - 1) * N, H, H);
+    it.rows = N;
+    it.w_map = 0;
+    it.bias = bias_src;
+    it.out = static_cast<char*>(enc) + static_cast<size_t>(j) * N * H * es;
+    items[0] = it;
+    rc = cl.run(items);
+    if (rc) return rc;
+  }
+  rc = launch_enc_scores(dtype, enc, enc_proj, enc_scores, static_cast<long long>(Ls) * N, H, stream);
+  if (rc) return rc;
+  // Decoder: the cell, then the attention over the encoder rows; its result is both the step's
+  // output and the next step's recurrent input.
+  for (int t = 0; t < Lt; ++t) {
+    CellItem it = blank_item();
+    add_seg(it, 1, static_cast<int64_t>(t) * N, H, 0);
+    if (t > 0) add_seg(it, 3, static_cast<int64_t>(t - 1) * N, H, H);
+    it.rows = N;
+    it.w_map = 1;
+    it.bias = bias_trg;
+    char* dec_t = static_cast<char*>(dec) + static_cast<size_t>(t) * N * H * es;
+    it.out = dec_t;
+    items[0] = it;
+    rc = cl.run(items);
+    if (rc) return rc;
+    rc = launch_attn_step(dtype, enc, enc_scores, dec_t, dec_proj, src_lens,
+                          static_cast<char*>(out) + static_cast<size_t>(t) * N * H * es, Ls, N, H, stream);
     if (rc) return rc;
   }
   return FTB_OK;

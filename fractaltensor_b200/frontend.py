@@ -10,6 +10,7 @@ over ``FractalTensor`` values (flat ``.data`` buffer plus nested ``.indices``):
     flash_attention(qsss, ksss, vsss)                  examples/flash_attention/flash_attention.py:75-88
     embed(words, embedding)                            examples/stacked_rnn/rnn_utils.py:80-90 (the lookup in front)
     sparse_attention(query, key, value, random_attn)   examples/sparse_attention/sparse_attention.py:41-76, 109-114
+    rnn_attention(src_embs, trg_embs, ...)             examples/rnn_attention/rnn_attention.py:86-110 (behind the lookups)
 
 The functions here keep those argument lists and return the same nested values,
 but run the whole nest as one fused wavefront on the GPU.  Arguments may be the
@@ -303,3 +304,47 @@ def sparse_attention(query_proj, key_proj, value_proj, random_attn, window_size=
                              window_size=window_size, dilation=dilation, n_global=n_global, scale=scale,
                              as_shipped=as_shipped)
     return FractalTensor.from_dense(o.reshape(*lead, S, 1, d), depth)
+
+
+def _tensor_of(x):
+    return x.data if hasattr(x, "data") and not isinstance(x, torch.Tensor) else x
+
+
+def _pad_time_major(x, dtype):
+    """Batch-major ragged FractalTensor [N][L_n] of [1,H] -> ([Lmax, N, H] zero-padded, lens, row index)."""
+    lens = [len(seq) for seq in x.indices]
+    if not lens or min(lens) <= 0:
+        raise ValueError("empty batch or empty sequence")
+    flat = _cuda(x.data.reshape(sum(lens), -1), dtype)
+    N, L, H = len(lens), max(lens), flat.shape[1]
+    # position in the padded [L, N] grid of every row of the batch-major buffer
+    idx = torch.tensor([t * N + n for n in range(N) for t in range(lens[n])], dtype=torch.long, device=flat.device)
+    padded = torch.zeros(L * N, H, dtype=flat.dtype, device=flat.device)
+    padded.index_copy_(0, idx, flat)
+    return padded.reshape(L, N, H), lens, idx
+
+
+def rnn_attention(src_embs, trg_embs, src_params, trg_params, attn_params, dtype=None):
+    """The attention RNN behind the word lookups (examples/rnn_attention/rnn_attention.py:86-110):
+    ``src_enc_outs = map(scan(cell))`` over the source sequences, then ``map(attn_layer)`` over the
+    (encoder states, target sequence) pairs.
+
+    src_embs, trg_embs: FractalTensors [N][L_n] of [1,H] rows (ragged or not, any order);
+    src_params, trg_params: (W [H,H], U [H,H], b [1,H]) as CellParams; attn_params: (encoder_proj
+    [H,1], decoder_proj [H,1]).  Returns the attention vectors with the nesting of trg_embs."""
+    src, src_lens, _ = _pad_time_major(src_embs, dtype)
+    trg, trg_lens, trg_idx = _pad_time_major(trg_embs, dtype)
+    if len(src_lens) != len(trg_lens):
+        raise ValueError("rnn_attention: source and target batches differ in size")
+    dt, dev = src.dtype, src.device
+    H = src.shape[2]
+    par = lambda t: _cuda(_tensor_of(t), dt).contiguous()
+    Ws, Us, bs = (par(t) for t in src_params)
+    Wt, Ut, bt = (par(t) for t in trg_params)
+    enc_proj, dec_proj = (par(t).reshape(H) for t in attn_params)
+    lens = torch.tensor(src_lens, dtype=torch.int32, device=dev)
+    _, out = ops.rnn_attention(src, trg.to(dt), ops.rnn_pack_weights(Ws, Us), ops.rnn_pack_weights(Wt, Ut),
+                               bs.reshape(H).float().contiguous(), bt.reshape(H).float().contiguous(), enc_proj,
+                               dec_proj, lens)
+    rows = out.reshape(-1, H).index_select(0, trg_idx)
+    return FractalTensor(rows.contiguous(), [list(range(n)) for n in trg_lens], (1, H))

@@ -347,6 +347,56 @@ def sparse_attention(q, k, v, rand_pos, window_size=5, dilation=2, n_global=3, s
     return out
 
 
+def rnn_pack_weights(W, U):
+    """Tanh RNN cell h = tanh(x W + s U + b): W [I,H], U [H,H] -> Wp [H, I+H] (K-major rows)."""
+    _req(W, "W")
+    _req(U, "U", W.dtype)
+    I, H = W.shape
+    if tuple(U.shape) != (H, H):
+        raise ValueError("expected W [I,H] and U [H,H]")
+    Wp = torch.empty(H, I + H, dtype=W.dtype, device=W.device)
+    with torch.cuda.device(W.device):
+        check(lib.ftb_rnn_pack_weights(_ptr(W), _ptr(U), _ptr(Wp), I, H, _dtype_code(W), _stream()),
+              "ftb_rnn_pack_weights")
+    return Wp
+
+
+def rnn_attention(src, trg, Wp_src, Wp_trg, bias_src, bias_trg, enc_proj, dec_proj, src_lens=None):
+    """Attention RNN (examples/rnn_attention/rnn_attention.py:40-110) on time-major padded batches.
+
+    src [Ls,N,H], trg [Lt,N,H]; Wp_* from rnn_pack_weights (I = H); bias_* fp32 [H] or None;
+    enc_proj, dec_proj [H]; src_lens int32 [N] on the device or None (every sequence Ls long).
+    Returns (enc [Ls,N,H], out [Lt,N,H]): the encoder states and the attention vectors, which are
+    the program's result.  Rows past a sequence's own length are not meaningful."""
+    _req(src, "src")
+    _req(trg, "trg", src.dtype)
+    if src.dim() != 3 or trg.dim() != 3 or trg.shape[1:] != src.shape[1:]:
+        raise ValueError("rnn_attention: expected src [Ls,N,H] and trg [Lt,N,H]")
+    Ls, N, H = src.shape
+    Lt = trg.shape[0]
+    _req_like(Wp_src, "Wp_src", src.dtype, (H, 2 * H), src)
+    _req_like(Wp_trg, "Wp_trg", src.dtype, (H, 2 * H), src)
+    _req_like(enc_proj, "enc_proj", src.dtype, (H,), src)
+    _req_like(dec_proj, "dec_proj", src.dtype, (H,), src)
+    for b_, name in ((bias_src, "bias_src"), (bias_trg, "bias_trg")):
+        if b_ is not None:
+            _req_like(b_, name, torch.float32, (H,), src)
+    if src_lens is not None:
+        _req_like(src_lens, "src_lens", torch.int32, (N,), src)
+    enc = torch.empty_like(src)
+    dec = torch.empty_like(trg)
+    out = torch.empty_like(trg)
+    scores = torch.empty(Ls, N, dtype=torch.float32, device=src.device)
+    ws = workspace(src.device)
+    opt = lambda t: _ptr(t) if t is not None else None
+    with torch.cuda.device(src.device):
+        check(lib.ftb_rnn_attention_fwd(_ptr(src), _ptr(trg), _ptr(Wp_src), _ptr(Wp_trg), opt(bias_src), opt(bias_trg),
+                                        _ptr(enc_proj), _ptr(dec_proj), opt(src_lens), _ptr(enc), _ptr(scores),
+                                        _ptr(dec), _ptr(out), Ls, Lt, N, H, _dtype_code(src), _ptr(ws), ws.numel(),
+                                        _stream()), "ftb_rnn_attention_fwd")
+    return enc, out
+
+
 def gemm_nt(A, Bt, out=None, bn=0, pair=0):
     """A: [M,K]; Bt: [N,K] -> A @ Bt^T."""
     _req(A, "A")

@@ -243,6 +243,29 @@ int ftb_sparse_attn_fwd(const void* q, const void* k, const void* v, const int* 
                         int heads, int S, int d, int window, int dilation, int n_global, int R, float scale,
                         int as_shipped, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Packs the weights of a tanh RNN cell h = tanh(x.W + s.U + b) (cell(),
+ * examples/rnn_attention/rnn_attention.py:40-48): W [I, H], U [H, H] of `dtype` ->
+ * Wp [H, I + H], row u = (W[:, u] | U[:, u]). */
+int ftb_rnn_pack_weights(const void* W, const void* U, void* Wp, int I, int H, int dtype, void* stream);
+
+/* Attention RNN forward: model() of examples/rnn_attention/rnn_attention.py:86-110 behind the word
+ * lookups.  Encoder: e_j = tanh(x_j.Ws + e_{j-1}.Us + bs) scanned over the source from zeros.
+ * Decoder scan (attn_func, lines 52-70), carried value v: dec_t = tanh(y_t.Wt + v_{t-1}.Ut + bt),
+ * score_j = e_j.enc_proj + dec_t.dec_proj, w = softmax over the source positions, v_t = sum_j w_j e_j;
+ * the program's result is the v_t.
+ * Time-major padded batches: src [Ls, N, H], trg [Lt, N, H] of `dtype` (fp32: CUDA cores; fp16 /
+ * bf16: tensor cores, fp32 accumulation); Wp_src, Wp_trg from ftb_rnn_pack_weights with I = H;
+ * bias_src, bias_trg: fp32 [H] or NULL; enc_proj, dec_proj: [H] of `dtype`; src_lens: int32 [N] on
+ * the device, sequence n attends to source positions j < src_lens[n] (NULL: all Ls).
+ * Outputs (caller-owned): enc [Ls, N, H] encoder states, enc_scores fp32 [Ls, N] (e_j.enc_proj),
+ * dec [Lt, N, H] decoder states, out [Lt, N, H] the attention vectors.  Rows of a sequence past its
+ * own source / target length hold values nobody should read.  H % 64 == 0, Ls <= 12288.
+ * One launch per source position, one for the scores, two per target position. */
+int ftb_rnn_attention_fwd(const void* src, const void* trg, const void* Wp_src, const void* Wp_trg,
+                          const float* bias_src, const float* bias_trg, const void* enc_proj, const void* dec_proj,
+                          const int* src_lens, void* enc, float* enc_scores, void* dec, void* out, int Ls, int Lt,
+                          int N, int H, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Embedding lookup out[t, :] = table[ids[t], :] for t < T.  Stands in for the lookup in front of
  * the reference's RNN examples, ops.index(ops.slices(embedding, dim=0), word) mapped over a batch
  * of word sequences (examples/stacked_rnn/rnn_utils.py:80-90): `ids` is the flat int64 buffer of

@@ -264,6 +264,41 @@ def sparse_attention_dense(q, k, v, rand_pos, window_size=5, dilation=2, n_globa
     return out
 
 
+def rnn_attention_dense(src, trg, src_lens, trg_lens, Ws, Us, bs, Wt, Ut, bt, enc_proj, dec_proj):
+    """Attention RNN: model() of examples/rnn_attention/rnn_attention.py:86-110 behind the lookups.
+
+    Per sequence pair: the encoder is a tanh RNN over the source rows,
+    ``e_j = tanh(x_j @ Ws + e_{j-1} @ Us + bs)`` (cell(), lines 40-48, scanned from zeros, 99-103);
+    the decoder scan (attn_func / attn_layer, lines 52-83) carries the attention vector:
+    ``dec_t = tanh(y_t @ Wt + v_{t-1} @ Ut + bt)``, ``score_j = e_j @ enc_proj + dec_t @ dec_proj``,
+    ``w = softmax_j(score)``, ``v_t = sum_j w_j e_j``, v_{-1} = 0; the program returns the v_t.
+    src: [sum(src_lens), H] and trg: [sum(trg_lens), H], the sequences one after the other;
+    Ws, Us, Wt, Ut: [H, H]; bs, bt: [1, H]; enc_proj, dec_proj: [H, 1].
+    Returns (enc [sum(src_lens), H], out [sum(trg_lens), H])."""
+    H = src.shape[1]
+    encs, outs = [], []
+    so = to = 0
+    for ls, lt in zip(src_lens, trg_lens):
+        ls, lt = int(ls), int(lt)
+        e = torch.zeros(1, H, dtype=src.dtype)
+        rows = []
+        for j in range(ls):
+            e = torch.tanh(src[so + j:so + j + 1] @ Ws + e @ Us + bs)
+            rows.append(e)
+        E = torch.cat(rows, dim=0)  # [ls, H]
+        es = E @ enc_proj            # [ls, 1]
+        v = torch.zeros(1, H, dtype=src.dtype)
+        for t in range(lt):
+            dec = torch.tanh(trg[to + t:to + t + 1] @ Wt + v @ Ut + bt)
+            w = torch.softmax(es + dec @ dec_proj, dim=0)  # over the encoder positions
+            v = (w * E).sum(dim=0, keepdim=True)
+            outs.append(v)
+        encs.append(E)
+        so += ls
+        to += lt
+    return torch.cat(encs, dim=0), torch.cat(outs, dim=0)
+
+
 def embedding_gather_dense(table, ids):
     """One table row per word, in the order of the flat word buffer.
 

@@ -266,6 +266,57 @@ def main():
          window_size=5, dilation=2)
     print("sparse attention", out.shape)
 
+    # ---------------------------------------------------------------- attention RNN
+    def run_rnn_attention(src_lens, trg_lens, H, seed, w_bound):
+        """model() of examples/rnn_attention/rnn_attention.py:86-110 behind the word lookups: a tanh RNN
+        over each source sequence, then the attention scan over each target sequence, with the
+        reference's own scan / map / reduce / softmax / scale / add on ragged batches."""
+        g = torch.Generator().manual_seed(seed)
+        uni = lambda *shape: (torch.rand(*shape, generator=g) * 2 - 1) * w_bound
+        N = len(src_lens)
+        src = torch.randn(sum(src_lens), H, generator=g)
+        trg = torch.randn(sum(trg_lens), H, generator=g)
+        Ws, Us, bs, Wt, Ut, bt = uni(H, H), uni(H, H), uni(1, H), uni(H, H), uni(H, H), uni(1, H)
+        enc_proj, dec_proj = torch.rand(H, 1, generator=g), torch.rand(H, 1, generator=g)
+
+        def tensor(t):
+            x = Tensor(tuple(t.shape), kaleido.float32, device="cpu")
+            x.data = t.clone()
+            return x
+
+        src_params = tuple(tensor(t) for t in (Ws, Us, bs))
+        trg_params = tuple(tensor(t) for t in (Wt, Ut, bt))
+        encoder_proj, decoder_proj = tensor(enc_proj), tensor(dec_proj)
+
+        def cell(state, hidden, i2h, h2h, bias):
+            return ops.tanh(hidden @ i2h + state @ h2h + bias)
+
+        def attn_func(state, cur, encoders, params):
+            decoder = cell(state, cur, *params)
+            scores = ops.map(lambda x: x @ encoder_proj + decoder @ decoder_proj, encoders)
+            weights = ops.slices(ops.softmax(ops.flatten(scores)), dim=0)
+            return ops.reduce(lambda s, x: ops.add(s, x),
+                              ops.map(lambda x: ops.scale(*x), ops.zip(weights, encoders)))
+
+        def attn_layer(srcs, trgs, params):
+            return ops.scan(lambda s, x: attn_func(s, x, srcs, params), trgs,
+                            initializer=ops.zeros(shape=(1, H), device="cpu"))
+
+        def ragged(t, lens):
+            return ft(t.reshape(-1, 1, H), (1, H), [list(range(n)) for n in lens])
+
+        src_embs, trg_embs = ragged(src, src_lens), ragged(trg, trg_lens)
+        src_enc_outs = ops.map(lambda xs: ops.scan(lambda s_, x: cell(s_, x, *src_params), xs,
+                                                   initializer=ops.zeros(shape=(1, H), device="cpu")), src_embs)
+        yss = ops.map(lambda x: attn_layer(*x, trg_params), ops.zip(src_enc_outs, trg_embs))
+        return dict(src=src, trg=trg, Ws=Ws, Us=Us, bs=bs, Wt=Wt, Ut=Ut, bt=bt, enc_proj=enc_proj, dec_proj=dec_proj,
+                    enc=src_enc_outs.data.reshape(-1, H).clone(), out=yss.data.reshape(-1, H).clone())
+
+    r = run_rnn_attention([5, 3, 7], [4, 6, 2], 16, 23, 0.25)
+    save("rnn_attention_small", src_lens=np.array([5, 3, 7]), trg_lens=np.array([4, 6, 2]),
+         **{k_: v_.numpy() for k_, v_ in r.items()})
+    print("rnn attention", r["out"].shape)
+
     # ---------------------------------------------------------------------- dilated
     def run_dilated(D, L, N, H, seed, w_bound):
         x, W, U, _ = dense.make_lstm_inputs(D, L, N, H, H, seed, w_bound)

@@ -74,6 +74,14 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
     assert sp(window=9, dilation=4) == 1   # half = 16 >= S: the wrap is a single step
     assert sp(window=63, dilation=1, S=128, R=2) == 1  # more than 64 keys per token
     assert sp(pos=z) == 1             # R > 0 without positions
+    ra = lambda **kw: lib.ftb_rnn_attention_fwd(
+        one, one, one, one, z, z, one, one, z, one, kw.get("scores", one), one, one, kw.get("Ls", 4), kw.get("Lt", 3),
+        2, kw.get("H", 64), 1, one, 256, z)
+    assert ra(H=48) == 1
+    assert ra(Ls=0) == 1
+    assert ra(Ls=20000) == 1          # the scores of one sequence must fit in shared memory
+    assert ra(scores=z) == 1
+    assert lib.ftb_rnn_pack_weights(one, one, z, 64, 64, 1, z) == 1
     rows = (ctypes.c_int * 3)(4, 5, 1)  # not sorted by decreasing length
     assert lib.ftb_lstm_stacked_varlen_fwd(one, one, z, one, one, rows, 1, 3, 64, 64, 1, None, one, 256, z) == 1
     rows = (ctypes.c_int * 3)(4, 2, 0)  # a step without sequences

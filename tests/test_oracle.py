@@ -201,3 +201,14 @@ def test_sparse_attention_matches_reference_frontend(golden_dir):
     rows = [x + S - 1 if x < 0 else (x - S if x >= S else x) for x in range(i - half, i + half + 1, dil)]
     rows += g["rand_pos"][i - 3].tolist()
     assert torch.allclose(g["out"][i], g["v"][rows].sum(dim=0), atol=1e-5)
+
+
+def test_rnn_attention_matches_reference_frontend(golden_dir):
+    """The attention RNN (tanh encoder scan, attention scan over the targets) run through the
+    reference's own scan / map / reduce / softmax / scale / add on ragged batches."""
+    g = _load(golden_dir, "rnn_attention_small.npz")
+    enc, out = dense.rnn_attention_dense(g["src"], g["trg"], g["src_lens"], g["trg_lens"], g["Ws"], g["Us"], g["bs"],
+                                         g["Wt"], g["Ut"], g["bt"], g["enc_proj"], g["dec_proj"])
+    assert enc.shape == g["enc"].shape and out.shape == g["out"].shape
+    assert (enc - g["enc"]).abs().max().item() <= 1e-6
+    assert (out - g["out"]).abs().max().item() <= 1e-6
