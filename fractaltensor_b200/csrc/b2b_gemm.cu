@@ -84,7 +84,9 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   __shared__ int s_abort;
 
   if (threadIdx.x == 0) B2B_WALL(0);
-  if (*reinterpret_cast<volatile int*>(status) != 0) return;
+  // The call behind this one may be scheduled as SMs free up; it touches no global memory
+  // before its own grid_dependency_wait().
+  grid_launch_dependents();
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -96,14 +98,6 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   uint8_t* sD = sA + kAStages * sh.a_bytes;
   constexpr int nchunks = NCH;
   constexpr int k_halves = KK / 64, p_halves = PP / 64;
-
-  // Contiguous tile range of this CTA.
-  const int per = sh.total_tiles / gridDim.x, rem = sh.total_tiles % gridDim.x;
-  const int first = blockIdx.x * per + (blockIdx.x < rem ? blockIdx.x : rem);
-  const int count = per + (blockIdx.x < rem ? 1 : 0);
-  const int units = count * nchunks;
-  const int batch0 = count > 0 ? first / sh.tiles_per_batch : 0;
-  const int batch_last = count > 0 ? (first + count - 1) / sh.tiles_per_batch : -1;
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&mapA);
@@ -135,6 +129,18 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
+  // Set-up is done; from here on the kernel reads and writes global memory, so the call before it
+  // in the stream must have finished.  A non-zero status word (sticky) turns the call into a no-op.
+  grid_dependency_wait();
+  const bool live = *reinterpret_cast<volatile int*>(status) == 0;
+  // Contiguous tile range of this CTA.
+  const int per = live ? sh.total_tiles / gridDim.x : 0, rem = live ? sh.total_tiles % gridDim.x : 0;
+  const int first = blockIdx.x * per + (blockIdx.x < rem ? blockIdx.x : rem);
+  const int count = per + (blockIdx.x < rem ? 1 : 0);
+  const int units = count * nchunks;
+  const int batch0 = count > 0 ? first / sh.tiles_per_batch : 0;
+  const int batch_last = count > 0 ? (first + count - 1) / sh.tiles_per_batch : -1;
+
   // TMEM columns: S0 [0,128), S1 [128,256), O0 [256,256+P), O1 [384,384+P); P_u (16-bit pairs)
   // overlays the first 64 columns of S_u.
 
@@ -368,9 +374,10 @@ int launch(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mC, 
   auto kfn = b2b_gemm_kernel<T, KK, PP, NCH>;
   if (!ensure_dynamic_smem(kfn, kSmemBudget + 1024, configured)) return FTB_ERR_LAUNCH;
   const int grid = sh.total_tiles < sm_count ? sh.total_tiles : sm_count;
-  kfn<<<grid, kThreads, smem_bytes, stream>>>(mA, mB, mC, mD, sh, status);
+  const cudaError_t err = launch_dependent(kfn, dim3(grid), dim3(kThreads), smem_bytes, stream, mA, mB, mC, mD, sh, status);
   count_launch();
-  return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+  if (err != cudaSuccess) cudaGetLastError();
+  return err == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
 
 }  // namespace

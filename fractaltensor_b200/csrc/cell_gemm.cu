@@ -130,9 +130,9 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
   __shared__ uint32_t peer_tmem_base_s;
   __shared__ int s_abort;
 
-  // A launch that follows a failed one does nothing.  (Not for pairs: both CTAs of
-  // a pair must take the same path, and the persistent schedule is a single launch.)
-  if (!PAIR && *reinterpret_cast<volatile int*>(status) != 0) return;
+  // One launch per level: the next level's launch may be scheduled as SMs free up; it touches no
+  // global memory before its own grid_dependency_wait().
+  grid_launch_dependents();
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -176,7 +176,12 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
-  const int total = batch.total_tiles;
+  // Set-up is done; what follows reads and writes global memory, so the launch before this one
+  // must have finished.  A launch that follows a failed one does nothing.  (Not for pairs: both
+  // CTAs of a pair must take the same path, and the persistent schedule is a single launch.)
+  grid_dependency_wait();
+  const bool live = PAIR || *reinterpret_cast<volatile int*>(status) == 0;
+  const int total = live ? batch.total_tiles : 0;
   if (PAIR) {
     // Both CTAs of a pair must hold their accumulators at the same TMEM columns.
     if (threadIdx.x == 0 && rank == 1) st_shared_cluster_u32(map_to_cta(smem_u32(&peer_tmem_base_s), 0), tmem_base);
@@ -624,7 +629,7 @@ int launch_one(const CUtensorMap* maps, const CUtensorMap& mapW, const CUtensorM
   cfg.blockDim = dim3(C::kThreads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attrs[2];
+  cudaLaunchAttribute attrs[3];
   int na = 0;
   if (PAIR) {
     attrs[na].id = cudaLaunchAttributeClusterDimension;
@@ -651,6 +656,13 @@ int launch_one(const CUtensorMap* maps, const CUtensorMap& mapW, const CUtensorM
     // CTA's counter always makes progress.
     attrs[na].id = cudaLaunchAttributeCooperative;
     attrs[na].val.cooperative = 1;
+    ++na;
+  }
+  if (!PERSIST && grid < sm_count) {
+    // Level launches follow one another on the stream: when a level leaves SMs idle, let the next one
+    // set up there while this one drains (with grids that fill the device it was measured slower).
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
   }
   cfg.attrs = attrs;

@@ -26,6 +26,8 @@ embedding_gather_kernel(const unsigned char* __restrict__ table, const long long
   const int lane = threadIdx.x & 31;
   const long long warp = (static_cast<long long>(blockIdx.x) * kGatherThreads + threadIdx.x) >> 5;
   const long long n_warps = (static_cast<long long>(gridDim.x) * kGatherThreads) >> 5;
+  grid_launch_dependents();
+  grid_dependency_wait();
   for (long long t = warp; t < T; t += n_warps) {
     const long long id = ids[t];
     const bool ok = id >= 0 && id < V;
@@ -70,9 +72,10 @@ extern "C" int ftb_embedding_gather(const void* table, const long long* ids, voi
   const long long ctas_needed = (warps_needed * 32 + kGatherThreads - 1) / kGatherThreads;
   const long long full = static_cast<long long>(current_sm_count()) * 8;  // 8 CTAs of 256 threads per SM
   const int grid = static_cast<int>(ctas_needed < full ? ctas_needed : full);
-  embedding_gather_kernel<<<grid, kGatherThreads, 0, stream>>>(static_cast<const unsigned char*>(table), ids,
-                                                               static_cast<unsigned char*>(out), T, V,
-                                                               static_cast<int>(row_bytes), vec16 ? 1 : 0, status);
+  const cudaError_t err = launch_dependent(embedding_gather_kernel, dim3(grid), dim3(kGatherThreads), 0, stream,
+                                           static_cast<const unsigned char*>(table), ids, static_cast<unsigned char*>(out),
+                                           T, V, static_cast<int>(row_bytes), vec16 ? 1 : 0, status);
   count_launch();
-  return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+  if (err != cudaSuccess) cudaGetLastError();
+  return err == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }

@@ -60,6 +60,8 @@ online_softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int ro
   __shared__ float final_m, final_d;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int cached_floats = width < cache_floats ? width : cache_floats;  // prefix of the row kept on chip
+  grid_launch_dependents();
+  grid_dependency_wait();  // the kernel before this one (the projection GEMM, say) wrote x
   // 16-byte accesses need rows that start on a 16-byte boundary.
   const bool vec = ((width | ld) & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
 
@@ -150,6 +152,8 @@ online_softmax_warp_kernel(const float* __restrict__ x, float* __restrict__ y, i
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = kSoftmaxThreads / 32;
   const int n4 = width / 4;
+  grid_launch_dependents();
+  grid_dependency_wait();
   for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
     const float4* x4 = reinterpret_cast<const float4*>(x + static_cast<size_t>(r) * ld);
     float4* y4 = reinterpret_cast<float4*>(y + static_cast<size_t>(r) * ld);
@@ -206,10 +210,11 @@ int online_softmax_rows(const float* x, float* y, int rows, int width, int ld, c
   if (aligned16 && ((width | ld) & 3) == 0 && width <= 32 * 4 * kMaxV && rows >= 8) {
     const int64_t ctas = (static_cast<int64_t>(rows) + kSoftmaxThreads / 32 - 1) / (kSoftmaxThreads / 32);
     const int64_t full = static_cast<int64_t>(current_sm_count()) * 4;
-    online_softmax_warp_kernel<<<static_cast<int>(ctas < full ? ctas : full), kSoftmaxThreads, 0, stream>>>(x, y, rows,
-                                                                                                            width, ld);
+    const cudaError_t err = launch_dependent(online_softmax_warp_kernel, dim3(static_cast<int>(ctas < full ? ctas : full)),
+                                             dim3(kSoftmaxThreads), 0, stream, x, y, rows, width, ld);
     count_launch();
-    return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+    if (err != cudaSuccess) cudaGetLastError();
+    return err == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
   }
   // Row cache: the row, or its first 48 K floats, in up to 192 KB of shared memory.
   constexpr int kMaxCacheFloats = 48 * 1024;
@@ -228,12 +233,16 @@ int online_softmax_rows(const float* x, float* y, int rows, int width, int ld, c
   per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
   const int64_t want = static_cast<int64_t>(current_sm_count()) * per_sm;
   const int grid = static_cast<int>(rows < want ? rows : want);
+  cudaError_t err;
   if (per_sm <= 2)
-    online_softmax_kernel<1024><<<grid, 1024, smem, stream>>>(x, y, rows, width, ld, cache_floats);
+    err = launch_dependent(online_softmax_kernel<1024>, dim3(grid), dim3(1024), smem, stream, x, y, rows, width, ld,
+                           cache_floats);
   else
-    online_softmax_kernel<kSoftmaxThreads><<<grid, kSoftmaxThreads, smem, stream>>>(x, y, rows, width, ld, cache_floats);
+    err = launch_dependent(online_softmax_kernel<kSoftmaxThreads>, dim3(grid), dim3(kSoftmaxThreads), smem, stream, x, y,
+                           rows, width, ld, cache_floats);
   count_launch();
-  return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+  if (err != cudaSuccess) cudaGetLastError();
+  return err == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
 }  // namespace ftb
 

@@ -53,6 +53,8 @@ row_dot_kernel(const T* __restrict__ rows, const T* __restrict__ proj, float* __
   const int lane = threadIdx.x & 31;
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  grid_launch_dependents();
+  grid_dependency_wait();  // the encoder's last level wrote the rows
   for (long long r = warp; r < n_rows; r += n_warps) {
     float s = 0.f;
     for (int h = lane; h < H; h += 32) s = fmaf(ld_f32<T>(rows + r * H + h), ld_f32<T>(proj + h), s);
@@ -72,6 +74,10 @@ attn_step_kernel(const T* __restrict__ enc, const float* __restrict__ enc_scores
   extern __shared__ float s_w[];  // [Ls] scores, then weights
   __shared__ float s_red[kStepThreads / 32];
   const int n = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  // Launched behind the decoder cell of this step; the next step's cell may be scheduled now and
+  // waits for this kernel before it reads the attention vectors.
+  grid_launch_dependents();
+  grid_dependency_wait();
   int len = src_lens ? src_lens[n] : Ls;
   len = len < 0 ? 0 : (len > Ls ? Ls : len);
 
@@ -138,20 +144,23 @@ int enc_scores_t(const void* enc, const void* proj, float* scores, long long n_r
   const long long ctas = (n_rows + 7) / 8;
   const long long full = static_cast<long long>(current_sm_count()) * 8;
   const int grid = static_cast<int>(ctas < full ? ctas : full);
-  row_dot_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(enc), static_cast<const T*>(proj), scores, n_rows, H);
+  const cudaError_t err = launch_dependent(row_dot_kernel<T>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(enc),
+                                           static_cast<const T*>(proj), scores, n_rows, H);
   count_launch();
-  return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+  if (err != cudaSuccess) cudaGetLastError();
+  return err == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
 
 template <typename T>
 int attn_step_t(const void* enc, const float* enc_scores, const void* dec_t, const void* dec_proj, const int* src_lens,
                 void* out_t, int Ls, int N, int H, cudaStream_t stream) {
   const dim3 grid(N, (H + kStepThreads - 1) / kStepThreads);
-  attn_step_kernel<T><<<grid, kStepThreads, static_cast<size_t>(Ls) * sizeof(float), stream>>>(
-      static_cast<const T*>(enc), enc_scores, static_cast<const T*>(dec_t), static_cast<const T*>(dec_proj), src_lens,
-      static_cast<T*>(out_t), Ls, N, H);
+  const cudaError_t err = launch_dependent(attn_step_kernel<T>, grid, dim3(kStepThreads), static_cast<size_t>(Ls) * sizeof(float),
+                                           stream, static_cast<const T*>(enc), enc_scores, static_cast<const T*>(dec_t),
+                                           static_cast<const T*>(dec_proj), src_lens, static_cast<T*>(out_t), Ls, N, H);
   count_launch();
-  return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+  if (err != cudaSuccess) cudaGetLastError();
+  return err == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
 
 }  // namespace

@@ -306,6 +306,8 @@ sparse_attn_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
   const int S = a.S, ng = a.n_global, G = 2 * a.n_global;
   const long long total = a.heads_total * S;
   const bool small = total <= 0xffffffffLL;
+  grid_launch_dependents();
+  grid_dependency_wait();
 
   for (long long first = warp * TPW; first < total; first += n_warps * TPW) {
     const long long item = first + lane / LPT;
@@ -399,7 +401,9 @@ sparse_attn_tile_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
     s_abort = 0;
     fence_barrier_init();
   }
+  grid_launch_dependents();
   __syncthreads();
+  grid_dependency_wait();  // set-up done; the first copy below reads global memory
 
   long long tile = blockIdx.x;
   if (tile >= n_tiles) return;
@@ -478,11 +482,12 @@ int launch_sparse(const void* q, const void* k, const void* v, const int* rand_p
       const long long n_tiles = a.heads_total * a.tiles_per_head;
       const long long full = static_cast<long long>(current_sm_count()) * 2;  // two CTAs per SM, persistent
       const int grid = static_cast<int>(n_tiles < full ? n_tiles : full);
-      kfn<<<grid, kSparseThreads, 2 * stage, stream>>>(static_cast<const T*>(q), static_cast<const T*>(k),
-                                                       static_cast<const T*>(v), rand_pos, static_cast<T*>(o), a,
-                                                       status);
+      const cudaError_t err = launch_dependent(kfn, dim3(grid), dim3(kSparseThreads), 2 * stage, stream,
+                                               static_cast<const T*>(q), static_cast<const T*>(k),
+                                               static_cast<const T*>(v), rand_pos, static_cast<T*>(o), a, status);
       count_launch();
-      return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+      if (err != cudaSuccess) cudaGetLastError();
+      return err == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
     }
   }
   a.TT = a.tiles_per_head = a.stage_bytes = 0;
@@ -490,11 +495,12 @@ int launch_sparse(const void* q, const void* k, const void* v, const int* rand_p
   const long long ctas_needed = (warps_needed * 32 + kSparseThreads - 1) / kSparseThreads;
   const long long full = static_cast<long long>(current_sm_count()) * 8;
   const int grid = static_cast<int>(ctas_needed < full ? ctas_needed : full);
-  sparse_attn_kernel<T, LPT><<<grid, kSparseThreads, 0, stream>>>(
-      static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), rand_pos, static_cast<T*>(o), a,
-      status);
+  const cudaError_t err = launch_dependent(sparse_attn_kernel<T, LPT>, dim3(grid), dim3(kSparseThreads), 0, stream,
+                                           static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v),
+                                           rand_pos, static_cast<T*>(o), a, status);
   count_launch();
-  return cudaGetLastError() == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+  if (err != cudaSuccess) cudaGetLastError();
+  return err == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
 }
 
 template <typename T>

@@ -50,6 +50,28 @@ inline bool ensure_dynamic_smem(Kernel kfn, int bytes, std::atomic<unsigned long
   return true;
 }
 
+// Launches `kfn` so that it may start while the kernel before it in the stream is still draining
+// (programmatic dependent launch): its CTAs are scheduled as SMs free up and run their set-up
+// (barriers, tensor memory, descriptor prefetch) early.  The kernel must execute
+// `griddepcontrol.wait` before its first access to global memory; that instruction returns once
+// the kernel before it has completed and its writes are visible.  Behind a kernel that never
+// signals, or as the first kernel of a stream, this is an ordinary launch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kfn)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kfn, static_cast<KArgs>(args)...);
+}
+
 // Process-wide count of kernels this library has launched (reported by ftb_launch_count()).
 void count_launch(int n = 1);
 long long launches_so_far();
