@@ -547,6 +547,31 @@ def test_b2b_config2_full_size(ops):
     assert (out3.float() - 2 * out.float()).abs().max().item() <= 1e-3
 
 
+def test_b2b_chain_of_dependent_calls(ops):
+    """Calls that follow one another on a stream and feed each other: every call is launched as a
+    dependent launch and may be scheduled while the call before it drains, so each must wait for that
+    call before it reads its inputs (and before it overwrites a buffer the call before it reads).
+    Ten links, config-2 sized so that a call spans the whole device, compared with the same chain run
+    with a synchronisation between the links; then in place ping-pong between two buffers."""
+    A, B, C = dense.make_b2b_inputs(4, 16384, 128, 128, 128, 3)
+    Ad, Bd, Cd = _dev(A, B, C)
+    x = Ad
+    for _ in range(10):
+        x = ops.b2b_gemm(x, Bd, Cd)
+    ops.check_status()
+    y = Ad
+    for _ in range(10):
+        y = ops.b2b_gemm(y, Bd, Cd)
+        torch.cuda.synchronize()
+    assert torch.equal(x, y)
+    bufs = [Ad.clone(), torch.empty_like(Ad)]
+    for i in range(10):
+        ops.b2b_gemm(bufs[i & 1], Bd, Cd, out=bufs[(i + 1) & 1])
+    ops.check_status()
+    assert torch.equal(bufs[0], y)
+    assert torch.isfinite(y.float()).all() and y.float().abs().max().item() > 1e-3
+
+
 # ------------------------------------------------------------- flash attention
 def test_flash_attention_golden(ops, golden_dir):
     """The reference frontend's output for d=32 is reproduced with d zero-padded to 128
