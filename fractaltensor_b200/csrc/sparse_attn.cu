@@ -157,6 +157,14 @@ struct SparseArgs {
   int TT;              // tokens per tile
   int tiles_per_head;  // ceil(S / TT)
   int stage_bytes;     // K rows | V rows | queries | positions of one stage
+  // Which tiles of a head a launch of the tiled kernel walks: `per_head` of them, the idx-th being
+  // tile idx (idx < lead), else tile idx + skip.  All tiles: per_head = tiles_per_head, lead = 0,
+  // skip = 0.  Interior tiles only (no global token, no wrapped window position): lead = 0,
+  // skip = leading edge tiles.  Edge tiles only: lead = leading edge tiles, skip = interior tiles.
+  int per_head, lead, skip;
+  // A launch that walks interior and edge tiles with different routines: the edge enumeration
+  // (the one above is then the interior one).
+  int edge_per_head, edge_lead, edge_skip;
 };
 
 // Where the rows of one token's head come from: global memory, and for the tiled kernel the stage
@@ -286,6 +294,68 @@ __device__ __forceinline__ void attend_token(const SparseArgs& a, const Rows<T>&
   store_row_global<T, LPT>(out_row, gl, acc);
 }
 
+// One token of an interior tile with the numbers of window and random keys known at compile time
+// (the example's 5 and 3): no per-key bookkeeping, one softmax over the KW + KR scores.  Window rows
+// come from the stage, random rows from global memory; the random rows of K and V are requested
+// first, so that they arrive while the window part is computed out of shared memory.
+template <typename T, int LPT, int KW, int KR>
+__device__ __forceinline__ void attend_fast(const SparseArgs& a, const T* sk, const T* sv, int lo, const T* kh,
+                                            const T* vh, int i, int gl, unsigned gmask, const float (&qv)[kEPL],
+                                            const int* sp, T* __restrict__ out_row, int* __restrict__ status) {
+  constexpr int d = kEPL * LPT;
+  const int half = (KW - 1) * a.dilation / 2;
+  const float scale2 = a.scale * 1.4426950408889634f;
+  float kr[KR][kEPL], vr[KR][kEPL];
+#pragma unroll
+  for (int r = 0; r < KR; ++r) {
+    int x = sp[r];
+    if (x < 0 || x >= a.S) {
+      if (gl == 0) atomicCAS(status, 0, FTB_ERR_INDEX);
+      x = 0;
+    }
+    load_row_global<T, LPT>(kh + static_cast<long long>(x) * d, gl, kr[r]);
+    load_row_global<T, LPT>(vh + static_cast<long long>(x) * d, gl, vr[r]);
+  }
+  float sc[KW + KR];
+  const int row0 = i - half - lo;  // the first window row inside the stage
+#pragma unroll
+  for (int j = 0; j < KW; ++j) {
+    float kw[kEPL];
+    load_row_shared<T, LPT>(sk + (row0 + j * a.dilation) * d, gl, kw);
+    sc[j] = group_dot<LPT>(qv, kw, gmask) * scale2;
+  }
+#pragma unroll
+  for (int r = 0; r < KR; ++r) sc[KW + r] = group_dot<LPT>(qv, kr[r], gmask) * scale2;
+  float m = sc[0];
+#pragma unroll
+  for (int j = 1; j < KW + KR; ++j) m = fmaxf(m, sc[j]);
+  float z = 0.f;
+#pragma unroll
+  for (int j = 0; j < KW + KR; ++j) {
+    sc[j] = exp2_fast(sc[j] - m);
+    z += sc[j];
+  }
+  float acc[kEPL];
+#pragma unroll
+  for (int e = 0; e < kEPL; ++e) acc[e] = 0.f;
+#pragma unroll
+  for (int j = 0; j < KW; ++j) {
+    float vw[kEPL];
+    load_row_shared<T, LPT>(sv + (row0 + j * a.dilation) * d, gl, vw);
+#pragma unroll
+    for (int e = 0; e < kEPL; ++e) acc[e] = fmaf(sc[j], vw[e], acc[e]);
+  }
+#pragma unroll
+  for (int r = 0; r < KR; ++r) {
+#pragma unroll
+    for (int e = 0; e < kEPL; ++e) acc[e] = fmaf(sc[KW + r], vr[r][e], acc[e]);
+  }
+  const float inv = 1.f / z;
+#pragma unroll
+  for (int e = 0; e < kEPL; ++e) acc[e] *= inv;
+  store_row_global<T, LPT>(out_row, gl, acc);
+}
+
 template <int LPT>
 __device__ __forceinline__ unsigned group_mask(int lane) {
   return LPT == 32 ? 0xffffffffu : (((1u << (LPT & 31)) - 1u) << (lane - lane % LPT));
@@ -330,22 +400,26 @@ sparse_attn_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
 }
 
 // ------------------------------------------------------------------ tiled kernel
-template <typename T, int LPT>
-__global__ void __launch_bounds__(kSparseThreads)
-sparse_attn_tile_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
-                        const int* __restrict__ rand_pos, T* __restrict__ o, SparseArgs a, int* __restrict__ status) {
+// The walk of one CTA over its work items: item number first, first + step, ... of the enumeration
+// (per_head, lead, skip).  it_base = tiles the CTA has walked before (the stages and barrier phases
+// carry on from there); returns that count plus the tiles of this walk, or -1 after a wait ran out.  KW > 0: the items are interior tiles and a token has KW window and KR
+// random keys (attend_fast); KW = 0: any tile, any key counts (attend_token).
+template <typename T, int LPT, int KW, int KR>
+__device__ __forceinline__ int walk_tiles(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                                          const int* __restrict__ rand_pos, T* __restrict__ o, const SparseArgs& a,
+                                          int per_head, int lead, int skip, long long first, long long step,
+                                          int it_base, unsigned char* smem, uint64_t* full, int* s_abort_p,
+                                          int* __restrict__ status) {
   constexpr int d = kEPL * LPT;
   constexpr int TPW = 32 / LPT;
-  extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full[2];
-  __shared__ int s_abort;
+  volatile int* s_abort = s_abort_p;
 
   const int tid = threadIdx.x, lane = tid & 31, gl = lane % LPT;
   const unsigned gmask = group_mask<LPT>(lane);
   const int S = a.S, ng = a.n_global, G = 2 * a.n_global, TT = a.TT;
   const int half = (a.window - 1) * a.dilation / 2;
   const int rows_max = TT + 2 * half;
-  const long long n_tiles = a.heads_total * a.tiles_per_head;
+  const long long n_tiles = a.heads_total * per_head;  // work items of this enumeration
 
   auto stage_k = [&](int s) { return reinterpret_cast<T*>(smem + static_cast<size_t>(s) * a.stage_bytes); };
   auto stage_v = [&](int s) { return stage_k(s) + static_cast<size_t>(rows_max) * d; };
@@ -358,8 +432,9 @@ sparse_attn_tile_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
   };
   auto tile_of = [&](long long t) {
     Tile x;
-    x.head = t / a.tiles_per_head;
-    x.t0 = static_cast<int>(t - x.head * a.tiles_per_head) * TT;
+    x.head = t / per_head;
+    const int idx = static_cast<int>(t - x.head * per_head);
+    x.t0 = (idx < lead ? idx : idx + skip) * TT;
     x.nt = min(TT, S - x.t0);
     x.lo = max(0, x.t0 - half);
     x.hi = min(S, x.t0 + x.nt + half);
@@ -395,31 +470,22 @@ sparse_attn_tile_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
     }
   };
 
-  if (tid == 0) {
-    mbar_init(&full[0], 1);
-    mbar_init(&full[1], 1);
-    s_abort = 0;
-    fence_barrier_init();
-  }
-  grid_launch_dependents();
-  __syncthreads();
-  grid_dependency_wait();  // set-up done; the first copy below reads global memory
-
-  long long tile = blockIdx.x;
-  if (tile >= n_tiles) return;
+  long long tile = first;
+  if (tile >= n_tiles) return it_base;
   {
     const Tile x = tile_of(tile);
-    if (tid == 0) issue(x, 0);
+    if (tid == 0) issue(x, it_base & 1);
     int pre[kPosRegs];
     fetch_pos(x, pre);
-    park_pos(0, pre);
+    park_pos(it_base & 1, pre);
   }
   __syncthreads();
 
-  for (int it = 0; tile < n_tiles; tile += gridDim.x, ++it) {
+  int it = it_base;
+  for (; tile < n_tiles; tile += step, ++it) {
     const int s = it & 1;
     const Tile x = tile_of(tile);
-    const long long next = tile + gridDim.x;
+    const long long next = tile + step;
     int pre[kPosRegs];
     if (next < n_tiles) {
       // stage s ^ 1 was last read in the previous round; the barrier that closed it orders those
@@ -428,7 +494,7 @@ sparse_attn_tile_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
       if (tid == 0) issue(y, s ^ 1);
       fetch_pos(y, pre);
     }
-    if (!mbar_wait(&full[s], (it >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) break;
+    if (!mbar_wait(&full[s], (it >> 1) & 1, s_abort, status, FTB_ERR_TIMEOUT_TMA)) return -1;
 
     Rows<T> rw;
     rw.kh = k + x.head * S * d;
@@ -445,11 +511,52 @@ sparse_attn_tile_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
       const int i = x.t0 + tok;
       float qv[kEPL];
       load_row_shared<T, LPT>(stage_q(s) + tok * d, gl, qv);
-      attend_token<T, LPT>(a, rw, i, gl, gmask, interior, qv, [&](int r) { return sp[tok * a.R + r]; },
-                           o + (x.head * S + i) * d, status);
+      if constexpr (KW > 0) {
+        attend_fast<T, LPT, KW, KR>(a, rw.sk, rw.sv, x.lo, rw.kh, rw.vh, i, gl, gmask, qv, sp + tok * KR,
+                                    o + (x.head * S + i) * d, status);
+      } else {
+        attend_token<T, LPT>(a, rw, i, gl, gmask, interior, qv, [&](int r) { return sp[tok * a.R + r]; },
+                             o + (x.head * S + i) * d, status);
+      }
     }
     if (next < n_tiles) park_pos(s ^ 1, pre);
     __syncthreads();
+  }
+  return it;
+}
+
+// ------------------------------------------------------------------ tiled kernel
+// KW = 0: every CTA walks the enumeration (per_head, lead, skip) with the general routine.  KW > 0:
+// every CTA first walks its share of the edge tiles with the general routine, then its share of the
+// interior tiles with the routine built for KW window and KR random keys; the two walks are separate
+// pieces of code, so the register count is the larger of the two, not their sum.
+template <typename T, int LPT, int KW, int KR>
+__global__ void __launch_bounds__(kSparseThreads)
+sparse_attn_tile_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                        const int* __restrict__ rand_pos, T* __restrict__ o, SparseArgs a, int* __restrict__ status) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full[2];
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    s_abort = 0;
+    fence_barrier_init();
+  }
+  grid_launch_dependents();
+  __syncthreads();
+  grid_dependency_wait();  // set-up done; the first copy of the walk reads global memory
+  if constexpr (KW > 0) {
+    // Edge tiles are handed out from the last CTA down, interior tiles from the first up: when the
+    // edge tiles are fewer than the CTAs, the CTAs with one interior tile more do not get them.
+    const int done = walk_tiles<T, LPT, 0, 0>(q, k, v, rand_pos, o, a, a.edge_per_head, a.edge_lead, a.edge_skip,
+                                              gridDim.x - 1 - blockIdx.x, gridDim.x, 0, smem, full, &s_abort, status);
+    if (done >= 0)
+      walk_tiles<T, LPT, KW, KR>(q, k, v, rand_pos, o, a, a.per_head, a.lead, a.skip, blockIdx.x, gridDim.x, done,
+                                 smem, full, &s_abort, status);
+  } else {
+    walk_tiles<T, LPT, 0, 0>(q, k, v, rand_pos, o, a, a.per_head, a.lead, a.skip, blockIdx.x, gridDim.x, 0, smem, full,
+                             &s_abort, status);
   }
 }
 
@@ -473,24 +580,48 @@ int launch_sparse(const void* q, const void* k, const void* v, const int* rand_p
     }
   }
   if (TT > 0) {
-    static std::atomic<unsigned long long> configured{0};
-    auto kfn = sparse_attn_tile_kernel<T, LPT>;
-    if (ensure_dynamic_smem(kfn, kMaxTileSmem, configured)) {
+    static std::atomic<unsigned long long> configured{0}, configured_fast{0};
+    auto kfn = sparse_attn_tile_kernel<T, LPT, 0, 0>;
+    auto kfast = sparse_attn_tile_kernel<T, LPT, 5, 3>;
+    if (ensure_dynamic_smem(kfn, kMaxTileSmem, configured) && ensure_dynamic_smem(kfast, kMaxTileSmem, configured_fast)) {
       a.TT = TT;
       a.tiles_per_head = (a.S + TT - 1) / TT;
       a.stage_bytes = stage;
-      const long long n_tiles = a.heads_total * a.tiles_per_head;
+      // Edge tiles: those with a global token or a window position that wraps, at both ends of a head.
+      const int m = a.n_global > half ? a.n_global : half;
+      int lead = (m + TT - 1) / TT, trail = a.tiles_per_head - (a.S - m) / TT;
+      if (m == 0) lead = trail = 0;
+      const int interior = a.tiles_per_head - lead - trail;
       const long long full = static_cast<long long>(current_sm_count()) * 2;  // two CTAs per SM, persistent
-      const int grid = static_cast<int>(n_tiles < full ? n_tiles : full);
-      const cudaError_t err = launch_dependent(kfn, dim3(grid), dim3(kSparseThreads), 2 * stage, stream,
-                                               static_cast<const T*>(q), static_cast<const T*>(k),
-                                               static_cast<const T*>(v), rand_pos, static_cast<T*>(o), a, status);
-      count_launch();
-      if (err != cudaSuccess) cudaGetLastError();
-      return err == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+      auto run = [&](auto fn, const SparseArgs& b, long long ctas_wanted) -> int {
+        const int grid = static_cast<int>(ctas_wanted < full ? ctas_wanted : full);
+        const cudaError_t err = launch_dependent(fn, dim3(grid), dim3(kSparseThreads), 2 * stage, stream,
+                                                 static_cast<const T*>(q), static_cast<const T*>(k),
+                                                 static_cast<const T*>(v), rand_pos, static_cast<T*>(o), b, status);
+        count_launch();
+        if (err != cudaSuccess) cudaGetLastError();
+        return err == cudaSuccess ? FTB_OK : FTB_ERR_LAUNCH;
+      };
+      a.edge_per_head = a.edge_lead = a.edge_skip = 0;
+      if (a.window == 5 && a.R == 3 && !a.as_shipped && interior > 0) {
+        // The example's key counts: interior tiles by the routine built for them, the edge tiles of
+        // every head by the general one on a share of the CTAs in proportion to their number.
+        a.per_head = interior;
+        a.lead = 0;
+        a.skip = lead;
+        a.edge_per_head = lead + trail;
+        a.edge_lead = lead;
+        a.edge_skip = interior;
+        const long long ctas = a.heads_total * a.tiles_per_head;
+        return run(kfast, a, ctas);
+      }
+      a.per_head = a.tiles_per_head;
+      a.lead = a.skip = 0;
+      return run(kfn, a, a.heads_total * a.tiles_per_head);
     }
   }
-  a.TT = a.tiles_per_head = a.stage_bytes = 0;
+  a.TT = a.tiles_per_head = a.stage_bytes = a.per_head = a.lead = a.skip = 0;
+  a.edge_per_head = a.edge_lead = a.edge_skip = 0;
   const long long warps_needed = (a.heads_total * a.S + 32 / LPT - 1) / (32 / LPT);
   const long long ctas_needed = (warps_needed * 32 + kSparseThreads - 1) / kSparseThreads;
   const long long full = static_cast<long long>(current_sm_count()) * 8;
@@ -549,7 +680,8 @@ extern "C" int ftb_sparse_attn_fwd(const void* q, const void* k, const void* v, 
   a.R = R;
   a.as_shipped = as_shipped ? 1 : 0;
   a.scale = scale;
-  a.TT = a.tiles_per_head = a.stage_bytes = 0;
+  a.TT = a.tiles_per_head = a.stage_bytes = a.per_head = a.lead = a.skip = 0;
+  a.edge_per_head = a.edge_lead = a.edge_skip = 0;
   int* status = static_cast<int*>(workspace);  // sticky, as for the other single-kernel entry points
   switch (dtype) {
     case FTB_F32: return launch_sparse_d<float>(d, q, k, v, rand_pos, o, a, status, stream);

@@ -77,6 +77,10 @@ CASES = [
     (1, 3, 128, 64, 31, 2, 16, 33),  # 64 keys per windowed token, 32 global keys
     (1, 1, 12, 64, 5, 2, 6, 2),      # every token is global
     (1, 2, 70, 64, 9, 4, 32, 1),     # 64 global keys: two per lane
+    (2, 3, 300, 64, 5, 2, 3, 3),     # the example's key counts: interior tiles by the kernel built for them
+    (1, 2, 300, 128, 5, 3, 2, 3),    # the same with dilation 3 and 128 elements per head
+    (1, 2, 1000, 32, 5, 1, 0, 3),    # no global tokens, dilation 1
+    (1, 1, 200, 256, 5, 2, 30, 3),   # 60 global keys, 256 elements per head
 ]
 
 
