@@ -27,7 +27,12 @@
 // shared memory.  Window rows, queries and positions then cost shared-memory latency; only the R
 // random rows per token (and window positions that wrap around the ends of the sequence) are
 // gathered from global memory, 16 bytes per lane.
-// Direct kernel (fallback when a tile does not fit in shared memory or R > 16): the same token
+// With the example's key counts (window 5, 3 random keys) the interior tiles -- no global token,
+// no window position that wraps -- go through a routine with those counts at compile time: all
+// eight scores in registers, one softmax, no per-key bookkeeping (16.7 M warp instructions instead
+// of 29 M at the example's size).  Every CTA first walks its share of the edge tiles of all heads
+// with the general routine, then its share of the interior tiles.
+// Direct kernel (fallback when a tile does not fit in shared memory or R > 16): the general token
 // routine with every row gathered from global memory.
 //
 // `as_shipped`: the example calls ops.softmax(x) without a dimension and the reference's softmax
