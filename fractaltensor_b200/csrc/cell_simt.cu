@@ -17,7 +17,9 @@ namespace {
 constexpr int TM = 32;   // rows per tile
 constexpr int TN = 32;   // accumulator columns per tile (8 LSTM units)
 constexpr int TK = 32;   // K chunk
-constexpr int kSimtThreads = 128;
+constexpr int kGroupThreads = 128;  // threads that share one slice of K
+constexpr int kSplitK = 4;          // slices of K per tile, one per group of 128 threads
+constexpr int kSimtThreads = kGroupThreads * kSplitK;
 
 struct SimtArgs {
   const float* act[kNumActMaps];
@@ -28,11 +30,21 @@ struct SimtArgs {
 
 __device__ __forceinline__ float sigmoid_acc(float x) { return 1.f / (1.f + expf(-x)); }
 
+__device__ __forceinline__ void group_barrier(int group) {
+  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(kGroupThreads) : "memory");
+}
+
+// One CTA computes one 32 x 32 tile.  A wavefront level is a few hundred tiles of a short K loop
+// on a 148-SM device, so a tile's latency is what counts: the K chunks of the tile are dealt out to
+// four groups of 128 threads (each with its own shared-memory buffers and its own named barrier),
+// every group accumulates its quarter of K in the same 32 x 32 layout, and group 0 adds the four
+// partial sums in a fixed order and runs the epilogue.
 template <int EPI>
 __global__ void __launch_bounds__(kSimtThreads)
 cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ CellBatch batch) {
-  __shared__ __align__(16) float sA[TM][TK + 4];  // [row][k]: a thread reads four k of a row at once
-  __shared__ __align__(16) float sW[TK][TN + 4];  // [k][column]
+  __shared__ __align__(16) float sA[kSplitK][TM][TK + 4];  // [group][row][k]: a thread reads four k of a row at once
+  __shared__ __align__(16) float sW[kSplitK][TK][TN + 4];  // [group][k][column]
+  __shared__ __align__(16) float sP[kSplitK - 1][kGroupThreads][8];  // partial sums of groups 1..3
 
   // A kernel launched behind this one as a dependent (the attention step of the attention RNN) may
   // be scheduled while this one drains; this kernel itself waits for the one before it.
@@ -47,15 +59,20 @@ cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ 
   const int n_tile = local / it.m_tiles;
   const int m_tile = local - n_tile * it.m_tiles;
 
-  const int tx = threadIdx.x & 7;   // 4 consecutive columns: one LSTM unit
-  const int ty = threadIdx.x >> 3;  // 2 consecutive rows
+  const int grp = threadIdx.x / kGroupThreads;  // which slice of K
+  const int tg = threadIdx.x % kGroupThreads;   // thread within the group
+  const int tx = tg & 7;   // 4 consecutive columns: one LSTM unit
+  const int ty = tg >> 3;  // 2 consecutive rows
   float acc[2][4] = {};
 
-  // K is walked in chunks of TK over the cell's segments.  The next chunk's global loads are
-  // issued into registers before the current chunk is multiplied out of shared memory, so their
-  // latency overlaps the arithmetic instead of preceding it (same summation order either way).
-  const int ld_r = threadIdx.x >> 3;        // first row (A) / column (W) this thread loads; second is +16
-  const int ld_kq = (threadIdx.x & 7) * 4;  // its four consecutive k
+  // K is walked in chunks of TK over the cell's segments; this group takes chunks [c_begin, c_end) of
+  // the walk.  The next chunk's global loads are issued into registers before the current chunk is
+  // multiplied out of shared memory, so their latency overlaps the arithmetic.
+  int total_chunks = 0;
+  for (int s = 0; s < it.nseg; ++s) total_chunks += it.seg_kb[s] * (64 / TK);
+  const int c_begin = total_chunks * grp / kSplitK, c_end = total_chunks * (grp + 1) / kSplitK;
+  const int ld_r = tg >> 3;        // first row (A) / column (W) this thread loads; second is +16
+  const int ld_kq = (tg & 7) * 4;  // its four consecutive k
   const bool a_ok0 = m_tile * TM + ld_r < it.rows, a_ok1 = m_tile * TM + ld_r + 16 < it.rows;
   float4 va0 = make_float4(0.f, 0.f, 0.f, 0.f), va1 = va0, vw0 = va0, vw1 = va0;
   auto fetch = [&](int s, int k0) {
@@ -69,38 +86,62 @@ cell_simt_kernel(const __grid_constant__ SimtArgs args, const __grid_constant__ 
     vw0 = *reinterpret_cast<const float4*>(W + static_cast<size_t>(ld_r) * args.ldw + k0 + ld_kq);
     vw1 = *reinterpret_cast<const float4*>(W + static_cast<size_t>(ld_r + 16) * args.ldw + k0 + ld_kq);
   };
+  // (segment, k offset) of chunk c_begin
   int s = 0, k0 = 0;
-  if (it.nseg > 0) fetch(0, 0);
-  while (s < it.nseg) {
-    *reinterpret_cast<float4*>(&sA[ld_r][ld_kq]) = va0;
-    *reinterpret_cast<float4*>(&sA[ld_r + 16][ld_kq]) = va1;
-    sW[ld_kq + 0][ld_r] = vw0.x; sW[ld_kq + 1][ld_r] = vw0.y; sW[ld_kq + 2][ld_r] = vw0.z; sW[ld_kq + 3][ld_r] = vw0.w;
-    sW[ld_kq + 0][ld_r + 16] = vw1.x; sW[ld_kq + 1][ld_r + 16] = vw1.y;
-    sW[ld_kq + 2][ld_r + 16] = vw1.z; sW[ld_kq + 3][ld_r + 16] = vw1.w;
-    __syncthreads();
+  {
+    int skip = c_begin;
+    while (s < it.nseg && skip >= it.seg_kb[s] * (64 / TK)) {
+      skip -= it.seg_kb[s] * (64 / TK);
+      ++s;
+    }
+    k0 = skip * TK;
+  }
+  if (c_begin < c_end) fetch(s, k0);
+  for (int c = c_begin; c < c_end; ++c) {
+    *reinterpret_cast<float4*>(&sA[grp][ld_r][ld_kq]) = va0;
+    *reinterpret_cast<float4*>(&sA[grp][ld_r + 16][ld_kq]) = va1;
+    sW[grp][ld_kq + 0][ld_r] = vw0.x; sW[grp][ld_kq + 1][ld_r] = vw0.y; sW[grp][ld_kq + 2][ld_r] = vw0.z; sW[grp][ld_kq + 3][ld_r] = vw0.w;
+    sW[grp][ld_kq + 0][ld_r + 16] = vw1.x; sW[grp][ld_kq + 1][ld_r + 16] = vw1.y;
+    sW[grp][ld_kq + 2][ld_r + 16] = vw1.z; sW[grp][ld_kq + 3][ld_r + 16] = vw1.w;
+    group_barrier(grp);
     int ns = s, nk0 = k0 + TK;
     if (nk0 >= it.seg_kb[s] * 64) {
       ++ns;
       nk0 = 0;
     }
-    if (ns < it.nseg) fetch(ns, nk0);
+    if (c + 1 < c_end) fetch(ns, nk0);
 #pragma unroll
     for (int k4 = 0; k4 < TK; k4 += 4) {
-      const float4 r0 = *reinterpret_cast<const float4*>(&sA[2 * ty][k4]);
-      const float4 r1 = *reinterpret_cast<const float4*>(&sA[2 * ty + 1][k4]);
+      const float4 r0 = *reinterpret_cast<const float4*>(&sA[grp][2 * ty][k4]);
+      const float4 r1 = *reinterpret_cast<const float4*>(&sA[grp][2 * ty + 1][k4]);
       const float a0[4] = {r0.x, r0.y, r0.z, r0.w}, a1[4] = {r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float4 w = *reinterpret_cast<const float4*>(&sW[k4 + j][4 * tx]);
+        const float4 w = *reinterpret_cast<const float4*>(&sW[grp][k4 + j][4 * tx]);
         acc[0][0] = fmaf(a0[j], w.x, acc[0][0]); acc[0][1] = fmaf(a0[j], w.y, acc[0][1]);
         acc[0][2] = fmaf(a0[j], w.z, acc[0][2]); acc[0][3] = fmaf(a0[j], w.w, acc[0][3]);
         acc[1][0] = fmaf(a1[j], w.x, acc[1][0]); acc[1][1] = fmaf(a1[j], w.y, acc[1][1]);
         acc[1][2] = fmaf(a1[j], w.z, acc[1][2]); acc[1][3] = fmaf(a1[j], w.w, acc[1][3]);
       }
     }
-    __syncthreads();
+    group_barrier(grp);
     s = ns;
     k0 = nk0;
+  }
+
+  // Partial sums of groups 1..3 to group 0, added in group order.
+  if (grp > 0) {
+    *reinterpret_cast<float4*>(&sP[grp - 1][tg][0]) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+    *reinterpret_cast<float4*>(&sP[grp - 1][tg][4]) = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
+  }
+  __syncthreads();
+  if (grp > 0) return;
+#pragma unroll
+  for (int g = 0; g < kSplitK - 1; ++g) {
+    const float4 p0 = *reinterpret_cast<const float4*>(&sP[g][tg][0]);
+    const float4 p1 = *reinterpret_cast<const float4*>(&sP[g][tg][4]);
+    acc[0][0] += p0.x; acc[0][1] += p0.y; acc[0][2] += p0.z; acc[0][3] += p0.w;
+    acc[1][0] += p1.x; acc[1][1] += p1.y; acc[1][2] += p1.z; acc[1][3] += p1.w;
   }
 
   const int col0 = n_tile * TN + 4 * tx;
