@@ -72,7 +72,7 @@ extern "C" int ftb_embedding_gather(const void* table, const long long* ids, voi
   const long long ctas_needed = (warps_needed * 32 + kGatherThreads - 1) / kGatherThreads;
   const long long full = static_cast<long long>(current_sm_count()) * 8;  // 8 CTAs of 256 threads per SM
   const int grid = static_cast<int>(ctas_needed < full ? ctas_needed : full);
-  const cudaError_t err = launch_dependent(embedding_gather_kernel, dim3(grid), dim3(kGatherThreads), 0, stream,
+  const cudaError_t err = launch_light(embedding_gather_kernel, dim3(grid), dim3(kGatherThreads), 0, stream,
                                            static_cast<const unsigned char*>(table), ids, static_cast<unsigned char*>(out),
                                            T, V, static_cast<int>(row_bytes), vec16 ? 1 : 0, status);
   count_launch();

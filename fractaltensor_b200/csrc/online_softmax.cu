@@ -210,7 +210,7 @@ int online_softmax_rows(const float* x, float* y, int rows, int width, int ld, c
   if (aligned16 && ((width | ld) & 3) == 0 && width <= 32 * 4 * kMaxV && rows >= 8) {
     const int64_t ctas = (static_cast<int64_t>(rows) + kSoftmaxThreads / 32 - 1) / (kSoftmaxThreads / 32);
     const int64_t full = static_cast<int64_t>(current_sm_count()) * 4;
-    const cudaError_t err = launch_dependent(online_softmax_warp_kernel, dim3(static_cast<int>(ctas < full ? ctas : full)),
+    const cudaError_t err = launch_light(online_softmax_warp_kernel, dim3(static_cast<int>(ctas < full ? ctas : full)),
                                              dim3(kSoftmaxThreads), 0, stream, x, y, rows, width, ld);
     count_launch();
     if (err != cudaSuccess) cudaGetLastError();
@@ -235,10 +235,10 @@ int online_softmax_rows(const float* x, float* y, int rows, int width, int ld, c
   const int grid = static_cast<int>(rows < want ? rows : want);
   cudaError_t err;
   if (per_sm <= 2)
-    err = launch_dependent(online_softmax_kernel<1024>, dim3(grid), dim3(1024), smem, stream, x, y, rows, width, ld,
+    err = launch_light(online_softmax_kernel<1024>, dim3(grid), dim3(1024), smem, stream, x, y, rows, width, ld,
                            cache_floats);
   else
-    err = launch_dependent(online_softmax_kernel<kSoftmaxThreads>, dim3(grid), dim3(kSoftmaxThreads), smem, stream, x, y,
+    err = launch_light(online_softmax_kernel<kSoftmaxThreads>, dim3(grid), dim3(kSoftmaxThreads), smem, stream, x, y,
                            rows, width, ld, cache_floats);
   count_launch();
   if (err != cudaSuccess) cudaGetLastError();

@@ -144,7 +144,7 @@ int enc_scores_t(const void* enc, const void* proj, float* scores, long long n_r
   const long long ctas = (n_rows + 7) / 8;
   const long long full = static_cast<long long>(current_sm_count()) * 8;
   const int grid = static_cast<int>(ctas < full ? ctas : full);
-  const cudaError_t err = launch_dependent(row_dot_kernel<T>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(enc),
+  const cudaError_t err = launch_light(row_dot_kernel<T>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(enc),
                                            static_cast<const T*>(proj), scores, n_rows, H);
   count_launch();
   if (err != cudaSuccess) cudaGetLastError();
@@ -155,7 +155,7 @@ template <typename T>
 int attn_step_t(const void* enc, const float* enc_scores, const void* dec_t, const void* dec_proj, const int* src_lens,
                 void* out_t, int Ls, int N, int H, cudaStream_t stream) {
   const dim3 grid(N, (H + kStepThreads - 1) / kStepThreads);
-  const cudaError_t err = launch_dependent(attn_step_kernel<T>, grid, dim3(kStepThreads), static_cast<size_t>(Ls) * sizeof(float),
+  const cudaError_t err = launch_light(attn_step_kernel<T>, grid, dim3(kStepThreads), static_cast<size_t>(Ls) * sizeof(float),
                                            stream, static_cast<const T*>(enc), enc_scores, static_cast<const T*>(dec_t),
                                            static_cast<const T*>(dec_proj), src_lens, static_cast<T*>(out_t), Ls, N, H);
   count_launch();

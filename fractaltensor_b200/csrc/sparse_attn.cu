@@ -631,7 +631,7 @@ int launch_sparse(const void* q, const void* k, const void* v, const int* rand_p
   const long long ctas_needed = (warps_needed * 32 + kSparseThreads - 1) / kSparseThreads;
   const long long full = static_cast<long long>(current_sm_count()) * 8;
   const int grid = static_cast<int>(ctas_needed < full ? ctas_needed : full);
-  const cudaError_t err = launch_dependent(sparse_attn_kernel<T, LPT>, dim3(grid), dim3(kSparseThreads), 0, stream,
+  const cudaError_t err = launch_light(sparse_attn_kernel<T, LPT>, dim3(grid), dim3(kSparseThreads), 0, stream,
                                            static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v),
                                            rand_pos, static_cast<T*>(o), a, status);
   count_launch();

@@ -72,6 +72,28 @@ inline cudaError_t launch_dependent(void (*kfn)(KArgs...), dim3 grid, dim3 block
   return cudaLaunchKernelEx(&cfg, kfn, static_cast<KArgs>(args)...);
 }
 
+#ifndef FTB_LIGHT_DEPENDENT
+#define FTB_LIGHT_DEPENDENT 1
+#endif
+// The same for kernels with next to no set-up (row-wise kernels).  Measured against plain launches:
+// attention RNN 1.16 against 1.22 ms, online softmax 88 against 91 us, embedding lookup equal,
+// projection + softmax 65 against 62 us; -DFTB_LIGHT_DEPENDENT=0 builds them as plain launches.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_light(void (*kfn)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = FTB_LIGHT_DEPENDENT;
+  return cudaLaunchKernelEx(&cfg, kfn, static_cast<KArgs>(args)...);
+}
+
 // Process-wide count of kernels this library has launched (reported by ftb_launch_count()).
 void count_launch(int n = 1);
 long long launches_so_far();
