@@ -572,6 +572,34 @@ def test_b2b_chain_of_dependent_calls(ops):
     assert torch.isfinite(y.float()).all() and y.float().abs().max().item() > 1e-3
 
 
+def test_b2b_chain_in_a_cuda_graph(ops):
+    """The same kind of chain captured in a CUDA graph (the dependent launches become programmatic
+    edges of the graph) and replayed: equal to the eager result, replay after replay."""
+    A, B, C = dense.make_b2b_inputs(2, 4096, 128, 128, 128, 5)
+    Ad, Bd, Cd = _dev(A, B, C)
+    mid, out = torch.empty_like(Ad), torch.empty_like(Ad)
+    ops.b2b_gemm(Ad, Bd, Cd, out=mid)   # warm: workspace, lazy initialisation
+    ops.b2b_gemm(mid, Bd, Cd, out=out)
+    torch.cuda.synchronize()
+    want = out.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ops.b2b_gemm(Ad, Bd, Cd, out=mid)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.b2b_gemm(Ad, Bd, Cd, out=mid)
+        ops.b2b_gemm(mid, Bd, Cd, out=out)
+    for _ in range(3):
+        out.zero_()
+        mid.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    ops.check_status()
+
+
 # ------------------------------------------------------------- flash attention
 def test_flash_attention_golden(ops, golden_dir):
     """The reference frontend's output for d=32 is reproduced with d zero-padded to 128
