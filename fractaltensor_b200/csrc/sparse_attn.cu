@@ -661,10 +661,11 @@ extern "C" int ftb_sparse_attn_fwd(const void* q, const void* k, const void* v, 
                                    float scale, int as_shipped, int dtype, void* workspace, size_t workspace_bytes,
                                    void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (!q || !k || !v || !o || B < 0 || heads <= 0 || S <= 0 || d <= 0) return FTB_ERR_ARG;
+  if (B < 0 || heads <= 0 || S <= 0 || d <= 0) return FTB_ERR_ARG;
+  if (B > 0 && (!q || !k || !v || !o)) return FTB_ERR_ARG;  // an empty batch has no storage to point at
   if (dtype != FTB_F32 && dtype != FTB_F16 && dtype != FTB_BF16) return FTB_ERR_ARG;
   if (window < 1 || window % 2 == 0 || dilation < 1 || n_global < 0 || R < 0) return FTB_ERR_ARG;
-  if (R > 0 && S > 2 * n_global && !rand_pos) return FTB_ERR_ARG;
+  if (B > 0 && R > 0 && S > 2 * n_global && !rand_pos) return FTB_ERR_ARG;
   if (d != 32 && d != 64 && d != 128 && d != 256) return FTB_ERR_ARG;
   const long long half = static_cast<long long>(window - 1) * dilation / 2;
   // The wrap of a window position is a single step: the window must fit in the sequence.

@@ -105,3 +105,29 @@ def test_rnn_attention_dense_entry(ops):
                                                  d64["dec_proj"])
         assert (enc[:, n].cpu().double() - e_ref).abs().max().item() <= 2e-2
         assert (out[:, n].cpu().double() - o_ref).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_rnn_attention_smallest_shapes(ops, dt):
+    """One sequence, one source and one target position; and a batch that is not a multiple of any tile."""
+    from fractaltensor_b200 import frontend
+    for src_lens, trg_lens in (([1], [1]), ([1, 2, 1], [2, 1, 3])):
+        H = 64
+        p, g = _params(H, 3 + len(src_lens), 1.0 / (H ** 0.5))
+        src = torch.randn(sum(src_lens), H, generator=g).to(dt)
+        trg = torch.randn(sum(trg_lens), H, generator=g).to(dt)
+        pq = {k: v.to(dt) for k, v in p.items()}
+        out = frontend.rnn_attention(_ragged(src, src_lens), _ragged(trg, trg_lens),
+                                     (pq["Ws"].cuda(), pq["Us"].cuda(), pq["bs"].cuda()),
+                                     (pq["Wt"].cuda(), pq["Ut"].cuda(), pq["bt"].cuda()),
+                                     (pq["enc_proj"].cuda(), pq["dec_proj"].cuda()))
+        ops.check_status()
+        d64 = {k: v.double() for k, v in pq.items()}
+        _, ref = dense.rnn_attention_dense(src.double(), trg.double(), src_lens, trg_lens, d64["Ws"], d64["Us"],
+                                           d64["bs"], d64["Wt"], d64["Ut"], d64["bt"], d64["enc_proj"], d64["dec_proj"])
+        err = (out.data.reshape(-1, H).cpu().double() - ref).abs().max().item()
+        assert err <= (1e-5 if dt == torch.float32 else 2e-2), err
+        # with a single source position the attention vector is that encoder state, whatever the scores
+        if src_lens == [1]:
+            enc1 = torch.tanh(src.double() @ d64["Ws"] + d64["bs"])
+            assert (out.data.reshape(-1, H).cpu().double() - enc1).abs().max().item() <= (1e-5 if dt == torch.float32 else 2e-2)

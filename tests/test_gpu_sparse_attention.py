@@ -143,3 +143,17 @@ def test_sparse_attention_rejects_host_tensors(ops):
         ops.sparse_attention(q, k, v, pos)
     with pytest.raises(ValueError):
         ops.sparse_attention(q.cuda(), k.cuda(), v.cuda(), pos.cuda().long())
+
+
+def test_sparse_attention_empty_batch_and_single_tile_edges(ops):
+    """No heads at all is a no-op; a sequence of exactly one tile with every kind of token in it."""
+    q = torch.empty(0, 4, 64, 64, device="cuda")
+    pos = torch.empty(0, 4, 58, 3, dtype=torch.int32, device="cuda")
+    out = ops.sparse_attention(q, q.clone(), q.clone(), pos)
+    ops.check_status()
+    assert out.shape == q.shape
+    q, k, v, pos = _inputs(3, 2, 64, 64, 3, 3, 9, torch.float32)
+    out = ops.sparse_attention(q.cuda(), k.cuda(), v.cuda(), pos.cuda())
+    ops.check_status()
+    ref = dense.sparse_attention_dense(q.double(), k.double(), v.double(), pos)
+    assert (out.cpu().double() - ref).abs().max().item() <= 2e-6 * max(1.0, ref.abs().max().item())
