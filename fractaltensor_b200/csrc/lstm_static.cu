@@ -30,6 +30,7 @@
 // (examples/stacked_rnn/stacked_lstm1.py:66-76).
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "ptx.cuh"
 #include "tmap.h"
@@ -42,6 +43,12 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int kEpiWarps = 8;
+#ifndef FTB_STATIC_FIRST
+#define FTB_STATIC_FIRST 2
+#endif
+// An epilogue warp reads its four 32-column accumulator chunks in two rounds: kFirstRound chunks,
+// their gate arithmetic, then the rest.
+constexpr int kFirstRound = FTB_STATIC_FIRST;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr int kStages = 6;
 constexpr uint32_t kABytes = BM * BK * 2;
@@ -78,7 +85,11 @@ __device__ __forceinline__ bool for_each_half(int L, F f) {
 }
 
 template <typename T>
+#ifdef FTB_STATIC_MAXNREG
+__global__ void __maxnreg__(FTB_STATIC_MAXNREG)
+#else
 __global__ void __launch_bounds__(kThreads, 1)
+#endif
 lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapH,
                    const __grid_constant__ CUtensorMap mapW, const StaticArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -300,39 +311,52 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
         T* out_row = reinterpret_cast<T*>(a.hs) + (static_cast<size_t>(l) * a.L + t) * a.N * a.H +
                      static_cast<size_t>(row) * a.H;
+        // After the last read of the accumulator the MMA warp gets it back, before the arithmetic of
+        // the chunks just read: it is the accumulator of the tile after next, whose input half is the
+        // very next thing the tensor pipe has to do.
+        auto round = [&](auto c0_, auto n_, auto last_) {
+          constexpr int c0 = decltype(c0_)::value, n = decltype(n_)::value;
+          uint32_t r[n][32];
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          const int ch = half * 4 + cc;
-          uint32_t r[32];
-          tmem_ld32(taddr + ch * 32, r);
+          for (int cd = 0; cd < n; ++cd) tmem_ld32(taddr + (half * 4 + c0 + cd) * 32, r[cd]);
           tmem_ld_wait();
-          const int col0 = col_base + ch * 32;
-          const int unit0 = col0 >> 2;
-          float hn[8];
+          if constexpr (decltype(last_)::value) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+          }
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            float gi = __uint_as_float(r[4 * u + 0]);
-            float gf = __uint_as_float(r[4 * u + 1]);
-            float go = __uint_as_float(r[4 * u + 2]);
-            float gc = __uint_as_float(r[4 * u + 3]);
-            if (bias != nullptr) {
-              const float4 b = __ldg(reinterpret_cast<const float4*>(bias + col0) + u);
-              gi += b.x; gf += b.y; go += b.z; gc += b.w;
+          for (int cd = 0; cd < n; ++cd) {
+            const int cc = c0 + cd;
+            const int col0 = col_base + (half * 4 + cc) * 32;
+            const int unit0 = col0 >> 2;
+            float hn[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              float gi = __uint_as_float(r[cd][4 * u + 0]);
+              float gf = __uint_as_float(r[cd][4 * u + 1]);
+              float go = __uint_as_float(r[cd][4 * u + 2]);
+              float gc = __uint_as_float(r[cd][4 * u + 3]);
+              if (bias != nullptr) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(bias + col0) + u);
+                gi += b.x; gf += b.y; go += b.z; gc += b.w;
+              }
+              const float c_new = sigmoid_fast(gf) * creg[8 * cc + u] + sigmoid_fast(gi) * tanh_fast(gc);
+              creg[8 * cc + u] = c_new;
+              hn[u] = sigmoid_fast(go) * tanh_fast(c_new);
             }
-            const float c_new = sigmoid_fast(gf) * creg[8 * cc + u] + sigmoid_fast(gi) * tanh_fast(gc);
-            creg[8 * cc + u] = c_new;
-            hn[u] = sigmoid_fast(go) * tanh_fast(c_new);
+            if (row_ok) {
+              uint4 v;
+              v.x = Fmt<T>::pack2(hn[0], hn[1]);
+              v.y = Fmt<T>::pack2(hn[2], hn[3]);
+              v.z = Fmt<T>::pack2(hn[4], hn[5]);
+              v.w = Fmt<T>::pack2(hn[6], hn[7]);
+              *reinterpret_cast<uint4*>(out_row + unit0) = v;
+            }
           }
-          if (row_ok) {
-            uint4 v;
-            v.x = Fmt<T>::pack2(hn[0], hn[1]);
-            v.y = Fmt<T>::pack2(hn[2], hn[3]);
-            v.z = Fmt<T>::pack2(hn[4], hn[5]);
-            v.w = Fmt<T>::pack2(hn[6], hn[7]);
-            *reinterpret_cast<uint4*>(out_row + unit0) = v;
-          }
-        }
-        tc_fence_before();
+        };
+        round(std::integral_constant<int, 0>{}, std::integral_constant<int, kFirstRound>{}, std::false_type{});
+        round(std::integral_constant<int, kFirstRound>{}, std::integral_constant<int, 4 - kFirstRound>{}, std::true_type{});
         fence_proxy_async_all();  // plain stores of h -> other CTAs' TMA loads
         __threadfence();
         __syncwarp();
@@ -341,7 +365,6 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
 #ifdef FTB_TRACE
           if (a.trace && warp == 2) a.trace[(static_cast<size_t>(l * a.L + t) * a.tiles_per_cell + tile) * 4 + 3] = globaltimer_ns();
 #endif
-          mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
         }
       }
       // Final cell state of the sweep.
