@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libftb200.so")
-SOURCES = ["tmap.cu", "pack.cu", "cell_gemm.cu", "cell_simt.cu", "lstm_static.cu", "lstm_wmajor.cu", "rnn_cluster.cu", "wavefront.cu", "b2b_gemm.cu", "flash_attn.cu",
+SOURCES = ["tmap.cu", "pack.cu", "cell_gemm.cu", "cell_simt.cu", "lstm_simt_static.cu", "lstm_static.cu", "lstm_wmajor.cu", "rnn_cluster.cu", "wavefront.cu", "b2b_gemm.cu", "flash_attn.cu",
            "online_softmax.cu", "embedding.cu", "sparse_attn.cu", "rnn_attention.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

@@ -27,6 +27,9 @@ int launch_cell_gemm(int dtype, int epi, int bn, int pair, const CUtensorMap* ma
 int launch_cell_gemm_persistent(int dtype, int epi, int bn, int pair, const CUtensorMap* maps,
                                 const CUtensorMap& mapW, const CUtensorMap& mapC, const CellBatch& header,
                                 const PlanView& plan, int* status, int sm_count, cudaStream_t stream);
+bool lstm_simt_static_supported(int D, int N, int I, int H, int sm_count);
+int launch_lstm_simt_static(const float* x, const float* Wp, const float* bias_p, float* hs, float* c, int D, int L,
+                            int N, int I, int H, int* done, int* status, int sm_count, cudaStream_t stream);
 bool lstm_static_supported(int dtype, int D, int N, int I, int H, int G, int sm_count);
 int launch_lstm_static(int dtype, const void* x, const void* Wp, const float* bias_p, void* hs, float* c, int D, int L,
                        int N, int I, int H, int G, int* done, int* status, unsigned long long* trace,
@@ -501,6 +504,21 @@ int ftb_lstm_stacked_fwd(const void* x, const void* Wp, const float* bias_p, voi
 
   const int n_cells = D * L;
   const PlanLayout lay = plan_layout(n_cells, stacked_max_tiles_per_cell(N, H));
+  if (dtype == FTB_F32 && schedule != 1 && (schedule >= 2 || workspace_bytes >= lay.total)) {
+    // fp32: one persistent launch, a CTA per accumulator tile with its weights in shared memory
+    // (csrc/lstm_simt_static.cu), when a layer's tiles fit on the device.
+    if (workspace_bytes < lay.total) return FTB_ERR_WORKSPACE;
+    const bool can = lstm_simt_static_supported(D, N, I, H, cl.sm_count);
+    if (schedule >= 2 && !can) return FTB_ERR_ARG;
+    if (can) {
+      rc = launch_lstm_simt_static(static_cast<const float*>(x), static_cast<const float*>(Wp), bias_p,
+                                   static_cast<float*>(hs), c, D, L, N, I, H,
+                                   reinterpret_cast<int*>(static_cast<char*>(workspace) + lay.done), status,
+                                   cl.sm_count, stream);
+      // A refused cooperative launch falls back to one launch per level under the automatic choice.
+      if (rc != FTB_ERR_LAUNCH || schedule != 0) return rc;
+    }
+  }
   const bool persistent = dtype != FTB_F32 && schedule != 1 && (schedule >= 2 || workspace_bytes >= lay.total);
   if (persistent) {
     if (workspace_bytes < lay.total) return FTB_ERR_WORKSPACE;

@@ -104,6 +104,45 @@ def test_stacked_lstm_config1_fp32(ops, golden_dir):
     _assert_fp32(hs[-1][:, g["samples"].long()], g["top"])
 
 
+@pytest.mark.parametrize("shape", [
+    (4, 64, 32, 256, 256),   # benchmark config 1: 128 CTAs, every layer resident
+    (3, 9, 40, 128, 128),    # two row tiles per cell, rows 40..63 of the second are padding
+    (1, 7, 10, 64, 128),     # one layer whose input is narrower than its state
+    (6, 5, 64, 256, 256),    # 64 tiles per layer: the CTAs sweep the layers in groups of two
+    (2, 4, 8, 512, 512),     # a tile's operands exceed shared memory: one launch per level
+])
+def test_stacked_lstm_fp32_persistent_schedule(ops, shape, monkeypatch):
+    """fp32: the persistent kernel (weights resident in shared memory, cell state in registers)
+    against the oracle, bit for bit against one launch per level, and the fallback when the
+    cooperative launch is refused."""
+    from fractaltensor_b200 import _lib
+    D, L, N, I, H = shape
+    x, W, U, b = dense.make_lstm_inputs(D, L, N, I, H, 11, 1.0 / 16, bias=True)
+    n0 = _lib.lib.ftb_launch_count()
+    hs, c = _run_stacked(ops, x, W, U, b)
+    launches = _lib.lib.ftb_launch_count() - n0
+    rhs, rc = dense.stacked_lstm_dense(*_f32(x, W, U, b))
+    _assert_fp32(hs, rhs)
+    _assert_fp32(c, rc)
+    n0 = _lib.lib.ftb_launch_count()
+    hs1, c1 = _run_stacked(ops, x, W, U, b, schedule=1)
+    level_launches = _lib.lib.ftb_launch_count() - n0
+    assert torch.equal(hs, hs1) and torch.equal(c, c1)
+    if H <= 256:
+        assert level_launches - launches >= L - 1   # one launch instead of one per level
+        hs2, c2 = _run_stacked(ops, x, W, U, b, schedule=2)
+        assert torch.equal(hs, hs2) and torch.equal(c, c2)
+        monkeypatch.setenv("FTB_REFUSE_COOPERATIVE", "1")
+        hs3, c3 = _run_stacked(ops, x, W, U, b)
+        assert torch.equal(hs, hs3) and torch.equal(c, c3)
+        with pytest.raises(RuntimeError):
+            _run_stacked(ops, x, W, U, b, schedule=2)
+    else:
+        assert level_launches == launches
+        with pytest.raises(RuntimeError):
+            _run_stacked(ops, x, W, U, b, schedule=2)
+
+
 @pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape,kw", [
     ((1, 1, 128, 64, 64), {}),          # one cell, no recurrent term
