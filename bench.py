@@ -372,7 +372,8 @@ def other_configs(ops, dev, pk, cpu):
     ms = timed(lambda: ops.lstm_stacked(x1, Wp1), 10)
     out.append(tensor_entry("1: stacked LSTM fp32 D4 H256 N32 L64", ms, 4 * 64 * 32 * 2 * 1024 * 512,
                             samples_steps_per_s=32 * 64 / (ms * 1e-3),
-                            note="fp32 on CUDA cores (the 1e-5 bound rules out tf32 tensor cores); 67 dependent levels; "
+                            note="fp32 on CUDA cores (the 1e-5 bound rules out tf32 tensor cores); one persistent launch, "
+                                 "weights resident in shared memory; 67 dependent levels; "
                                  "the tensor roofline is quoted for context",
                             cpu_baseline=cpu.get("1")))
     return out

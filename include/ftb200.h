@@ -62,7 +62,12 @@ int ftb_lstm_pack_weights(const void* W, const void* U, const void* bias, void* 
  *  [1] bn                accumulator tile width, 128 or 256
  *  [2] schedule          1 = one kernel launch per wavefront level; 2 = one persistent
  *                        cooperative kernel, cells chained through completion counters
- *                        in the workspace (16-bit dtypes only); 3 = persistent with static
+ *                        in the workspace (16-bit dtypes; for the fp32 stacked LSTM 2 and 3 both
+ *                        name its one persistent kernel: a CTA keeps a 32 x 32 tile of one layer
+ *                        with its weights in shared memory and its cell state in registers over
+ *                        the whole sweep, the automatic choice when [I + H] x 32 weights and 32
+ *                        rows of operands fit in shared memory and a layer's tiles fit on the
+ *                        device); 3 = persistent with static
  *                        tile ownership (stacked LSTM: every CTA pair keeps its slice of a
  *                        layer, cell state in registers, over a whole sweep; needs a layer
  *                        group's tiles to fit on the device; the automatic choice when so and
