@@ -53,6 +53,7 @@ constexpr int kFirstEpiWarp = 4;
 __host__ __device__ constexpr int epi_warps(int mode) { return mode == 0 ? 16 : 8; }
 __host__ __device__ constexpr int cta_threads(int mode) { return 32 * (kFirstEpiWarp + epi_warps(mode)); }
 constexpr uint32_t kStageBytes = 16384;
+
 constexpr int kMaxLayers = 16;
 
 enum ClusterMode : int { kDilated = 0, kGrid = 1 };
@@ -64,6 +65,20 @@ __device__ unsigned long long* g_cluster_trace = nullptr;
   if (g_cluster_trace != nullptr && rank == 0) g_cluster_trace[(static_cast<size_t>(cid) * n_steps + (i)) * 16 + (s)] = globaltimer_ns()
 #else
 #define FTB_CL_STAMP(i, s)
+#endif
+#ifdef FTB_ACCT
+// Debug builds: cycles a role of CTA rank 0 spends in each of its waits, summed over the launch and
+// written once at the end: [cluster][16].
+__device__ unsigned long long* g_cluster_acct = nullptr;
+#define ACCT_DECL(n) long long acct_[n] = {}; long long acct_t0_ = 0; (void)acct_t0_
+#define ACCT_BEGIN() acct_t0_ = clock64()
+#define ACCT_END(k) acct_[k] += clock64() - acct_t0_
+#define ACCT_WRITE(k, slot) if (g_cluster_acct != nullptr && rank == 0) g_cluster_acct[static_cast<size_t>(cid) * 16 + (slot)] = acct_[k]
+#else
+#define ACCT_DECL(n)
+#define ACCT_BEGIN()
+#define ACCT_END(k)
+#define ACCT_WRITE(k, slot)
 #endif
 
 struct ClusterArgs {
@@ -296,6 +311,7 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
   __shared__ uint64_t self_full[2];   // the slot holds the whole previous output (bytes counted)
   __shared__ uint64_t self_free[2];   // producers only: every CTA of the cluster has multiplied the slot's contents
   __shared__ uint64_t stg_ready;      // the eight epilogue warps have written the step's staging tile
+  __shared__ int seg_seq;             // operand segments issued into the ring so far (two producer warps)
   __shared__ int out_issued;          // epilogue warps that have staged a step's outputs, summed over steps
   __shared__ int out_stored;          // steps whose output staging tile the publisher has finished reading
   __shared__ uint64_t tfull_bar[2], tempty_bar[2];
@@ -342,6 +358,8 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
   uint8_t* s_out = s_stg + (self_chain ? 2 * stage_tile_bytes : 0);  // two row-major output tiles for the TMA stores
   uint8_t* s_ring = s_out + 2 * kOutTileBytes;
   const int n_ring = self_chain ? kRing : 12;
+  // ring stages a segment (the H / 64 K blocks of NB rows) takes
+  const int seg_stages = (a.H / BK + kBlocksPerStage - 1) / kBlocksPerStage;
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&map0);
@@ -361,6 +379,7 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
     mbar_init(&self_free[0], a.CL);
     mbar_init(&self_free[1], a.CL);
     mbar_init(&stg_ready, kEpiWarps);
+    seg_seq = 0;
     out_issued = 0;
     out_stored = 0;
     mbar_init(&tfull_bar[0], 1);
@@ -387,41 +406,84 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
   const int n_steps = a.L;
   const int my_flag_cell0 = MODE == kDilated ? (layer * a.L) : ((layer * a.A + row_a) * a.L);
 
-  if (warp == 0) {
-    // ------------------------------------------ producer of the TMA-fed operand blocks
-    int stage = 0;
+  if (warp == 0 || warp == 3) {
+    // ------------------------------------------ producers of the TMA-fed operand blocks
+    // One three-dimensional copy per segment: the NB rows of all its K blocks land in consecutive
+    // [NB x 64] tiles of the ring (a segment never wraps: the ring is a whole number of segments long)
+    // and complete on the barrier of the segment's first stage; the MMA warp frees a segment through
+    // the empty barrier of that same stage.
+    // Two warps share the work by segment: warp 0 takes a step's first segment (the input), warp 3
+    // its second (the state that arrives through global memory), so one segment's flag wait overlaps
+    // the other's ring wait and copy.  Both walk every segment to keep the ring position, and the ring
+    // is filled in segment order whichever warp fills it: a warp waits for `seg_seq` to reach its
+    // segment's number before it touches the ring (otherwise the warp with the lighter segments could
+    // lap the other one and meet a stage's barrier a whole round early, where the parity test cannot
+    // tell "not yet filled" from "already drained").
+    const int mine = warp == 0 ? 0 : 1;
+    int stage = 0, q = 0;
     uint32_t phase = 0;
     bool ok = true;
+    volatile int* seq = &seg_seq;
+    ACCT_DECL(4);
     for (int i = 0; i < n_steps && ok; ++i) {
       const StepPlan p = plan_step<MODE, NB>(a, layer, row_a, slice, rank, i);
       for (int s = 0; s < p.nseg && ok; ++s) {
         const Segment& sg = p.seg[s];
-        if (sg.flags != nullptr && !warp_wait_flags(sg.flags, sg.nflags, lane, &s_abort, status)) {
-          ok = false;
-          break;
-        }
-        bool fine = true;
-        if (lane == 0) {
-          // (Producers write their outputs with TMA stores and consumers read them with TMA loads: both
-          // sides are in the async proxy, so the flag's release/acquire is all the ordering there is.)
-          FTB_CL_STAMP(i, 7 + 2 * s);
-          for (int kb0 = 0; kb0 < sg.nkb && fine; kb0 += kBlocksPerStage) {
-            const int nb = min(kBlocksPerStage, sg.nkb - kb0);
-            fine = mbar_wait(&ring_empty[stage], phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT);
-            if (!fine) break;
-            mbar_arrive_expect_tx(&ring_full[stage], nb * kBlockBytes);
-            for (int b = 0; b < nb; ++b)
-              tma_load_2d(s_ring + stage * kStageBytes + b * kBlockBytes, maps[sg.map], &ring_full[stage],
-                          (kb0 + b) * BK, sg.row);
-            if (++stage == n_ring) {
-              stage = 0;
-              phase ^= 1u;
-            }
+        if ((s & 1) == mine) {
+          ACCT_BEGIN();
+          if (sg.flags != nullptr && !warp_wait_flags(sg.flags, sg.nflags, lane, &s_abort, status)) {
+            ok = false;
+            break;
           }
-          FTB_CL_STAMP(i, 8 + 2 * s);
+          ACCT_END(0);
+          bool fine = true;
+          if (lane == 0) {
+            // (Producers write their outputs with TMA stores and consumers read them with TMA loads: both
+            // sides are in the async proxy, so the flag's release/acquire is all the ordering there is.)
+            FTB_CL_STAMP(i, 7 + 2 * s);
+            ACCT_BEGIN();
+            if (*seq != q) {
+              const uint64_t t0 = globaltimer_ns();
+              uint32_t it = 0;
+              while (*seq != q) {
+                if (((++it) & 0xFF) == 0 && (s_abort || globaltimer_ns() - t0 > FTB_WAIT_TIMEOUT_NS)) break;
+              }
+              if (*seq != q) {
+                fine = false;
+                if (!s_abort) {
+                  s_abort = 1;
+                  atomicCAS(status, 0, FTB_ERR_TIMEOUT_SLOT);
+                }
+              }
+            }
+            ACCT_END(1);
+            ACCT_BEGIN();
+            if (fine) fine = mbar_wait(&ring_empty[stage], phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT);
+            ACCT_END(2);
+            ACCT_BEGIN();
+            if (fine) {
+              mbar_arrive_expect_tx(&ring_full[stage], sg.nkb * kBlockBytes);
+              tma_load_3d(s_ring + stage * kStageBytes, maps[sg.map], &ring_full[stage], 0, sg.row, 0);
+              *seq = q + 1;
+            }
+            ACCT_END(3);
+            FTB_CL_STAMP(i, 8 + 2 * s);
+          }
+          ok = __all_sync(0xffffffffu, fine);
         }
-        ok = __all_sync(0xffffffffu, fine);
+        ++q;
+        stage += seg_stages;
+        if (stage == n_ring) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
+    }
+    if (lane == 0) {
+      ACCT_WRITE(0, mine * 4 + 0);  // flags
+      ACCT_WRITE(1, mine * 4 + 1);  // segment order
+      ACCT_WRITE(2, mine * 4 + 2);  // ring slots
+      ACCT_WRITE(3, mine * 4 + 3);  // issue
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
@@ -432,53 +494,85 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
       uint32_t phase = 0;
       bool ok = mbar_wait(&res_full, 0, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
       tc_fence_after();
+      ACCT_DECL(6);
+#ifdef FTB_ACCT
+      const long long acct_loop0 = clock64();
+#endif
+      // What this thread needs of a step's plan, without the addresses the other roles compute (it is
+      // the one thread every MMA of the CTA goes through: its own instructions are the step's floor).
+      const int kbh = a.H / BK;
+      const int d_layer = MODE == kDilated ? a.dil[layer] : 1;
       for (int i = 0; i < n_steps && ok; ++i) {
-        const StepPlan p = plan_step<MODE, NB>(a, layer, row_a, slice, rank, i);
+        int nseg, wkb0[2];
+        bool self;
+        if (MODE == kDilated) {
+          nseg = (d_layer > 1 && i >= d_layer) ? 2 : 1;
+          wkb0[0] = 0;
+          wkb0[1] = kbh;
+          self = d_layer == 1 && i >= 1;
+        } else {
+          nseg = row_a > 0 ? 2 : 1;
+          wkb0[0] = 2 * kbh;  // packed K order of a grid cell: [state_x | state_y | input]
+          wkb0[1] = 0;
+          self = i > 0;
+        }
         const int acc = i & 1;
+        ACCT_BEGIN();
         ok = mbar_wait(&tempty_bar[acc], ((i >> 1) & 1) ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_EPI);
+        ACCT_END(0);
         if (!ok) break;
         tc_fence_after();
         FTB_CL_STAMP(i, 0);
         const uint32_t d_tmem = tmem_base + acc * NB;
         uint32_t accumulate = 0;  // the first MMA of a step overwrites the accumulator
-        for (int s = 0; s < p.nseg && ok; ++s) {
-          const Segment& sg = p.seg[s];
-          for (int kb = 0; kb < sg.nkb; ++kb) {
-            const int ab = kb % kBlocksPerStage;
-            if (ab == 0) {
-              ok = mbar_wait(&ring_full[stage], phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
-              if (!ok) break;
-              if (kb == 0) { FTB_CL_STAMP(i, 12 + s); }
-            }
-            const uint64_t bd = ring_desc0 + static_cast<uint64_t>((stage * kStageBytes + ab * kBlockBytes) >> 4);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (s >= nseg) break;
+          ACCT_BEGIN();
+          ok = mbar_wait(&ring_full[stage], phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
+          ACCT_END(1);
+          if (!ok) break;
+          tc_fence_after();
+          FTB_CL_STAMP(i, 12 + s);
+          const uint64_t bd0 = ring_desc0 + static_cast<uint64_t>((stage * kStageBytes) >> 4);
+          const uint32_t aw = tmem_w + wkb0[s] * 32;
+          ACCT_BEGIN();
+          for (int kb = 0; kb < kbh; ++kb) {
 #pragma unroll
             for (int kk = 0; kk < BK / 16; ++kk) {
-              umma_ts(d_tmem, tmem_w + (sg.wkb0 + kb) * 32 + kk * 8, bd + 2 * kk, idesc, accumulate);
+              umma_ts(d_tmem, aw + kb * 32 + kk * 8, bd0 + static_cast<uint64_t>((kb * kBlockBytes) >> 4) + 2 * kk, idesc,
+                      accumulate);
               accumulate = 1;
             }
-            if (ab == kBlocksPerStage - 1 || kb == sg.nkb - 1) {
-              umma_commit(&ring_empty[stage]);
-              if (++stage == n_ring) {
-                stage = 0;
-                phase ^= 1u;
-              }
-            }
+          }
+          ACCT_END(4);
+          ACCT_BEGIN();
+          umma_commit(&ring_empty[stage]);  // the whole segment, on its first stage's barrier
+          ACCT_END(5);
+          stage += seg_stages;
+          if (stage == n_ring) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
         if (!ok) break;
         FTB_CL_STAMP(i, 1);
-        if (p.self) {
+        if (self) {
           // The cluster's own output of step i-1, copied by its producers into slot (i-1) & 1 of every CTA.
           const int slot = (i - 1) & 1;
           mbar_arrive_expect_tx(&self_full[slot], self_slot_bytes);
+          ACCT_BEGIN();
           ok = mbar_wait(&self_full[slot], ((i - 1) >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
+          ACCT_END(2);
           if (!ok) break;
+          tc_fence_after();
           FTB_CL_STAMP(i, 2);
           const uint32_t sb = smem_u32(s_self + slot * self_slot_bytes);
-          for (int j = 0; j < p.self_nkb * (BK / 16); ++j) {
+          const uint32_t aw = tmem_w + kbh * 32;
+          for (int j = 0; j < kbh * (BK / 16); ++j) {
             // K = 16 is two 16-byte chunks, NB * 16 bytes apart; 8-row groups are 128 bytes apart
             const uint64_t bd = make_sdesc_plain(sb + static_cast<uint32_t>(2 * j) * NB * 16, NB * 16, 128);
-            umma_ts(d_tmem, tmem_w + p.self_wkb0 * 32 + j * 8, bd, idesc, accumulate);
+            umma_ts(d_tmem, aw + j * 8, bd, idesc, accumulate);
             accumulate = 1;
           }
           umma_commit_to(&self_free[slot], producer_mask);
@@ -486,6 +580,15 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
         umma_commit(&tfull_bar[acc]);
         FTB_CL_STAMP(i, 3);
       }
+#ifdef FTB_ACCT
+      acct_[3] = clock64() - acct_loop0;
+#endif
+      ACCT_WRITE(0, 8);   // accumulator free
+      ACCT_WRITE(1, 9);   // ring data
+      ACCT_WRITE(2, 10);  // self operand
+      ACCT_WRITE(3, 11);  // whole loop
+      ACCT_WRITE(4, 15);  // MMA issue (ring operands)
+      if (MODE == kDilated && a.dil[layer] > 1) { ACCT_WRITE(5, 10); }  // commits (the slot of the self operand, unused here)
     }
   } else if (warp == 2) {
     // ------------------------------------------------ output store and flag publisher
@@ -500,8 +603,10 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
       const bool ydir = MODE == kGrid && rank >= a.CL / 2;
       const CUtensorMap* om = n_valid == NB ? (ydir ? &mapO1 : &mapO0) : (ydir ? &mapT1 : &mapT0);
       const int unit0 = MODE == kDilated ? rank * 32 : (ydir ? rank - a.CL / 2 : rank) * 128;
+      ACCT_DECL(2);
       for (int i = 0; i < n_steps; ++i) {
         const int want = kEpiWarps * (i + 1);
+        ACCT_BEGIN();
         if (*issued < want) {
           const uint64_t t0 = globaltimer_ns();
           uint32_t it = 0;
@@ -517,6 +622,8 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
             break;
           }
         }
+        ACCT_END(0);
+        ACCT_BEGIN();
         __threadfence_block();
         const int cell_row = (MODE == kDilated ? (layer * a.L + i) : ((layer * a.A + row_a) * a.L + i)) * a.N + slice * NB;
         tma_store_2d(om, s_out + (i & 1) * kOutTileBytes, unit0, cell_row);
@@ -525,8 +632,11 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
         *stored = i + 1;  // the tile may be overwritten (two steps from now)
         tma_store_wait<0>();
         st_release_gpu(a.flags + ((my_flag_cell0 + i) * a.S + slice) * a.CL + rank, 1);
+        ACCT_END(1);
         FTB_CL_STAMP(i, 11);
       }
+      ACCT_WRITE(0, 13);  // staged outputs
+      ACCT_WRITE(1, 14);  // store, wait, flag
     }
   } else if (warp >= kFirstEpiWarp) {
     // ---------------------------------------------------------------- epilogue
@@ -591,6 +701,7 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
     const uint32_t stg_unit_off = static_cast<uint32_t>(u_local >> 3) * NB * 16 + (u_local & 7) * 2;
     const uint32_t out_unit_off = static_cast<uint32_t>(u_local) * 2;
     volatile int* stored = &out_stored;
+    ACCT_DECL(2);
 
     bool ok = true;
     for (int i = 0; i < n_steps && ok; ++i) {
@@ -613,7 +724,9 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
         // one polling lane per warp, sleeping between polls; the others wait at the warp vote
         bool mine = true;
         if (lane == 0) {
+          ACCT_BEGIN();
           mine = mbar_wait_sleep(&tfull_bar[acc], (i >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA);
+          ACCT_END(0);
           // the output tile of two steps ago must have left shared memory
           if (mine && *stored < i - 1) {
             const uint64_t t0 = globaltimer_ns();
@@ -714,6 +827,7 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
         atomicAdd(&out_issued, 1);
       }
     }
+    if (warp == kFirstEpiWarp && lane == 0) { ACCT_WRITE(0, 12); }  // accumulator complete
   }
 
   // ------------------------------------------------------------------ teardown
@@ -729,6 +843,14 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// Tensor map of a row-major [rows, H] activation matrix as the kernel's operand loads see it: three
+// dimensions (64 columns of a K block, rows, K blocks), so that one copy brings the NB rows of all
+// H / 64 K blocks of a segment into consecutive 128-byte-swizzled [NB x 64] tiles of the ring.
+int make_operand_map(CUtensorMap* out, const void* base, int dtype, uint64_t rows, int H, int nb) {
+  return make_tmap_3d(out, base, dtype, 64, rows, static_cast<uint64_t>(H / 64), static_cast<uint64_t>(H) * 2, 128, 64,
+                      static_cast<uint32_t>(nb), static_cast<uint32_t>(H / 64));
 }
 
 template <typename T, int MODE, int NB>
@@ -822,8 +944,8 @@ int launch_lstm_dilated_cluster(int dtype, const void* x, const void* Wp, const 
   a.W0 = Wp; a.bias0 = bias_p; a.out0 = hs; a.c = c; a.flags = flags; a.status = status;
   CUtensorMap m[8];
   int rc;
-  if ((rc = make_tmap_2d(&m[0], x, dtype, static_cast<uint64_t>(L) * N, H, H, kDilatedNB, 64))) return rc;
-  if ((rc = make_tmap_2d(&m[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, kDilatedNB, 64))) return rc;
+  if ((rc = make_operand_map(&m[0], x, dtype, static_cast<uint64_t>(L) * N, H, kDilatedNB))) return rc;
+  if ((rc = make_operand_map(&m[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, kDilatedNB))) return rc;
   m[2] = m[1];
   m[3] = m[1];
   // output boxes: NB (or the last slice's) rows x the 32 units of a CTA, un-swizzled
@@ -864,10 +986,10 @@ int launch_grid_rnn_cluster(int dtype, const void* X, const void* Y, const void*
   CUtensorMap m[8];
   int rc;
   const uint64_t grid_rows = static_cast<uint64_t>(A) * B * N;
-  if ((rc = make_tmap_2d(&m[0], X, dtype, grid_rows, H, H, kGridNB, 64))) return rc;
-  if ((rc = make_tmap_2d(&m[1], Y, dtype, grid_rows, H, H, kGridNB, 64))) return rc;
-  if ((rc = make_tmap_2d(&m[2], hx, dtype, grid_rows * D, H, H, kGridNB, 64))) return rc;
-  if ((rc = make_tmap_2d(&m[3], hy, dtype, grid_rows * D, H, H, kGridNB, 64))) return rc;
+  if ((rc = make_operand_map(&m[0], X, dtype, grid_rows, H, kGridNB))) return rc;
+  if ((rc = make_operand_map(&m[1], Y, dtype, grid_rows, H, kGridNB))) return rc;
+  if ((rc = make_operand_map(&m[2], hx, dtype, grid_rows * D, H, kGridNB))) return rc;
+  if ((rc = make_operand_map(&m[3], hy, dtype, grid_rows * D, H, kGridNB))) return rc;
   // output boxes: NB (or the last slice's) rows x the 128 units of a CTA, un-swizzled
   const int tail = N - (a.S - 1) * kGridNB;
   if ((rc = make_tmap_2d(&m[4], hx, dtype, grid_rows * D, H, H, kGridNB, 128, false))) return rc;
@@ -884,6 +1006,11 @@ int launch_grid_rnn_cluster(int dtype, const void* X, const void* Y, const void*
 
 }  // namespace ftb
 
+#ifdef FTB_ACCT
+extern "C" int ftb_debug_set_cluster_acct(unsigned long long* buf) {
+  return cudaMemcpyToSymbol(ftb::g_cluster_acct, &buf, sizeof(buf)) == cudaSuccess ? 0 : 1;
+}
+#endif
 #ifdef FTB_TRACE
 extern "C" int ftb_debug_set_cluster_trace(unsigned long long* buf) {
   return cudaMemcpyToSymbol(ftb::g_cluster_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 1;
