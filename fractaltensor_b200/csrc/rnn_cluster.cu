@@ -84,10 +84,12 @@ __device__ unsigned long long* g_cluster_acct = nullptr;
 struct ClusterArgs {
   int D, L, N, H;  // layers, steps of a chain (dilated: time steps; grid: B), batch, hidden size
   int A;           // grid: rows of the grid (chains per layer and slice); dilated: 1
-  int S;           // batch slices of NB columns
+  int S;           // grid: batch slices of NB columns; dilated: flag slots per cell (slices of 64)
   int CL;          // CTAs per cluster
   int max_dil;
   int dil[kMaxLayers];
+  int nb[kMaxLayers];              // dilated: batch columns per cluster of the layer (64 or 128)
+  int first_cluster[kMaxLayers + 1];  // dilated: index of the layer's first cluster
   const void* W0;       // dilated: Wp [D,4H,2H]; grid: Wpx [D,H,3H]
   const void* W1;       // grid: Wpy
   const float* bias0;   // dilated: bias_p [D,4H]; grid: bias_x [D,H]   (or nullptr)
@@ -156,6 +158,12 @@ __device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, 
       }
     }
   }
+}
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
+  if constexpr (N == 32) tmem_ld32(taddr, r);
+  else tmem_ld16(taddr, r);
 }
 
 // Shared-memory operand descriptor for an un-swizzled K-major tile: core matrices of 8 rows x 16 B
@@ -232,8 +240,13 @@ __device__ __forceinline__ StepPlan plan_step(const ClusterArgs& a, int layer, i
     } else {
       x.map = 1;
       x.row = ((layer - 1) * a.L + i) * a.N + slice * NB;
-      x.flags = a.flags + (((layer - 1) * a.L + i) * a.S + slice) * a.CL;
-      x.nflags = a.CL;
+      // One flag slot per 64 sequences of a cell; a cluster publishes in the slot of its first 64.  The
+      // layer below may be cut differently: its clusters that hold this slice's rows own consecutive slots.
+      const int nbp = a.nb[layer - 1];
+      const int first = (slice * NB / nbp) * (nbp / 64);
+      x.flags = a.flags + (((layer - 1) * a.L + i) * a.S + first) * a.CL;
+      // (only the clusters that exist: the last slice of the batch may be short)
+      x.nflags = (nbp < NB ? min(NB / nbp, (a.N - slice * NB + nbp - 1) / nbp) : 1) * a.CL;
     }
     if (i >= d) {
       if (d == 1) {
@@ -246,7 +259,7 @@ __device__ __forceinline__ StepPlan plan_step(const ClusterArgs& a, int layer, i
         h.row = (layer * a.L + i - d) * a.N + slice * NB;
         h.nkb = kbh;
         h.wkb0 = kbh;
-        h.flags = a.flags + ((layer * a.L + i - d) * a.S + slice) * a.CL;
+        h.flags = a.flags + ((layer * a.L + i - d) * a.S + slice * (NB / 64)) * a.CL;
         h.nflags = a.CL;
       }
     }
@@ -293,12 +306,11 @@ __device__ __forceinline__ StepPlan plan_step(const ClusterArgs& a, int layer, i
 // outputs (dilated: hs; grid: hx, hy) as un-swizzled boxes of NB rows x this CTA's units; mapT0/mapT1:
 // the same with the row count of the last, partial batch slice.
 template <typename T, int MODE, int NB>
-__global__ void __launch_bounds__(cta_threads(MODE), 1)
-rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
-                   const __grid_constant__ CUtensorMap map2, const __grid_constant__ CUtensorMap map3,
-                   const __grid_constant__ CUtensorMap mapO0, const __grid_constant__ CUtensorMap mapO1,
-                   const __grid_constant__ CUtensorMap mapT0, const __grid_constant__ CUtensorMap mapT1,
-                   const ClusterArgs a) {
+__device__ __forceinline__ void cluster_body(const CUtensorMap& map0, const CUtensorMap& map1, const CUtensorMap& map2,
+                                             const CUtensorMap& map3, const CUtensorMap& mapO0,
+                                             const CUtensorMap& mapO1, const CUtensorMap& mapT0,
+                                             const CUtensorMap& mapT1, const ClusterArgs& a, const int cid,
+                                             const int layer, const int row_a, const int slice) {
   constexpr int kEpiWarps = epi_warps(MODE);
   constexpr int kSub = kEpiWarps / 4;              // epilogue warps per TMEM lane quadrant
   constexpr int kBlocksPerStage = 128 / NB;        // [NB x 64] 16-bit blocks per 16 KB stage
@@ -325,19 +337,6 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   int* status = a.status;
 
-  // Which chain this cluster runs.
-  const int cid = blockIdx.x / a.CL;
-  int layer, row_a, slice;
-  if (MODE == kDilated) {
-    layer = cid / a.S;
-    slice = cid - layer * a.S;
-    row_a = 0;
-  } else {
-    slice = cid % a.S;
-    const int ra = cid / a.S;
-    layer = ra / a.A;
-    row_a = ra - layer * a.A;
-  }
   const int kbh = a.H / BK;
   const int n_wkb = MODE == kDilated ? 2 * kbh : 3 * kbh;  // K blocks of this CTA's weight tile, all in TMEM
   const int K = n_wkb * BK;
@@ -631,7 +630,7 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
         tma_store_wait_read<0>();
         *stored = i + 1;  // the tile may be overwritten (two steps from now)
         tma_store_wait<0>();
-        st_release_gpu(a.flags + ((my_flag_cell0 + i) * a.S + slice) * a.CL + rank, 1);
+        st_release_gpu(a.flags + ((my_flag_cell0 + i) * a.S + slice * (MODE == kDilated ? NB / 64 : 1)) * a.CL + rank, 1);
         ACCT_END(1);
         FTB_CL_STAMP(i, 11);
       }
@@ -641,7 +640,7 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
   } else if (warp >= kFirstEpiWarp) {
     // ---------------------------------------------------------------- epilogue
     constexpr int kCols = NB / kSub;  // batch columns per warp (32 in both modes)
-    static_assert(kCols == 32, "an epilogue warp takes 32 accumulator columns");
+    static_assert(kCols == 32 || kCols == 16, "an epilogue warp takes 16 or 32 accumulator columns");
     const int q = warp & 3;
     const int sub = (warp - kFirstEpiWarp) >> 2;
     const int r_loc = q * 32 + lane;  // row of the 128-row tile = TMEM lane
@@ -747,7 +746,7 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
       float v[kCols];
       {
         uint32_t r[kCols];
-        tmem_ld32(taddr, r);
+        tmem_ld_cols<kCols>(taddr, r);
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < kCols; ++k) v[k] = __uint_as_float(r[k]);
@@ -845,6 +844,45 @@ rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_consta
   }
 }
 
+// Grid RNN: every cluster has the same shape; cluster -> (layer, grid row, batch slice).
+template <typename T, int MODE, int NB>
+__global__ void __launch_bounds__(cta_threads(MODE), 1)
+rnn_cluster_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+                   const __grid_constant__ CUtensorMap map2, const __grid_constant__ CUtensorMap map3,
+                   const __grid_constant__ CUtensorMap mapO0, const __grid_constant__ CUtensorMap mapO1,
+                   const __grid_constant__ CUtensorMap mapT0, const __grid_constant__ CUtensorMap mapT1,
+                   const ClusterArgs a) {
+  const int cid = blockIdx.x / a.CL;
+  const int slice = cid % a.S;
+  const int ra = cid / a.S;
+  const int layer = ra / a.A;
+  const int row_a = ra - layer * a.A;
+  cluster_body<T, MODE, NB>(map0, map1, map2, map3, mapO0, mapO1, mapT0, mapT1, a, cid, layer, row_a, slice);
+}
+
+// Dilated LSTM: a layer's clusters take 64 or 128 sequences each (a.nb[layer]).  A layer whose step
+// depends on its own previous step (dilation 1) is a chain of hand-offs inside the cluster, whose
+// latency grows with the slice (state bytes every CTA receives, accumulator columns per epilogue
+// warp): it runs on slices of 64; the other layers, whose steps are bound by throughput, on 128.
+// x128/h128/o128/t128: the input, the hidden states, the output tile and the output tile of the
+// batch's last (short) slice as boxes of 128 rows; x64... the same with 64 rows.
+template <typename T>
+__global__ void __launch_bounds__(cta_threads(kDilated), 1)
+rnn_cluster_dilated_kernel(const __grid_constant__ CUtensorMap x128, const __grid_constant__ CUtensorMap h128,
+                           const __grid_constant__ CUtensorMap x64, const __grid_constant__ CUtensorMap h64,
+                           const __grid_constant__ CUtensorMap o128, const __grid_constant__ CUtensorMap o64,
+                           const __grid_constant__ CUtensorMap t128, const __grid_constant__ CUtensorMap t64,
+                           const ClusterArgs a) {
+  const int cid = blockIdx.x / a.CL;
+  int layer = 0;
+  while (layer + 1 < a.D && cid >= a.first_cluster[layer + 1]) ++layer;
+  const int slice = cid - a.first_cluster[layer];
+  if (a.nb[layer] == 64)
+    cluster_body<T, kDilated, 64>(x64, h64, h64, h64, o64, o64, t64, t64, a, cid, layer, 0, slice);
+  else
+    cluster_body<T, kDilated, 128>(x128, h128, h128, h128, o128, o128, t128, t128, a, cid, layer, 0, slice);
+}
+
 // Tensor map of a row-major [rows, H] activation matrix as the kernel's operand loads see it: three
 // dimensions (64 columns of a K block, rows, K blocks), so that one copy brings the NB rows of all
 // H / 64 K blocks of a segment into consecutive 128-byte-swizzled [NB x 64] tiles of the ring.
@@ -853,17 +891,16 @@ int make_operand_map(CUtensorMap* out, const void* base, int dtype, uint64_t row
                       static_cast<uint32_t>(nb), static_cast<uint32_t>(H / 64));
 }
 
-template <typename T, int MODE, int NB>
-int launch(const CUtensorMap* m, const ClusterArgs& a, int grid, uint32_t smem_bytes, cudaStream_t stream) {
-  static std::atomic<unsigned long long> configured{0};
-  auto kfn = rnn_cluster_kernel<T, MODE, NB>;
+template <typename Kernel>
+int launch_kernel(Kernel kfn, int threads, std::atomic<unsigned long long>& configured, const CUtensorMap* m,
+                  const ClusterArgs& a, int grid, uint32_t smem_bytes, cudaStream_t stream) {
   // the largest request of this instantiation (static shared memory comes on top of it)
   constexpr int kMaxDynamic = 226 * 1024;
   if (smem_bytes > static_cast<uint32_t>(kMaxDynamic) || !ensure_dynamic_smem(kfn, kMaxDynamic, configured))
     return FTB_ERR_LAUNCH;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(cta_threads(MODE));
+  cfg.blockDim = dim3(threads);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
@@ -903,6 +940,17 @@ int launch(const CUtensorMap* m, const ClusterArgs& a, int grid, uint32_t smem_b
   return FTB_OK;
 }
 
+template <typename T, int MODE, int NB>
+int launch(const CUtensorMap* m, const ClusterArgs& a, int grid, uint32_t smem_bytes, cudaStream_t stream) {
+  static std::atomic<unsigned long long> configured{0};
+  return launch_kernel(rnn_cluster_kernel<T, MODE, NB>, cta_threads(MODE), configured, m, a, grid, smem_bytes, stream);
+}
+template <typename T>
+int launch_dilated(const CUtensorMap* m, const ClusterArgs& a, int grid, uint32_t smem_bytes, cudaStream_t stream) {
+  static std::atomic<unsigned long long> configured{0};
+  return launch_kernel(rnn_cluster_dilated_kernel<T>, cta_threads(kDilated), configured, m, a, grid, smem_bytes, stream);
+}
+
 uint32_t smem_for(bool any_self, int H, int NB, int self_units, int out_units, int ring_self) {
   // worst case over the chains of the launch; must agree with the kernel's carve-up
   const uint32_t out_tiles = 2u * NB * out_units * 2;
@@ -914,17 +962,34 @@ uint32_t smem_for(bool any_self, int H, int NB, int self_units, int out_units, i
 }  // namespace
 
 // ------------------------------------------------------------------ dilated LSTM
-constexpr int kDilatedNB = 128;
+namespace {
+// Slice width per layer: 64 for the layers with dilation 1 when the clusters still fit, else 128
+// everywhere.  Returns the number of clusters, 0 when even slices of 128 do not fit.
+int dilated_slices(const int* dilations, int D, int N, int CL, int sm_count, int* nb) {
+  const int s128 = (N + 127) / 128, s64 = (N + 63) / 64;
+  auto narrow = [&](int l) { return N <= 64 || (dilations != nullptr && dilations[l] == 1); };
+  int mixed = 0;
+  for (int l = 0; l < D; ++l) mixed += narrow(l) ? s64 : s128;
+  const bool use_mixed = s64 <= 8 && mixed * CL <= sm_count;
+  int total = 0;
+  for (int l = 0; l < D; ++l) {
+    const bool n64 = use_mixed && narrow(l);
+    if (nb != nullptr) nb[l] = n64 ? 64 : 128;
+    total += n64 ? s64 : s128;
+  }
+  return s128 <= 8 && total * CL <= sm_count ? total : 0;
+}
+}  // namespace
 
 bool lstm_dilated_cluster_supported(int dtype, int D, int N, int H, int sm_count) {
   if (dtype != FTB_F16 && dtype != FTB_BF16) return false;
   if (H != 64 && H != 128 && H != 256) return false;  // 4H / 128 = 2, 4 or 8 CTAs per cluster
   if (D < 1 || D > kMaxLayers || N < 1) return false;
-  const int S = (N + kDilatedNB - 1) / kDilatedNB;
-  return S <= 8 && D * S * (4 * H / 128) <= sm_count;
+  return dilated_slices(nullptr, D, N, 4 * H / 128, sm_count, nullptr) > 0;
 }
 
-size_t lstm_dilated_cluster_flag_ints(int D, int L) { return static_cast<size_t>(D) * L * 8 * 8; }
+// one flag per (cell, slot of 64 sequences, CTA of the cluster); at most 16 slots (8 slices of 128) x 8 CTAs
+size_t lstm_dilated_cluster_flag_ints(int D, int L) { return static_cast<size_t>(D) * L * 16 * 8; }
 
 // x: [L,N,H]; Wp: [D,4H,2H]; hs: [D,L,N,H]; c: [D, max_dil*N, H]; flags: D*L*S*CL ints (zeroed here).
 int launch_lstm_dilated_cluster(int dtype, const void* x, const void* Wp, const float* bias_p, void* hs, float* c,
@@ -932,7 +997,7 @@ int launch_lstm_dilated_cluster(int dtype, const void* x, const void* Wp, const 
                                 cudaStream_t stream) {
   ClusterArgs a = {};
   a.D = D; a.L = L; a.N = N; a.H = H; a.A = 1;
-  a.S = (N + kDilatedNB - 1) / kDilatedNB;
+  a.S = 2 * ((N + 127) / 128);  // flag slots per cell
   a.CL = 4 * H / 128;
   a.max_dil = 1;
   bool any_self = false;
@@ -941,25 +1006,30 @@ int launch_lstm_dilated_cluster(int dtype, const void* x, const void* Wp, const 
     a.max_dil = std::max(a.max_dil, dilations[l]);
     any_self = any_self || dilations[l] == 1;
   }
+  const int clusters = dilated_slices(dilations, D, N, a.CL, current_sm_count(), a.nb);
+  if (clusters <= 0) return FTB_ERR_ARG;
+  a.first_cluster[0] = 0;
+  for (int l = 0; l < D; ++l) a.first_cluster[l + 1] = a.first_cluster[l] + (N + a.nb[l] - 1) / a.nb[l];
   a.W0 = Wp; a.bias0 = bias_p; a.out0 = hs; a.c = c; a.flags = flags; a.status = status;
   CUtensorMap m[8];
   int rc;
-  if ((rc = make_operand_map(&m[0], x, dtype, static_cast<uint64_t>(L) * N, H, kDilatedNB))) return rc;
-  if ((rc = make_operand_map(&m[1], hs, dtype, static_cast<uint64_t>(D) * L * N, H, kDilatedNB))) return rc;
-  m[2] = m[1];
-  m[3] = m[1];
-  // output boxes: NB (or the last slice's) rows x the 32 units of a CTA, un-swizzled
-  const int tail = N - (a.S - 1) * kDilatedNB;
-  if ((rc = make_tmap_2d(&m[4], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, kDilatedNB, 32, false))) return rc;
-  if ((rc = make_tmap_2d(&m[6], hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, tail, 32, false))) return rc;
-  m[5] = m[4];
-  m[7] = m[6];
+  const uint64_t x_rows = static_cast<uint64_t>(L) * N, h_rows = static_cast<uint64_t>(D) * L * N;
+  if ((rc = make_operand_map(&m[0], x, dtype, x_rows, H, 128))) return rc;
+  if ((rc = make_operand_map(&m[1], hs, dtype, h_rows, H, 128))) return rc;
+  if ((rc = make_operand_map(&m[2], x, dtype, x_rows, H, 64))) return rc;
+  if ((rc = make_operand_map(&m[3], hs, dtype, h_rows, H, 64))) return rc;
+  // output boxes: the slice's (or the last, short slice's) rows x the 32 units of a CTA, un-swizzled
+  const int tail128 = N - ((N + 127) / 128 - 1) * 128, tail64 = N - ((N + 63) / 64 - 1) * 64;
+  if ((rc = make_tmap_2d(&m[4], hs, dtype, h_rows, H, H, 128, 32, false))) return rc;
+  if ((rc = make_tmap_2d(&m[5], hs, dtype, h_rows, H, H, 64, 32, false))) return rc;
+  if ((rc = make_tmap_2d(&m[6], hs, dtype, h_rows, H, H, tail128, 32, false))) return rc;
+  if ((rc = make_tmap_2d(&m[7], hs, dtype, h_rows, H, H, tail64, 32, false))) return rc;
   const size_t n_flags = static_cast<size_t>(D) * L * a.S * a.CL;
   if (cudaMemsetAsync(flags, 0, sizeof(int) * n_flags, stream) != cudaSuccess) return FTB_ERR_LAUNCH;
-  const int grid = D * a.S * a.CL;
-  const uint32_t smem = smem_for(any_self, H, kDilatedNB, 32, 32, 4);
-  if (dtype == FTB_F16) return launch<__half, kDilated, kDilatedNB>(m, a, grid, smem, stream);
-  return launch<__nv_bfloat16, kDilated, kDilatedNB>(m, a, grid, smem, stream);
+  const int grid = clusters * a.CL;
+  const uint32_t smem = smem_for(any_self, H, 128, 32, 32, 4);
+  if (dtype == FTB_F16) return launch_dilated<__half>(m, a, grid, smem, stream);
+  return launch_dilated<__nv_bfloat16>(m, a, grid, smem, stream);
 }
 
 // --------------------------------------------------------------------- grid RNN
