@@ -328,11 +328,11 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < nkb; ++kb) {
+          // (No tcgen05 fence after a barrier that TMA completes: it would drain the tensor pipe.)
           if (!mbar_wait(&full_bar[stage], phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) {
             ok = false;
             break;
           }
-          tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
           const uint32_t sb = sa + C::kABytes;
 #pragma unroll

@@ -251,8 +251,9 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
           }
           const uint32_t d_tmem = tmem_base + acc * BN;
           for (int kb = 0; kb < nkb; ++kb) {
+            // (No tcgen05 fence after a barrier that TMA completes: the fence orders against other threads'
+            // tcgen05 operations, which do not touch the stage, and it drains the tensor pipe.)
             if (!mbar_wait(&full_bar[stage], phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
-            tc_fence_after();
 #ifdef FTB_TRACE
             if (a.trace && !is_x && kb == 0) a.trace[(static_cast<size_t>(l * a.L + t) * a.tiles_per_cell + tile) * 4 + 1] = globaltimer_ns();
 #endif

@@ -531,7 +531,6 @@ __device__ __forceinline__ void cluster_body(const CUtensorMap& map0, const CUte
           ok = mbar_wait(&ring_full[stage], phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
           ACCT_END(1);
           if (!ok) break;
-          tc_fence_after();
           FTB_CL_STAMP(i, 12 + s);
           const uint64_t bd0 = ring_desc0 + static_cast<uint64_t>((stage * kStageBytes) >> 4);
           const uint32_t aw = tmem_w + wkb0[s] * 32;
@@ -564,7 +563,6 @@ __device__ __forceinline__ void cluster_body(const CUtensorMap& map0, const CUte
           ok = mbar_wait(&self_full[slot], ((i - 1) >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
           ACCT_END(2);
           if (!ok) break;
-          tc_fence_after();
           FTB_CL_STAMP(i, 2);
           const uint32_t sb = smem_u32(s_self + slot * self_slot_bytes);
           const uint32_t aw = tmem_w + kbh * 32;
