@@ -445,6 +445,34 @@ def test_dilated_schedules_agree_bit_for_bit(ops):
     _assert_16(ref, dense.dilated_lstm_dense(*_f32(x, W, U), dils, b.double()))
 
 
+@pytest.mark.parametrize("case", [
+    # N, H, dilations: which layers run on slices of 64 sequences and which on 128, and who waits for whom
+    (150, 128, [1, 2]),        # short last slice in both cuts: 3 slices of 64 feed 2 of 128
+    (200, 64, [2, 1, 1, 3]),   # slices of 64 above slices of 128 and above each other
+    (65, 256, [1, 1]),         # one full and one one-row slice
+    (40, 128, [2, 4]),         # at most 64 sequences: every layer on one slice of 64
+    (256, 256, [1, 2, 4]),     # the benchmark's cut: 4 + 2 + 2 clusters
+    (300, 128, [4, 1, 2]),     # 5 slices of 64, 3 of 128
+])
+def test_dilated_cluster_slice_widths(ops, case):
+    """The cluster schedule cuts layers with dilation 1 into slices of 64 sequences and the others into
+    slices of 128; a layer waits on the flags of a layer that may be cut differently.  Same bits as
+    one launch per level, for batch sizes that leave short last slices in either cut."""
+    N, H, dils = case
+    D, L = len(dils), 13
+    x, W, U, b = dense.make_lstm_inputs(D, L, N, H, H, 17, 1.0 / 8, dtype=torch.float16, bias=True)
+    xd, Wd, Ud, bd = _dev(x, W, U, b)
+    Wp, bp = ops.lstm_pack_weights(Wd, Ud, bd)
+    ref, rc = ops.lstm_dilated(xd, Wp, dils, bp, schedule=1)
+    ops.check_status()
+    hs, c = ops.lstm_dilated(xd, Wp, dils, bp, schedule=4)
+    ops.check_status()
+    assert torch.equal(hs, ref)
+    for l, d in enumerate(dils):  # a layer keeps one cell state per interleaved chain: d * N rows of its block
+        assert torch.equal(c[l, :d * N], rc[l, :d * N]), l
+    _assert_16(hs, dense.dilated_lstm_dense(*_f32(x, W, U), dils, b.double()))
+
+
 def test_dilated_config5a_prefix(ops):
     """benchmark config 5a shape (6 layers, dilations 1..32, H256, N256) on the first 64 steps
     (the recurrence up to step t only needs inputs up to t)."""
