@@ -963,19 +963,52 @@ uint32_t smem_for(bool any_self, int H, int NB, int self_units, int out_units, i
 namespace {
 // Slice width per layer: 64 for the layers with dilation 1 when the clusters still fit, else 128
 // everywhere.  Returns the number of clusters, 0 when even slices of 128 do not fit.
-int dilated_slices(const int* dilations, int D, int N, int CL, int sm_count, int* nb) {
+int dilated_slices(const int* dilations, int D, int N, int max_clusters, int* nb) {
   const int s128 = (N + 127) / 128, s64 = (N + 63) / 64;
   auto narrow = [&](int l) { return N <= 64 || (dilations != nullptr && dilations[l] == 1); };
   int mixed = 0;
   for (int l = 0; l < D; ++l) mixed += narrow(l) ? s64 : s128;
-  const bool use_mixed = s64 <= 8 && mixed * CL <= sm_count;
+  const bool use_mixed = s64 <= 8 && mixed <= max_clusters;
   int total = 0;
   for (int l = 0; l < D; ++l) {
     const bool n64 = use_mixed && narrow(l);
     if (nb != nullptr) nb[l] = n64 ? 64 : 128;
     total += n64 ? s64 : s128;
   }
-  return s128 <= 8 && total * CL <= sm_count ? total : 0;
+  return s128 <= 8 && total <= max_clusters ? total : 0;
+}
+
+// Clusters of `cl` CTAs of the dilated kernel that can be resident at once on the current device (a
+// cluster needs its CTAs' SMs inside one GPC, so this is less than SMs / cl: 15 clusters of 8 on a
+// 148-SM B200).  0 when the query fails.
+int dilated_max_clusters(int dtype, int cl, uint32_t smem) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cl * 32);
+  cfg.blockDim = dim3(cta_threads(kDilated));
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = cl;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  int n = 0;
+  cudaError_t e;
+  if (dtype == FTB_F16) {
+    static std::atomic<unsigned long long> configured{0};
+    if (!ensure_dynamic_smem(rnn_cluster_dilated_kernel<__half>, 226 * 1024, configured)) return 0;
+    e = cudaOccupancyMaxActiveClusters(&n, rnn_cluster_dilated_kernel<__half>, &cfg);
+  } else {
+    static std::atomic<unsigned long long> configured{0};
+    if (!ensure_dynamic_smem(rnn_cluster_dilated_kernel<__nv_bfloat16>, 226 * 1024, configured)) return 0;
+    e = cudaOccupancyMaxActiveClusters(&n, rnn_cluster_dilated_kernel<__nv_bfloat16>, &cfg);
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
 }
 }  // namespace
 
@@ -983,7 +1016,8 @@ bool lstm_dilated_cluster_supported(int dtype, int D, int N, int H, int sm_count
   if (dtype != FTB_F16 && dtype != FTB_BF16) return false;
   if (H != 64 && H != 128 && H != 256) return false;  // 4H / 128 = 2, 4 or 8 CTAs per cluster
   if (D < 1 || D > kMaxLayers || N < 1) return false;
-  return dilated_slices(nullptr, D, N, 4 * H / 128, sm_count, nullptr) > 0;
+  // (coarse: the launcher asks the driver how many clusters fit and falls back if these do not)
+  return dilated_slices(nullptr, D, N, sm_count / (4 * H / 128), nullptr) > 0;
 }
 
 // one flag per (cell, slot of 64 sequences, CTA of the cluster); at most 16 slots (8 slices of 128) x 8 CTAs
@@ -1004,8 +1038,9 @@ int launch_lstm_dilated_cluster(int dtype, const void* x, const void* Wp, const 
     a.max_dil = std::max(a.max_dil, dilations[l]);
     any_self = any_self || dilations[l] == 1;
   }
-  const int clusters = dilated_slices(dilations, D, N, a.CL, current_sm_count(), a.nb);
-  if (clusters <= 0) return FTB_ERR_ARG;
+  const uint32_t smem = smem_for(any_self, H, 128, 32, 32, 4);
+  const int clusters = dilated_slices(dilations, D, N, dilated_max_clusters(dtype, a.CL, smem), a.nb);
+  if (clusters <= 0) return FTB_ERR_LAUNCH;  // does not fit on this device: the caller's generic wavefront takes it
   a.first_cluster[0] = 0;
   for (int l = 0; l < D; ++l) a.first_cluster[l + 1] = a.first_cluster[l] + (N + a.nb[l] - 1) / a.nb[l];
   a.W0 = Wp; a.bias0 = bias_p; a.out0 = hs; a.c = c; a.flags = flags; a.status = status;
@@ -1025,7 +1060,6 @@ int launch_lstm_dilated_cluster(int dtype, const void* x, const void* Wp, const 
   const size_t n_flags = static_cast<size_t>(D) * L * a.S * a.CL;
   if (cudaMemsetAsync(flags, 0, sizeof(int) * n_flags, stream) != cudaSuccess) return FTB_ERR_LAUNCH;
   const int grid = clusters * a.CL;
-  const uint32_t smem = smem_for(any_self, H, 128, 32, 32, 4);
   if (dtype == FTB_F16) return launch_dilated<__half>(m, a, grid, smem, stream);
   return launch_dilated<__nv_bfloat16>(m, a, grid, smem, stream);
 }
