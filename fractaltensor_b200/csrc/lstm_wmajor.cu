@@ -67,10 +67,13 @@ struct WCfg {
   static constexpr uint32_t kAccCols = 2 * NB;  // two tiles in flight
   // Recurrent weight blocks resident in TMEM beside the accumulators (32 columns per block).
   static constexpr int kTmemBlocks = (512 - kAccCols) / 32;
-  static constexpr int kActStages = NB == 128 ? 6 : 4;
+  static constexpr int kActStages = NB == 128 ? 5 : 3;
   // A weight stage holds two K blocks (32 KB): half as many commits and barrier waits per byte.
   static constexpr int kWStages = (14 - kActStages) / 2;
-  static constexpr uint32_t kSmemBytes = (kActStages + 2 * kWStages) * kBlockBytes + 1024;
+  // The step's output tile, row-major [NB sequences][32 units], staged for one TMA store (13 ring
+  // stages of 16 KB are left beside it).
+  static constexpr uint32_t kOutBytes = NB * (BMW / 4) * 2;
+  static constexpr uint32_t kSmemBytes = (kActStages + 2 * kWStages) * kBlockBytes + kOutBytes + 1024;
 };
 
 struct WArgs {
@@ -185,7 +188,8 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
 template <typename T, int NB>
 __global__ void __launch_bounds__(kThreads, 1)
 lstm_wmajor_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapH,
-                   const __grid_constant__ CUtensorMap mapW, const WArgs a) {
+                   const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapO,
+                   const WArgs a) {
   using C = WCfg<NB>;
   constexpr int AS = C::kActStages, WS = C::kWStages;
   extern __shared__ uint8_t smem_raw[];
@@ -201,12 +205,14 @@ lstm_wmajor_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* s_act = smem;
   uint8_t* s_w = s_act + AS * kBlockBytes;
+  uint8_t* s_out = s_w + 2 * WS * kBlockBytes;
   int* status = a.status;
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&mapX);
     prefetch_tmap(&mapH);
     prefetch_tmap(&mapW);
+    prefetch_tmap(&mapO);
     for (int i = 0; i < AS; ++i) {
       mbar_init(&act_full[i], 1);
       mbar_init(&act_empty[i], 1);
@@ -274,7 +280,8 @@ lstm_wmajor_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         bool fine = true;
         if (lane == 0) {
           FTB_WM_STAMP(l, t, is_x ? 1 : 0);
-          fence_proxy_async_all();  // other CTAs' plain stores of h -> this thread's TMA loads
+          // (The hidden states were written by TMA stores and are read by TMA loads: both sides are in
+          // the async proxy, so the flag's release/acquire is all the ordering there is.)
           for (int kb0 = 0; kb0 < nkb && fine; kb0 += C::kActBlocks) {
             const int nb = min(C::kActBlocks, nkb - kb0);
             fine = mbar_wait(&act_empty[stage], phase ^ 1u, &s_abort, status, FTB_ERR_TIMEOUT_SLOT);
@@ -469,7 +476,11 @@ lstm_wmajor_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         tc_fence_after();
         if (warp == kFirstEpiWarp && lane == 0) { FTB_WM_STAMP(l, t, 10); }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * NB + half * kCols;
-        T* out = reinterpret_cast<T*>(a.hs) + (static_cast<size_t>(l) * a.L + t) * a.N * a.H + unit;
+        // The step's output goes through a row-major [NB][32] tile in shared memory and one TMA store.
+        // The previous step's tile must have left shared memory: the publishing thread arrives here
+        // only after its store has completed.
+        T* s_tile = reinterpret_cast<T*>(s_out) + (r_loc >> 2);
+        asm volatile("bar.sync 2, %0;" ::"n"(32 * kEpiWarps) : "memory");
 #pragma unroll
         for (int ch = 0; ch < kChunks; ++ch) {
           float v[kChunk];
@@ -492,17 +503,21 @@ lstm_wmajor_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             creg[ci] = c_new;
             const float h_new = sigmoid_fast(go) * tanh_fast(c_new);
             const int n = half * kCols + ch * kChunk + 4 * kq + gate;
-            if (n < a.N) store_h<T>(out + static_cast<size_t>(n) * a.H, h_new);
+            store_h<T>(s_tile + n * (BMW / 4), h_new);  // rows past the batch stay in the tile
           }
         }
         if (warp == kFirstEpiWarp && lane == 0) { FTB_WM_STAMP(l, t, 11); }
-        // Publish: every epilogue thread's plain stores of h are ordered before the one release store
-        // by the barrier of the eight epilogue warps; they feed other CTAs' TMA loads (proxy fence).
+        // Publish: once the eight epilogue warps have written the tile, one thread stores it with TMA
+        // (the first a.N rows), waits for the store and releases the tile's flag; the readers are other
+        // CTAs' TMA loads.
         tc_fence_before();
-        fence_proxy_async_all();
+        fence_proxy_async_smem();  // plain shared-memory stores -> the TMA store's reads
         if (lane == 0) mbar_arrive(&tempty_bar[acc]);
         asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
         if (warp == kFirstEpiWarp && lane == 0) {
+          tma_store_2d(&mapO, s_out, n_tile * (BMW / 4), (l * a.L + t) * a.N);
+          tma_store_commit();
+          tma_store_wait<0>();
           st_release_gpu(a.done + (l * a.L + t) * a.n_tiles + n_tile, 1);
           FTB_WM_STAMP(l, t, 12);
         }
@@ -534,8 +549,8 @@ lstm_wmajor_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
 }
 
 template <typename T, int NB>
-int launch(const CUtensorMap& mX, const CUtensorMap& mH, const CUtensorMap& mW, const WArgs& a, int grid,
-           cudaStream_t stream) {
+int launch(const CUtensorMap& mX, const CUtensorMap& mH, const CUtensorMap& mW, const CUtensorMap& mO, const WArgs& a,
+           int grid, cudaStream_t stream) {
   using C = WCfg<NB>;
   static std::atomic<unsigned long long> configured{0};
   auto kfn = lstm_wmajor_kernel<T, NB>;
@@ -567,7 +582,7 @@ int launch(const CUtensorMap& mX, const CUtensorMap& mH, const CUtensorMap& mW, 
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  if (cudaLaunchKernelEx(&cfg, kfn, mX, mH, mW, a) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kfn, mX, mH, mW, mO, a) != cudaSuccess) {
     cudaGetLastError();
     return FTB_ERR_LAUNCH;
   }
@@ -605,19 +620,21 @@ int launch_lstm_wmajor(int dtype, const void* x, const void* Wp, const float* bi
   a.status = status;
   a.trace = trace;
   const int K = I + H;
-  CUtensorMap mX, mH, mW;
+  CUtensorMap mX, mH, mW, mO;
   int rc;
   if ((rc = make_tmap_2d(&mX, x, dtype, static_cast<uint64_t>(L) * N, I, I, NB, 64))) return rc;
   if ((rc = make_tmap_2d(&mH, hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, NB, 64))) return rc;
   if ((rc = make_tmap_2d(&mW, Wp, dtype, static_cast<uint64_t>(D) * 4 * H, K, K, BMW, 64))) return rc;
+  // output boxes: the batch's N rows x the 32 units of a CTA, un-swizzled
+  if ((rc = make_tmap_2d(&mO, hs, dtype, static_cast<uint64_t>(D) * L * N, H, H, N, BMW / 4, false))) return rc;
   if (cudaMemsetAsync(done, 0, sizeof(int) * static_cast<size_t>(D) * L * a.n_tiles, stream) != cudaSuccess)
     return FTB_ERR_LAUNCH;
   const int grid = std::min(G, D) * a.n_tiles;
 #define FTB_WM_LAUNCH(TT)                                              \
   switch (NB) {                                                        \
-    case 32: return launch<TT, 32>(mX, mH, mW, a, grid, stream);       \
-    case 64: return launch<TT, 64>(mX, mH, mW, a, grid, stream);       \
-    default: return launch<TT, 128>(mX, mH, mW, a, grid, stream);      \
+    case 32: return launch<TT, 32>(mX, mH, mW, mO, a, grid, stream);       \
+    case 64: return launch<TT, 64>(mX, mH, mW, mO, a, grid, stream);       \
+    default: return launch<TT, 128>(mX, mH, mW, mO, a, grid, stream);      \
   }
   if (dtype == FTB_F16) {
     FTB_WM_LAUNCH(__half)
