@@ -54,7 +54,10 @@ constexpr int kStages = 6;
 constexpr uint32_t kABytes = BM * BK * 2;
 constexpr uint32_t kBBytes = (BN / 2) * BK * 2;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;
+// One [128 rows x 64 units] output tile per CTA, in the 128-byte-swizzled layout of the tensor map
+// the next cells load it with, so that one TMA store publishes a step's hidden states.
+constexpr uint32_t kOutTileBytes = BM * (BN / 4) * 2;
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + kOutTileBytes + 1024;
 constexpr uint32_t kTmemCols = 2 * BN;
 
 struct StaticArgs {
@@ -67,6 +70,7 @@ struct StaticArgs {
   float* c_out;        // [D, N, H]
   int* done;           // [D * L] completion counters, zero before the launch
   int* status;
+  int tma_out;         // 1: every row tile is full (N % 128 == 0), outputs leave through TMA stores
   unsigned long long* trace;  // debug builds (FTB_TRACE): [D*L][tiles_per_cell][4] globaltimer stamps, else nullptr
 };
 
@@ -105,6 +109,7 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = the pair's leader: it issues the MMAs
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* s_out = smem + kStages * kStageBytes;  // the CTA's output tile (TMA-store path)
   int* status = a.status;
 
   if (threadIdx.x == 0) {
@@ -146,7 +151,8 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
   const int tile = blockIdx.x - j * a.tiles_per_cell;
   const int n_tile = tile / a.m_tiles;
   const int m_tile = tile - n_tile * a.m_tiles;  // parity == rank
-  const int target = kEpiWarps * a.tiles_per_cell;
+  // completions a cell's counter collects: one per tile with TMA stores, one per epilogue warp without
+  const int target = (a.tma_out ? 1 : kEpiWarps) * a.tiles_per_cell;
   const int n_groups = (a.D + a.G - 1) / a.G;
   const int kb_x0 = a.I / BK, kb_h = a.H / BK;
 
@@ -204,7 +210,8 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
               }
             }
             if (!flag_wait_ge(dep, target, &s_abort, status, FTB_ERR_TIMEOUT_DEP)) return false;
-            fence_proxy_async_all();
+            // plain stores of h by other CTAs -> this thread's TMA loads; TMA-stored h needs no fence
+            if (!a.tma_out) fence_proxy_async_all();
 #ifdef FTB_TRACE
             if (a.trace && !is_x) a.trace[(static_cast<size_t>(l * a.L + t) * a.tiles_per_cell + tile) * 4 + 0] = globaltimer_ns();
 #endif
@@ -312,6 +319,11 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
         T* out_row = reinterpret_cast<T*>(a.hs) + (static_cast<size_t>(l) * a.L + t) * a.N * a.H +
                      static_cast<size_t>(row) * a.H;
+        // With TMA stores the step's [128 x 64] tile is built in shared memory first (row r_loc, 16-byte
+        // chunk = 8 units, chunk index XOR row % 8: the tensor map's 128-byte swizzle).  The previous
+        // step's tile must have left shared memory: the storing thread arrives here after its store.
+        uint8_t* tile_row = s_out + r_loc * 128;
+        if (a.tma_out) asm volatile("bar.sync 2, %0;" ::"n"(32 * kEpiWarps) : "memory");
         // After the last read of the accumulator the MMA warp gets it back, before the arithmetic of
         // the chunks just read: it is the accumulator of the tile after next, whose input half is the
         // very next thing the tensor pipe has to do.
@@ -346,26 +358,48 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
               creg[8 * cc + u] = c_new;
               hn[u] = sigmoid_fast(go) * tanh_fast(c_new);
             }
-            if (row_ok) {
-              uint4 v;
-              v.x = Fmt<T>::pack2(hn[0], hn[1]);
-              v.y = Fmt<T>::pack2(hn[2], hn[3]);
-              v.z = Fmt<T>::pack2(hn[4], hn[5]);
-              v.w = Fmt<T>::pack2(hn[6], hn[7]);
+            uint4 v;
+            v.x = Fmt<T>::pack2(hn[0], hn[1]);
+            v.y = Fmt<T>::pack2(hn[2], hn[3]);
+            v.z = Fmt<T>::pack2(hn[4], hn[5]);
+            v.w = Fmt<T>::pack2(hn[6], hn[7]);
+            if (a.tma_out) {
+              const int chunk = half * 4 + cc;
+              *reinterpret_cast<uint4*>(tile_row + ((chunk ^ (r_loc & 7)) << 4)) = v;
+            } else if (row_ok) {
               *reinterpret_cast<uint4*>(out_row + unit0) = v;
             }
           }
         };
         round(std::integral_constant<int, 0>{}, std::integral_constant<int, kFirstRound>{}, std::false_type{});
         round(std::integral_constant<int, kFirstRound>{}, std::integral_constant<int, 4 - kFirstRound>{}, std::true_type{});
-        fence_proxy_async_all();  // plain stores of h -> other CTAs' TMA loads
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) {
-          red_release_gpu_add(a.done + l * a.L + t, 1);
+        if (a.tma_out) {
+          // One thread stores the tile once the eight warps have written it, waits for the store and
+          // counts the tile in; the readers are other CTAs' TMA loads (same proxy: no fence).
+          fence_proxy_async_smem();
+          asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+          if (warp == 2 && lane == 0) {
+            // (a pair covers 256 rows: with 128 sequences the second CTA's tile is all padding)
+            if (m_tile * BM < a.N) {
+              tma_store_2d(&mapH, s_out, n_tile * (BN / 4), (l * a.L + t) * a.N + m_tile * BM);
+              tma_store_commit();
+              tma_store_wait<0>();
+            }
+            red_release_gpu_add(a.done + l * a.L + t, 1);
 #ifdef FTB_TRACE
-          if (a.trace && warp == 2) a.trace[(static_cast<size_t>(l * a.L + t) * a.tiles_per_cell + tile) * 4 + 3] = globaltimer_ns();
+            if (a.trace) a.trace[(static_cast<size_t>(l * a.L + t) * a.tiles_per_cell + tile) * 4 + 3] = globaltimer_ns();
 #endif
+          }
+        } else {
+          fence_proxy_async_all();  // plain stores of h -> other CTAs' TMA loads
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) {
+            red_release_gpu_add(a.done + l * a.L + t, 1);
+#ifdef FTB_TRACE
+            if (a.trace && warp == 2) a.trace[(static_cast<size_t>(l * a.L + t) * a.tiles_per_cell + tile) * 4 + 3] = globaltimer_ns();
+#endif
+          }
         }
       }
       // Final cell state of the sweep.
@@ -466,6 +500,7 @@ int launch_lstm_static(int dtype, const void* x, const void* Wp, const float* bi
   a.c_out = c;
   a.done = done;
   a.status = status;
+  a.tma_out = (N % BM == 0) ? 1 : 0;
   a.trace = trace;
   const int K = I + H;
   CUtensorMap mX, mH, mW;
