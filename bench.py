@@ -33,7 +33,7 @@ FLOPS_PER_SAMPLE_STEP = CFG["D"] * 2 * 4 * CFG["H"] * (CFG["I"] + CFG["H"])  # a
 # DRAM bytes (read + write) of one launch of the dominant kernel at the 1-GPU workload, from a
 # one-pass ncu capture of this command (775.7 MB read + 832.0 MB written; compulsory: 268 MB
 # weights + 52 MB x read, 839 MB hidden states written).
-TRAFFIC_BYTES_PER_LAUNCH = 1607.7e6
+TRAFFIC_BYTES_PER_LAUNCH = 1550.9e6
 
 
 def workload_config(world):
