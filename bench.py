@@ -31,7 +31,7 @@ METRIC = "lstm_samples_steps_per_s_h1024_d16"
 UNIT = "samples*steps/s"
 FLOPS_PER_SAMPLE_STEP = CFG["D"] * 2 * 4 * CFG["H"] * (CFG["I"] + CFG["H"])  # all layers
 # DRAM bytes (read + write) of one launch of the dominant kernel at the 1-GPU workload, from a
-# one-pass ncu capture of this command (775.7 MB read + 832.0 MB written; compulsory: 268 MB
+# one-pass ncu capture of this command (717.7 MB read + 833.2 MB written; compulsory: 268 MB
 # weights + 52 MB x read, 839 MB hidden states written).
 TRAFFIC_BYTES_PER_LAUNCH = 1550.9e6
 
