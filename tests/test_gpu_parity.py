@@ -487,6 +487,52 @@ def test_dilated_config5a_prefix(ops):
     assert torch.isfinite(hs.float()).all()
 
 
+@pytest.mark.parametrize("seed", [1, 2])
+def test_schedules_agree_on_random_shapes(ops, seed):
+    """Every schedule of the stacked and dilated LSTM (16-bit) that accepts a randomly drawn shape gives
+    the bits of one launch per level: batch sizes around the 64-, 128- and 256-row tile edges, depths
+    that do not fill a layer group, dilations in any order."""
+    import random
+    from fractaltensor_b200._lib import FtbError
+    rng = random.Random(seed)
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    uni = lambda b, *sh: (torch.rand(*sh, device="cuda", generator=g) * 2 - 1) * b
+    for _ in range(6):
+        dt = rng.choice([torch.bfloat16, torch.float16])
+        D, L, H = rng.choice([1, 2, 3, 5]), rng.randint(1, 9), rng.choice([64, 128, 256, 512])
+        N = rng.choice([1, 17, 64, 100, 128, 129, 200, 256, 300, 384])
+        x = torch.randn(L, N, H, device="cuda", generator=g).to(dt)
+        Wp, bp = ops.lstm_pack_weights(uni(1 / 8, D, 4, H, H).to(dt), uni(1 / 8, D, 4, H, H).to(dt), uni(1 / 8, D, 4, H).to(dt))
+        ref = ops.lstm_stacked(x, Wp, bp, schedule=1)
+        ops.check_status()
+        ran = 0
+        for sched in (0, 2, 3, 4):
+            try:
+                out = ops.lstm_stacked(x, Wp, bp, schedule=sched)
+            except FtbError:
+                continue  # the schedule does not take this shape
+            ops.check_status()
+            ran += 1
+            assert torch.equal(out[0], ref[0]) and torch.equal(out[1], ref[1]), ("stacked", D, L, N, H, sched)
+        assert ran >= 2
+    for _ in range(6):
+        dt = rng.choice([torch.bfloat16, torch.float16])
+        D, L, H = rng.choice([1, 2, 3, 4]), rng.randint(2, 20), rng.choice([64, 128, 256])
+        N = rng.choice([1, 30, 64, 65, 128, 150, 200, 256, 300, 400])
+        dil = [rng.choice([1, 1, 2, 3, 4]) for _ in range(D)]
+        x = torch.randn(L, N, H, device="cuda", generator=g).to(dt)
+        Wp, bp = ops.lstm_pack_weights(uni(1 / 8, D, 4, H, H).to(dt), uni(1 / 8, D, 4, H, H).to(dt), uni(1 / 8, D, 4, H).to(dt))
+        ref, _ = ops.lstm_dilated(x, Wp, dil, bp, schedule=1)
+        ops.check_status()
+        for sched in (0, 2, 4):
+            try:
+                hs, _ = ops.lstm_dilated(x, Wp, dil, bp, schedule=sched)
+            except FtbError:
+                continue
+            ops.check_status()
+            assert torch.equal(hs, ref), ("dilated", dil, L, N, H, sched)
+
+
 # -------------------------------------------------------------------- grid RNN
 def _run_grid(ops, X, Y, p, **kw):
     Xd, Yd = _dev(X, Y)
