@@ -240,7 +240,10 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = make_idesc_f16(2 * BM, BN, Fmt<T>::kind, 0, 0);
+      const uint64_t a_desc0 = make_sdesc_sw128(smem_u32(smem), 16, 1024);
+      const uint64_t b_desc0 = make_sdesc_sw128(smem_u32(smem) + kABytes, 16, 1024);
       int stage = 0;
+      uint32_t stage_off = 0;  // stage * kStageBytes / 16
       uint32_t phase = 0;
       int k_base = 0;  // tiles this CTA has started before the current sweep
       bool ok = true;
@@ -257,6 +260,7 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             tc_fence_after();
           }
           const uint32_t d_tmem = tmem_base + acc * BN;
+          uint32_t accumulate = is_x ? 0u : 1u;  // the first MMA of a tile overwrites the accumulator
           for (int kb = 0; kb < nkb; ++kb) {
             // (No tcgen05 fence after a barrier that TMA completes: the fence orders against other threads'
             // tcgen05 operations, which do not touch the stage, and it drains the tensor pipe.)
@@ -264,17 +268,20 @@ lstm_static_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
 #ifdef FTB_TRACE
             if (a.trace && !is_x && kb == 0) a.trace[(static_cast<size_t>(l * a.L + t) * a.tiles_per_cell + tile) * 4 + 1] = globaltimer_ns();
 #endif
-            const uint32_t sa = smem_u32(smem + stage * kStageBytes);
-            const uint32_t sb = sa + kABytes;
+            // This thread's own instructions are the floor of a K block: the operand descriptors are the
+            // stage-0 descriptors plus byte offsets / 16, nothing is rebuilt per MMA.
+            const uint64_t ad = a_desc0 + stage_off;
+            const uint64_t bd = b_desc0 + stage_off;
 #pragma unroll
             for (int kk = 0; kk < BK / 16; ++kk) {
-              const uint64_t ad = make_sdesc_sw128(sa + kk * 32, 16, 1024);
-              const uint64_t bd = make_sdesc_sw128(sb + kk * 32, 16, 1024);
-              umma_ss_pair(d_tmem, ad, bd, idesc, (is_x && (kb | kk) == 0) ? 0u : 1u);
+              umma_ss_pair(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, accumulate);
+              accumulate = 1u;
             }
             umma_commit_pair(&empty_bar[stage]);
+            stage_off += kStageBytes >> 4;
             if (++stage == kStages) {
               stage = 0;
+              stage_off = 0;
               phase ^= 1u;
             }
           }
