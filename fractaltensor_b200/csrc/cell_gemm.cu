@@ -316,10 +316,15 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
       constexpr uint32_t idesc = make_idesc_f16(PAIR ? 2 * BM : BM, BN, Fmt<T>::kind, 0, 0);
       ItemCursor<PERSIST> cur(batch, plan);
       int stage = 0;
+      uint32_t stage_off = 0;  // stage * kStageBytes / 16
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      // Operand descriptors of stage 0; a stage's are these plus its byte offset / 16 (nothing is rebuilt
+      // per MMA: this thread's own instructions are part of a K block's time).
+      const uint64_t a_desc0 = make_sdesc_sw128(smem_u32(smem), 16, 1024);
+      const uint64_t b_desc0 = make_sdesc_sw128(smem_u32(smem) + C::kABytes, 16, 1024);
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         const CellItem* it = cur.seek(tile);
         int nkb = 0;
@@ -333,23 +338,23 @@ cell_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
             ok = false;
             break;
           }
-          const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
-          const uint32_t sb = sa + C::kABytes;
+          const uint64_t ad = a_desc0 + stage_off;
+          const uint64_t bd = b_desc0 + stage_off;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t ad = make_sdesc_sw128(sa + k * 32, 16, 1024);
-            const uint64_t bd = make_sdesc_sw128(sb + k * 32, 16, 1024);
             if (PAIR)
-              umma_ss_pair(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_ss_pair(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
             else
-              umma_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_ss(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           if (PAIR)
             umma_commit_pair(&empty_bar[stage]);
           else
             umma_commit(&empty_bar[stage]);
+          stage_off += C::kStageBytes >> 4;
           if (++stage == S) {
             stage = 0;
+            stage_off = 0;
             phase ^= 1u;
           }
         }
