@@ -489,6 +489,7 @@ __device__ __forceinline__ void cluster_body(const CUtensorMap& map0, const CUte
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(128, NB, Fmt<T>::kind, 0, 0);
       const uint64_t ring_desc0 = make_sdesc_sw128(smem_u32(s_ring), 16, 1024);
+      const uint64_t self_desc0 = make_sdesc_plain(smem_u32(s_self), NB * 16, 128);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = mbar_wait(&res_full, 0, &s_abort, status, FTB_ERR_TIMEOUT_TMA);
@@ -564,13 +565,17 @@ __device__ __forceinline__ void cluster_body(const CUtensorMap& map0, const CUte
           ACCT_END(2);
           if (!ok) break;
           FTB_CL_STAMP(i, 2);
-          const uint32_t sb = smem_u32(s_self + slot * self_slot_bytes);
-          const uint32_t aw = tmem_w + kbh * 32;
-          for (int j = 0; j < kbh * (BK / 16); ++j) {
-            // K = 16 is two 16-byte chunks, NB * 16 bytes apart; 8-row groups are 128 bytes apart
-            const uint64_t bd = make_sdesc_plain(sb + static_cast<uint32_t>(2 * j) * NB * 16, NB * 16, 128);
-            umma_ts(d_tmem, aw + j * 8, bd, idesc, accumulate);
+          // K = 16 is two 16-byte chunks, NB * 16 bytes apart; 8-row groups are 128 bytes apart; the
+          // descriptor of MMA j is the slot's plus j * 2 * NB (bytes / 16): nothing is rebuilt per MMA.
+          uint64_t bd = self_desc0 + static_cast<uint64_t>((slot * self_slot_bytes) >> 4);
+          uint32_t aw = tmem_w + kbh * 32;
+          const int n_self = kbh * (BK / 16);
+#pragma unroll 4
+          for (int j = 0; j < n_self; ++j) {
+            umma_ts(d_tmem, aw, bd, idesc, accumulate);
             accumulate = 1;
+            aw += 8;
+            bd += 2 * NB;
           }
           umma_commit_to(&self_free[slot], producer_mask);
         }
