@@ -217,25 +217,31 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(128, 128, Fmt<T>::kind, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_f16(128, 128, Fmt<T>::kind, 0, 1);  // V is MN-major
-      const uint32_t aQ = smem_u32(sQ), aKV = smem_u32(sKV);
-      uint32_t full_phase[kKVSlots] = {};
+      // This thread's own instructions sit between every softmax hand-off and the MMAs that follow it:
+      // operand descriptors are base descriptors plus byte offsets / 16 (nothing is rebuilt per MMA),
+      // and the K/V slots' phases are bits of one register.
+      const uint64_t dQ = make_sdesc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t dK = make_sdesc_sw128(smem_u32(sKV), 16, 1024);
+      const uint64_t dV = make_sdesc_sw128(smem_u32(sKV), kHalfBytes, 1024);
+      uint32_t full_bits = 0;  // bit s: parity of the next fill of slot s
       bool ok = mbar_wait(&ctl.q_full, 0, s_abort, status, FTB_ERR_TIMEOUT_TMA);
 
+      // (No tcgen05 fence after these waits: TMA completes the barriers, and the fence would drain the
+      // tensor pipe.)
       auto wait_slot = [&](int n) -> bool {  // n-th tile of the K0, V0, K1, V1, ... stream
         const int slot = n % kKVSlots;
-        if (!mbar_wait(&ctl.kv_full[slot], full_phase[slot], s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
-        full_phase[slot] ^= 1u;
-        tc_fence_after();
+        if (!mbar_wait(&ctl.kv_full[slot], (full_bits >> slot) & 1u, s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
+        full_bits ^= 1u << slot;
         return true;
       };
       // S_t(j) = Q_t . K_j^T
       auto issue_s = [&](int t, int j) {
-        const uint32_t aK = aKV + ((2 * j) % kKVSlots) * kTileBytes;
+        const uint64_t dq = dQ + static_cast<uint64_t>((t * kTileBytes) >> 4);
+        const uint64_t dk = dK + static_cast<uint64_t>((((2 * j) % kKVSlots) * kTileBytes) >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(tmem_base + t * 128, make_sdesc_sw128(aQ + t * kTileBytes + off, 16, 1024),
-                  make_sdesc_sw128(aK + off, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+          const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+          umma_ss(tmem_base + t * 128, dq + off, dk + off, idesc_qk, k != 0 ? 1u : 0u);
         }
         umma_commit(&ctl.s_full[t]);
       };
@@ -243,11 +249,11 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
       // key halves start 64 columns apart); B = V, MN-major: 16 keys = two 8-row groups
       // (1024 B apart), the two 64-column halves of d are 16 KB apart.
       auto issue_pv = [&](int t, int j, bool first) {
-        const uint32_t aV = aKV + ((2 * j + 1) % kKVSlots) * kTileBytes;
+        const uint64_t dv = dV + static_cast<uint64_t>((((2 * j + 1) % kKVSlots) * kTileBytes) >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + (k >> 2) * 64 + (k & 3) * 8,
-                  make_sdesc_sw128(aV + k * 2048, kHalfBytes, 1024), idesc_pv, (!first || k != 0) ? 1u : 0u);
+          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + (k >> 2) * 64 + (k & 3) * 8, dv + k * (2048 >> 4),
+                  idesc_pv, (!first || k != 0) ? 1u : 0u);
         umma_commit(&ctl.pv_done[t]);
       };
 
