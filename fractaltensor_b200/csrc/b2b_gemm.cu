@@ -215,16 +215,17 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           cur_batch = b;
         }
         if (c == 0 && !mbar_wait(&a_full[stage], a_phase, &s_abort, status, FTB_ERR_TIMEOUT_TMA)) return false;
-        tc_fence_after();
+        // (No tcgen05 fence: TMA completes both barriers, and the accumulator's previous contents were
+        // consumed by an MMA this thread issued earlier.)
         if (u == 0) B2B_WALL(1);
-        const uint32_t aA = smem_u32(sA + stage * sh.a_bytes);
-        const uint32_t aB = aBC + bc_pair(n) * bc_pair_bytes + c * (kTile * kSlabBytes);
+        const uint64_t dA = make_sdesc_sw128(smem_u32(sA + stage * sh.a_bytes), 16, 1024);
+        const uint64_t dB = make_sdesc_sw128(aBC + bc_pair(n) * bc_pair_bytes + c * (kTile * kSlabBytes), 16, 1024);
+        const uint32_t slabB = (sh.N * kSlabBytes) >> 4;
 #pragma unroll
         for (int k = 0; k < KK / 16; ++k) {
-          const uint32_t offA = (k >> 2) * (kTile * kSlabBytes) + (k & 3) * 32;
-          const uint32_t offB = (k >> 2) * (sh.N * kSlabBytes) + (k & 3) * 32;
-          umma_ss(tmem_base + (u & 1) * 128, make_sdesc_sw128(aA + offA, 16, 1024), make_sdesc_sw128(aB + offB, 16, 1024),
-                  idesc1, k != 0 ? 1u : 0u);
+          const uint32_t offA = ((k >> 2) * (kTile * kSlabBytes) + (k & 3) * 32) >> 4;
+          const uint32_t offB = (k >> 2) * slabB + (k & 3) * 2;
+          umma_ss(tmem_base + (u & 1) * 128, dA + offA, dB + offB, idesc1, k != 0 ? 1u : 0u);
         }
         if (c == nchunks - 1) {
           umma_commit(&a_empty[stage]);
@@ -248,11 +249,12 @@ b2b_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         // (S of the next unit is ready early), and a parity wait must not fall two phases behind.
         if (!mbar_wait(&p_full[u & 1], (u >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_EPI)) return false;
         tc_fence_after();
+        const uint64_t dC = make_sdesc_sw128(aC + (2 * c) * (PP * kSlabBytes), 16, 1024);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t offC = (2 * c + (kk >> 2)) * (PP * kSlabBytes) + (kk & 3) * 32;
-          umma_ts(tmem_base + 256 + ob * 128, tmem_base + (u & 1) * 128 + kk * 8, make_sdesc_sw128(aC + offC, 16, 1024),
-                  idesc2, (c | kk) != 0 ? 1u : 0u);
+          const uint32_t offC = ((kk >> 2) * (PP * kSlabBytes) + (kk & 3) * 32) >> 4;
+          umma_ts(tmem_base + 256 + ob * 128, tmem_base + (u & 1) * 128 + kk * 8, dC + offC, idesc2,
+                  (c | kk) != 0 ? 1u : 0u);
         }
         if (c == nchunks - 1) {
           umma_commit(&o_full[ob]);
