@@ -723,11 +723,11 @@ __device__ __forceinline__ void cluster_body(const CUtensorMap& map0, const CUte
         for (int ci = 0; ci < kOwn; ++ci) creg[ci] = 0.f;
       }
       {
-        // one polling lane per warp, sleeping between polls; the others wait at the warp vote
-        bool mine = true;
+        // every lane waits on the accumulator's barrier (a single sleeping lane per warp and a vote
+        // were measured slower: this wait is on the chain of a step)
+        bool mine = mbar_wait(&tfull_bar[acc], (i >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA);
         if (lane == 0) {
           ACCT_BEGIN();
-          mine = mbar_wait_sleep(&tfull_bar[acc], (i >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA);
           ACCT_END(0);
           // the output tile of two steps ago must have left shared memory
           if (mine && *stored < i - 1) {
