@@ -613,8 +613,7 @@ __device__ __forceinline__ void cluster_body(const CUtensorMap& map0, const CUte
           const uint64_t t0 = globaltimer_ns();
           uint32_t it = 0;
           while (*issued < want) {
-            __nanosleep(64);
-            if (((++it) & 0x3F) == 0 && (s_abort || globaltimer_ns() - t0 > FTB_WAIT_TIMEOUT_NS)) break;
+            if (((++it) & 0xFF) == 0 && (s_abort || globaltimer_ns() - t0 > FTB_WAIT_TIMEOUT_NS)) break;
           }
           if (*issued < want) {
             if (!s_abort) {
