@@ -465,9 +465,9 @@ lstm_wmajor_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         const int k = k_base + t;
         const int acc = k & 1;
         {
-          // one polling lane per warp, sleeping between polls; the others wait at the warp vote
-          bool mine = true;
-          if (lane == 0) mine = mbar_wait_sleep(&tfull_bar[acc], (k >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA);
+          // every lane waits on the accumulator's barrier (a single sleeping lane per warp and a vote were
+          // measured slower: this wait is on the chain of a step)
+          const bool mine = mbar_wait(&tfull_bar[acc], (k >> 1) & 1, &s_abort, status, FTB_ERR_TIMEOUT_MMA);
           if (!__all_sync(0xffffffffu, mine)) {
             ok = false;
             break;
