@@ -141,25 +141,6 @@ __device__ __forceinline__ bool warp_wait_flags(const int* flags, int n, int lan
   }
 }
 
-__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, volatile int* s_abort, int* g_status,
-                                                int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t it = 0;
-  for (;;) {
-    __nanosleep(32);
-    if (mbar_try_wait(bar, parity)) return true;
-    if (((++it) & 0x3F) == 0) {
-      if (*s_abort) return false;
-      if (globaltimer_ns() - t0 > FTB_WAIT_TIMEOUT_NS) {
-        *s_abort = 1;
-        atomicCAS(g_status, 0, code);
-        return false;
-      }
-    }
-  }
-}
-
 template <int N>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
   if constexpr (N == 32) tmem_ld32(taddr, r);
